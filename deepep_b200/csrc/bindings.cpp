@@ -1,0 +1,213 @@
+// Python module `deepep_b200._C`: sessions, workspace layout and kernel launchers.
+//
+// Parity: csrc/bindings/module.cpp:17-95 of the reference (runtime factories + the
+// notify/dispatch/combine/low-latency op families, `runtime_protocol`).  Tensors cross this
+// boundary as raw device addresses (`tensor.data_ptr()`), so the module needs no libtorch.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "kernels/api.h"
+#include "kernels/ll_api.h"
+#include "kernels/mega_api.h"
+#include "runtime/session.h"
+
+namespace py = pybind11;
+using namespace dep;
+
+namespace {
+
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+  }
+}
+
+template <class T> T* ptr(const py::dict& d, const char* key) {
+  if (!d.contains(key) || d[key].is_none()) return nullptr;
+  return reinterpret_cast<T*>(d[key].cast<uintptr_t>());
+}
+int geti(const py::dict& d, const char* key, int dflt = 0) { return d.contains(key) ? d[key].cast<int>() : dflt; }
+long long getl(const py::dict& d, const char* key, long long dflt = 0) { return d.contains(key) ? d[key].cast<long long>() : dflt; }
+float getf(const py::dict& d, const char* key, float dflt = 0.f) { return d.contains(key) ? d[key].cast<float>() : dflt; }
+
+constexpr long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
+
+WsLayout make_layout(int world, int max_tokens, int hidden, int topk, long long ll_bytes, long long mega_bytes) {
+  if (world < 1 || world > kMaxRanks) throw std::invalid_argument("world size must be in [1, 8]");
+  if (max_tokens < 1 || max_tokens > kChunkTokens * kMaxChunks) throw std::invalid_argument("num_max_tokens_per_rank must be in [1, 16384]");
+  if (topk < 1 || topk > kMaxTopk) throw std::invalid_argument("num_topk must be in [1, 16]");
+  if (hidden < 8 || hidden % 8) throw std::invalid_argument("hidden must be a positive multiple of 8");
+  WsLayout l{};
+  l.world = world; l.max_tokens = max_tokens; l.hidden = hidden; l.topk = topk;
+  l.stage_row_bytes = (int)align_up((long long)hidden * 2, 128);
+  long long at = kControlBytes;
+  auto take = [&](long long bytes) { long long o = at; at = align_up(at + bytes, 1024); return o; };
+  l.gather_hdr = take((long long)world * 4 * sizeof(int));
+  l.gather_idx = take((long long)world * max_tokens * topk * sizeof(int));
+  l.gather_w = take((long long)world * max_tokens * topk * sizeof(float));
+  l.stage = take((long long)world * max_tokens * l.stage_row_bytes);
+  l.partial = take((long long)max_tokens * world * hidden * 2);
+  l.wret = take((long long)max_tokens * topk * sizeof(float));
+  l.ll = take(ll_bytes);
+  l.mega = take(mega_bytes);
+  l.total = align_up(at, 2 << 20);
+  return l;
+}
+
+RankCtx ctx_of(const py::handle& session) { return session.cast<Session&>().ctx(); }
+
+void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
+               uintptr_t stream) {
+  NotifyParams p{};
+  p.lay = lay;
+  const int n = (int)args.size();
+  if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
+  for (int i = 0; i < n; ++i) {
+    const py::dict& d = args[i];
+    NotifyArgs& a = p.r[i];
+    a.ctx = ctx_of(sessions[i]);
+    a.topk_idx = ptr<const long long>(d, "topk_idx");
+    a.topk_w = ptr<const float>(d, "topk_w");
+    a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K");
+    a.expand = geti(d, "expand", 1); a.alignment = geti(d, "alignment", 1); a.meta_stride = geti(d, "meta_stride");
+    a.hist = ptr<int>(d, "hist"); a.hits = ptr<int>(d, "hits"); a.own_hits = ptr<int>(d, "own_hits"); a.cnt = ptr<int>(d, "cnt");
+    a.send_slot = ptr<int>(d, "send_slot"); a.slot_row = ptr<int>(d, "slot_row"); a.stage_meta = ptr<int>(d, "stage_meta");
+    a.chunk_start = ptr<int>(d, "chunk_start"); a.rank_tokens = ptr<int>(d, "rank_tokens"); a.rank_rows = ptr<int>(d, "rank_rows");
+    a.expert_counts = ptr<int>(d, "expert_counts"); a.expert_offsets = ptr<int>(d, "expert_offsets");
+    a.recv_row_src = ptr<int>(d, "recv_row_src"); a.recv_w = ptr<float>(d, "recv_w"); a.recv_idx = ptr<long long>(d, "recv_idx");
+    a.mailbox = sessions[i].cast<Session&>().mailbox_device();
+    a.rcap = getl(d, "rcap");
+    if (a.T < 0 || a.T > lay.max_tokens) throw std::invalid_argument("token count exceeds num_max_tokens_per_rank");
+    if (a.K != lay.topk) throw std::invalid_argument("top-k width differs from the buffer's num_topk");
+    if (a.E < a.ctx.world || a.E > kMaxExperts || a.E % a.ctx.world) throw std::invalid_argument("num_experts must be a multiple of the world size and at most 1024");
+    if (a.alignment < 1) throw std::invalid_argument("expert_alignment must be positive");
+  }
+  check(launch_notify(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "ep_notify launch");
+}
+
+void op_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int send_blocks,
+                 int recv_blocks, uintptr_t stream) {
+  DispatchParams p{};
+  p.lay = lay; p.send_blocks = send_blocks; p.recv_blocks = recv_blocks;
+  const int n = (int)args.size();
+  if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
+  if (send_blocks < 1 || recv_blocks < 1) throw std::invalid_argument("sender and receiver block counts must be positive");
+  for (int i = 0; i < n; ++i) {
+    const py::dict& d = args[i];
+    DispatchArgs& a = p.r[i];
+    a.ctx = ctx_of(sessions[i]);
+    a.x = ptr<const void>(d, "x"); a.x_sf = ptr<const float>(d, "x_sf");
+    a.T = geti(d, "T"); a.mode = geti(d, "mode");
+    a.send_slot = ptr<const int>(d, "send_slot"); a.stage_meta = ptr<const int>(d, "stage_meta");
+    a.chunk_start = ptr<const int>(d, "chunk_start"); a.rank_tokens = ptr<const int>(d, "rank_tokens");
+    a.meta_stride = geti(d, "meta_stride");
+    a.recv_x = ptr<void>(d, "recv_x"); a.recv_sf = ptr<float>(d, "recv_sf");
+    if (a.mode != p.r[0].mode) throw std::invalid_argument("all ranks must use the same dispatch mode");
+    if (a.mode != kDispatchBf16 && lay.hidden % 128) throw std::invalid_argument("fp8 dispatch needs hidden % 128 == 0");
+  }
+  check(launch_dispatch(p, n, reinterpret_cast<cudaStream_t>(stream)), "ep_dispatch_ht launch");
+}
+
+void op_combine(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int send_blocks,
+                int recv_blocks, uintptr_t stream) {
+  CombineParams p{};
+  p.lay = lay; p.send_blocks = send_blocks; p.recv_blocks = recv_blocks;
+  const int n = (int)args.size();
+  if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
+  if (send_blocks < 1 || recv_blocks < 1) throw std::invalid_argument("sender and receiver block counts must be positive");
+  for (int i = 0; i < n; ++i) {
+    const py::dict& d = args[i];
+    CombineArgs& a = p.r[i];
+    a.ctx = ctx_of(sessions[i]);
+    a.x = ptr<const __nv_bfloat16>(d, "x"); a.w = ptr<const float>(d, "w");
+    a.stage_meta = ptr<const int>(d, "stage_meta"); a.chunk_start = ptr<const int>(d, "chunk_start");
+    a.rank_tokens = ptr<const int>(d, "rank_tokens"); a.send_slot = ptr<const int>(d, "send_slot");
+    a.topk_idx = ptr<const long long>(d, "topk_idx");
+    a.T = geti(d, "T"); a.meta_stride = geti(d, "meta_stride"); a.K = geti(d, "K"); a.E = geti(d, "E"); a.expand = geti(d, "expand", 1);
+    a.bias0 = ptr<const __nv_bfloat16>(d, "bias0"); a.bias1 = ptr<const __nv_bfloat16>(d, "bias1");
+    a.out = ptr<__nv_bfloat16>(d, "out"); a.out_w = ptr<float>(d, "out_w");
+  }
+  check(launch_combine(p, n, reinterpret_cast<cudaStream_t>(stream)), "ep_combine_ht launch");
+}
+
+void op_barrier(const std::vector<py::object>& sessions, uintptr_t stream) {
+  BarrierParams p{};
+  const int n = (int)sessions.size();
+  if (n < 1 || n > kMaxRanks) throw std::invalid_argument("1..8 sessions expected");
+  for (int i = 0; i < n; ++i) p.r[i] = ctx_of(sessions[i]);
+  check(launch_barrier(p, n, reinterpret_cast<cudaStream_t>(stream)), "ep_barrier launch");
+}
+
+}  // namespace
+
+void bind_low_latency(py::module_& m);
+void bind_mega(py::module_& m);
+
+PYBIND11_MODULE(_C, m) {
+  m.attr("runtime_protocol") = 1;
+  m.attr("max_ranks") = kMaxRanks;
+  m.attr("chunk_tokens") = kChunkTokens;
+  m.attr("max_topk") = kMaxTopk;
+  m.attr("max_experts") = kMaxExperts;
+  m.attr("control_bytes") = (long long)kControlBytes;
+  m.attr("row_slot_shift") = kRowSlotShift;
+
+  py::class_<WsLayout>(m, "WsLayout")
+      .def_readonly("gather_hdr", &WsLayout::gather_hdr).def_readonly("gather_idx", &WsLayout::gather_idx)
+      .def_readonly("gather_w", &WsLayout::gather_w).def_readonly("stage", &WsLayout::stage)
+      .def_readonly("partial", &WsLayout::partial).def_readonly("wret", &WsLayout::wret)
+      .def_readonly("ll", &WsLayout::ll).def_readonly("mega", &WsLayout::mega).def_readonly("total", &WsLayout::total)
+      .def_readonly("max_tokens", &WsLayout::max_tokens).def_readonly("hidden", &WsLayout::hidden)
+      .def_readonly("topk", &WsLayout::topk).def_readonly("world", &WsLayout::world)
+      .def_readonly("stage_row_bytes", &WsLayout::stage_row_bytes);
+  m.def("make_layout", &make_layout, py::arg("world"), py::arg("max_tokens"), py::arg("hidden"), py::arg("topk"),
+        py::arg("ll_bytes") = 0, py::arg("mega_bytes") = 0);
+
+  py::class_<Session>(m, "Session")
+      .def(py::init<int, int, size_t, double>(), py::arg("rank"), py::arg("world"), py::arg("bytes"), py::arg("timeout"))
+      .def("ipc_handle", [](const Session& s) { return py::bytes(s.ipc_handle()); })
+      .def("open_peers", [](Session& s, const std::vector<py::bytes>& hs) {
+        std::vector<std::string> v;
+        for (const auto& h : hs) v.push_back(std::string(h));
+        s.open_peers(v);
+      })
+      .def("attach_peers", &Session::attach_peers)
+      .def("close", &Session::close)
+      .def("set_timeout", &Session::set_timeout)
+      .def("clear_status", &Session::clear_status)
+      .def("mapped", &Session::mapped)
+      .def("peer", &Session::peer)
+      .def_property_readonly("workspace", &Session::workspace)
+      .def_property_readonly("bytes", &Session::bytes)
+      .def_property_readonly("rank", &Session::rank)
+      .def_property_readonly("world", &Session::world)
+      .def_property_readonly("instance_id", &Session::instance_id)
+      .def_property_readonly("poisoned", &Session::poisoned)
+      .def_property_readonly("closed", &Session::closed)
+      .def("status", [](const Session& s) {
+        StatusBlock b = s.status();
+        py::dict d;
+        d["code"] = b.code; d["op"] = b.op; d["rank"] = b.rank; d["peer"] = b.peer; d["where"] = b.where;
+        d["expected"] = b.expected; d["seen"] = b.seen;
+        return d;
+      })
+      .def("mailbox", [](const Session& s, int n) {
+        std::vector<int> v(s.mailbox_host(), s.mailbox_host() + std::min(n, kMailboxInts));
+        return v;
+      })
+      .def("wait_probe", [](Session& s, uintptr_t stream) {
+        check(launch_wait_probe(s.ctx(), reinterpret_cast<cudaStream_t>(stream)), "wait probe launch");
+      });
+  m.def("live_instances", &live_instances);
+
+  m.def("notify", &op_notify);
+  m.def("dispatch", &op_dispatch);
+  m.def("combine", &op_combine);
+  m.def("barrier", &op_barrier);
+  bind_low_latency(m);
+  bind_mega(m);
+}

@@ -1,0 +1,93 @@
+// Host-callable launchers of the expert-parallel kernels and their argument blocks.
+//
+// Every launcher takes `nranks` argument blocks: 1 in production (one process
+// per GPU) or several virtual ranks that share one GPU (single-launch protocol
+// test).  Pointers are device pointers valid on the current device.
+#pragma once
+#include "common.cuh"
+
+namespace dep {
+
+// ---------------------------------------------------------------- notify (routing layout)
+// Counterpart of the reference's notify kernel (csrc/kernels/notify/notify.cpp:1426-1970):
+// counts, prefix offsets, rank-level dedup map and receive-side expansion lists.
+struct NotifyArgs {
+  RankCtx ctx;
+  const long long* topk_idx;   // [T][K]; <0 or >=E marks an empty slot
+  const float* topk_w;         // [T][K] or null
+  int T, E, K;
+  int expand;                  // 1: rows per (token, slot) sorted by local expert; 0: rows per (source, token)
+  int alignment;               // every local expert's row block starts at a multiple of this
+  int meta_stride;             // ints per stage_meta record: 2 + max(2, min(K, E / world))
+  // scratch owned by the buffer
+  int* hist;                   // [P][NT][E]
+  int* hits;                   // [P][NT]
+  int* own_hits;               // [NT][P]
+  int* cnt;                    // [P][E]
+  // outputs owned by the handle
+  int* send_slot;              // [T][P]  staging index on each destination, -1 if not routed there
+  int* slot_row;               // [T][K]  row on the destination rank (expanded layout), -1 if empty
+  int* stage_meta;             // [P * Tmax][meta_stride]: token, n, n x (row | slot << 27); rank layout: token, 1, row, slot mask
+  int* chunk_start;            // [P][NT + 1] staged-row index at the start of every source chunk
+  int* rank_tokens;            // [P] tokens each source holds
+  int* rank_rows;              // [P + 1] exclusive prefix of staged rows per source
+  int* expert_counts;          // [L] unaligned rows per local expert
+  int* expert_offsets;         // [L + 1] aligned exclusive prefix
+  int* recv_row_src;           // [rcap] (source * Tmax + token) * K + slot of every output row, -1 for padding
+  float* recv_w;               // [rcap] (expanded) or [rcap][K] (rank layout); may be null
+  long long* recv_idx;         // [rcap][K] destination-local expert ids (rank layout) or null
+  int* mailbox;                // mapped host memory: [0] rows, [1] staged rows, [2] max tokens, [3] epoch, [4..] counts
+  long long rcap;
+};
+struct NotifyParams { WsLayout lay; NotifyArgs r[kMaxRanks]; };
+cudaError_t launch_notify(const NotifyParams& p, int nranks, int blocks, cudaStream_t stream);
+
+// ---------------------------------------------------------------- high-throughput dispatch
+// Counterpart of csrc/kernels/dispatch/dispatch.cpp:463-590 of the reference: payload scatter
+// + receive-side expansion + completion flags, here with an optional fused bf16 -> e4m3 quantiser.
+enum DispatchMode : int { kDispatchBf16 = 0, kDispatchFp8Given = 1, kDispatchFp8Fused = 2 };
+struct DispatchArgs {
+  RankCtx ctx;
+  const void* x;               // [T][H] bf16/fp16 (modes 0, 2) or e4m3 (mode 1)
+  const float* x_sf;           // [T][H/128] (mode 1)
+  int T, mode;
+  const int* send_slot;        // [T][P]
+  const int* stage_meta;
+  const int* chunk_start;
+  const int* rank_tokens;
+  int meta_stride, pad;
+  void* recv_x;                // [R][H] 2-byte (mode 0) or e4m3 (modes 1, 2)
+  float* recv_sf;              // [R][H/128] or null
+};
+struct DispatchParams { WsLayout lay; int send_blocks, recv_blocks; DispatchArgs r[kMaxRanks]; };
+cudaError_t launch_dispatch(const DispatchParams& p, int nranks, cudaStream_t stream);
+
+// ---------------------------------------------------------------- high-throughput combine
+// Counterpart of csrc/kernels/combine/combine.cpp:2224-2917 (EP8 form): expert ranks reduce the
+// rows of one (source token, this rank) in fp32, return one bf16 partial, the source reduces
+// the partials of its destinations in rank order and adds the optional biases.
+struct CombineArgs {
+  RankCtx ctx;
+  const __nv_bfloat16* x;      // [R][H] expert outputs
+  const float* w;              // [R] (expanded) / [R][K] (rank layout) value channel, or null
+  const int* stage_meta;
+  const int* chunk_start;
+  const int* rank_tokens;
+  const int* send_slot;        // [T][P]
+  const long long* topk_idx;   // [T][K] of the source tokens (validity of returned weights)
+  int T, meta_stride, K, E, expand, pad;
+  const __nv_bfloat16* bias0;  // [T][H] or null
+  const __nv_bfloat16* bias1;
+  __nv_bfloat16* out;          // [T][H]
+  float* out_w;                // [T][K] or null
+};
+struct CombineParams { WsLayout lay; int send_blocks, recv_blocks; CombineArgs r[kMaxRanks]; };
+cudaError_t launch_combine(const CombineParams& p, int nranks, cudaStream_t stream);
+
+// ---------------------------------------------------------------- barrier
+struct BarrierParams { RankCtx r[kMaxRanks]; };
+cudaError_t launch_barrier(const BarrierParams& p, int nranks, cudaStream_t stream);
+// Waits on a flag nobody writes: exercises the bounded-wait + status path without a fault.
+cudaError_t launch_wait_probe(const RankCtx& ctx, cudaStream_t stream);
+
+}  // namespace dep

@@ -1,0 +1,212 @@
+"""CUDA engine: drives the native kernels for one rank, or for several virtual ranks on one GPU.
+
+All methods take *lists* with one entry per rank handled by this process.  A
+production ``ElasticBuffer`` passes one-element lists; :class:`VirtualWorld`
+passes one entry per virtual rank so the whole cross-rank protocol runs inside
+one cooperative launch on a single GPU.
+
+Parity: host op wrappers ``csrc/ops/{notify,dispatch,combine}.cpp`` of the
+reference (argument validation, tiling, launch); the count read-back is the
+single host synchronisation of a fresh dispatch
+(``deep_ep/backends/mesh_clos/elastic.py:1473-1479``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops import require_native
+
+STATUS_NAMES = {0: "ok", 1: "timeout", 2: "bad argument", 3: "aborted"}
+OP_NAMES = {0: "barrier", 1: "notify", 2: "dispatch", 3: "combine", 4: "ll_dispatch", 5: "ll_combine", 6: "mega_moe"}
+
+
+class CommunicationError(RuntimeError):
+    pass
+
+
+@dataclass
+class RoutingPlan:
+    """Device-side routing metadata of one dispatch (what an ``EPHandle`` owns)."""
+    num_tokens: int
+    num_experts: int
+    num_topk: int
+    expand: bool
+    alignment: int
+    meta_stride: int
+    num_rows: int                       # output rows (exact, or the worst case without a host sync)
+    num_staged_rows: int
+    expert_counts_list: Optional[List[int]]
+    topk_idx: torch.Tensor
+    send_slot: torch.Tensor
+    slot_row: torch.Tensor
+    stage_meta: torch.Tensor
+    chunk_start: torch.Tensor
+    rank_tokens: torch.Tensor
+    rank_rows: torch.Tensor
+    expert_counts: torch.Tensor
+    expert_offsets: torch.Tensor
+    recv_row_src: torch.Tensor
+    recv_w: Optional[torch.Tensor]
+    recv_idx: Optional[torch.Tensor]
+    has_weights: bool = False
+
+    def tensors(self):
+        return [t for t in (self.topk_idx, self.send_slot, self.slot_row, self.stage_meta, self.chunk_start, self.rank_tokens,
+                            self.rank_rows, self.expert_counts, self.expert_offsets, self.recv_row_src, self.recv_w,
+                            self.recv_idx) if t is not None]
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class CudaEngine:
+    def __init__(self, sessions: Sequence, layout, device: torch.device, num_sms: int = 0):
+        self.C = require_native("ElasticBuffer")
+        self.sessions = list(sessions)
+        self.layout = layout
+        self.device = device
+        self.n = len(self.sessions)
+        self.world = layout.world
+        props = torch.cuda.get_device_properties(device)
+        self.sm_count = props.multi_processor_count
+        per_rank = max(2, self.sm_count // self.n)
+        self.default_blocks = min(per_rank, num_sms) if num_sms else min(per_rank, 64)
+        nt = -(-layout.max_tokens // self.C.chunk_tokens)
+        self._nt = nt
+        self._scratch = []
+        for _ in range(self.n):
+            self._scratch.append(dict(
+                hist=torch.empty((self.world * nt * self.C.max_experts,), dtype=torch.int32, device=device),
+                hits=torch.empty((self.world * nt,), dtype=torch.int32, device=device),
+                own_hits=torch.empty((nt * self.world,), dtype=torch.int32, device=device),
+                cnt=torch.empty((self.world * self.C.max_experts,), dtype=torch.int32, device=device)))
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def check_status(self) -> None:
+        for s in self.sessions:
+            st = s.status()
+            if st["code"] != 0:
+                raise CommunicationError(
+                    f"rank {st['rank']}: {OP_NAMES.get(st['op'], st['op'])} {STATUS_NAMES.get(st['code'], st['code'])} "
+                    f"at wait site {st['where']} on peer {st['peer']} (expected {st['expected']}, saw {st['seen']}); "
+                    "restart the distributed job")
+
+    def split_blocks(self, total: int, send_fraction: float) -> Tuple[int, int]:
+        total = max(2, total or self.default_blocks)
+        send = min(total - 1, max(1, int(round(total * send_fraction))))
+        return send, total - send
+
+    def row_capacity(self, num_experts: int, alignment: int, expand: bool) -> int:
+        local = num_experts // self.world
+        k = self.layout.topk
+        per_token = min(k, local) if expand else 1
+        cap = self.world * self.layout.max_tokens * per_token
+        if expand and alignment > 1:
+            cap += local * (alignment - 1)
+        return cap
+
+    # ------------------------------------------------------------------ ops
+    def notify(self, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[Optional[torch.Tensor]], num_experts: int,
+               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0) -> List[RoutingPlan]:
+        C, lay, dev = self.C, self.layout, self.device
+        P, K = self.world, lay.topk
+        local = num_experts // P
+        stride = 2 + max(2, min(K, local))
+        rcap = self.row_capacity(num_experts, alignment, expand)
+        plans, args = [], []
+        for i in range(self.n):
+            idx = topk_idx[i]
+            T = idx.shape[0]
+            i32 = dict(dtype=torch.int32, device=dev)
+            plan = RoutingPlan(
+                num_tokens=T, num_experts=num_experts, num_topk=K, expand=expand, alignment=alignment, meta_stride=stride,
+                num_rows=rcap, num_staged_rows=0, expert_counts_list=None, topk_idx=idx,
+                send_slot=torch.empty((max(T, 1), P), **i32), slot_row=torch.empty((max(T, 1), K), **i32),
+                stage_meta=torch.empty((P * lay.max_tokens, stride), **i32),
+                chunk_start=torch.empty((P, self._nt + 1), **i32), rank_tokens=torch.empty((P,), **i32),
+                rank_rows=torch.empty((P + 1,), **i32), expert_counts=torch.empty((local,), **i32),
+                expert_offsets=torch.empty((local + 1,), **i32), recv_row_src=torch.empty((rcap,), **i32),
+                recv_w=(torch.empty((rcap,) if expand else (rcap, K), dtype=torch.float32, device=dev)
+                        if topk_w[i] is not None else None),
+                recv_idx=None if expand else torch.empty((rcap, K), dtype=torch.int64, device=dev),
+                has_weights=topk_w[i] is not None)
+            plans.append(plan)
+            sc = self._scratch[i]
+            args.append(dict(topk_idx=idx.data_ptr(), topk_w=_ptr(topk_w[i]), T=T, E=num_experts, K=K, expand=int(expand),
+                             alignment=alignment, meta_stride=stride, hist=sc["hist"].data_ptr(), hits=sc["hits"].data_ptr(),
+                             own_hits=sc["own_hits"].data_ptr(), cnt=sc["cnt"].data_ptr(), send_slot=plan.send_slot.data_ptr(),
+                             slot_row=plan.slot_row.data_ptr(), stage_meta=plan.stage_meta.data_ptr(),
+                             chunk_start=plan.chunk_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
+                             rank_rows=plan.rank_rows.data_ptr(), expert_counts=plan.expert_counts.data_ptr(),
+                             expert_offsets=plan.expert_offsets.data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(),
+                             recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap))
+        nblocks = blocks or max(1, min(32, self.sm_count // self.n))
+        C.notify(lay, self.sessions, args, nblocks, self._stream())
+        if cpu_sync:
+            torch.cuda.current_stream(dev).synchronize()
+            self.check_status()
+            for plan, s in zip(plans, self.sessions):
+                box = s.mailbox(4 + local)
+                if box[0] < 0:
+                    raise CommunicationError("notify did not complete; restart the distributed job")
+                plan.num_rows, plan.num_staged_rows = box[0], box[1]
+                plan.expert_counts_list = box[4:4 + local]
+        return plans
+
+    def dispatch(self, xs: Sequence, plans: Sequence[RoutingPlan], mode: int, blocks: int = 0, out_dtype=None):
+        """xs[i] is a tensor (modes 0, 2) or a (fp8, scales) pair (mode 1). Returns [(recv_x, recv_sf | None)]."""
+        lay, dev = self.layout, self.device
+        H = lay.hidden
+        outs, args = [], []
+        for i, plan in enumerate(plans):
+            x, sf = (xs[i] if isinstance(xs[i], (tuple, list)) else (xs[i], None))
+            rows = plan.num_rows
+            if mode == 0:
+                recv_x = torch.empty((rows, H), dtype=x.dtype, device=dev)
+                recv_sf = None
+            else:
+                recv_x = torch.empty((rows, H), dtype=torch.float8_e4m3fn, device=dev)
+                recv_sf = torch.empty((rows, H // 128), dtype=torch.float32, device=dev)
+            if plan.expand and plan.alignment > 1:
+                recv_x.view(torch.uint8).zero_()
+                if recv_sf is not None:
+                    recv_sf.zero_()
+            outs.append((recv_x, recv_sf))
+            args.append(dict(x=x.data_ptr(), x_sf=_ptr(sf), T=plan.num_tokens, mode=mode, send_slot=plan.send_slot.data_ptr(),
+                             stage_meta=plan.stage_meta.data_ptr(), chunk_start=plan.chunk_start.data_ptr(),
+                             rank_tokens=plan.rank_tokens.data_ptr(), meta_stride=plan.meta_stride,
+                             recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf)))
+        send, recv = self.split_blocks(blocks, 0.4)
+        self.C.dispatch(lay, self.sessions, args, send, recv, self._stream())
+        return outs
+
+    def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[RoutingPlan], ws: Sequence[Optional[torch.Tensor]],
+                bias: Sequence = None, blocks: int = 0):
+        lay, dev = self.layout, self.device
+        H, K = lay.hidden, lay.topk
+        outs, args = [], []
+        for i, plan in enumerate(plans):
+            T = plan.num_tokens
+            out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+            out_w = torch.empty((T, K), dtype=torch.float32, device=dev) if ws[i] is not None else None
+            b = bias[i] if bias is not None else None
+            b0, b1 = (b if isinstance(b, (tuple, list)) else (b, None)) if b is not None else (None, None)
+            outs.append((out, out_w))
+            args.append(dict(x=xs[i].data_ptr(), w=_ptr(ws[i]), stage_meta=plan.stage_meta.data_ptr(),
+                             chunk_start=plan.chunk_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
+                             send_slot=plan.send_slot.data_ptr(), topk_idx=plan.topk_idx.data_ptr(), T=T,
+                             meta_stride=plan.meta_stride, K=K, E=plan.num_experts, expand=int(plan.expand),
+                             bias0=_ptr(b0), bias1=_ptr(b1), out=out.data_ptr(), out_w=_ptr(out_w)))
+        send, recv = self.split_blocks(blocks, 0.6)
+        self.C.combine(lay, self.sessions, args, send, recv, self._stream())
+        return outs
+
+    def barrier(self) -> None:
+        self.C.barrier(self.sessions, self._stream())

@@ -1,0 +1,124 @@
+"""High-throughput notify/dispatch/combine kernels, N virtual ranks on one GPU, against the CPU oracle."""
+import pytest
+import torch
+
+from deepep_b200.oracle import reference as R
+from helpers import bits_equal, make_routes, make_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(world, tokens, hidden, experts, topk, mode, *, expand=True, alignment=1, dmode=0, seed=0, max_tokens=None,
+             with_bias=False, repeats=1):
+    from deepep_b200.parallel.virtual import VirtualWorld
+
+    dev = torch.device("cuda")
+    max_tokens = max_tokens or max(tokens)
+    xs = [torch.randn((t, hidden), generator=torch.Generator().manual_seed(seed + r)).bfloat16() for r, t in enumerate(tokens)]
+    idx = [make_routes(mode, t, experts, topk, world, seed + 10 * r) for r, t in enumerate(tokens)]
+    wts = [make_weights(t, topk, seed + r) for r, t in enumerate(tokens)]
+    with VirtualWorld(world, max_tokens, hidden, topk, timeout=10.0) as vw:
+        eng = vw.engine
+        for rep in range(repeats):
+            plans = eng.notify([i.to(dev) for i in idx], [w.to(dev) for w in wts], experts, expand=expand, alignment=alignment)
+            if dmode == 1:
+                from deepep_b200.utils.math import per_token_cast_to_fp8
+                q = [per_token_cast_to_fp8(x) for x in xs]
+                dev_x = [(a.to(dev), b.to(dev)) for a, b in q]
+                ref_x = q
+            else:
+                dev_x = [x.to(dev) for x in xs]
+                ref_x = xs
+            outs = eng.dispatch(dev_x, plans, dmode)
+            ref, lays = R.dispatch(ref_x, idx, wts, experts, do_expand=expand, expert_alignment=alignment,
+                                   quantize_fp8=(dmode == 2))
+            torch.cuda.synchronize()
+            eng.check_status()
+            for r in range(world):
+                (rx, rsf), plan, lay = outs[r], plans[r], lays[r]
+                assert plan.num_rows == lay.num_rows, (r, plan.num_rows, lay.num_rows)
+                assert plan.expert_counts_list == lay.expert_counts.tolist()
+                exp_x = ref[r][0]
+                if dmode == 0:
+                    assert bits_equal(rx, exp_x), f"rank {r} payload differs"
+                else:
+                    valid = lay.row_index
+                    assert bits_equal(rx.cpu()[valid], exp_x[0][valid]), f"rank {r} fp8 payload differs"
+                    assert bits_equal(rsf.cpu()[valid], exp_x[1][valid]), f"rank {r} scales differ"
+                if expand:
+                    assert torch.equal(plan.recv_w[:plan.num_rows].cpu(), ref[r][2])
+                else:
+                    assert torch.equal(plan.recv_idx[:plan.num_rows].cpu(), ref[r][1])
+                    assert torch.equal(plan.recv_w[:plan.num_rows].cpu(), ref[r][2])
+            # combine: expert output = received row scaled by a per-row factor (bf16), value channel = 0.5 - w
+            eouts, evals = [], []
+            for r in range(world):
+                rx = outs[r][0] if dmode == 0 else None
+                base = ref[r][0] if dmode == 0 else None
+                if dmode != 0:
+                    base = torch.randn((lays[r].num_rows, hidden), generator=torch.Generator().manual_seed(99 + r)).bfloat16()
+                eo = (base.float() * 0.5).bfloat16()
+                eouts.append(eo)
+                evals.append(0.5 - ref[r][2])
+            bias = None
+            if with_bias:
+                bias = [(torch.randn((t, hidden), generator=torch.Generator().manual_seed(5 + r)).bfloat16(),
+                         torch.randn((t, hidden), generator=torch.Generator().manual_seed(6 + r)).bfloat16()) for r, t in enumerate(tokens)]
+            couts = eng.combine([e.to(dev) for e in eouts], plans, [v.to(dev) for v in evals],
+                                bias=None if bias is None else [(a.to(dev), b.to(dev)) for a, b in bias])
+            cref = R.combine(eouts, lays, tokens, topk, topk_weights=evals, bias=bias)
+            torch.cuda.synchronize()
+            eng.check_status()
+            for r in range(world):
+                assert bits_equal(couts[r][0], cref[r][0]), f"rank {r} combined payload differs"
+                assert torch.equal(couts[r][1].cpu(), cref[r][1]), f"rank {r} returned weights differ"
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("mode", ["random", "invalid"])
+def test_expand_bf16(world, mode):
+    run_case(world, [100] * world, 512, 16 * world if world < 8 else 64, 4, mode)
+
+
+def test_uneven_tokens_and_empty_rank():
+    run_case(4, [130, 0, 64, 7], 256, 32, 6, "empty", repeats=2)
+
+
+def test_alignment_padding():
+    run_case(2, [96, 80], 512, 16, 4, "random", alignment=8)
+
+
+def test_rank_layout():
+    run_case(4, [70, 90, 64, 65], 512, 32, 4, "invalid", expand=False)
+
+
+def test_fp8_given_and_fused():
+    run_case(2, [128, 100], 1024, 16, 4, "random", dmode=1)
+    run_case(2, [128, 100], 1024, 16, 4, "random", dmode=2)
+    run_case(2, [50, 60], 384, 16, 4, "random", dmode=1)   # scale rows not 16-byte aligned
+
+
+def test_bias_and_hotspot():
+    run_case(4, [128] * 4, 1024, 32, 8, "hotspot", with_bias=True)
+
+
+def test_large_hidden_repeat():
+    run_case(2, [300, 280], 7168, 64, 8, "random", repeats=3)
+
+
+def test_wait_timeout_reports_status():
+    """A wait on a flag nobody writes runs out, the kernel returns, the host sees TIMEOUT."""
+    from deepep_b200.parallel.virtual import VirtualWorld
+    from deepep_b200.parallel.engine_cuda import CommunicationError
+
+    with VirtualWorld(1, 64, 256, 2, timeout=0.005) as vw:
+        s = vw.sessions[0]
+        s.wait_probe(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        st = s.status()
+        assert st["code"] == 1 and st["where"] == 99
+        with pytest.raises(CommunicationError):
+            vw.engine.check_status()
+        s.clear_status()
+        torch.cuda.synchronize()
+        assert s.status()["code"] == 0
