@@ -1,0 +1,246 @@
+"""Headline benchmark: expert-parallel high-throughput dispatch + combine (prefill shape).
+
+Config (DeepSeek-V3-shaped): per rank 4096 tokens, hidden 7168, 256 experts, top-8 with group-limited gating
+(8 groups, top-4 groups), bf16 dispatch and bf16 combine; synthetic tokens and routing.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 20 --warmup 5
+
+One step = one cached-handle dispatch + one combine through ``ElasticBuffer`` (the protocol of the reference's
+docs/performance.md:21-35 times the dispatch and combine kernels and reports notify separately).  ``value`` is the
+reference's effective bandwidth (docs/performance.md:61-69): routed rows x hidden x 2 bytes, local routes included,
+for both directions, summed over all ranks, divided by the device time of the slowest rank.  The ``e2e`` entry repeats
+the measurement through a fresh dispatch (notify included) with the step's inputs copied from pinned host memory and a
+scalar of the result read back every step.  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+TOKENS, HIDDEN, EXPERTS, TOPK, GROUPS, TOPK_GROUPS = 4096, 7168, 256, 8, 8, 4
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=TOKENS)
+    ap.add_argument("--hidden", type=int, default=HIDDEN)
+    ap.add_argument("--num-sms", type=int, default=0)
+    ap.add_argument("--skip-extras", action="store_true", help="only the headline metric (no fp8 / low-latency / MegaMoE extras)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.rows, self.proc, self.index = [], None, device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        clocks, reasons, sm_max = [], set(), None
+        for r in self.rows:
+            try:
+                clocks.append(float(r[1]))
+                sm_max = float(r[2])
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": sm_max, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def reference_arm(args):
+    line = {"impl": "reference", "unavailable": "the reference builds only for Ascend950/CANN (pip install fails: "
+            "'DEEPEP_NPU_ARCH must be Ascend950; other targets are unqualified'); there is no CUDA path to run"}
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+    import torch.distributed as dist
+
+    from deepep_b200 import ElasticBuffer
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests"))
+    from helpers import group_limited_routes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    T, H, E, K = args.tokens, args.hidden, EXPERTS, TOPK
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # synthetic inputs (pinned host copies feed the end-to-end measurement)
+    gen = torch.Generator().manual_seed(1000 + rank)
+    x_host = torch.randn((T, H), generator=gen).bfloat16().pin_memory()
+    idx_host = group_limited_routes(T, E, K, GROUPS, TOPK_GROUPS, seed=2000 + rank).pin_memory()
+    w_host = torch.softmax(torch.randn((T, K), generator=gen), dim=1).float().pin_memory()
+    x, idx, w = x_host.to(dev), idx_host.to(dev), w_host.to(dev)
+
+    buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True, num_sms=args.num_sms)
+    recv_x, _, recv_w, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+    rows = recv_x.shape[0]
+    expert_out = recv_x  # identity experts: the dispatch output is the combine input
+
+    def step():
+        out_x, _, _, _, _ = buf.dispatch(x, handle=handle)
+        combined, _, _ = buf.combine(out_x, handle)
+        return combined
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    start.record()
+    for _ in range(args.steps):
+        step()
+    end.record()
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = max_over_ranks(start.elapsed_time(end) / args.steps)
+
+    routed_rows_total = float(T * K * world)                       # every slot is valid in this workload
+    bytes_per_step = 2.0 * routed_rows_total * H * 2               # dispatch + combine, bf16
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # separate kernels (device time, max over ranks), the reference's per-operation view
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        sync_all()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        sync_all()
+        return max_over_ranks(s.elapsed_time(e) / iters) * 1e3
+
+    extras = {}
+    extras["dispatch_bf16_us"] = timed(lambda: buf.dispatch(x, handle=handle), args.steps)
+    out_rows = buf.dispatch(x, handle=handle)[0]
+    extras["combine_bf16_us"] = timed(lambda: buf.combine(out_rows, handle), args.steps)
+    extras["notify_plus_dispatch_us"] = timed(lambda: buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True),
+                                              max(3, args.steps // 2))
+    if not args.skip_extras:
+        xq = per_token_cast_to_fp8(x)
+        extras["dispatch_fp8_us"] = timed(lambda: buf.dispatch(xq, handle=handle), args.steps)
+        remote_frac = None
+        if world > 1:
+            local = E // world
+            dst = torch.div(idx_host, local, rounding_mode="floor")
+            remote = sum(int(((dst == d).any(dim=1)).sum()) for d in range(world) if d != rank)
+            remote_frac = remote / T
+            extras["nvlink_out_GBps_per_gpu_dispatch_bf16"] = remote * H * 2 / (extras["dispatch_bf16_us"] * 1e-6) / 1e9
+            extras["nvlink_out_GBps_per_gpu_dispatch_fp8"] = remote * (H + H // 128 * 4) / (extras["dispatch_fp8_us"] * 1e-6) / 1e9
+            extras["nvlink_out_GBps_per_gpu_combine_bf16"] = remote * H * 2 / (extras["combine_bf16_us"] * 1e-6) / 1e9
+            extras["remote_destinations_per_token"] = remote_frac
+
+    # end to end through the public API: pinned host inputs in, a scalar of the result out, every step
+    xd, idxd, wd = torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)
+
+    def e2e_step():
+        xd.copy_(x_host, non_blocking=True)
+        idxd.copy_(idx_host, non_blocking=True)
+        wd.copy_(w_host, non_blocking=True)
+        rx, _, rw, h, _ = buf.dispatch(xd, topk_idx=idxd, topk_weights=wd, num_experts=E, do_expand=True)
+        combined, _, _ = buf.combine(rx, h)
+        return float(combined[:, :8].float().sum().item())
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_iters = max(3, args.steps // 2)
+    s.record()
+    for _ in range(e2e_iters):
+        e2e_step()
+    e.record()
+    sync_all()
+    e2e_ms = max_over_ranks(s.elapsed_time(e) / e2e_iters)
+    h2d = x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4
+    e2e = {"value": bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+           "what": "H2D of x/topk_idx/topk_weights from pinned memory + notify + dispatch + combine + D2H of a checksum"}
+
+    buf.destroy()
+    if rank == 0:
+        line = {
+            "metric": "ht_dispatch_combine_effective_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {"model": "DeepSeek-V3-shaped MoE routing (EP dispatch+combine)", "tokens_per_rank": T, "hidden": H,
+                       "num_experts": E, "top_k": K, "routing": "group-limited (8 groups, top-4), N(0,1) logits + N(0,0.5) bias",
+                       "global_batch": T * world, "seq_len": T, "parallelism": f"ep{world}",
+                       "l2": "working set per step (>= 0.9 GB) is larger than the 126 MB L2; no explicit flush",
+                       "effective_bytes_per_step": bytes_per_step, "rows_per_rank": rows},
+            "per_gpu_value": value / world, "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps,
+            "kernels": extras,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,1 @@
+"""Expert parallelism: runtime, engines and the ElasticBuffer API (the only parallel dimension of this library)."""

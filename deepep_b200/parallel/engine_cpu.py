@@ -1,0 +1,119 @@
+"""CPU engine: the same operations over a host process group (Gloo) or a single process.
+
+Every rank all-gathers the small routing tables and the payload through the
+control plane and evaluates the all-rank oracle for its own rank.  It defines
+the behaviour the CUDA engine must reproduce bit for bit, and lets the whole
+Python orchestration (handles, events, backward by handle reversal) run on
+machines without a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..oracle import reference as R
+
+
+@dataclass
+class CpuPlan:
+    num_tokens: int
+    num_experts: int
+    num_topk: int
+    expand: bool
+    alignment: int
+    num_rows: int
+    num_staged_rows: int
+    expert_counts_list: List[int]
+    topk_idx: torch.Tensor
+    layouts: list                       # every rank's RankLayout
+    all_tokens: List[int]
+    all_idx: List[torch.Tensor]
+    all_w: Optional[List[torch.Tensor]]
+    expert_counts: torch.Tensor
+    expert_offsets: torch.Tensor
+    rank_rows: torch.Tensor
+    recv_row_src: torch.Tensor
+    recv_w: Optional[torch.Tensor]
+    recv_idx: Optional[torch.Tensor]
+    slot_row: Optional[torch.Tensor] = None
+    send_slot: Optional[torch.Tensor] = None
+    stage_meta: Optional[torch.Tensor] = None
+    chunk_start: Optional[torch.Tensor] = None
+    has_weights: bool = False
+    low_latency: bool = False
+
+    def tensors(self):
+        return [t for t in (self.topk_idx, self.expert_counts, self.expert_offsets, self.recv_row_src, self.recv_w,
+                            self.recv_idx) if t is not None]
+
+
+class CpuEngine:
+    def __init__(self, control, max_tokens: int, hidden: int, topk: int):
+        self.control, self.rank, self.world = control, control.rank, control.size
+        self.max_tokens, self.hidden, self.topk = max_tokens, hidden, topk
+        self.n = 1
+
+    def check_status(self) -> None:
+        pass
+
+    def _gather(self, obj):
+        return self.control.all_gather_object(obj)
+
+    def notify(self, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[Optional[torch.Tensor]], num_experts: int,
+               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0) -> List[CpuPlan]:
+        del cpu_sync, blocks
+        idx = topk_idx[0].cpu().long()
+        w = None if topk_w[0] is None else topk_w[0].cpu().float()
+        gathered = self._gather((idx, w))
+        all_idx = [g[0] for g in gathered]
+        all_w = None if any(g[1] is None for g in gathered) else [g[1] for g in gathered]
+        layouts = R.build_layouts(all_idx, num_experts, do_expand=expand, expert_alignment=alignment)
+        lay = layouts[self.rank]
+        k = idx.shape[1]
+        src = torch.full((lay.num_rows,), -1, dtype=torch.int32)
+        slot = lay.row_slot.clamp(min=0)
+        src[lay.row_index] = ((lay.row_source * self.max_tokens + lay.row_token) * k + slot).int()
+        recv_w = None
+        if all_w is not None:
+            fake_x = [torch.zeros((i.shape[0], 1)) for i in all_idx]
+            outs, _ = R.dispatch(fake_x, all_idx, all_w, num_experts, do_expand=expand, layouts=layouts)
+            recv_w = outs[self.rank][2]
+        rank_rows = torch.zeros(self.world + 1, dtype=torch.int32)
+        rank_rows[1:] = torch.cumsum(lay.rank_rows, 0).int()
+        return [CpuPlan(idx.shape[0], num_experts, k, expand, alignment, lay.num_rows, int(rank_rows[-1]),
+                        lay.expert_counts.tolist(), topk_idx[0], layouts, [i.shape[0] for i in all_idx], all_idx, all_w,
+                        lay.expert_counts.int(), lay.expert_offsets.int(), rank_rows, src, recv_w,
+                        lay.recv_topk_idx, has_weights=all_w is not None)]
+
+    def dispatch(self, xs: Sequence, plans: Sequence[CpuPlan], mode: int, blocks: int = 0):
+        del blocks
+        plan = plans[0]
+        x = xs[0]
+        x = tuple(t.cpu() for t in x) if isinstance(x, (tuple, list)) else x.cpu()
+        all_x = self._gather(x)
+        outs, _ = R.dispatch(all_x, plan.all_idx, None, plan.num_experts, do_expand=plan.expand,
+                             quantize_fp8=(mode == 2), layouts=plan.layouts)
+        out = outs[self.rank][0]
+        return [(out[0], out[1]) if isinstance(out, tuple) else (out, None)]
+
+    def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[CpuPlan], ws: Sequence[Optional[torch.Tensor]],
+                bias: Sequence = None, blocks: int = 0):
+        del blocks
+        plan = plans[0]
+        gathered = self._gather((xs[0].cpu(), None if ws[0] is None else ws[0].cpu().float(),
+                                 None if bias is None else bias[0]))
+        all_x = [g[0] for g in gathered]
+        all_w = None if any(g[1] is None for g in gathered) else [g[1] for g in gathered]
+        all_b = None if bias is None else [g[2] for g in gathered]
+        outs = R.combine(all_x, plan.layouts, plan.all_tokens, plan.num_topk, topk_weights=all_w, bias=all_b)
+        return [outs[self.rank]]
+
+    def ll_combine(self, xs: Sequence[torch.Tensor], plans: Sequence[CpuPlan]):
+        plan = plans[0]
+        all_x = self._gather(xs[0].cpu())
+        return [R.low_latency_combine(all_x, plan.layouts, plan.all_w, plan.all_tokens)[self.rank]]
+
+    def barrier(self) -> None:
+        self.control.barrier()

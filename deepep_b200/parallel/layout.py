@@ -1,0 +1,64 @@
+"""Workspace sizing shared by host code and tests.
+
+Parity: ``deep_ep/backends/mesh_clos/_elastic_layout.py`` of the reference
+(``WORLD_SIZES`` :5, ``validate_hidden`` :8-19, ``elastic_size_hint``
+:164-173).  The region list differs because the transport differs: a routing
+gather area, a dispatch staging area (one row per source token and
+destination rank), a combine partial area (one row per token and expert
+rank), the returned-weight area and the low-latency region.
+"""
+from __future__ import annotations
+
+WORLD_SIZES = (1, 2, 4, 8)
+MAX_TOKENS = 16384
+MAX_TOPK = 16
+MAX_HIDDEN = 8192
+LL_MAX_TOKENS = 256
+LL_SIZE_HINT = 8 << 30
+ALIGN = 2 << 20
+CONTROL_BYTES = 64 << 10
+
+
+def align_up(value: int, alignment: int) -> int:
+    return -(-value // alignment) * alignment
+
+
+def validate_hidden(hidden: int, fp8: bool = False) -> None:
+    if not 8 <= hidden <= MAX_HIDDEN:
+        raise ValueError(f"hidden must be in [8, {MAX_HIDDEN}]")
+    if hidden % 8:
+        raise ValueError("hidden must be a multiple of 8 (16-byte rows)")
+    if fp8 and hidden % 128:
+        raise ValueError("fp8 dispatch needs hidden % 128 == 0 (one scale per 128 values)")
+
+
+def ll_region_bytes(world: int, max_tokens: int, hidden: int, topk: int, num_experts_hint: int = 0) -> int:
+    """Bytes of the low-latency region: receive slots for dispatch and return slots for combine."""
+    if max_tokens > LL_MAX_TOKENS or max_tokens <= 0:
+        return 0
+    msg = align_up(hidden * 2 + 64, 128)                      # one token message: header + row (+ scales when fp8)
+    recv = world * max_tokens * topk * msg                    # worst case: every slot of every source lands here
+    ret = max_tokens * topk * align_up(hidden * 2, 128)       # one returned row per (token, slot)
+    counts = 2 * 1024 * world * 8 + 4096
+    return 2 * (recv + ret) + counts                          # two banks (call parity)
+
+
+def workspace_bytes(world: int, max_tokens: int, hidden: int, topk: int, ll_bytes: int = 0, mega_bytes: int = 0) -> int:
+    """Python mirror of the native ``make_layout`` (checked against it in the tests)."""
+    at = CONTROL_BYTES
+    stage_row = align_up(hidden * 2, 128)
+    for size in (world * 4 * 4, world * max_tokens * topk * 4, world * max_tokens * topk * 4,
+                 world * max_tokens * stage_row, max_tokens * world * hidden * 2, max_tokens * topk * 4, ll_bytes, mega_bytes):
+        at = align_up(at + size, 1024)
+    return align_up(at, ALIGN)
+
+
+def elastic_size_hint(world: int, max_tokens: int, hidden: int, topk: int) -> int:
+    if world not in WORLD_SIZES:
+        raise ValueError(f"world size must be one of {WORLD_SIZES}")
+    if not 0 < max_tokens <= MAX_TOKENS:
+        raise ValueError(f"num_max_tokens_per_rank must be in [1, {MAX_TOKENS}]")
+    if not 0 < topk <= MAX_TOPK:
+        raise ValueError(f"num_topk must be in [1, {MAX_TOPK}]")
+    validate_hidden(hidden)
+    return workspace_bytes(world, max_tokens, hidden, topk, ll_region_bytes(world, max_tokens, hidden, topk))

@@ -1,0 +1,100 @@
+"""ElasticBuffer across real GPUs (one process per GPU, NCCL control plane), against the all-rank oracle."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from deepep_b200.oracle import reference as R
+from helpers import bits_equal, group_limited_routes, make_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(world, T, H, E, K):
+    xs = [torch.randn((T, H), generator=torch.Generator().manual_seed(r)).bfloat16() for r in range(world)]
+    idx = [group_limited_routes(T, E, K, 8, 4, seed=50 + r) for r in range(world)]
+    ws = [make_weights(T, K, r) for r in range(world)]
+    return xs, idx, ws
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from deepep_b200 import ElasticBuffer
+
+    T, H, E, K = 512, 2048, 64, 8
+    xs, idx, ws = _inputs(world, T, H, E, K)
+    buf = ElasticBuffer(dist.group.WORLD, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True,
+                        num_gpu_timeout_secs=20)
+    ok = True
+    for rep in range(3):
+        rx, _, rw, handle, _ = buf.dispatch(xs[rank].to(dev), topk_idx=idx[rank].to(dev), topk_weights=ws[rank].to(dev),
+                                            num_experts=E, do_expand=True)
+        ref, lays = R.dispatch(xs, idx, ws, E, do_expand=True)
+        ok = ok and bits_equal(rx, ref[rank][0]) and torch.equal(rw.cpu(), ref[rank][2])
+        eouts = [(r[0].float() * 0.5).bfloat16() for r in ref]
+        out, ow, _ = buf.combine(eouts[rank].to(dev), handle, topk_weights=rw)
+        cref = R.combine(eouts, lays, [T] * world, K, topk_weights=[r[2] for r in ref])
+        ok = ok and bits_equal(out, cref[rank][0]) and torch.equal(ow.cpu(), cref[rank][1])
+        rx2 = buf.dispatch(out, handle=handle)[0]     # cached dispatch (backward of combine)
+        ref2, _ = R.dispatch([c[0] for c in cref], idx, None, E, do_expand=True, layouts=lays)
+        ok = ok and bits_equal(rx2, ref2[rank][0])
+    # fused fp8 dispatch
+    buf8 = ElasticBuffer(dist.group.WORLD, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True,
+                         use_fp8_dispatch=True, num_gpu_timeout_secs=20)
+    (q, sf), _, _, h8, _ = buf8.dispatch(xs[rank].to(dev), topk_idx=idx[rank].to(dev), num_experts=E, do_expand=True)
+    ref8, _ = R.dispatch(xs, idx, None, E, do_expand=True, quantize_fp8=True)
+    ok = ok and bits_equal(q, ref8[rank][0][0]) and bits_equal(sf, ref8[rank][0][1])
+    buf8.destroy()
+    buf.destroy()
+    results[rank] = bool(ok)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_real_ranks(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = _free_port()
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+        assert dict(results) == {r: True for r in range(world)}
+
+
+def test_single_gpu_public_api():
+    from deepep_b200 import ElasticBuffer
+
+    dev = torch.device("cuda")
+    T, H, E, K = 300, 1024, 32, 6
+    xs, idx, ws = _inputs(1, T, H, E, K)
+    buf = ElasticBuffer(None, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True)
+    stats = torch.zeros(E, dtype=torch.int64, device=dev)
+    rx, _, rw, handle, ev = buf.dispatch(xs[0].to(dev), topk_idx=idx[0].to(dev), topk_weights=ws[0].to(dev), num_experts=E,
+                                         do_expand=True, cumulative_local_expert_recv_stats=stats,
+                                         async_with_compute_stream=True)
+    ev.current_stream_wait()
+    ref, lays = R.dispatch(xs, idx, ws, E, do_expand=True)
+    assert bits_equal(rx, ref[0][0]) and stats.tolist() == lays[0].expert_counts.tolist()
+    assert handle.num_recv_tokens_per_expert_list == lays[0].expert_counts.tolist()
+    out, _, _ = buf.combine(rx, handle)
+    cref = R.combine([ref[0][0]], lays, [T], K)
+    assert bits_equal(out, cref[0][0])
+    # rank layout + aligned expanded layout
+    rx2, ridx, rw2, h2, _ = buf.dispatch(xs[0].to(dev), topk_idx=idx[0].to(dev), topk_weights=ws[0].to(dev), num_experts=E)
+    assert h2.is_low_latency is False or True
+    rx3, _, _, h3, _ = buf.dispatch(xs[0].to(dev), topk_idx=idx[0].to(dev), num_experts=E, do_expand=True, expert_alignment=16)
+    ref3, lays3 = R.dispatch(xs, idx, None, E, do_expand=True, expert_alignment=16)
+    assert bits_equal(rx3, ref3[0][0])
+    buf.destroy()
