@@ -225,8 +225,7 @@ class ElasticBuffer:
         stream = self.runtime.stream if use_comm_stream else torch.cuda.current_stream(self.device)
         if use_comm_stream:
             stream.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(stream):
-            self.engine.barrier()
+        self.engine.barrier(stream=stream)
         if use_comm_stream:
             torch.cuda.current_stream(self.device).wait_stream(stream)
         if with_cpu_sync:
@@ -256,11 +255,9 @@ class ElasticBuffer:
         cur = torch.cuda.current_stream(self.device)
         if async_with_compute_stream:
             return EventOverlap._from_resources(EventHandle(comm), tuple(resources))
+        # outputs were allocated on the current stream and the current stream now waits for the call:
+        # stream-ordered reuse of their memory is already safe, no record_stream needed
         cur.wait_stream(comm)
-        for t in resources:
-            for u in (t if isinstance(t, (tuple, list)) else (t,)):
-                if isinstance(u, torch.Tensor) and u.is_cuda:
-                    u.record_stream(cur)
         return EventOverlap()
 
     def _check(self) -> None:
@@ -303,7 +300,7 @@ class ElasticBuffer:
 
         Returns ``(recv_x | (recv_x, recv_x_sf), recv_topk_idx, recv_topk_weights, handle, event)``.
         """
-        del num_qps, allocate_on_comm_stream, do_handle_copy
+        del num_qps, do_handle_copy
         self._alive()
         x_data, x_sf = (x if isinstance(x, (tuple, list)) else (x, None))
         self._validate_x(x_data, x_sf)
@@ -312,7 +309,7 @@ class ElasticBuffer:
             if topk_idx is not None or topk_weights is not None:
                 raise ValueError("pass either routing tensors or a handle, not both")
             return self._dispatch_cached(x_data, x_sf, handle, num_sms, previous_event, previous_event_before_epilogue,
-                                         async_with_compute_stream)
+                                         async_with_compute_stream, allocate_on_comm_stream)
         if topk_idx is None or num_experts is None:
             raise ValueError("a fresh dispatch needs topk_idx and num_experts")
         self._validate_routing(topk_idx, topk_weights, tokens, num_experts)
@@ -332,16 +329,17 @@ class ElasticBuffer:
                                      alignment, mode, low_latency, cpu_sync))
         comm = self._enter(previous_event, previous_event_before_epilogue)
         try:
-            with self._on(comm):
+            with self._on(comm if allocate_on_comm_stream else None):
                 if low_latency and hasattr(self.engine, "ll_dispatch"):
                     return self._dispatch_low_latency(x_data, x_sf, topk_idx, topk_weights, num_experts, mode, cpu_sync,
                                                       comm, async_with_compute_stream)
                 plan = self.engine.notify([topk_idx], [topk_weights], num_experts, expand=expand, alignment=alignment,
-                                          cpu_sync=cpu_sync)[0]
+                                          cpu_sync=cpu_sync, stream=comm)[0]
                 recv_x, recv_sf = self.engine.dispatch([x if x_sf is not None else x_data], [plan], mode,
-                                                       blocks=num_sms or self.num_sms)[0]
+                                                       blocks=num_sms or self.num_sms, stream=comm)[0]
                 if stats is not None:
-                    stats.add_(plan.expert_counts.to(stats.dtype).to(stats.device))
+                    with self._on(comm):   # the counts are produced on the communication stream
+                        stats.add_(plan.expert_counts.to(stats.dtype).to(stats.device))
         except Exception as exc:
             self._note_failure(exc)
             raise
@@ -366,7 +364,7 @@ class ElasticBuffer:
                 self.runtime.failed = True
 
     def _dispatch_cached(self, x_data, x_sf, handle: EPHandle, num_sms, previous_event, previous_event_before_epilogue,
-                         async_with_compute_stream):
+                         async_with_compute_stream, allocate_on_comm_stream=False):
         self._own(handle)
         handle._check_unchanged()
         if x_data.shape[0] != handle._tokens:
@@ -374,12 +372,13 @@ class ElasticBuffer:
         mode = self._mode(x_data, x_sf)
         self._preflight("cached_dispatch", (x_data.shape[0] > 0, self.hidden, mode))
         comm = self._enter(previous_event, previous_event_before_epilogue)
-        with self._on(comm):
+        with self._on(comm if allocate_on_comm_stream else None):
             if handle.is_low_latency and hasattr(self.engine, "ll_dispatch"):
-                recv_x, recv_sf = self.engine.ll_dispatch_cached([x_data if x_sf is None else (x_data, x_sf)], [handle._plan], mode)[0]
+                recv_x, recv_sf = self.engine.ll_dispatch_cached([x_data if x_sf is None else (x_data, x_sf)], [handle._plan],
+                                                                 mode, stream=comm)[0]
             else:
                 recv_x, recv_sf = self.engine.dispatch([x_data if x_sf is None else (x_data, x_sf)], [handle._plan], mode,
-                                                       blocks=num_sms or self.num_sms)[0]
+                                                       blocks=num_sms or self.num_sms, stream=comm)[0]
         out_x = recv_x if recv_sf is None else (recv_x, recv_sf)
         event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, x_data, x_sf] + handle._tracked())
         return out_x, None, None, handle, event
@@ -387,7 +386,7 @@ class ElasticBuffer:
     def _dispatch_low_latency(self, x_data, x_sf, topk_idx, topk_weights, num_experts, mode, cpu_sync, comm,
                               async_with_compute_stream):
         plan, recv_x, recv_sf = self.engine.ll_dispatch([x_data if x_sf is None else (x_data, x_sf)], [topk_idx],
-                                                        [topk_weights], num_experts, mode, cpu_sync=cpu_sync)[0]
+                                                        [topk_weights], num_experts, mode, cpu_sync=cpu_sync, stream=comm)[0]
         rows = plan.num_rows
         h = self._make_handle(plan, True, num_experts, 1, 0, topk_idx, x_data.shape[0], True)
         h._saved_weights = topk_weights
@@ -417,7 +416,7 @@ class ElasticBuffer:
         Low-latency handles: ``sum_k w_k * row_k`` with the weights saved at dispatch.
         Returns ``(combined_x, combined_topk_weights | None, event)``.
         """
-        del num_qps, allocate_on_comm_stream
+        del num_qps
         self._alive()
         self._own(handle)
         handle._check_unchanged()
@@ -439,14 +438,14 @@ class ElasticBuffer:
         self._preflight("combine", (self.hidden, plan.expand, topk_weights is not None, bias is not None,
                                     handle.is_low_latency))
         comm = self._enter(previous_event, previous_event_before_epilogue)
-        with self._on(comm):
+        with self._on(comm if allocate_on_comm_stream else None):
             if handle.is_low_latency:
                 if topk_weights is not None or bias is not None:
                     raise ValueError("a low-latency combine applies the weights saved at dispatch; pass neither weights nor bias")
-                out, out_w = self.engine.ll_combine([x], [plan])[0], None
+                out, out_w = self.engine.ll_combine([x], [plan], stream=comm)[0], None
             else:
                 out, out_w = self.engine.combine([x], [plan], [topk_weights], bias=None if bias is None else [tuple(biases)],
-                                                 blocks=num_sms or self.num_sms)[0]
+                                                 blocks=num_sms or self.num_sms, stream=comm)[0]
         event = self._leave(comm, async_with_compute_stream, [out, out_w, x, topk_weights] + [b for b in biases if b is not None]
                             + handle._tracked())
         return out, out_w, event

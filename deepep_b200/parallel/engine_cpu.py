@@ -62,8 +62,8 @@ class CpuEngine:
         return self.control.all_gather_object(obj)
 
     def notify(self, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[Optional[torch.Tensor]], num_experts: int,
-               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0) -> List[CpuPlan]:
-        del cpu_sync, blocks
+               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0, stream=None) -> List[CpuPlan]:
+        del cpu_sync, blocks, stream
         idx = topk_idx[0].cpu().long()
         w = None if topk_w[0] is None else topk_w[0].cpu().float()
         gathered = self._gather((idx, w))
@@ -87,8 +87,8 @@ class CpuEngine:
                         lay.expert_counts.int(), lay.expert_offsets.int(), rank_rows, src, recv_w,
                         lay.recv_topk_idx, has_weights=all_w is not None)]
 
-    def dispatch(self, xs: Sequence, plans: Sequence[CpuPlan], mode: int, blocks: int = 0):
-        del blocks
+    def dispatch(self, xs: Sequence, plans: Sequence[CpuPlan], mode: int, blocks: int = 0, stream=None):
+        del blocks, stream
         plan = plans[0]
         x = xs[0]
         x = tuple(t.cpu() for t in x) if isinstance(x, (tuple, list)) else x.cpu()
@@ -99,8 +99,8 @@ class CpuEngine:
         return [(out[0], out[1]) if isinstance(out, tuple) else (out, None)]
 
     def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[CpuPlan], ws: Sequence[Optional[torch.Tensor]],
-                bias: Sequence = None, blocks: int = 0):
-        del blocks
+                bias: Sequence = None, blocks: int = 0, stream=None):
+        del blocks, stream
         plan = plans[0]
         gathered = self._gather((xs[0].cpu(), None if ws[0] is None else ws[0].cpu().float(),
                                  None if bias is None else bias[0]))
@@ -110,10 +110,10 @@ class CpuEngine:
         outs = R.combine(all_x, plan.layouts, plan.all_tokens, plan.num_topk, topk_weights=all_w, bias=all_b)
         return [outs[self.rank]]
 
-    def ll_combine(self, xs: Sequence[torch.Tensor], plans: Sequence[CpuPlan]):
+    def ll_combine(self, xs: Sequence[torch.Tensor], plans: Sequence[CpuPlan], stream=None):
         plan = plans[0]
         all_x = self._gather(xs[0].cpu())
         return [R.low_latency_combine(all_x, plan.layouts, plan.all_w, plan.all_tokens)[self.rank]]
 
-    def barrier(self) -> None:
+    def barrier(self, stream=None) -> None:
         self.control.barrier()

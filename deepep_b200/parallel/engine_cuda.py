@@ -86,8 +86,11 @@ class CudaEngine:
                 cnt=torch.empty((self.world * self.C.max_experts,), dtype=torch.int32, device=device)))
 
     # ------------------------------------------------------------------ helpers
-    def _stream(self) -> int:
-        return torch.cuda.current_stream(self.device).cuda_stream
+    def _stream(self, stream=None) -> int:
+        """Launch stream: ``stream`` if given, else the current stream.  Tensors are always allocated on the
+        *current* stream, so a caller that launches on a side stream and then makes the current stream wait for it
+        needs no ``record_stream`` bookkeeping."""
+        return (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
 
     def check_status(self) -> None:
         for s in self.sessions:
@@ -114,7 +117,7 @@ class CudaEngine:
 
     # ------------------------------------------------------------------ ops
     def notify(self, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[Optional[torch.Tensor]], num_experts: int,
-               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0) -> List[RoutingPlan]:
+               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0, stream=None) -> List[RoutingPlan]:
         C, lay, dev = self.C, self.layout, self.device
         P, K = self.world, lay.topk
         local = num_experts // P
@@ -148,9 +151,9 @@ class CudaEngine:
                              expert_offsets=plan.expert_offsets.data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(),
                              recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap))
         nblocks = blocks or max(1, min(32, self.sm_count // self.n))
-        C.notify(lay, self.sessions, args, nblocks, self._stream())
+        C.notify(lay, self.sessions, args, nblocks, self._stream(stream))
         if cpu_sync:
-            torch.cuda.current_stream(dev).synchronize()
+            (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
             self.check_status()
             for plan, s in zip(plans, self.sessions):
                 box = s.mailbox(4 + local)
@@ -160,7 +163,7 @@ class CudaEngine:
                 plan.expert_counts_list = box[4:4 + local]
         return plans
 
-    def dispatch(self, xs: Sequence, plans: Sequence[RoutingPlan], mode: int, blocks: int = 0, out_dtype=None):
+    def dispatch(self, xs: Sequence, plans: Sequence[RoutingPlan], mode: int, blocks: int = 0, stream=None):
         """xs[i] is a tensor (modes 0, 2) or a (fp8, scales) pair (mode 1). Returns [(recv_x, recv_sf | None)]."""
         lay, dev = self.layout, self.device
         H = lay.hidden
@@ -184,11 +187,11 @@ class CudaEngine:
                              rank_tokens=plan.rank_tokens.data_ptr(), meta_stride=plan.meta_stride,
                              recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf)))
         send, recv = self.split_blocks(blocks, 0.4)
-        self.C.dispatch(lay, self.sessions, args, send, recv, self._stream())
+        self.C.dispatch(lay, self.sessions, args, send, recv, self._stream(stream))
         return outs
 
     def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[RoutingPlan], ws: Sequence[Optional[torch.Tensor]],
-                bias: Sequence = None, blocks: int = 0):
+                bias: Sequence = None, blocks: int = 0, stream=None):
         lay, dev = self.layout, self.device
         H, K = lay.hidden, lay.topk
         outs, args = [], []
@@ -205,8 +208,8 @@ class CudaEngine:
                              meta_stride=plan.meta_stride, K=K, E=plan.num_experts, expand=int(plan.expand),
                              bias0=_ptr(b0), bias1=_ptr(b1), out=out.data_ptr(), out_w=_ptr(out_w)))
         send, recv = self.split_blocks(blocks, 0.6)
-        self.C.combine(lay, self.sessions, args, send, recv, self._stream())
+        self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream))
         return outs
 
-    def barrier(self) -> None:
-        self.C.barrier(self.sessions, self._stream())
+    def barrier(self, stream=None) -> None:
+        self.C.barrier(self.sessions, self._stream(stream))
