@@ -155,6 +155,7 @@ PYBIND11_MODULE(_C, m) {
   m.attr("max_experts") = kMaxExperts;
   m.attr("control_bytes") = (long long)kControlBytes;
   m.attr("row_slot_shift") = kRowSlotShift;
+  m.attr("control_dbg_offset") = (long long)offsetof(Control, dbg);
 
   py::class_<WsLayout>(m, "WsLayout")
       .def_readonly("gather_hdr", &WsLayout::gather_hdr).def_readonly("gather_idx", &WsLayout::gather_idx)
@@ -179,6 +180,7 @@ PYBIND11_MODULE(_C, m) {
       .def("close", &Session::close)
       .def("set_timeout", &Session::set_timeout)
       .def("clear_status", &Session::clear_status)
+      .def("read_control", [](const Session& s) { return py::bytes(s.read_control()); })
       .def("mapped", &Session::mapped)
       .def("peer", &Session::peer)
       .def_property_readonly("workspace", &Session::workspace)

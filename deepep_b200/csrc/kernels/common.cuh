@@ -64,6 +64,8 @@ struct Control {
   unsigned long long mega_flag[kMaxRanks][4];
   unsigned long long disp_chunk[kMaxRanks][kMaxChunks];
   unsigned long long comb_chunk[kMaxRanks][kMaxChunks];
+  // diagnostics: where a pipeline wait gave up (warp-indexed records of 4 words)
+  unsigned long long dbg[256];
 };
 constexpr size_t kControlBytes = 64 << 10;
 static_assert(sizeof(Control) <= kControlBytes, "control block overflows its reservation");
@@ -181,11 +183,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// The hardware may park the thread for up to the hinted time before reporting "not yet",
+// which keeps waiting warps from competing for issue slots with the warps that do the work.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
   return ok != 0;
 }
 // Bounded wait on a local mbarrier (completion of this CTA's own bulk loads).

@@ -9,6 +9,11 @@
 // The optional fp32 value channel (used for dispatch-backward) is returned per slot and is
 // never multiplied into the payload.
 //
+// Both sides are the same shared-memory ring pipeline: warp 0 streams whole rows into a ring
+// of row slots with bulk copies (up to ~220 KB in flight per SM), warps 1..7 each take every
+// 7th group, wait for the group's slots, reduce them in place from shared memory and hand the
+// result to a bulk store.  Row movement never touches registers unless a sum is needed.
+//
 // Parity: csrc/kernels/combine/combine.cpp:2224-2917 of the reference in its EP8 form
 // (rank-level dedup, no gateway stage): same numeric contract (fp32 sum -> bf16 partial ->
 // fp32 sum -> bf16), but no entry/exit device barriers, no prepare kernel and no final
@@ -17,9 +22,13 @@
 
 namespace dep {
 
-constexpr int kCombStages = 2;
+constexpr int kRingMaxSlots = 32;
+constexpr int kRingMaxRows = 8;      // larger groups are summed straight from global memory (see ring_rows)
+constexpr int kCombineThreads = 256;
+constexpr int kConsumerWarps = kCombineThreads / 32 - 1;
 
 __device__ __forceinline__ void fence_barrier_init2() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
 
 __device__ __forceinline__ void add_bf16x8(float acc[8], const int4& v) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -37,114 +46,317 @@ __device__ __forceinline__ int4 pack_bf16x8(const float acc[8]) {
   return out;
 }
 
-__global__ void __launch_bounds__(256, 1) ep_combine_ht_kernel(const __grid_constant__ CombineParams p) {
+// Slots are filled strictly in ring order by one producer thread, but the uses of one slot are
+// consumed by different warps.  An mbarrier wait only names a phase parity, so a warp waiting for
+// use u of a slot could mistake the completed use u - 2 for its own.  `issued` (the number of fills
+// the producer has started) removes the ambiguity: a consumer first waits until fill k was issued,
+// after which the slot's barrier can only be in the phase of use k.
+struct Ring {
+  uint64_t* full;
+  uint64_t* empty;
+  volatile unsigned* issued;
+  uint8_t* slots;
+  int num_slots, slot_bytes;
+  const Control* ctl;
+  __device__ __forceinline__ uint8_t* slot(unsigned k) const { return slots + (size_t)(k % num_slots) * slot_bytes; }
+  __device__ __forceinline__ uint32_t phase(unsigned k) const { return (k / num_slots) & 1u; }
+  // Bounded; also gives up as soon as the rank is aborted.
+  __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) const {
+    for (unsigned i = 1; i < (1u << 28); ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((i & 255u) == 0 && ld_volatile_int(&ctl->abort)) break;
+    }
+    if ((threadIdx.x & 31) == 0) {  // leave a record of the wait that gave up
+      unsigned long long* d = const_cast<unsigned long long*>(ctl->dbg) + ((blockIdx.x & 7) * 8 + (threadIdx.x >> 5)) * 4;
+      d[0] = 0xdead0000ull | blockIdx.x;
+      d[1] = (unsigned long long)(bar - full);   // < 32: full[slot]; >= 32: empty[slot - 32]
+      d[2] = parity;
+      d[3] += 1;
+    }
+    return false;
+  }
+  // producer (one thread)
+  __device__ __forceinline__ bool push(unsigned k, const void* src, uint32_t bytes) const {
+    if (!wait(&empty[k % num_slots], phase(k) ^ 1u)) return false;
+    mbar_expect_tx(&full[k % num_slots], bytes);
+    bulk_g2s(slot(k), src, bytes, &full[k % num_slots]);
+    __threadfence_block();
+    *issued = k + 1;
+    return true;
+  }
+  __device__ __forceinline__ bool push_empty(unsigned k) const {
+    if (!wait(&empty[k % num_slots], phase(k) ^ 1u)) return false;
+    mbar_arrive(&full[k % num_slots]);
+    __threadfence_block();
+    *issued = k + 1;
+    return true;
+  }
+  // warp-collective: lane 0 watches the fill counter, then every lane acquires the slot's barrier
+  __device__ __forceinline__ bool wait_full(unsigned k) const {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+      for (unsigned i = 1; *issued <= k; ++i) {
+        __nanosleep(100);
+        if ((i & 63u) == 0 && (ld_volatile_int(&ctl->abort) || i > (1u << 24))) { ok = 0; break; }
+      }
+      __threadfence_block();
+    }
+    if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
+    return wait(&full[k % num_slots], phase(k));
+  }
+  __device__ __forceinline__ void release(unsigned k) const { mbar_arrive(&empty[k % num_slots]); }
+};
+
+// Sum `n` (<= kRingMaxRows) ring slots starting at k (fp32, slot order) into slot k; biases are added last.
+__device__ __forceinline__ void reduce_slots(const Ring& ring, unsigned k, int n, int units, int lane,
+                                             const int4* bias0, const int4* bias1) {
+  const int4* rows[kRingMaxRows];
+#pragma unroll
+  for (int i = 0; i < kRingMaxRows; ++i) rows[i] = reinterpret_cast<const int4*>(ring.slot(k + (i < n ? i : 0)));
+  int4* out = reinterpret_cast<int4*>(ring.slot(k));
+  int u = lane;
+  for (; u + 32 < units; u += 64) {   // two independent 16-byte columns per step
+    float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < kRingMaxRows; ++i)
+      if (i < n) { int4 v0 = rows[i][u], v1 = rows[i][u + 32]; add_bf16x8(a0, v0); add_bf16x8(a1, v1); }
+    if (bias0) { add_bf16x8(a0, __ldg(bias0 + u)); add_bf16x8(a1, __ldg(bias0 + u + 32)); }
+    if (bias1) { add_bf16x8(a0, __ldg(bias1 + u)); add_bf16x8(a1, __ldg(bias1 + u + 32)); }
+    out[u] = pack_bf16x8(a0);
+    out[u + 32] = pack_bf16x8(a1);
+  }
+  for (; u < units; u += 32) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < kRingMaxRows; ++i)
+      if (i < n) add_bf16x8(acc, rows[i][u]);
+    if (bias0) add_bf16x8(acc, __ldg(bias0 + u));
+    if (bias1) add_bf16x8(acc, __ldg(bias1 + u));
+    out[u] = pack_bf16x8(acc);
+  }
+}
+
+// lane 0: store slot k to `dst`, then hand the slot back as soon as the copy engine has read it.
+// (A slot is never kept across groups: the producer refills slots strictly in ring order, so a slot
+// held until the warp's next group could block the producer from ever loading that group.)
+__device__ __forceinline__ void store_and_release(const Ring& ring, unsigned k, void* dst, uint32_t bytes) {
+  bulk_s2g(dst, ring.slot(k), bytes);
+  bulk_commit();
+  bulk_wait_read<0>();
+  ring.release(k);
+}
+
+__global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const __grid_constant__ CombineParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const CombineArgs& a = p.r[blockIdx.y];
   const WsLayout& lay = p.lay;
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, Tmax = lay.max_tokens, H = lay.hidden, K = a.K;
   const int NT = (Tmax + kChunkTokens - 1) / kChunkTokens;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_bytes = H * 2, units = H / 8;  // 16-byte units per row
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpCombine] + 1;
 
-  if ((int)blockIdx.x < p.send_blocks) {
-    // ================================================================ expert side: reduce + return
-    const int slot_bytes = (row_bytes + 127) & ~127;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * kCombStages;
-    uint8_t* slots = smem + 128 + (size_t)warp * kCombStages * slot_bytes;
-    if (lane == 0) {
-      for (int s = 0; s < kCombStages; ++s) mbar_init(&bars[s], 1);
-      fence_barrier_init2();
-    }
-    __syncthreads();
-    uint32_t parity[kCombStages] = {0, 0};
+  Ring ring;
+  ring.slot_bytes = (row_bytes + 127) & ~127;
+  ring.num_slots = min(kRingMaxSlots, (int)((220 << 10) / ring.slot_bytes));
+  ring.full = reinterpret_cast<uint64_t*>(smem);
+  ring.empty = ring.full + kRingMaxSlots;
+  ring.issued = reinterpret_cast<volatile unsigned*>(ring.empty + kRingMaxSlots);
+  if (threadIdx.x == 0) *ring.issued = 0;
+  ring.slots = smem + 1024;
+  ring.ctl = ctl;
+  const int ring_rows = min(kRingMaxRows, ring.num_slots);  // rows of one group that may sit in the ring
+  if (threadIdx.x < ring.num_slots) {
+    mbar_init(&ring.full[threadIdx.x], 1);
+    mbar_init(&ring.empty[threadIdx.x], 1);
+    fence_barrier_init2();
+  }
+  __syncthreads();
+
+  const bool expert_side = (int)blockIdx.x < p.send_blocks;
+  int alive = 1;
+  if (expert_side) {
     int ok = 1;
     if (threadIdx.x < P) ok = wait_flag_ge(&ctl->comb_ack[threadIdx.x], epoch - 1, ctx, kOpCombine, 0, threadIdx.x);
-    int alive = __syncthreads_and(ok);
+    alive = __syncthreads_and(ok);
+  }
+
+  if (alive && expert_side) {
+    // ================================================================ expert side: reduce + return
     int max_nt = 0;
     for (int r = 0; r < P; ++r) max_nt = max(max_nt, (a.rank_tokens[r] + kChunkTokens - 1) / kChunkTokens);
     const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
-    int it = 0;  // rows handled by this warp; picks the shared-memory slot
-    for (int item = blockIdx.x; item < max_nt * P && alive; item += p.send_blocks) {
-      const int c = item / P, s_rank = (me + item % P) % P;
-      if (c * kChunkTokens >= a.rank_tokens[s_rank]) continue;
-      const int j0 = a.chunk_start[s_rank * (NT + 1) + c], j1 = a.chunk_start[s_rank * (NT + 1) + c + 1];
-      uint8_t* partial = ctx.ws[s_rank] + lay.partial;
-      float* wret = reinterpret_cast<float*>(ctx.ws[s_rank] + lay.wret);
-      for (int j = j0 + warp; j < j1; j += nwarps, ++it) {
-        const int s = it & 1;
-        const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + j) * a.meta_stride;
-        const int t = rec[0], n = rec[1];
-        uint8_t* buf = slots + (size_t)s * slot_bytes;
-        uint8_t* dst = partial + ((size_t)t * P + me) * row_bytes;
-        if (lane == 0) bulk_wait_read<kCombStages - 1>();  // this slot's previous store has left shared memory
-        __syncwarp();
-        if (n == 1) {
-          if (lane == 0) {
-            mbar_expect_tx(&bars[s], row_bytes);
-            bulk_g2s(buf, x + (size_t)(rec[2] & kRowMask) * row_bytes, row_bytes, &bars[s]);
-          }
-          if (!mbar_wait(&bars[s], parity[s])) report_failure(ctx, kStatusTimeout, kOpCombine, 10, me, 0, 0);
-          parity[s] ^= 1;
-        } else {
-          for (int u = lane; u < units; u += 32) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int i = 0; i < n; ++i)
-              add_bf16x8(acc, __ldg(reinterpret_cast<const int4*>(x + (size_t)(rec[2 + i] & kRowMask) * row_bytes) + u));
-            reinterpret_cast<int4*>(buf)[u] = pack_bf16x8(acc);
-          }
-          fence_proxy_async_smem();
-        }
-        __syncwarp();
-        if (lane == 0) { bulk_s2g(dst, buf, row_bytes); bulk_commit(); }
-        if (a.w) {
-          if (a.expand) {
-            if (lane < n) wret[(size_t)t * K + (rec[2 + lane] >> kRowSlotShift)] = a.w[rec[2 + lane] & kRowMask];
-          } else if (lane < K && ((rec[3] >> lane) & 1)) {
-            wret[(size_t)t * K + lane] = a.w[(size_t)(rec[2] & kRowMask) * K + lane];
+    unsigned k = 0;
+    long long t_a = 0, t_b = 0, t_c = 0, t_d = 0, t0 = clock64(), tt;
+    if (warp == 0) {
+      if (lane == 0) {
+        bool okp = true;
+        for (int item = blockIdx.x; item < max_nt * P && okp; item += p.send_blocks) {
+          const int c = item / P, s_rank = (me + item % P) % P;
+          if (c * kChunkTokens >= a.rank_tokens[s_rank]) continue;
+          const int j0 = a.chunk_start[s_rank * (NT + 1) + c], j1 = a.chunk_start[s_rank * (NT + 1) + c + 1];
+          for (int j = j0; j < j1 && okp; ++j) {
+            const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + j) * a.meta_stride;
+            tt = clock64();
+            const int n = rec[1];
+            t_a += clock64() - tt;
+            if (n <= ring_rows) {
+              for (int i = 0; i < n && okp; ++i) {
+                tt = clock64();
+                const uint8_t* src = x + (size_t)(rec[2 + i] & kRowMask) * row_bytes;
+                t_a += clock64() - tt; tt = clock64();
+                okp = ring.wait(&ring.empty[k % ring.num_slots], ring.phase(k) ^ 1u);
+                t_b += clock64() - tt; tt = clock64();
+                okp = ring.push(k++, src, row_bytes);
+                t_c += clock64() - tt;
+              }
+            } else {
+              okp = ring.push_empty(k++);
+            }
           }
         }
+        if (blockIdx.x < 8) { unsigned long long* d = ctl->dbg + (blockIdx.x * 8 + warp) * 4; d[0] = t_a; d[1] = t_b; d[2] = t_c; d[3] = clock64() - t0; }
       }
-      if (lane == 0) { bulk_wait<0>(); fence_proxy_async(); }
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x == 0) st_release_sys(&control_of(ctx.ws[s_rank])->comb_chunk[me][c], epoch);
+    } else {
+      const int cw = warp - 1;
+      unsigned q = 0;
+      bool dead = false;
+      for (int item = blockIdx.x; item < max_nt * P; item += p.send_blocks) {
+        const int c = item / P, s_rank = (me + item % P) % P;
+        if (c * kChunkTokens >= a.rank_tokens[s_rank]) continue;
+        const int j0 = a.chunk_start[s_rank * (NT + 1) + c], j1 = a.chunk_start[s_rank * (NT + 1) + c + 1];
+        uint8_t* partial = ctx.ws[s_rank] + lay.partial;
+        float* wret = reinterpret_cast<float*>(ctx.ws[s_rank] + lay.wret);
+        for (int j = j0; j < j1; ++j, ++q) {
+          const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + j) * a.meta_stride;
+          const int t = rec[0], n = rec[1];
+          const int nslots = n <= ring_rows ? n : 1;
+          if ((int)(q % kConsumerWarps) == cw && !dead) {
+            tt = clock64();
+            for (int i = 0; i < nslots && !dead; ++i) dead = !ring.wait_full(k + i);
+            t_a += clock64() - tt; tt = clock64();
+            if (!dead) {
+              if (n > ring_rows) {  // rare: more rows than a group may hold in the ring
+                int4* out = reinterpret_cast<int4*>(ring.slot(k));
+                for (int u = lane; u < units; u += 32) {
+                  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                  for (int i = 0; i < n; ++i)
+                    add_bf16x8(acc, __ldg(reinterpret_cast<const int4*>(x + (size_t)(rec[2 + i] & kRowMask) * row_bytes) + u));
+                  out[u] = pack_bf16x8(acc);
+                }
+                fence_proxy_async_smem();
+              } else if (n > 1) {
+                reduce_slots(ring, k, n, units, lane, nullptr, nullptr);
+                fence_proxy_async_smem();
+              }
+              __syncwarp();
+              t_b += clock64() - tt; tt = clock64();
+              if (lane == 0) {
+                for (int i = 1; i < nslots; ++i) ring.release(k + i);
+                store_and_release(ring, k, partial + ((size_t)t * P + me) * row_bytes, row_bytes);
+              }
+              t_c += clock64() - tt;
+              if (a.w) {
+                if (a.expand) {
+                  if (lane < n) wret[(size_t)t * K + (rec[2 + lane] >> kRowSlotShift)] = a.w[rec[2 + lane] & kRowMask];
+                } else if (lane < K && ((rec[3] >> lane) & 1)) {
+                  wret[(size_t)t * K + lane] = a.w[(size_t)(rec[2] & kRowMask) * K + lane];
+                }
+              }
+            }
+          }
+          k += nslots;
+        }
+        // all partials of this (source, chunk) are complete: publish
+        tt = clock64();
+        if (lane == 0) { bulk_wait<0>(); fence_proxy_async(); }
+        __threadfence_system();
+        consumer_barrier();
+        t_d += clock64() - tt;
+        if (warp == 1 && lane == 0 && !ld_volatile_int(&ctl->abort))
+          st_release_sys(&control_of(ctx.ws[s_rank])->comb_chunk[me][c], epoch);
+      }
+      if (blockIdx.x < 8 && lane == 0) { unsigned long long* d = ctl->dbg + (blockIdx.x * 8 + warp) * 4; d[0] = t_a; d[1] = t_b; d[2] = t_c; d[3] = t_d; }
     }
-  } else {
+  } else if (alive) {
     // ================================================================ source side: final reduction
     const int rb = blockIdx.x - p.send_blocks;
     const int nchunks = (a.T + kChunkTokens - 1) / kChunkTokens;
     const uint8_t* partial = ctx.ws[me] + lay.partial;
     const float* wret = reinterpret_cast<const float*>(ctx.ws[me] + lay.wret);
-    int alive = 1;
-    for (int c = rb; c < nchunks && alive; c += p.recv_blocks) {
-      int ok = 1;
-      if (threadIdx.x < P) ok = wait_flag_ge(&ctl->comb_chunk[threadIdx.x][c], epoch, ctx, kOpCombine, 1, threadIdx.x);
-      alive = __syncthreads_and(ok);
-      if (!alive) break;
-      const int t1 = min(a.T, (c + 1) * kChunkTokens);
-      for (int t = c * kChunkTokens + warp; t < t1; t += nwarps) {
-        const int slot = lane < P ? a.send_slot[(size_t)t * P + lane] : -1;
-        const unsigned mask = __ballot_sync(0xffffffffu, slot >= 0);
-        const uint8_t* prow = partial + (size_t)t * P * row_bytes;
-        int4* orow = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.out) + (size_t)t * row_bytes);
-        for (int u = lane; u < units; u += 32) {
-          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (unsigned m = mask; m; m &= m - 1)
-            add_bf16x8(acc, ld_cg_int4(prow + (size_t)(__ffs(m) - 1) * row_bytes + (size_t)u * 16));
-          if (a.bias0) add_bf16x8(acc, __ldg(reinterpret_cast<const int4*>(a.bias0 + (size_t)t * H) + u));
-          if (a.bias1) add_bf16x8(acc, __ldg(reinterpret_cast<const int4*>(a.bias1 + (size_t)t * H) + u));
-          orow[u] = pack_bf16x8(acc);
-        }
-        if (a.out_w && lane < K) {
-          long long e = a.topk_idx[(size_t)t * K + lane];
-          bool valid = e >= 0 && e < a.E;
-          for (int q = 0; q < lane && valid; ++q) valid = a.topk_idx[(size_t)t * K + q] != e;
-          a.out_w[(size_t)t * K + lane] = valid ? __ldcg(wret + (size_t)t * K + lane) : 0.f;
+    uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
+    unsigned k = 0;
+    if (warp == 0) {
+      bool okp = true;
+      for (int c = rb; c < nchunks && okp; c += p.recv_blocks) {
+        int ok = 1;
+        if (lane < P) ok = wait_flag_ge(&ctl->comb_chunk[lane][c], epoch, ctx, kOpCombine, 1, lane);
+        okp = __all_sync(0xffffffffu, ok);
+        if (!okp) break;
+        fence_proxy_async();
+        const int t1 = min(a.T, (c + 1) * kChunkTokens);
+        for (int t = c * kChunkTokens; t < t1 && okp; ++t) {
+          const int slot = lane < P ? a.send_slot[(size_t)t * P + lane] : -1;
+          unsigned mask = __ballot_sync(0xffffffffu, slot >= 0);
+          if (lane == 0) {
+            if (mask == 0 || __popc(mask) > ring_rows) { okp = ring.push_empty(k++); mask = 0; }
+            for (; mask && okp; mask &= mask - 1)
+              okp = ring.push(k++, partial + ((size_t)t * P + (__ffs(mask) - 1)) * row_bytes, row_bytes);
+          }
+          okp = __shfl_sync(0xffffffffu, okp, 0);
+          k = __shfl_sync(0xffffffffu, k, 0);
         }
       }
+    } else {
+      const int cw = warp - 1;
+      unsigned q = 0;
+      bool dead = false;
+      for (int c = rb; c < nchunks; c += p.recv_blocks) {
+        const int t1 = min(a.T, (c + 1) * kChunkTokens);
+        for (int t = c * kChunkTokens; t < t1; ++t, ++q) {
+          const int slot = lane < P ? a.send_slot[(size_t)t * P + lane] : -1;
+          const unsigned dmask = __ballot_sync(0xffffffffu, slot >= 0);
+          const int n = __popc(dmask);
+          const int nslots = (n && n <= ring_rows) ? n : 1;
+          if ((int)(q % kConsumerWarps) == cw && !dead) {
+            for (int i = 0; i < nslots && !dead; ++i) dead = !ring.wait_full(k + i);
+            if (!dead) {
+              const int4* b0 = a.bias0 ? reinterpret_cast<const int4*>(a.bias0 + (size_t)t * H) : nullptr;
+              const int4* b1 = a.bias1 ? reinterpret_cast<const int4*>(a.bias1 + (size_t)t * H) : nullptr;
+              if (n > ring_rows) {  // more partials than a group may hold in the ring: read them directly
+                int4* dst = reinterpret_cast<int4*>(ring.slot(k));
+                for (int u = lane; u < units; u += 32) {
+                  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                  for (unsigned m = dmask; m; m &= m - 1)
+                    add_bf16x8(acc, ld_cg_int4(partial + ((size_t)t * P + (__ffs(m) - 1)) * row_bytes + (size_t)u * 16));
+                  if (b0) add_bf16x8(acc, __ldg(b0 + u));
+                  if (b1) add_bf16x8(acc, __ldg(b1 + u));
+                  dst[u] = pack_bf16x8(acc);
+                }
+                fence_proxy_async_smem();
+              } else if (n != 1 || b0 || b1) {
+                reduce_slots(ring, k, n, units, lane, b0, b1);
+                fence_proxy_async_smem();
+              }
+              __syncwarp();
+              if (lane == 0) {
+                for (int i = 1; i < nslots; ++i) ring.release(k + i);
+                store_and_release(ring, k, out + (size_t)t * row_bytes, row_bytes);
+              }
+              if (a.out_w && lane < K) {
+                long long e = a.topk_idx[(size_t)t * K + lane];
+                bool valid = e >= 0 && e < a.E;
+                for (int z = 0; z < lane && valid; ++z) valid = a.topk_idx[(size_t)t * K + z] != e;
+                a.out_w[(size_t)t * K + lane] = valid ? __ldcg(wret + (size_t)t * K + lane) : 0.f;
+              }
+            }
+          }
+          k += nslots;
+        }
+      }
+      if (lane == 0) bulk_wait<0>();
     }
   }
 
@@ -157,13 +369,17 @@ __global__ void __launch_bounds__(256, 1) ep_combine_ht_kernel(const __grid_cons
 
 cudaError_t launch_combine(const CombineParams& p, int nranks, cudaStream_t stream) {
   const size_t slot = ((size_t)p.lay.hidden * 2 + 127) & ~(size_t)127;
-  int warps = (int)((220 << 10) / (kCombStages * slot));
-  if (warps < 1) return cudaErrorInvalidValue;
-  if (warps > 8) warps = 8;
-  const size_t smem = 128 + (size_t)warps * kCombStages * slot;
-  cudaError_t e = cudaFuncSetAttribute(ep_combine_ht_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  dim3 grid(p.send_blocks + p.recv_blocks, nranks), block(warps * 32);
+  size_t nslots = (220 << 10) / slot;
+  if (nslots > kRingMaxSlots) nslots = kRingMaxSlots;
+  if (nslots < 2) return cudaErrorInvalidValue;
+  const size_t smem = 1024 + nslots * slot;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(ep_combine_ht_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  dim3 grid(p.send_blocks + p.recv_blocks, nranks), block(kCombineThreads);
   void* args[] = {const_cast<CombineParams*>(&p)};
   return cudaLaunchCooperativeKernel((const void*)ep_combine_ht_kernel, grid, block, args, smem, stream);
 }

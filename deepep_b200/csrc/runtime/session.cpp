@@ -120,6 +120,12 @@ void Session::clear_status() {
   check(cudaMemset(&c->abort, 0, sizeof(int)), "abort clear");
 }
 
+std::string Session::read_control() const {
+  std::string out(sizeof(Control), '\0');
+  check(cudaMemcpy(&out[0], ws_, sizeof(Control), cudaMemcpyDeviceToHost), "control block read");
+  return out;
+}
+
 void Session::release_all(bool ignore_errors) {
   CudaApi& api = cuda_api();
   cudaError_t first = cudaSuccess;

@@ -59,6 +59,7 @@ class Session {
   bool mapped() const;                                          // every peer mapping is non-null
   StatusBlock status() const { return *status_host_; }
   void clear_status();                                          // also clears the device abort word
+  std::string read_control() const;                             // copy of the control block (diagnostics)
   int* mailbox_host() const { return mailbox_host_; }
   int* mailbox_device() const { return mailbox_dev_; }
 
