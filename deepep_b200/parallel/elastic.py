@@ -399,7 +399,8 @@ class ElasticBuffer:
     def _make_handle(self, plan, expand, num_experts, alignment, num_sms, topk_idx, tokens, low_latency) -> EPHandle:
         counts = plan.expert_counts_list
         h = EPHandle(expand, num_experts, alignment, self.num_max_tokens_per_rank, num_sms, topk_idx,
-                     plan.num_staged_rows, plan.num_rows, counts, plan.rank_rows[1:], plan.expert_offsets[1:],
+                     plan.num_staged_rows, plan.num_rows, counts,
+                     None if plan.rank_rows is None else plan.rank_rows[1:], plan.expert_offsets[1:],
                      plan.expert_counts, plan.recv_row_src, getattr(plan, "slot_row", None),
                      getattr(plan, "stage_meta", None), getattr(plan, "chunk_start", None), is_low_latency=low_latency)
         h._plan, h._buffer_id, h._tokens, h._hidden = plan, self._id, tokens, self.hidden

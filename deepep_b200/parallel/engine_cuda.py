@@ -40,18 +40,21 @@ class RoutingPlan:
     num_staged_rows: int
     expert_counts_list: Optional[List[int]]
     topk_idx: torch.Tensor
-    send_slot: torch.Tensor
-    slot_row: torch.Tensor
-    stage_meta: torch.Tensor
-    chunk_start: torch.Tensor
-    rank_tokens: torch.Tensor
-    rank_rows: torch.Tensor
+    send_slot: Optional[torch.Tensor]
+    slot_row: Optional[torch.Tensor]
+    stage_meta: Optional[torch.Tensor]
+    chunk_start: Optional[torch.Tensor]
+    rank_tokens: Optional[torch.Tensor]
+    rank_rows: Optional[torch.Tensor]
     expert_counts: torch.Tensor
     expert_offsets: torch.Tensor
     recv_row_src: torch.Tensor
     recv_w: Optional[torch.Tensor]
     recv_idx: Optional[torch.Tensor]
     has_weights: bool = False
+    low_latency: bool = False
+    num_rows_dev: Optional[torch.Tensor] = None
+    topk_w: Optional[torch.Tensor] = None
 
     def tensors(self):
         return [t for t in (self.topk_idx, self.send_slot, self.slot_row, self.stage_meta, self.chunk_start, self.rank_tokens,
@@ -210,6 +213,76 @@ class CudaEngine:
         send, recv = self.split_blocks(blocks, 0.6)
         self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream))
         return outs
+
+    # ------------------------------------------------------------------ low latency
+    def ll_blocks(self) -> int:
+        return max(1, min(32, self.sm_count // self.n))
+
+    def ll_dispatch(self, xs: Sequence, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[torch.Tensor], num_experts: int,
+                    mode: int, cpu_sync: bool = True, stream=None, outputs: Optional[list] = None):
+        """One kernel: routing exchange + row push + expert-major receive.  Returns [(plan, recv_x, recv_sf | None)].
+
+        Outputs have the worst-case row count; with ``cpu_sync`` they are trimmed to the exact count after one
+        host synchronisation.  ``outputs`` lets a caller supply pre-allocated buffers (CUDA-graph capture).
+        """
+        lay, dev = self.layout, self.device
+        P, K, H = self.world, lay.topk, lay.hidden
+        local = num_experts // P
+        cap = P * lay.max_tokens * min(K, local)
+        res, args = [], []
+        for i in range(self.n):
+            x, sf = (xs[i] if isinstance(xs[i], (tuple, list)) else (xs[i], None))
+            T = x.shape[0]
+            i32 = dict(dtype=torch.int32, device=dev)
+            if outputs is not None:
+                o = outputs[i]
+            else:
+                o = dict(recv_x=torch.empty((cap, H), dtype=x.dtype if mode == 0 else torch.float8_e4m3fn, device=dev),
+                         recv_sf=None if mode == 0 else torch.empty((cap, H // 128), dtype=torch.float32, device=dev),
+                         recv_w=torch.empty((cap,), dtype=torch.float32, device=dev),
+                         recv_row_src=torch.empty((cap,), **i32), expert_counts=torch.empty((local,), **i32),
+                         expert_offsets=torch.empty((local + 1,), **i32), num_rows=torch.empty((1,), **i32))
+            plan = RoutingPlan(num_tokens=T, num_experts=num_experts, num_topk=K, expand=True, alignment=1, meta_stride=0,
+                               num_rows=cap, num_staged_rows=0, expert_counts_list=None, topk_idx=topk_idx[i], send_slot=None,
+                               slot_row=None, stage_meta=None, chunk_start=None, rank_tokens=None, rank_rows=None,
+                               expert_counts=o["expert_counts"], expert_offsets=o["expert_offsets"],
+                               recv_row_src=o["recv_row_src"], recv_w=o["recv_w"], recv_idx=None, has_weights=True)
+            plan.num_rows_dev, plan.topk_w, plan.low_latency = o["num_rows"], topk_w[i], True
+            res.append((plan, o["recv_x"], o["recv_sf"]))
+            args.append(dict(x=x.data_ptr(), x_sf=_ptr(sf), topk_idx=topk_idx[i].data_ptr(), topk_w=topk_w[i].data_ptr(), T=T,
+                             E=num_experts, mode=mode, recv_x=o["recv_x"].data_ptr(), recv_sf=_ptr(o["recv_sf"]),
+                             recv_w=o["recv_w"].data_ptr(), recv_row_src=o["recv_row_src"].data_ptr(),
+                             expert_counts=o["expert_counts"].data_ptr(), expert_offsets=o["expert_offsets"].data_ptr(),
+                             num_rows=o["num_rows"].data_ptr(), use_mailbox=int(cpu_sync), capacity=cap))
+        self.C.ll_dispatch(lay, self.sessions, args, self.ll_blocks(), self._stream(stream))
+        if cpu_sync:
+            (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
+            self.check_status()
+            out = []
+            for (plan, rx, rsf), s in zip(res, self.sessions):
+                box = s.mailbox(4 + local)
+                plan.num_rows, plan.expert_counts_list = box[0], box[4:4 + local]
+                out.append((plan, rx[:box[0]], None if rsf is None else rsf[:box[0]]))
+            return out
+        return res
+
+    def ll_dispatch_cached(self, xs: Sequence, plans: Sequence[RoutingPlan], mode: int, stream=None):
+        """Re-run the self-contained low-latency dispatch with the routing saved in the plans (backward of combine)."""
+        res = self.ll_dispatch(xs, [p.topk_idx for p in plans], [p.topk_w for p in plans], plans[0].num_experts, mode,
+                               cpu_sync=False, stream=stream)
+        return [(rx[:p.num_rows], None if rsf is None else rsf[:p.num_rows]) for (_, rx, rsf), p in zip(res, plans)]
+
+    def ll_combine(self, xs: Sequence[torch.Tensor], plans: Sequence[RoutingPlan], stream=None, outs: Optional[list] = None):
+        lay, dev = self.layout, self.device
+        results, args = [], []
+        for i, plan in enumerate(plans):
+            out = outs[i] if outs is not None else torch.empty((plan.num_tokens, lay.hidden), dtype=torch.bfloat16, device=dev)
+            results.append(out)
+            args.append(dict(x=xs[i].data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(), num_rows=plan.num_rows_dev.data_ptr(),
+                             topk_idx=plan.topk_idx.data_ptr(), topk_w=plan.topk_w.data_ptr(), T=plan.num_tokens,
+                             E=plan.num_experts, out=out.data_ptr()))
+        self.C.ll_combine(lay, self.sessions, args, self.ll_blocks(), self._stream(stream))
+        return results
 
     def barrier(self, stream=None) -> None:
         self.C.barrier(self.sessions, self._stream(stream))

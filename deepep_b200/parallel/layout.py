@@ -32,15 +32,20 @@ def validate_hidden(hidden: int, fp8: bool = False) -> None:
         raise ValueError("fp8 dispatch needs hidden % 128 == 0 (one scale per 128 values)")
 
 
-def ll_region_bytes(world: int, max_tokens: int, hidden: int, topk: int, num_experts_hint: int = 0) -> int:
-    """Bytes of the low-latency region: receive slots for dispatch and return slots for combine."""
+def ll_region_bytes(world: int, max_tokens: int, hidden: int, topk: int) -> int:
+    """Bytes of the low-latency region (two banks); 0 when the buffer is too large for that path.
+
+    Mirror of ``make_ll_layout`` in ``csrc/kernels/ll_api.h``: routing gather tables, per-row flags,
+    one staging slot per (source rank, token), one return slot per (token, top-k slot).
+    """
     if max_tokens > LL_MAX_TOKENS or max_tokens <= 0:
         return 0
-    msg = align_up(hidden * 2 + 64, 128)                      # one token message: header + row (+ scales when fp8)
-    recv = world * max_tokens * topk * msg                    # worst case: every slot of every source lands here
-    ret = max_tokens * topk * align_up(hidden * 2, 128)       # one returned row per (token, slot)
-    counts = 2 * 1024 * world * 8 + 4096
-    return 2 * (recv + ret) + counts                          # two banks (call parity)
+    msg = align_up(hidden * 2, 128)
+    at = 0
+    for size in (world * 16, world * max_tokens * topk * 4, world * max_tokens * topk * 4, world * 8, world * max_tokens * 8,
+                 world * max_tokens * msg, max_tokens * topk * 8, max_tokens * topk * hidden * 2):
+        at = align_up(at + size, 1024)
+    return 2 * at
 
 
 def workspace_bytes(world: int, max_tokens: int, hidden: int, topk: int, ll_bytes: int = 0, mega_bytes: int = 0) -> int:
