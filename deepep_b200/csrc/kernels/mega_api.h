@@ -1,6 +1,91 @@
-// Fused MoE (MegaMoE) launchers.
+// Fused MoE (MegaMoE): argument blocks and launchers.
+//
+// Counterpart of the reference's experiments/megamoe (csrc/forward.cpp:237-478, kernels/mega_moe/*):
+// dispatch -> grouped GEMM1 (fp8 activations x fp4 weights, block-scaled) -> SwiGLU + MXFP8 requant ->
+// grouped GEMM2 -> combine into the source rank -> weighted unpermute.
 #pragma once
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace dep {
+
+constexpr int kGemmBM = 128;   // token rows per tile (TMEM lanes)
+constexpr int kGemmBN = 128;   // output columns per tile
+constexpr int kGemmBK = 128;   // K elements per pipeline stage (one 128-byte swizzle row of fp8)
+constexpr int kSfChunk = 512;  // bytes of block scales of 128 rows x 128 K-elements (ue8m0 per 32)
+
+// Scale factors of a [rows, K] operand are stored as 512-byte chunks, one per (128-row block, 128-K block):
+// byte (r % 32) * 16 + (r % 128) / 32 * 4 + (k / 32) % 4 of chunk (r / 128) * (K / 128) + k / 128.
+// This is the image tcgen05.cp 32x128b.warpx4 moves into tensor memory without any shuffling.
+__host__ __device__ inline long long sf_offset(long long row, long long k, long long K) {
+  return ((row / 128) * (K / 128) + k / 128) * kSfChunk + (row % 32) * 16 + (row % 128) / 32 * 4 + (k / 32) % 4;
+}
+
+enum GemmEpilogue : int {
+  kEpiStoreF32 = 0,        // C fp32 [rows, N] (tests)
+  kEpiSwigluQuant = 1,     // tile = [64 gate | 64 up] columns -> silu(gate) * up -> e4m3 + ue8m0 per 32
+  kEpiCombine = 2          // bf16 rows written into the source rank's combine slots over NVLink
+};
+
+struct MegaGemmParams {
+  CUtensorMap tmap_a;        // activations [rows_pad, K] e4m3, box 128 x 128, 128-byte swizzle
+  CUtensorMap tmap_b;        // weights [experts * n_total, K] e2m1 (two per byte), unpacked to bytes by the copy engine
+  const uint8_t* sfa;        // chunked scales of A
+  const uint8_t* sfb;        // chunked scales of B
+  const int* mtile_expert;   // [max_mtiles] local expert of each 128-row tile
+  const int* num_mtiles;     // device scalar: tiles in use
+  int max_mtiles, n_tiles, k_steps, n_total;
+  int epi, b_tx_bytes;
+  // kEpiStoreF32
+  float* c;
+  int ldc, pad0;
+  // kEpiSwigluQuant
+  uint8_t* a2;               // [rows_pad, inter] e4m3
+  uint8_t* a2_sf;            // chunked scales of a2
+  int inter, pad1;
+  // kEpiCombine
+  const int* row_src;        // [rows_pad] (source * M + token) * topk + slot, -1 for padding rows
+  uint8_t* ws[kMaxRanks];    // every rank's workspace
+  long long comb_off;        // byte offset of the combine slots [M][topk][H] bf16 in a workspace
+  int max_tokens, topk, hidden, pad2;
+  int* error_flag;           // set when a pipeline wait ran out
+};
+cudaError_t launch_mega_gemm(const MegaGemmParams& p, int blocks, cudaStream_t stream);
+
+// Encodes a 2-D tensor map with a {128 (K), 128 (rows)} box and the 128-byte swizzle.
+// fp4 = true: elements are packed e2m1 pairs that the copy engine widens to one byte each in shared memory.
+bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, bool fp4, const char** error);
+
+// ---------------------------------------------------------------- routing + token pull
+struct MegaRouteArgs {
+  RankCtx ctx;
+  long long in_off;            // byte offset of the input block (x, x_sf, topk_idx, topk_w) in a workspace
+  int T, E, K, H;              // tokens of this rank, experts, top-k, hidden
+  int max_tokens, max_mtiles;
+  // outputs
+  uint8_t* a1;                 // [rows_pad, H] e4m3
+  uint8_t* a1_sf;              // chunked scales
+  int* row_src;                // [rows_pad]
+  int* mtile_expert;           // [max_mtiles]
+  int* num_mtiles;             // [1]
+  int* expert_rows;            // [L] rows per local expert
+  int* ticket;                 // [L] scratch: rows handed out so far
+};
+struct MegaRouteParams { WsLayout lay; MegaRouteArgs r[kMaxRanks]; };
+cudaError_t launch_mega_route(const MegaRouteParams& p, int nranks, int blocks, cudaStream_t stream);
+
+// Byte size and region offsets {hdr, x, x_sf, topk_idx, topk_w, total} of the symmetric input block.
+long long mega_input_bytes(int max_tokens, int hidden, int topk);
+void mega_input_offsets(int max_tokens, int hidden, int topk, long long* out6);
+
+struct MegaFinishArgs {
+  RankCtx ctx;
+  long long in_off, comb_off;
+  int T, E, K, H, max_tokens, pad;
+  __nv_bfloat16* y;            // [T, H]
+};
+struct MegaFinishParams { WsLayout lay; MegaFinishArgs r[kMaxRanks]; };
+cudaError_t launch_mega_finish(const MegaFinishParams& p, int nranks, int blocks, cudaStream_t stream);
+
 }  // namespace dep

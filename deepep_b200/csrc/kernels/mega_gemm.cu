@@ -1,0 +1,270 @@
+// Grouped block-scaled GEMM on the 5th-generation tensor cores (tcgen05 + tensor memory):
+//   C[rows of expert e, n] = sum_k A[row, k] * B[e][n, k]
+// A: e4m3 activations with one ue8m0 scale per 32 values of K; B: e2m1 weights (two per byte in
+// global memory, widened to one byte per value by the copy engine) with ue8m0 scales per 32.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0     one lane issues the TMA tile loads (A, B) and bulk loads (scale chunks) of a stage
+//   warp 1     allocates tensor memory; one lane copies the scales smem -> TMEM (tcgen05.cp) and
+//              issues four tcgen05.mma (M=128, N=128, K=32) per stage; tcgen05.commit frees the stage
+//   warps 2-5  epilogue: tcgen05.ld of the fp32 accumulator (one tile row per thread), then
+//              store fp32 | SwiGLU + MXFP8 requantisation | bf16 rows pushed into the source
+//              rank's combine slots over NVLink.  Two accumulator buffers let the epilogue of
+//              tile i overlap the MMAs of tile i + 1.
+// All waits are bounded; a wait that runs out sets an error flag, the CTA stops issuing work,
+// frees its tensor memory and returns.
+//
+// Parity: the cube-core GMM1/GMM2 stages and their vector-core epilogues of the reference's MegaMoE
+// (experiments/megamoe/csrc/kernels/mega_moe/mega_moe_wave_a8w4.hpp, catlass_gmm/block_mmad_a8w4.hpp,
+// epilogue/block_epilogue_activation_mx_quant.hpp, stage/gmm2_combine.hpp).
+#include "mega_api.h"
+#include "umma.cuh"
+
+namespace dep {
+
+constexpr int kGemmThreads = 192;
+constexpr int kGemmStages = 5;
+constexpr int kTileABytes = kGemmBM * kGemmBK;      // 16 KB
+constexpr int kTileBBytes = kGemmBN * kGemmBK;      // 16 KB in shared memory (one byte per value)
+constexpr int kStageBytes = kTileABytes + kTileBBytes;
+constexpr int kSfStageBytes = 2 * kSfChunk;
+constexpr int kEpiStageBytes = 4 * 32 * kGemmBN * 2;   // bf16 staging of the four epilogue warps
+constexpr int kTmemCols = 512;
+constexpr int kAccCols = kGemmBN;                    // fp32 accumulator columns per buffer
+constexpr int kSfColBase = 2 * kAccCols;             // scale columns start after the two accumulators
+constexpr size_t kGemmSmem = 1024 + (size_t)kGemmStages * (kStageBytes + kSfStageBytes) + kEpiStageBytes + 256;
+
+struct GemmBarriers {
+  uint64_t full[kGemmStages], empty[kGemmStages], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int failed;
+};
+
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  for (unsigned i = 0; i < (1u << 22); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *failed) return false;
+  }
+  *failed = 1;
+  return false;
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__global__ void __launch_bounds__(kGemmThreads, 1) mega_gemm_kernel(const __grid_constant__ MegaGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
+  uint8_t* tiles = smem;
+  uint8_t* sf_smem = tiles + (size_t)kGemmStages * kStageBytes;
+  uint8_t* epi_smem = sf_smem + (size_t)kGemmStages * kSfStageBytes;
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(epi_smem + kEpiStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&bars->acc_full[b], 1); mbar_init(&bars->acc_empty[b], 4); }
+    bars->failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    umma::prefetch_tensormap(&p.tmap_a);
+    umma::prefetch_tensormap(&p.tmap_b);
+  }
+  if (warp == 1) {
+    umma::tmem_alloc(&bars->tmem_base, kTmemCols);
+    umma::tmem_relinquish();
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* failed = &bars->failed;
+
+  const int num_mtiles = min(*p.num_mtiles, p.max_mtiles);
+  const int total_tiles = num_mtiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ============================================================ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*failed; tile += gridDim.x) {
+        const int mt = tile / p.n_tiles, nb = tile - mt * p.n_tiles;
+        const int brow = p.mtile_expert[mt] * p.n_total + nb * kGemmBN;
+        for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+          const int s = it % kGemmStages;
+          if (!bounded_wait(&bars->empty[s], ((it / kGemmStages) & 1u) ^ 1u, failed)) break;
+          uint8_t* a_dst = tiles + (size_t)s * kStageBytes;
+          uint8_t* sf_dst = sf_smem + (size_t)s * kSfStageBytes;
+          mbar_expect_tx(&bars->full[s], kTileABytes + p.b_tx_bytes + 2 * kSfChunk);
+          umma::tma_load_2d(a_dst, &p.tmap_a, ks * kGemmBK, mt * kGemmBM, &bars->full[s]);
+          umma::tma_load_2d(a_dst + kTileABytes, &p.tmap_b, ks * kGemmBK, brow, &bars->full[s]);
+          bulk_g2s(sf_dst, p.sfa + ((size_t)mt * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+          bulk_g2s(sf_dst + kSfChunk, p.sfb + ((size_t)(brow / 128) * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, /*e4m3*/ 0, /*e2m1*/ 5);
+      uint32_t it = 0, local_tile = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*failed; tile += gridDim.x, ++local_tile) {
+        const int buf = local_tile & 1;
+        if (!bounded_wait(&bars->acc_empty[buf], ((local_tile >> 1) & 1u) ^ 1u, failed)) break;
+        umma::fence_after_sync();
+        const uint32_t acc = tmem + buf * kAccCols;
+        for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+          const int s = it % kGemmStages;
+          if (!bounded_wait(&bars->full[s], (it / kGemmStages) & 1u, failed)) break;
+          umma::fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * kStageBytes);
+          const uint32_t sf_addr = smem_u32(sf_smem + (size_t)s * kSfStageBytes);
+          const uint32_t tsfa = tmem + kSfColBase + s * 8, tsfb = tsfa + 4;
+          umma::copy_sf_to_tmem(tsfa, umma::smem_desc_sf(sf_addr));
+          umma::copy_sf_to_tmem(tsfb, umma::smem_desc_sf(sf_addr + kSfChunk));
+          const uint64_t da = umma::smem_desc_sw128(a_addr), db = umma::smem_desc_sw128(a_addr + kTileABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)   // 32 K-values = 32 bytes = 2 descriptor units per step inside the swizzle row
+            umma::mma_block_scaled(acc, da + 2 * k, db + 2 * k, umma::with_sf_ids(idesc, k, k), tsfa, tsfb, ks > 0 || k > 0);
+          umma::commit(&bars->empty[s]);          // stage (tiles, scale columns) reusable once these MMAs finished
+        }
+        umma::commit(&bars->acc_full[buf]);        // accumulator complete
+      }
+    }
+  } else {
+    // ============================================================ epilogue (warps 2..5)
+    const int quad = warp & 3;                       // TMEM lanes [32 * quad, 32 * quad + 32)
+    const int row_in_tile = quad * 32 + lane;
+    uint8_t* stage = epi_smem + (size_t)(warp - 2) * 32 * kGemmBN * 2;
+    uint32_t local_tile = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !*failed; tile += gridDim.x, ++local_tile) {
+      const int mt = tile / p.n_tiles, nb = tile - mt * p.n_tiles, buf = local_tile & 1;
+      if (!bounded_wait(&bars->acc_full[buf], (local_tile >> 1) & 1u, failed)) break;
+      umma::fence_after_sync();
+      const uint32_t taddr = tmem + buf * kAccCols + ((uint32_t)(quad * 32) << 16);
+      const long long row = (long long)mt * kGemmBM + row_in_tile;
+      uint32_t v[32], u[32];
+      if (p.epi == kEpiStoreF32) {
+        for (int c = 0; c < kGemmBN; c += 32) {
+          umma::tmem_ld32(taddr + c, v);
+          umma::tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(p.c + row * p.ldc + nb * kGemmBN + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                             __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+        }
+      } else if (p.epi == kEpiSwigluQuant) {
+        // columns [0, 64) are gate rows of W1, [64, 128) the matching up rows: 64 outputs per tile row
+        for (int half = 0; half < 2; ++half) {
+          umma::tmem_ld32(taddr + half * 32, v);
+          umma::tmem_ld32(taddr + 64 + half * 32, u);
+          umma::tmem_ld_wait();
+          float h[32], amax = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float g = bf16_round(__uint_as_float(v[i])), up = bf16_round(__uint_as_float(u[i]));
+            const float act = g / (1.0f + __expf(fminf(fmaxf(-g, -80.f), 80.f))) * up;
+            h[i] = bf16_round(act);
+            amax = fmaxf(amax, fabsf(h[i]));
+          }
+          // MX scale: 2^(floor(log2(amax)) - 8), at least 2^-127; values saturate at 448
+          int e = (int)((__float_as_uint(fmaxf(amax, 1.1754944e-38f)) >> 23) & 0xff) - 127 - 8;
+          e = max(e, -127);
+          const float inv = __uint_as_float((uint32_t)(127 - e) << 23);   // 2^-e, exact (e in [-127, 120])
+          uint32_t q[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            q[i] = (uint32_t)__nv_cvt_float_to_fp8(h[4 * i] * inv, __NV_SATFINITE, __NV_E4M3) |
+                   ((uint32_t)__nv_cvt_float_to_fp8(h[4 * i + 1] * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
+                   ((uint32_t)__nv_cvt_float_to_fp8(h[4 * i + 2] * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
+                   ((uint32_t)__nv_cvt_float_to_fp8(h[4 * i + 3] * inv, __NV_SATFINITE, __NV_E4M3) << 24);
+          }
+          const long long col = (long long)nb * 64 + half * 32;
+          uint4* dst = reinterpret_cast<uint4*>(p.a2 + row * p.inter + col);
+          dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+          dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+          p.a2_sf[sf_offset(row, col, p.inter)] = (uint8_t)(e + 127);
+        }
+      } else {
+        // bf16 row segment -> shared staging -> one bulk copy per row into the source rank's combine slot
+        bulk_wait_read<0>();                    // this lane's previous copy has left its staging row
+        __syncwarp();
+        uint4* mine = reinterpret_cast<uint4*>(stage + (size_t)lane * kGemmBN * 2);
+        for (int c = 0; c < kGemmBN; c += 32) {
+          umma::tmem_ld32(taddr + c, v);
+          umma::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+              w[j] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            mine[c / 8 + i] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        const int code = p.row_src[row];
+        if (code >= 0) {
+          const int src = code / (p.max_tokens * p.topk), rem = code - src * p.max_tokens * p.topk;
+          uint8_t* dst = p.ws[src] + p.comb_off + ((size_t)rem * p.hidden + (size_t)nb * kGemmBN) * 2;
+          bulk_s2g(dst, mine, kGemmBN * 2);
+        }
+        bulk_commit();
+      }
+      umma::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+    }
+    if (p.epi == kEpiCombine) { bulk_wait<0>(); fence_proxy_async(); __threadfence_system(); }
+  }
+
+  umma::fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *failed && p.error_flag) *p.error_flag = 1;
+  if (warp == 1) {
+    umma::fence_after_sync();
+    umma::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+cudaError_t launch_mega_gemm(const MegaGemmParams& p, int blocks, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mega_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  void* args[] = {const_cast<MegaGemmParams*>(&p)};
+  return cudaLaunchKernel((const void*)mega_gemm_kernel, dim3(blocks), dim3(kGemmThreads), args, kGemmSmem, stream);
+}
+
+bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, bool fp4, const char** error) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) {
+      *error = "cuTensorMapEncodeTiled is not available";
+      return false;
+    }
+    encode = reinterpret_cast<EncodeFn>(fn);
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(fp4 ? k / 2 : k)};
+  cuuint32_t box[2] = {kGemmBK, 128};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base),
+                      dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    *error = "cuTensorMapEncodeTiled rejected the operand (check 16/32-byte alignment of base and row stride)";
+    return false;
+  }
+  return true;
+}
+
+}  // namespace dep

@@ -1,0 +1,111 @@
+// Thin wrappers over the Blackwell (sm_100a) tensor-core instruction set: tensor memory (TMEM)
+// management, tcgen05.mma with block scaling, tcgen05.cp / tcgen05.ld, TMA tile loads, and the
+// shared-memory / instruction descriptors they take.  Field positions follow the public PTX ISA
+// description of the tcgen05 descriptors.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace dep {
+namespace umma {
+
+// ---------------------------------------------------------------- descriptors
+// Shared-memory matrix descriptor, K-major operand tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what a TMA tile load with SWIZZLE_128B produces): 8-row groups are 1024 B apart.
+__host__ __device__ inline uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);       // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major): 1
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                            // layout: SWIZZLE_128B
+  return d;
+}
+// Descriptor of a scale-factor chunk for tcgen05.cp 32x128b: 32 rows of 16 bytes, no swizzle.
+__host__ __device__ inline uint64_t smem_desc_sf(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(128 >> 4) << 32;                   // 8 rows x 16 B between row groups
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+// Instruction descriptor of kind::mxf8f6f4 with block scaling (ue8m0 scales, one per 32 values of K).
+// a_fmt/b_fmt: 0 = e4m3, 1 = e5m2, 5 = e2m1.  A and B are K-major, D is fp32.
+__host__ __device__ inline uint32_t instr_desc_mxf8f6f4(int m, int n, int a_fmt, int b_fmt) {
+  uint32_t d = 0;
+  d |= (uint32_t)a_fmt << 7;
+  d |= (uint32_t)b_fmt << 10;
+  d |= (uint32_t)(n >> 3) << 17;
+  d |= 1u << 23;                                     // scale format: ue8m0
+  d |= (uint32_t)(m >> 4) << 24;
+  return d;
+}
+__host__ __device__ inline uint32_t with_sf_ids(uint32_t idesc, int a_sf_id, int b_sf_id) {
+  return idesc | ((uint32_t)b_sf_id << 4) | ((uint32_t)a_sf_id << 29);
+}
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------- tensor memory
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {  // one full warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {       // one full warp
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// ---------------------------------------------------------------- MMA, commit, copies
+// D[tmem] (+)= A[smem] * B[smem]^T with per-32 block scales read from TMEM.  One thread issues.
+__device__ __forceinline__ void mma_block_scaled(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t tmem_sfa, uint32_t tmem_sfb, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+// Arrive on an mbarrier once all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 rows x 16 bytes from shared memory into 4 TMEM columns, replicated to all four lane quadrants.
+__device__ __forceinline__ void copy_sf_to_tmem(uint32_t tmem_col, uint64_t sf_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(sf_desc) : "memory");
+}
+// 32 consecutive fp32 columns of this warp's 32 lanes.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// 2-D tile load through a tensor map into shared memory (this CTA only), completion on an mbarrier.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
+  return pred != 0;
+}
+#endif  // __CUDACC__
+
+}  // namespace umma
+}  // namespace dep

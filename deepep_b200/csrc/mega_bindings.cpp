@@ -1,3 +1,106 @@
+// Bindings of the fused-MoE kernels (see kernels/mega_api.h).
+// Parity: experiments/megamoe/csrc/bindings.cpp:11-29 and forward.cpp:295-478 of the reference.
 #include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "kernels/mega_api.h"
+#include "runtime/session.h"
+
 namespace py = pybind11;
-void bind_mega(py::module_& m) { (void)m; }
+using namespace dep;
+
+namespace {
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+  }
+}
+template <class T> T* ptr(const py::dict& d, const char* key) {
+  if (!d.contains(key) || d[key].is_none()) return nullptr;
+  return reinterpret_cast<T*>(d[key].cast<uintptr_t>());
+}
+int geti(const py::dict& d, const char* key, int dflt = 0) { return d.contains(key) ? d[key].cast<int>() : dflt; }
+long long getl(const py::dict& d, const char* key, long long dflt = 0) { return d.contains(key) ? d[key].cast<long long>() : dflt; }
+
+// One grouped GEMM launch.  `d` carries operand pointers and shapes; `session` is needed only by the
+// combine epilogue (peer workspaces).
+void op_mega_gemm(const py::dict& d, py::object session, int blocks, uintptr_t stream) {
+  MegaGemmParams p{};
+  const long long rows_pad = getl(d, "rows_pad"), k = getl(d, "k"), b_rows = getl(d, "b_rows");
+  if (rows_pad % kGemmBM || k % kGemmBK || b_rows % kGemmBN) throw std::invalid_argument("rows, K and weight rows must be multiples of 128");
+  const char* err = nullptr;
+  if (!encode_operand_map(&p.tmap_a, ptr<const void>(d, "a"), rows_pad, k, false, &err)) throw std::runtime_error(err);
+  if (!encode_operand_map(&p.tmap_b, ptr<const void>(d, "b"), b_rows, k, true, &err)) throw std::runtime_error(err);
+  p.sfa = ptr<const uint8_t>(d, "sfa"); p.sfb = ptr<const uint8_t>(d, "sfb");
+  p.mtile_expert = ptr<const int>(d, "mtile_expert"); p.num_mtiles = ptr<const int>(d, "num_mtiles");
+  p.max_mtiles = (int)(rows_pad / kGemmBM);
+  p.n_total = geti(d, "n_total"); p.n_tiles = p.n_total / kGemmBN; p.k_steps = (int)(k / kGemmBK);
+  if (p.n_total % kGemmBN) throw std::invalid_argument("output width must be a multiple of 128");
+  p.epi = geti(d, "epi");
+  p.b_tx_bytes = geti(d, "b_tx_bytes", kGemmBN * kGemmBK / 2);
+  p.c = ptr<float>(d, "c"); p.ldc = geti(d, "ldc");
+  p.a2 = ptr<uint8_t>(d, "a2"); p.a2_sf = ptr<uint8_t>(d, "a2_sf"); p.inter = geti(d, "inter");
+  p.row_src = ptr<const int>(d, "row_src");
+  p.comb_off = getl(d, "comb_off"); p.max_tokens = geti(d, "max_tokens"); p.topk = geti(d, "topk"); p.hidden = geti(d, "hidden");
+  p.error_flag = ptr<int>(d, "error_flag");
+  if (p.epi == kEpiCombine) {
+    RankCtx ctx = session.cast<Session&>().ctx();
+    for (int r = 0; r < ctx.world; ++r) p.ws[r] = ctx.ws[r];
+  }
+  check(launch_mega_gemm(p, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_gemm launch");
+}
+
+void op_mega_route(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
+                   uintptr_t stream) {
+  MegaRouteParams p{};
+  p.lay = lay;
+  const int n = (int)args.size();
+  if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
+  for (int i = 0; i < n; ++i) {
+    const py::dict& d = args[i];
+    MegaRouteArgs& a = p.r[i];
+    a.ctx = sessions[i].cast<Session&>().ctx();
+    a.in_off = getl(d, "in_off"); a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K"); a.H = geti(d, "H");
+    a.max_tokens = geti(d, "max_tokens"); a.max_mtiles = geti(d, "max_mtiles");
+    a.a1 = ptr<uint8_t>(d, "a1"); a.a1_sf = ptr<uint8_t>(d, "a1_sf"); a.row_src = ptr<int>(d, "row_src");
+    a.mtile_expert = ptr<int>(d, "mtile_expert"); a.num_mtiles = ptr<int>(d, "num_mtiles");
+    a.expert_rows = ptr<int>(d, "expert_rows"); a.ticket = ptr<int>(d, "ticket");
+    if (a.H % 128 || a.E % a.ctx.world || a.E > kMaxExperts) throw std::invalid_argument("hidden % 128 == 0 and experts % world == 0 are required");
+  }
+  check(launch_mega_route(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_route launch");
+}
+
+void op_mega_finish(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
+                    uintptr_t stream) {
+  MegaFinishParams p{};
+  p.lay = lay;
+  const int n = (int)args.size();
+  if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
+  for (int i = 0; i < n; ++i) {
+    const py::dict& d = args[i];
+    MegaFinishArgs& a = p.r[i];
+    a.ctx = sessions[i].cast<Session&>().ctx();
+    a.in_off = getl(d, "in_off"); a.comb_off = getl(d, "comb_off");
+    a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K"); a.H = geti(d, "H"); a.max_tokens = geti(d, "max_tokens");
+    a.y = ptr<__nv_bfloat16>(d, "y");
+  }
+  check(launch_mega_finish(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_finish launch");
+}
+}  // namespace
+
+void bind_mega(py::module_& m) {
+  m.attr("gemm_tile") = kGemmBM;
+  m.attr("sf_chunk") = kSfChunk;
+  m.def("mega_input_offsets", [](int max_tokens, int hidden, int topk) {
+    long long o[6];
+    mega_input_offsets(max_tokens, hidden, topk, o);
+    return std::vector<long long>(o, o + 6);
+  });
+  m.def("mega_gemm", &op_mega_gemm);
+  m.def("mega_route", &op_mega_route);
+  m.def("mega_finish", &op_mega_finish);
+}
