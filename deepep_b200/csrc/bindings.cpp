@@ -58,6 +58,20 @@ WsLayout make_layout(int world, int max_tokens, int hidden, int topk, long long 
   return l;
 }
 
+// Workspace that only carries the control block and the fused-MoE region (dispatch/combine regions are empty).
+WsLayout make_mega_layout(int world, int max_tokens, int hidden, int topk, long long mega_bytes) {
+  if (world < 1 || world > kMaxRanks) throw std::invalid_argument("world size must be in [1, 8]");
+  if (topk < 1 || topk > kMaxTopk) throw std::invalid_argument("num_topk must be in [1, 16]");
+  if (hidden < 128 || hidden % 128) throw std::invalid_argument("hidden must be a positive multiple of 128");
+  WsLayout l{};
+  l.world = world; l.max_tokens = max_tokens; l.hidden = hidden; l.topk = topk;
+  l.stage_row_bytes = hidden * 2;
+  l.gather_hdr = l.gather_idx = l.gather_w = l.stage = l.partial = l.wret = l.ll = kControlBytes;
+  l.mega = kControlBytes;
+  l.total = align_up(kControlBytes + mega_bytes, 2 << 20);
+  return l;
+}
+
 RankCtx ctx_of(const py::handle& session) { return session.cast<Session&>().ctx(); }
 
 void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
@@ -165,6 +179,7 @@ PYBIND11_MODULE(_C, m) {
       .def_readonly("max_tokens", &WsLayout::max_tokens).def_readonly("hidden", &WsLayout::hidden)
       .def_readonly("topk", &WsLayout::topk).def_readonly("world", &WsLayout::world)
       .def_readonly("stage_row_bytes", &WsLayout::stage_row_bytes);
+  m.def("make_mega_layout", &make_mega_layout);
   m.def("make_layout", &make_layout, py::arg("world"), py::arg("max_tokens"), py::arg("hidden"), py::arg("topk"),
         py::arg("ll_bytes") = 0, py::arg("mega_bytes") = 0);
 

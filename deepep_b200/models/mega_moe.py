@@ -1,0 +1,244 @@
+"""MegaMoE: the fused expert-parallel MoE forward (fp8 activations x fp4 weights).
+
+Public API (parity: ``experiments/megamoe/python/deep_ep_experimental/megamoe/api.py`` of the reference:
+``SymmBuffer`` :63-282, ``transform_weights_for_mega_moe`` :311-379, ``fp8_fp4_mega_moe`` :382-517,
+``mega_moe`` :520-567):
+
+    buf = SymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden)
+    l1, l2 = transform_weights_for_mega_moe((w1, w1_sf), (w2, w2_sf))
+    buf.x[:bs] = ...; buf.x_sf[:bs] = ...; buf.topk_idx[:bs] = ...; buf.topk_weights[:bs] = ...
+    fp8_fp4_mega_moe(y, l1, l2, buf)          # y[:bs] is overwritten
+
+Data path on each rank: (1) ``mega_route``: handshake, read every rank's routing table from peer memory,
+lay local experts out as 128-row tiles, pull the routed e4m3 rows + ue8m0 scales over NVLink; (2) grouped
+GEMM1 on tcgen05 with a SwiGLU + MXFP8 requantising epilogue; (3) grouped GEMM2 whose epilogue writes bf16
+rows straight into the source rank's combine slots over NVLink; (4) ``mega_finish``: handshake, then
+``y[t] = sum_k w[t, k] * row[t, k]`` in fp32.  The route weight is applied after the second GEMM.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops import require_native
+
+
+class _DevicePointer:
+    """Minimal ``__cuda_array_interface__`` holder so torch can view workspace memory."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def _view(ptr: int, nbytes: int, device) -> torch.Tensor:
+    return torch.as_tensor(_DevicePointer(ptr, nbytes), device=device)
+
+
+@dataclass
+class MegaWeights:
+    """One projection of all local experts in kernel layout."""
+    packed: torch.Tensor        # [L * N, K / 2] uint8 (two e2m1 per byte, low nibble first)
+    sf_chunks: torch.Tensor     # 512-byte scale chunks
+    experts: int
+    n: int
+    k: int
+
+
+def _sf_chunks(sf: torch.Tensor) -> torch.Tensor:
+    from ..oracle.megamoe import to_sf_chunks
+
+    return to_sf_chunks(sf)
+
+
+def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor], l2_weights: Tuple[torch.Tensor, torch.Tensor],
+                                   device=None) -> Tuple[MegaWeights, MegaWeights]:
+    """Rearrange ``(w1 [L, 2I, H/2], w1_sf [L, 2I, H/32])`` and ``(w2 [L, H, I/2], w2_sf [L, H, I/32])`` for the kernel.
+
+    W1 rows are regrouped so every 128-row tile holds 64 gate rows followed by the 64 matching up rows
+    (gate = first I rows, up = last I rows); scales go into the tensor-memory chunk layout.
+    """
+    (w1, w1_sf), (w2, w2_sf) = l1_weights, l2_weights
+    L, n1, hk = w1.shape
+    inter, hidden = n1 // 2, hk * 2
+    assert w2.shape == (L, hidden, inter // 2), "w2 must be [L, H, I / 2]"
+    assert hidden % 128 == 0 and inter % 128 == 0, "hidden and intermediate sizes must be multiples of 128"
+    device = device or w1.device
+    order = torch.arange(n1).view(2, inter // 64, 64).permute(1, 0, 2).reshape(-1)     # tile j: gate[64j:64j+64], up[64j:64j+64]
+    w1t = w1.view(torch.uint8)[:, order].reshape(L * n1, hk).contiguous()
+    w1_sft = w1_sf.view(torch.uint8).reshape(L, n1, hidden // 32)[:, order].reshape(L * n1, hidden // 32)
+    w2t = w2.view(torch.uint8).reshape(L * hidden, inter // 2).contiguous()
+    w2_sft = w2_sf.view(torch.uint8).reshape(L * hidden, inter // 32)
+    return (MegaWeights(w1t.to(device), _sf_chunks(w1_sft).to(device), L, n1, hidden),
+            MegaWeights(w2t.to(device), _sf_chunks(w2_sft).to(device), L, hidden, inter))
+
+
+class MegaEngine:
+    """Runs the four kernels for one rank, or for several virtual ranks that share a GPU."""
+
+    def __init__(self, sessions: Sequence, layout, device, num_experts: int, intermediate: int, num_sms: int = 0):
+        self.C = require_native("MegaMoE")
+        self.sessions, self.layout, self.device = list(sessions), layout, device
+        self.n, self.world = len(self.sessions), layout.world
+        self.M, self.H, self.K = layout.max_tokens, layout.hidden, layout.topk
+        self.E, self.I = num_experts, intermediate
+        self.L = num_experts // self.world
+        assert self.H % 128 == 0 and self.I % 128 == 0 and num_experts % self.world == 0
+        off = self.C.mega_input_offsets(self.M, self.H, self.K)
+        self.in_off = layout.mega
+        self.off_hdr, self.off_x, self.off_sf, self.off_idx, self.off_w, in_total = off
+        self.comb_off = layout.mega + in_total
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        self.gemm_blocks = num_sms or self.sm_count
+        rows = self.world * self.M * min(self.K, self.L) + self.L * 127
+        self.max_mtiles = -(-rows // 128)
+        self.rows_cap = self.max_mtiles * 128
+        u8, i32 = dict(dtype=torch.uint8, device=device), dict(dtype=torch.int32, device=device)
+        self.scratch = []
+        for _ in range(self.n):
+            self.scratch.append(dict(
+                a1=torch.empty((self.rows_cap, self.H), **u8), a1_sf=torch.zeros((self.max_mtiles * (self.H // 128) * 512,), **u8),
+                a2=torch.empty((self.rows_cap, self.I), **u8), a2_sf=torch.zeros((self.max_mtiles * (self.I // 128) * 512,), **u8),
+                row_src=torch.empty((self.rows_cap,), **i32), mtile_expert=torch.zeros((self.max_mtiles,), **i32),
+                num_mtiles=torch.zeros((1,), **i32), expert_rows=torch.zeros((self.L,), **i32),
+                ticket=torch.zeros((self.L,), **i32), err=torch.zeros((1,), **i32)))
+
+    @staticmethod
+    def mega_bytes(C, max_tokens: int, hidden: int, topk: int) -> int:
+        return C.mega_input_offsets(max_tokens, hidden, topk)[5] + max_tokens * topk * hidden * 2 + 1024
+
+    def input_views(self, i: int):
+        """(x e4m3 [M, H], x_sf uint8 [M, H/32], topk_idx int32 [M, K], topk_weights fp32 [M, K]) of rank slot i."""
+        base = self.sessions[i].workspace + self.in_off
+        M, H, K = self.M, self.H, self.K
+        x = _view(base + self.off_x, M * H, self.device).view(torch.float8_e4m3fn).view(M, H)
+        sf = _view(base + self.off_sf, M * (H // 32), self.device).view(M, H // 32)
+        idx = _view(base + self.off_idx, M * K * 4, self.device).view(torch.int32).view(M, K)
+        w = _view(base + self.off_w, M * K * 4, self.device).view(torch.float32).view(M, K)
+        return x, sf, idx, w
+
+    def forward(self, ys: Sequence[torch.Tensor], tokens: Sequence[int], l1: Sequence[MegaWeights], l2: Sequence[MegaWeights],
+                stream=None) -> None:
+        C, lay = self.C, self.layout
+        s = (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
+        route_args, finish_args = [], []
+        for i in range(self.n):
+            sc = self.scratch[i]
+            route_args.append(dict(in_off=self.in_off, T=tokens[i], E=self.E, K=self.K, H=self.H, max_tokens=self.M,
+                                   max_mtiles=self.max_mtiles, a1=sc["a1"].data_ptr(), a1_sf=sc["a1_sf"].data_ptr(),
+                                   row_src=sc["row_src"].data_ptr(), mtile_expert=sc["mtile_expert"].data_ptr(),
+                                   num_mtiles=sc["num_mtiles"].data_ptr(), expert_rows=sc["expert_rows"].data_ptr(),
+                                   ticket=sc["ticket"].data_ptr()))
+            finish_args.append(dict(in_off=self.in_off, comb_off=self.comb_off, T=tokens[i], E=self.E, K=self.K, H=self.H,
+                                    max_tokens=self.M, y=ys[i].data_ptr()))
+        aux_blocks = max(1, min(self.sm_count // self.n, 128))
+        C.mega_route(lay, self.sessions, route_args, aux_blocks, s)
+        for i in range(self.n):
+            sc, w1, w2 = self.scratch[i], l1[i], l2[i]
+            common = dict(mtile_expert=sc["mtile_expert"].data_ptr(), num_mtiles=sc["num_mtiles"].data_ptr(), rows_pad=self.rows_cap,
+                          error_flag=sc["err"].data_ptr())
+            C.mega_gemm(dict(common, a=sc["a1"].data_ptr(), sfa=sc["a1_sf"].data_ptr(), b=w1.packed.data_ptr(),
+                             sfb=w1.sf_chunks.data_ptr(), k=self.H, b_rows=w1.experts * w1.n, n_total=w1.n, epi=1,
+                             a2=sc["a2"].data_ptr(), a2_sf=sc["a2_sf"].data_ptr(), inter=self.I),
+                        self.sessions[i], self.gemm_blocks, s)
+            C.mega_gemm(dict(common, a=sc["a2"].data_ptr(), sfa=sc["a2_sf"].data_ptr(), b=w2.packed.data_ptr(),
+                             sfb=w2.sf_chunks.data_ptr(), k=self.I, b_rows=w2.experts * w2.n, n_total=w2.n, epi=2,
+                             row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M, topk=self.K,
+                             hidden=self.H),
+                        self.sessions[i], self.gemm_blocks, s)
+        C.mega_finish(lay, self.sessions, finish_args, aux_blocks, s)
+
+    def check(self) -> None:
+        for sc in self.scratch:
+            if int(sc["err"].item()) != 0:
+                raise RuntimeError("a pipeline wait ran out inside a MegaMoE GEMM kernel")
+
+
+class SymmBuffer:
+    """Symmetric input/output block of the fused MoE forward; construction is collective."""
+
+    def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
+                 intermediate_hidden: int, *, rank: Optional[int] = None, world_size: Optional[int] = None, device=None,
+                 num_gpu_timeout_secs: float = 100, num_sms: int = 0):
+        from ..parallel.runtime import ControlPlane, Runtime
+
+        C = require_native("MegaMoE SymmBuffer")
+        self.control = ControlPlane(group, rank, world_size)
+        self.rank, self.world_size = self.control.rank, self.control.size
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.num_experts, self.num_topk, self.hidden, self.intermediate_hidden = num_experts, num_topk, hidden, intermediate_hidden
+        self.num_max_tokens_per_rank = num_max_tokens_per_rank
+        mega = MegaEngine.mega_bytes(C, num_max_tokens_per_rank, hidden, num_topk)
+        # the generic regions are sized for one token: this buffer only uses the fused-MoE region
+        self.layout = C.make_mega_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, mega)
+        self.runtime = Runtime(self.control, self.layout, float(num_gpu_timeout_secs), self.device)
+        self.engine = MegaEngine([self.runtime.native], self.layout, self.device, num_experts, intermediate_hidden, num_sms)
+        self.x, self.x_sf, self.topk_idx, self.topk_weights = self.engine.input_views(0)
+        self.batch_size = 0
+        self._destroyed = False
+
+    def prepare(self, batch_size: int) -> "SymmBuffer":
+        if not 0 <= batch_size <= self.num_max_tokens_per_rank:
+            raise ValueError(f"batch size must be in [0, {self.num_max_tokens_per_rank}]")
+        self.batch_size = batch_size
+        return self
+
+    def validate_inputs(self, batch_size: int) -> None:
+        idx = self.topk_idx[:batch_size]
+        if bool(((idx >= self.num_experts)).any()):
+            raise ValueError("topk_idx holds expert ids outside [0, num_experts)")
+        if not bool(torch.isfinite(self.topk_weights[:batch_size]).all()):
+            raise ValueError("topk_weights must be finite")
+
+    def destroy(self) -> None:
+        if not self._destroyed:
+            self._destroyed = True
+            self.runtime.close()
+
+
+def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaWeights, sym_buffer: SymmBuffer, *,
+                     batch_size: Optional[int] = None, shared_weights=None, recipe=(1, 1, 32), activation: str = "swiglu",
+                     activation_clamp=None, fast_math: bool = True, timer=None) -> torch.Tensor:
+    """Fused MoE forward; overwrites ``y[:bs]`` (bf16 ``[bs, hidden]``) and returns it."""
+    del fast_math, timer
+    if shared_weights is not None:
+        raise NotImplementedError("shared-expert weights are not fused; run the shared expert as a separate dense layer")
+    if tuple(recipe) != (1, 1, 32):
+        raise NotImplementedError("the tensor-core path consumes one ue8m0 scale per 32 values: recipe must be (1, 1, 32)")
+    if activation != "swiglu" or activation_clamp is not None:
+        raise NotImplementedError("only unclamped SwiGLU is implemented")
+    if not isinstance(l1_weights, MegaWeights) or not isinstance(l2_weights, MegaWeights):
+        raise TypeError("pass the weights through transform_weights_for_mega_moe first")
+    bs = sym_buffer.batch_size if batch_size is None else batch_size
+    if y.dtype != torch.bfloat16 or y.dim() != 2 or y.shape[1] != sym_buffer.hidden or y.shape[0] < bs or not y.is_contiguous():
+        raise ValueError("y must be a contiguous bf16 [>= batch, hidden] tensor")
+    if l1_weights.k != sym_buffer.hidden or l1_weights.n != 2 * sym_buffer.intermediate_hidden:
+        raise ValueError("l1 weights do not match the buffer's hidden / intermediate sizes")
+    if l1_weights.experts * sym_buffer.world_size != sym_buffer.num_experts:
+        raise ValueError("each rank must hold num_experts / world_size experts")
+    sym_buffer.engine.forward([y], [bs], [l1_weights], [l2_weights])
+    return y
+
+
+def mega_moe(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, l1_weights: MegaWeights,
+             l2_weights: MegaWeights, sym_buffer: SymmBuffer) -> torch.Tensor:
+    """Convenience wrapper: quantise bf16 ``x`` to MXFP8, fill the symmetric inputs, run the fused forward."""
+    bs = x.shape[0]
+    codes, sf = quantize_mxfp8_cuda(x)
+    sym_buffer.x[:bs].copy_(codes)
+    sym_buffer.x_sf[:bs].copy_(sf)
+    sym_buffer.topk_idx[:bs].copy_(topk_idx.to(torch.int32))
+    sym_buffer.topk_weights[:bs].copy_(topk_weights.float())
+    y = torch.empty((bs, sym_buffer.hidden), dtype=torch.bfloat16, device=x.device)
+    return fp8_fp4_mega_moe(y, l1_weights, l2_weights, sym_buffer.prepare(bs))
+
+
+def quantize_mxfp8_cuda(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """MXFP8 quantiser in torch ops (any device): e4m3 codes and ue8m0 exponents per 32 values."""
+    from ..oracle.megamoe import quantize_mxfp8
+
+    return quantize_mxfp8(x)
+
+
+__all__ = ["MegaEngine", "MegaWeights", "SymmBuffer", "fp8_fp4_mega_moe", "mega_moe", "transform_weights_for_mega_moe"]
