@@ -91,6 +91,85 @@ def reference_arm(args):
         print(json.dumps(line), flush=True)
 
 
+def bench_low_latency(group, world, rank, dev, timed):
+    """Decode shape: 128 tokens per rank, hidden 7168, 384 experts, top-8, fused fp8 dispatch, bf16 combine, in CUDA graphs."""
+    from deepep_b200 import ElasticBuffer
+
+    T, H, E, K = 128, 7168, 384, 8
+    gen = torch.Generator().manual_seed(77 + rank)
+    x = torch.randn((T, H), generator=gen).bfloat16().to(dev)
+    idx = torch.stack([torch.randperm(E, generator=gen)[:K] for _ in range(T)]).to(torch.int64).to(dev)
+    w = torch.softmax(torch.randn((T, K), generator=gen), dim=1).float().to(dev)
+    buf = ElasticBuffer(group, num_max_tokens_per_rank=256, hidden=H, num_topk=K, use_fp8_dispatch=True, explicitly_destroy=True)
+    out = {}
+    (rx, rsf), _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_cpu_sync=False)
+    assert handle.is_low_latency
+    eo = torch.randn((rx.shape[0], H), device=dev).bfloat16()
+    buf.combine(eo, handle)
+    torch.cuda.synchronize()
+    g_d, g_c = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_d):
+        (rx, rsf), _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_cpu_sync=False)
+    with torch.cuda.graph(g_c):
+        buf.combine(eo, handle)
+    out["ll_dispatch_fp8_graph_us"] = timed(g_d.replay, 20)
+    out["ll_combine_bf16_graph_us"] = timed(g_c.replay, 20)
+    buf.destroy()
+    return out
+
+
+def bench_mega_moe(group, world, rank, dev, timed):
+    """Fused MoE forward: hidden 7168, intermediate 2048, 256 experts, top-8, e4m3 activations x e2m1 weights."""
+    from deepep_b200.models.mega_moe import MegaWeights, SymmBuffer, fp8_fp4_mega_moe
+
+    H, I, E, K = 7168, 2048, 256, 8
+    L = E // world
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    w1 = MegaWeights(torch.randint(0, 256, (L * 2 * I, H // 2), dtype=torch.uint8, device=dev, generator=g),
+                     torch.full((L * 2 * I // 128 * (H // 128) * 512,), 118, dtype=torch.uint8, device=dev), L, 2 * I, H)
+    w2 = MegaWeights(torch.randint(0, 256, (L * H, I // 2), dtype=torch.uint8, device=dev, generator=g),
+                     torch.full((L * H // 128 * (I // 128) * 512,), 120, dtype=torch.uint8, device=dev), L, H, I)
+    out = {}
+    for name, T in (("prefill", 4096), ("decode", 64)):
+        buf = SymmBuffer(group, E, T, K, H, I)
+        buf.x.view(torch.uint8).copy_(torch.randint(0, 120, (T, H), dtype=torch.uint8, device=dev, generator=g))
+        buf.x_sf.fill_(127)
+        buf.topk_idx.copy_(torch.topk(torch.rand((T, E), device=dev, generator=g), K, dim=1).indices.to(torch.int32))
+        buf.topk_weights.copy_(torch.softmax(torch.randn((T, K), device=dev, generator=g), dim=1))
+        y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        buf.prepare(T)
+        us = timed(lambda: fp8_fp4_mega_moe(y, w1, w2, buf), 5)
+        buf.engine.check()
+        out[f"mega_moe_{name}_us"] = us
+        out[f"mega_moe_{name}_tokens_per_s"] = world * T / (us * 1e-6)
+        buf.destroy()
+    return out
+
+
+def bench_baseline(group, world, rank, dev, timed, x, idx, w, E):
+    """NCCL all-to-all(v) dispatch+combine and NCCL + cuBLAS bf16 MoE layer on the same shapes (comparison only)."""
+    from baseline.nccl_moe import NcclExpertParallel, moe_forward
+
+    out = {}
+    ep = NcclExpertParallel(group, E)
+    plan = ep.plan(idx, w)
+
+    def a2a():
+        rows = ep.dispatch(x, plan)
+        return ep.combine(rows, plan, weighted=False)
+
+    out["baseline_nccl_dispatch_combine_us"] = timed(a2a, 5)
+    H, I = x.shape[1], 2048
+    L = E // world
+    w1 = torch.randn((L, 2 * I, H), device=dev, dtype=torch.bfloat16) * 0.02
+    w2 = torch.randn((L, H, I), device=dev, dtype=torch.bfloat16) * 0.02
+    for name, T in (("prefill", x.shape[0]), ("decode", 64)):
+        us = timed(lambda: moe_forward(ep, x[:T], idx[:T], w[:T], w1, w2), 3)
+        out[f"baseline_nccl_cublas_moe_{name}_us"] = us
+        out[f"baseline_nccl_cublas_moe_{name}_tokens_per_s"] = world * T / (us * 1e-6)
+    return out
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -195,6 +274,20 @@ def main():
             extras["nvlink_out_GBps_per_gpu_dispatch_fp8"] = remote * (H + H // 128 * 4) / (extras["dispatch_fp8_us"] * 1e-6) / 1e9
             extras["nvlink_out_GBps_per_gpu_combine_bf16"] = remote * H * 2 / (extras["combine_bf16_us"] * 1e-6) / 1e9
             extras["remote_destinations_per_token"] = remote_frac
+
+    if not args.skip_extras:
+        try:
+            extras.update(bench_low_latency(group, world, rank, dev, timed))
+        except Exception as exc:  # the headline number must survive a failing extra
+            extras["low_latency_error"] = repr(exc)[:200]
+        try:
+            extras.update(bench_mega_moe(group, world, rank, dev, timed))
+        except Exception as exc:
+            extras["mega_moe_error"] = repr(exc)[:200]
+        try:
+            extras.update(bench_baseline(group, world, rank, dev, timed, x, idx, w, E))
+        except Exception as exc:
+            extras["baseline_error"] = repr(exc)[:200]
 
     # end to end through the public API: pinned host inputs in, a scalar of the result out, every step
     xd, idxd, wd = torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)

@@ -1,0 +1,87 @@
+"""Fused MoE forward timing on one GPU (N virtual ranks share the device) with a per-kernel breakdown.
+
+    python benchmarks/bench_mega.py --world 1 --tokens 4096 --experts 32      # one rank's share of an EP8 layer
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--world", type=int, default=1)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--inter", type=int, default=2048)
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args()
+    from deepep_b200.models.mega_moe import MegaEngine, MegaWeights
+    from deepep_b200.ops import load_native
+
+    C = load_native()
+    dev = torch.device("cuda")
+    P, T, H, I, E, K = args.world, args.tokens, args.hidden, args.inter, args.experts, args.topk
+    L = E // P
+    layout = C.make_mega_layout(P, T, H, K, MegaEngine.mega_bytes(C, T, H, K))
+    sessions = [C.Session(r, P, layout.total, 30.0) for r in range(P)]
+    for s in sessions:
+        s.attach_peers([q.workspace for q in sessions])
+    eng = MegaEngine(sessions, layout, dev, E, I)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w1 = [MegaWeights(torch.randint(0, 256, (L * 2 * I, H // 2), dtype=torch.uint8, device=dev, generator=g),
+                      torch.full((L * 2 * I // 128 * (H // 128) * 512,), 118, dtype=torch.uint8, device=dev), L, 2 * I, H) for _ in range(P)]
+    w2 = [MegaWeights(torch.randint(0, 256, (L * H, I // 2), dtype=torch.uint8, device=dev, generator=g),
+                      torch.full((L * H // 128 * (I // 128) * 512,), 120, dtype=torch.uint8, device=dev), L, H, I) for _ in range(P)]
+    for r in range(P):
+        x, sf, ti, tw = eng.input_views(r)
+        x.view(torch.uint8).copy_(torch.randint(0, 120, (T, H), dtype=torch.uint8, device=dev, generator=g))
+        sf.fill_(127)
+        scores = torch.rand((T, E), device=dev, generator=g)
+        ti.copy_(torch.topk(scores, K, dim=1).indices.to(torch.int32))
+        tw.copy_(torch.softmax(torch.randn((T, K), device=dev, generator=g), dim=1))
+    ys = [torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(P)]
+
+    def run():
+        eng.forward(ys, [T] * P, w1, w2)
+
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    eng.check()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.iters):
+        run()
+    e.record()
+    torch.cuda.synchronize()
+    total_us = s.elapsed_time(e) / args.iters * 1e3
+    # per-kernel breakdown from the profiler (device time)
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+        torch.cuda.synchronize()
+    kern = {}
+    for evt in prof.events():
+        if evt.device_time > 0:
+            kern.setdefault(evt.name.split("(")[0][-40:], []).append(evt.device_time)
+    rows = P * T * K
+    flops = 2.0 * rows * (2 * I) * H + 2.0 * rows * H * I
+    print(json.dumps({"world": P, "tokens": T, "hidden": H, "inter": I, "experts": E, "topk": K, "total_us": total_us,
+                      "tokens_per_s": P * T / (total_us * 1e-6), "tflops": flops / (total_us * 1e-6) / 1e12,
+                      "kernels_us": {k: v for k, v in kern.items()}}))
+    torch.cuda.synchronize()
+    for s_ in sessions:
+        s_.close()
+
+
+if __name__ == "__main__":
+    main()

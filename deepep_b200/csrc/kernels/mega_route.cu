@@ -101,22 +101,13 @@ __global__ void __launch_bounds__(kRouteThreads) mega_route_kernel(const __grid_
   }
   __syncthreads();
   const int rows_cap = a.max_mtiles * kGemmBM;
-  // padding rows: no source, zero payload and scales
+  // padding rows carry no source; their payload is never read back (tile rows are independent in the GEMMs)
   for (int l = blockIdx.x; l < Lx; l += gridDim.x) {
     const int c = a.expert_rows[l], end = (c + kGemmBM - 1) / kGemmBM * kGemmBM;
-    for (int rr = c + warp; rr < end; rr += kRouteThreads / 32) {
-      const long long row = s_base[l] + rr;
-      if (row >= rows_cap) continue;
-      if (lane == 0) a.row_src[row] = -1;
-      for (int u = lane; u < H / 16; u += 32) reinterpret_cast<int4*>(a.a1 + row * H)[u] = make_int4(0, 0, 0, 0);
-      for (int g = lane; g < H / 128; g += 32) *reinterpret_cast<uint32_t*>(a.a1_sf + sf_offset(row, (long long)g * 128, H)) = 0u;
-    }
+    for (int rr = c + threadIdx.x; rr < end; rr += kRouteThreads)
+      if (s_base[l] + rr < rows_cap) a.row_src[s_base[l] + rr] = -1;
   }
-  grid.sync();
-  int* ticket = a.ticket;
-  if (blockIdx.x == 0) for (int l = threadIdx.x; l < Lx; l += kRouteThreads) ticket[l] = 0;
-  __threadfence();
-  grid.sync();
+  int* ticket = a.ticket;   // zeroed by the previous call's pass 2 epilogue (and at allocation)
 
   // ---- pass 2: hand out rows and pull the tokens (one warp per routed slot)
   if (alive) {
@@ -148,6 +139,8 @@ __global__ void __launch_bounds__(kRouteThreads) mega_route_kernel(const __grid_
       }
     }
   }
+  grid.sync();
+  if (blockIdx.x == 0) for (int l = threadIdx.x; l < Lx; l += kRouteThreads) ticket[l] = 0;   // ready for the next call
 }
 
 cudaError_t launch_mega_route(const MegaRouteParams& p, int nranks, int blocks, cudaStream_t stream) {
@@ -187,23 +180,44 @@ __global__ void __launch_bounds__(kRouteThreads) mega_finish_kernel(const __grid
         if (e >= 0 && e < a.E) valid |= 1u << k;
       }
       int4* out = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.y) + (size_t)t * H * 2);
-      for (int u = lane; u < H / 8; u += 32) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (unsigned m = valid; m; m &= m - 1) {
-          const int k = __ffs(m) - 1;
-          const int4 v = ld_cg_int4(comb + ((size_t)(t * K + k) * H) * 2 + (size_t)u * 16);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const uint8_t* rows = comb + (size_t)t * K * H * 2;
+      for (int u0 = lane; u0 < H / 8; u0 += 64) {      // two 16-byte columns per step, all slots' loads issued first
+        const bool two = u0 + 32 < H / 8;
+        int4 v0[kMaxTopk], v1[kMaxTopk];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(wk[k], __low2float(h[i])));
-            acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(wk[k], __high2float(h[i])));
+        for (int k = 0; k < kMaxTopk; ++k) {
+          if (k < K && ((valid >> k) & 1u)) {
+            v0[k] = ld_cg_int4(rows + (size_t)k * H * 2 + (size_t)u0 * 16);
+            if (two) v1[k] = ld_cg_int4(rows + (size_t)k * H * 2 + (size_t)(u0 + 32) * 16);
+          }
+        }
+        float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < kMaxTopk; ++k) {
+          if (k < K && ((valid >> k) & 1u)) {
+            const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[k]);
+            const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[k]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {   // product and sum rounded separately, as the CPU oracle does
+              a0[2 * i] = __fadd_rn(a0[2 * i], __fmul_rn(wk[k], __low2float(h0[i])));
+              a0[2 * i + 1] = __fadd_rn(a0[2 * i + 1], __fmul_rn(wk[k], __high2float(h0[i])));
+              if (two) {
+                a1[2 * i] = __fadd_rn(a1[2 * i], __fmul_rn(wk[k], __low2float(h1[i])));
+                a1[2 * i + 1] = __fadd_rn(a1[2 * i + 1], __fmul_rn(wk[k], __high2float(h1[i])));
+              }
+            }
           }
         }
         int4 o;
         __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        out[u] = o;
+        for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(a0[2 * i], a0[2 * i + 1]);
+        out[u0] = o;
+        if (two) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(a1[2 * i], a1[2 * i + 1]);
+          out[u0 + 32] = o;
+        }
       }
     }
   }
