@@ -1,0 +1,148 @@
+"""``Buffer``: upstream DeepEP's V1 interface (``get_dispatch_layout`` / ``dispatch`` / ``combine``).
+
+Parity: ``deep_ep/backends/direct/buffer.py`` of the reference (``get_dispatch_layout`` :420-463,
+``dispatch`` :465-680, ``combine`` :682-751, config getters, ``capture``, ``get_comm_stream``) and
+``deep_ep/buffer.py:8-16``.  The V1 layout is the rank layout of :class:`ElasticBuffer`
+(``do_expand=False``): one received row per (source rank, token), ``recv_topk_idx`` holding local
+expert ids.  Internode and the V1 low-latency entry points belong to multi-node RDMA deployments and
+raise ``NotImplementedError``; decode-size batches use ``ElasticBuffer``'s low-latency path.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .config import Config
+from .parallel.elastic import ElasticBuffer
+from .utils.event import EventHandle, EventOverlap
+
+topk_idx_t = torch.int64
+
+
+class Buffer:
+    num_sms: int = 20
+
+    def __init__(self, group, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0, low_latency_mode: bool = False,
+                 num_qps_per_rank: int = 24, allow_nvlink_for_low_latency_mode: bool = True, allow_mnnvl: bool = False,
+                 explicitly_destroy: bool = False, enable_shrink: bool = False, comm=None, *, machine_type="auto",
+                 rootinfo_path=None, hidden: int = 0, num_topk: int = 0, num_max_tokens_per_rank: int = 0):
+        del num_qps_per_rank, allow_nvlink_for_low_latency_mode, allow_mnnvl, comm, machine_type, rootinfo_path
+        if num_rdma_bytes:
+            raise NotImplementedError("internode (RDMA) buffers are outside this single-NVLink-domain library")
+        if low_latency_mode:
+            raise NotImplementedError("use ElasticBuffer with num_max_tokens_per_rank <= 256 for low-latency decode")
+        if enable_shrink:
+            raise NotImplementedError("rank shrinking is not supported")
+        self.group, self.num_nvl_bytes, self.explicitly_destroy = group, num_nvl_bytes, explicitly_destroy
+        self._shape = (num_max_tokens_per_rank, hidden, num_topk)
+        self._elastic: Optional[ElasticBuffer] = None
+        if all(self._shape):
+            self._ensure(*self._shape)
+
+    def _ensure(self, tokens: int, hidden: int, topk: int) -> ElasticBuffer:
+        """V1 sizes its buffer in bytes only; the workspace is created on first use from the tensors' shape."""
+        if self._elastic is None:
+            self._elastic = ElasticBuffer(self.group, num_max_tokens_per_rank=tokens, hidden=hidden, num_topk=topk,
+                                          explicitly_destroy=self.explicitly_destroy)
+        eb = self._elastic
+        if tokens > eb.num_max_tokens_per_rank or hidden != eb.hidden or topk != eb.num_topk:
+            raise ValueError("this Buffer was created for another (tokens, hidden, top-k) shape")
+        return eb
+
+    # ------------------------------------------------------------------ resources
+    def destroy(self) -> None:
+        if self._elastic is not None:
+            self._elastic.destroy()
+
+    @staticmethod
+    def set_num_sms(new_num_sms: int) -> None:
+        if new_num_sms <= 0 or new_num_sms % 2:
+            raise ValueError("the SM count must be a positive even number")
+        Buffer.num_sms = new_num_sms
+
+    set_num_compute_units = set_num_sms
+
+    @staticmethod
+    def capture() -> EventOverlap:
+        return EventOverlap(EventHandle())
+
+    def get_comm_stream(self):
+        return None if self._elastic is None else self._elastic.get_comm_stream()
+
+    @staticmethod
+    def get_dispatch_config(num_ranks: int) -> Config:
+        return Config(Buffer.num_sms, 6, 256, 6, 128)
+
+    @staticmethod
+    def get_combine_config(num_ranks: int) -> Config:
+        return Config(Buffer.num_sms, 4, 256, 6, 128)
+
+    @staticmethod
+    def get_low_latency_rdma_size_hint(num_max_dispatch_tokens_per_rank, hidden, num_ranks, num_experts) -> int:
+        from .parallel import layout as L
+
+        del num_experts
+        return L.elastic_size_hint(num_ranks, num_max_dispatch_tokens_per_rank, hidden, 8)
+
+    get_low_latency_scaleout_size_hint = get_low_latency_rdma_size_hint
+
+    # ------------------------------------------------------------------ V1 operations
+    def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: int, previous_event=None, async_finish: bool = False,
+                            allocate_on_comm_stream: bool = False):
+        """(num_tokens_per_rank, num_tokens_per_rdma_rank=None, num_tokens_per_expert, is_token_in_rank, event)."""
+        del allocate_on_comm_stream
+        world = 1 if self.group is None else torch.distributed.get_world_size(self.group)
+        if previous_event is not None and previous_event.event is not None:
+            previous_event.current_stream_wait()
+        local = num_experts // world
+        valid = (topk_idx >= 0) & (topk_idx < num_experts)
+        dst = torch.where(valid, torch.div(topk_idx, local, rounding_mode="floor"), torch.full_like(topk_idx, -1))
+        in_rank = torch.stack([(dst == r).any(dim=1) for r in range(world)], dim=1)
+        per_expert = torch.bincount(topk_idx[valid], minlength=num_experts).to(torch.int32)
+        event = EventOverlap(EventHandle()) if async_finish else EventOverlap()
+        return in_rank.sum(0).to(torch.int32), None, per_expert, in_rank, event
+
+    def dispatch(self, x, handle=None, num_tokens_per_rank=None, num_tokens_per_rdma_rank=None, is_token_in_rank=None,
+                 num_tokens_per_expert=None, topk_idx=None, topk_weights=None, expert_alignment: int = 1, num_worst_tokens: int = 0,
+                 config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
+                 allocate_on_comm_stream: bool = False):
+        """(recv_x, recv_topk_idx, recv_topk_weights, num_recv_tokens_per_expert_list, handle, event)."""
+        del num_tokens_per_rank, num_tokens_per_rdma_rank, is_token_in_rank
+        if expert_alignment != 1:
+            raise NotImplementedError("expert_alignment applies to the expanded layout: use ElasticBuffer(do_expand=True)")
+        data = x[0] if isinstance(x, (tuple, list)) else x
+        sms = config.num_sms if config is not None else 0
+        if handle is not None:
+            eb = self._ensure(data.shape[0], data.shape[1], handle.topk_idx.shape[1])
+            rx, _, _, h, ev = eb.dispatch(x, handle=handle, num_sms=sms, previous_event=previous_event,
+                                          async_with_compute_stream=async_finish, allocate_on_comm_stream=allocate_on_comm_stream)
+            return rx, None, None, None, h, ev
+        if topk_idx is None or num_tokens_per_expert is None:
+            raise ValueError("a fresh V1 dispatch needs topk_idx and num_tokens_per_expert (from get_dispatch_layout)")
+        eb = self._ensure(data.shape[0], data.shape[1], topk_idx.shape[1])
+        rx, ridx, rw, h, ev = eb.dispatch(x, topk_idx=topk_idx, topk_weights=topk_weights, num_experts=num_tokens_per_expert.numel(),
+                                          num_sms=sms, previous_event=previous_event, async_with_compute_stream=async_finish,
+                                          allocate_on_comm_stream=allocate_on_comm_stream, do_expand=False,
+                                          do_cpu_sync=(num_worst_tokens == 0), num_max_tokens_per_rank=10 ** 9)
+        return rx, ridx, rw, h.num_recv_tokens_per_expert_list, h, ev
+
+    def combine(self, x, handle, topk_weights=None, bias=None, config: Optional[Config] = None, previous_event=None,
+                async_finish: bool = False, allocate_on_comm_stream: bool = False):
+        """(combined_x, combined_topk_weights, event)."""
+        if self._elastic is None:
+            raise RuntimeError("combine needs the buffer that produced the handle")
+        return self._elastic.combine(x, handle, topk_weights=topk_weights, bias=bias, num_sms=config.num_sms if config else 0,
+                                     previous_event=previous_event, async_with_compute_stream=async_finish,
+                                     allocate_on_comm_stream=allocate_on_comm_stream)
+
+    # ------------------------------------------------------------------ not part of this library
+    def internode_dispatch(self, *a, **k): raise NotImplementedError("internode dispatch needs an RDMA fabric")
+    def internode_combine(self, *a, **k): raise NotImplementedError("internode combine needs an RDMA fabric")
+    def clean_low_latency_buffer(self, *a, **k): raise NotImplementedError("V1 low-latency mode: use ElasticBuffer")
+    def low_latency_dispatch(self, *a, **k): raise NotImplementedError("V1 low-latency mode: use ElasticBuffer")
+    def low_latency_combine(self, *a, **k): raise NotImplementedError("V1 low-latency mode: use ElasticBuffer")
+    def get_next_low_latency_combine_buffer(self, *a, **k): raise NotImplementedError("V1 low-latency mode: use ElasticBuffer")
+
+
+__all__ = ["Buffer", "topk_idx_t"]
