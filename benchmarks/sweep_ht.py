@@ -25,6 +25,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=7168)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--ll", action="store_true")
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--remote-only", action="store_true", help="route every token only to experts of the next rank (link stress)")
     args = ap.parse_args()
     from deepep_b200 import ElasticBuffer
     from helpers import group_limited_routes
@@ -37,9 +39,14 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
-    T, H, E, K = args.tokens, args.hidden, 256, 8
+    T, H, E, K = args.tokens, args.hidden, 256, args.topk
     x = torch.randn((T, H), device=dev).bfloat16()
-    idx = group_limited_routes(T, E, K, 8, 4, seed=rank).to(dev)
+    if args.remote_only:
+        local_e = E // world
+        base = ((rank + 1) % world) * local_e
+        idx = (base + torch.stack([torch.randperm(local_e, device=dev)[:K] for _ in range(T)])).to(torch.int64)
+    else:
+        idx = group_limited_routes(T, E, K, 8, 4, seed=rank).to(dev)
     w = torch.softmax(torch.randn((T, K), device=dev), dim=1)
     buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True)
     eng = buf.engine

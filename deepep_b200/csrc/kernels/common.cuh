@@ -215,6 +215,30 @@ template <int N> __device__ __forceinline__ void bulk_wait() {
 }
 
 __device__ __forceinline__ int4 ld_cg_int4(const void* p) { return __ldcg(reinterpret_cast<const int4*>(p)); }
+
+// Warp-wide copy of `units` 16-byte pieces from `src` to `ndst` destinations.  All loads of a batch of U pieces per
+// lane are issued before the first store, so a row costs a few memory latencies instead of one per piece.
+template <int U>
+__device__ __forceinline__ void warp_copy_row(int4* const* dst, int ndst, const int4* src, int units, int lane) {
+  for (int u0 = 0; u0 < units; u0 += 32 * U) {
+    int4 v[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const int u = u0 + i * 32 + lane;
+      if (u < units) v[i] = __ldcg(src + u);
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const int u = u0 + i * 32 + lane;
+      if (u < units)
+        for (int d = 0; d < ndst; ++d) dst[d][u] = v[i];
+    }
+  }
+}
+__device__ __forceinline__ void warp_copy_row1(int4* dst, const int4* src, int units, int lane) {
+  int4* one[1] = {dst};
+  warp_copy_row<8>(one, 1, src, units, lane);
+}
 #endif  // __CUDACC__
 
 }  // namespace dep

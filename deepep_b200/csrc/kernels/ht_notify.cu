@@ -40,20 +40,26 @@ __device__ __forceinline__ bool slot_counts(const int* row, int k, int E) {
   return true;
 }
 
+// One thread per token of the tile: the K ids of a row are fetched once (independent loads), duplicates
+// are resolved in registers, then the masks are updated with shared-memory atomics.
 __device__ void build_masks(TileMasks& m, const int* gidx_src, int tile, int T_r, int K, int E, int Lx) {
   for (int i = threadIdx.x; i < kMaxExperts * 2; i += blockDim.x) (&m.expert[0][0])[i] = 0u;
   if (threadIdx.x < kMaxRanks * 2) (&m.rank[0][0])[threadIdx.x] = 0u;
   __syncthreads();
-  for (int i = threadIdx.x; i < kChunkTokens * K; i += blockDim.x) {
-    int tl = i / K, k = i - tl * K, t = tile * kChunkTokens + tl;
-    if (t >= T_r) continue;
+  const int tl = threadIdx.x, t = tile * kChunkTokens + tl;
+  if (tl < kChunkTokens && t < T_r) {
     int row[kMaxTopk];
     const int* src = gidx_src + (size_t)t * K;
-    for (int j = 0; j <= k; ++j) row[j] = __ldcg(src + j);
-    if (!slot_counts(row, k, E)) continue;
-    int e = row[k];
-    atomicOr(&m.expert[e][tl >> 5], 1u << (tl & 31));
-    atomicOr(&m.rank[e / Lx][tl >> 5], 1u << (tl & 31));
+#pragma unroll
+    for (int k = 0; k < kMaxTopk; ++k) row[k] = k < K ? __ldcg(src + k) : -1;
+#pragma unroll
+    for (int k = 0; k < kMaxTopk; ++k) {
+      if (k < K && slot_counts(row, k, E)) {
+        const int e = row[k];
+        atomicOr(&m.expert[e][tl >> 5], 1u << (tl & 31));
+        atomicOr(&m.rank[e / Lx][tl >> 5], 1u << (tl & 31));
+      }
+    }
   }
   __syncthreads();
 }
@@ -190,7 +196,8 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
     int tl = threadIdx.x, t = tile * kChunkTokens + tl;
     if (tl < kChunkTokens && t < T_r) {
       int row[kMaxTopk];
-      for (int k = 0; k < K; ++k) row[k] = __ldcg(gidx_r + (size_t)t * K + k);
+#pragma unroll
+      for (int k = 0; k < kMaxTopk; ++k) row[k] = k < K ? __ldcg(gidx_r + (size_t)t * K + k) : -1;
       const int* hist_rt = a.hist + (size_t)task * E;
       const bool hit_me = (s_m.rank[me][tl >> 5] >> (tl & 31)) & 1u;
       if (hit_me) {

@@ -68,6 +68,10 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
   __shared__ int s_T[kMaxRanks];
   __shared__ int s_rows;
 
+  // phase stamps (nanoseconds since kernel start) of block 0, for diagnostics: Control::dbg[0..7]
+  const unsigned long long t_start = global_timer_ns();
+  auto stamp = [&](int i) { if (blockIdx.x == 0 && threadIdx.x == 0) ctl->dbg[i] = global_timer_ns() - t_start; };
+
   // ---- bank reuse: the call before last must have been consumed everywhere
   int ok = 1;
   if (threadIdx.x < P && epoch > 2)
@@ -77,14 +81,20 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
   // ---- my own routing: which destinations does each token reach
   for (int i = threadIdx.x; i < kMaxRanks * kLLWords; i += kLLThreads) (&s_own[0][0])[i] = 0u;
   __syncthreads();
-  for (int i = threadIdx.x; i < a.T * K; i += kLLThreads) {
-    const int t = i / K, k = i - t * K;
+  for (int t = threadIdx.x; t < a.T; t += kLLThreads) {   // one thread per token: K independent loads, dedup in registers
     int row[kMaxTopk];
-    for (int j = 0; j <= k; ++j) { long long v = a.topk_idx[(size_t)t * K + j]; row[j] = (v < 0 || v >= E) ? -1 : (int)v; }
-    if (counts_ll(row, k, E)) atomicOr(&s_own[row[k] / Lx][t >> 5], 1u << (t & 31));
+#pragma unroll
+    for (int k = 0; k < kMaxTopk; ++k) {
+      long long v = k < K ? a.topk_idx[(size_t)t * K + k] : -1;
+      row[k] = (v < 0 || v >= E) ? -1 : (int)v;
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxTopk; ++k)
+      if (k < K && counts_ll(row, k, E)) atomicOr(&s_own[row[k] / Lx][t >> 5], 1u << (t & 31));
   }
   __syncthreads();
 
+  stamp(0);
   if (alive) {
     // ---- routing table to every peer (block 0), rows to their destinations (all warps)
     if (blockIdx.x == 0) {
@@ -109,26 +119,45 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
       uint8_t* base = ctx.ws[d] + bank_off;
       uint8_t* dst = base + ll.stage + ((size_t)me * M + j) * ll.msg_bytes;
       if (a.mode == 2) {  // bf16 -> e4m3 with one fp32 scale per 128 values, straight into the peer
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + (size_t)t * H * 2;
-        for (int b = 0; b < nsf; ++b) {
-          uint2 raw = *reinterpret_cast<const uint2*>(src + (size_t)(b * 128 + lane * 4) * 2);
-          __nv_bfloat162 p0 = *reinterpret_cast<__nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
-          float v0 = __low2float(p0), v1 = __high2float(p0), v2 = __low2float(p1), v3 = __high2float(p1);
-          float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+        // a lane owns 8 consecutive values (16 B); 16 lanes cover one 128-value block, a warp step covers two blocks
+        const int4* src = reinterpret_cast<const int4*>(reinterpret_cast<const uint8_t*>(a.x) + (size_t)t * H * 2);
+        const int units = H / 8, half = lane >> 4;
+        constexpr int U = 8;
+        for (int u0 = 0; u0 < units; u0 += 32 * U) {
+          int4 v[U];
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-          amax = fmaxf(amax, 1e-4f);
-          const float inv = __frcp_rn(amax) * 448.0f;
-          uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(v0 * inv, __NV_SATFINITE, __NV_E4M3) |
-                       ((uint32_t)__nv_cvt_float_to_fp8(v1 * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
-                       ((uint32_t)__nv_cvt_float_to_fp8(v2 * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
-                       ((uint32_t)__nv_cvt_float_to_fp8(v3 * inv, __NV_SATFINITE, __NV_E4M3) << 24);
-          *reinterpret_cast<uint32_t*>(dst + b * 128 + lane * 4) = q;
-          if (lane == 0) reinterpret_cast<float*>(dst + H)[b] = amax / 448.0f;
+          for (int i = 0; i < U; ++i) {
+            const int u = u0 + i * 32 + lane;
+            if (u < units) v[i] = __ldg(src + u);
+          }
+#pragma unroll
+          for (int i = 0; i < U; ++i) {
+            const int u = u0 + i * 32 + lane;
+            if (u0 + i * 32 >= units) break;           // warp-uniform: H is a multiple of 128, so steps are all-or-nothing per half
+            float f[8];
+            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { f[2 * j] = __low2float(hh[j]); f[2 * j + 1] = __high2float(hh[j]); }
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            amax = fmaxf(amax, 1e-4f);
+            const float inv = __frcp_rn(amax) * 448.0f;
+            uint32_t q[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              q[j >> 2] |= (uint32_t)__nv_cvt_float_to_fp8(f[j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * (j & 3));
+            if (u < units) {
+              *reinterpret_cast<uint2*>(dst + (size_t)u * 8) = make_uint2(q[0], q[1]);
+              if ((lane & 15) == 0) reinterpret_cast<float*>(dst + H)[(u0 + i * 32) / 16 + half] = amax / 448.0f;
+            }
+          }
         }
       } else {
-        const int4* src = reinterpret_cast<const int4*>(reinterpret_cast<const uint8_t*>(a.x) + (size_t)t * row_bytes);
-        for (int u = lane; u < row_bytes / 16; u += 32) reinterpret_cast<int4*>(dst)[u] = __ldg(src + u);
+        warp_copy_row1(reinterpret_cast<int4*>(dst), reinterpret_cast<const int4*>(reinterpret_cast<const uint8_t*>(a.x) + (size_t)t * row_bytes),
+                       row_bytes / 16, lane);
         if (a.mode == 1)
           for (int q = lane; q < nsf; q += 32) reinterpret_cast<float*>(dst + H)[q] = a.x_sf[(size_t)t * nsf + q];
       }
@@ -137,6 +166,7 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
       if (lane == 0) st_release_sys(reinterpret_cast<unsigned long long*>(base + ll.row_flag) + (size_t)me * M + j, epoch);
     }
 
+    stamp(1);
     // ---- receive: wait for all routing tables, derive the layout
     uint8_t* mine = ctx.ws[me] + bank_off;
     ok = 1;
@@ -148,19 +178,25 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
     uint8_t* mine = ctx.ws[me] + bank_off;
     const int* gidx = reinterpret_cast<const int*>(mine + ll.gather_idx);
     const float* gw_ = reinterpret_cast<const float*>(mine + ll.gather_w);
+    stamp(2);
     if (threadIdx.x < kMaxRanks)
       s_T[threadIdx.x] = threadIdx.x < P ? __ldcg(reinterpret_cast<const int*>(mine + ll.gather_hdr) + threadIdx.x * 4) : 0;
     for (int i = threadIdx.x; i < E * kLLWords; i += kLLThreads) (&s_emask[0][0])[i] = 0u;
     for (int i = threadIdx.x; i < kMaxRanks * kLLWords; i += kLLThreads) (&s_hit[0][0])[i] = 0u;
     __syncthreads();
-    for (int i = threadIdx.x; i < P * M * K; i += kLLThreads) {
-      const int r = i / (M * K), rem = i - r * M * K, t = rem / K, k = rem - t * K;
+    for (int i = threadIdx.x; i < P * M; i += kLLThreads) {   // one thread per (source, token)
+      const int r = i / M, t = i - r * M;
       if (t >= s_T[r]) continue;
       int row[kMaxTopk];
-      for (int j = 0; j <= k; ++j) row[j] = __ldcg(gidx + ((size_t)r * M + t) * K + j);
-      if (!counts_ll(row, k, E) || row[k] / Lx != me) continue;
-      atomicOr(&s_emask[r * Lx + (row[k] - me * Lx)][t >> 5], 1u << (t & 31));
-      atomicOr(&s_hit[r][t >> 5], 1u << (t & 31));
+#pragma unroll
+      for (int k = 0; k < kMaxTopk; ++k) row[k] = k < K ? __ldcg(gidx + ((size_t)r * M + t) * K + k) : -1;
+#pragma unroll
+      for (int k = 0; k < kMaxTopk; ++k) {
+        if (k < K && counts_ll(row, k, E) && row[k] / Lx == me) {
+          atomicOr(&s_emask[r * Lx + (row[k] - me * Lx)][t >> 5], 1u << (t & 31));
+          atomicOr(&s_hit[r][t >> 5], 1u << (t & 31));
+        }
+      }
     }
     __syncthreads();
     for (int l = threadIdx.x; l < Lx; l += kLLThreads) {
@@ -195,6 +231,7 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
       }
     }
 
+    stamp(3);
     // ---- poll row flags and write the output rows
     const uint8_t* stage = mine + ll.stage;
     uint8_t* recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
@@ -220,10 +257,9 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
         }
       }
       const uint8_t* src = stage + ((size_t)r * M + j) * ll.msg_bytes;
-      for (int u = lane; u < row_bytes / 16; u += 32) {
-        const int4 v = ld_cg_int4(src + (size_t)u * 16);
-        for (int i = 0; i < n; ++i) reinterpret_cast<int4*>(recv_x + (size_t)rows[i] * row_bytes)[u] = v;
-      }
+      int4* outs[kMaxTopk];
+      for (int i = 0; i < n; ++i) outs[i] = reinterpret_cast<int4*>(recv_x + (size_t)rows[i] * row_bytes);
+      warp_copy_row<8>(outs, n, reinterpret_cast<const int4*>(src), row_bytes / 16, lane);
       if (fp8)
         for (int q = lane; q < nsf; q += 32) {
           const float v = __ldcg(reinterpret_cast<const float*>(src + H) + q);
@@ -232,7 +268,9 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
     }
   }
 
+  stamp(4);
   if (last_block_of_rank(ctl, kOpLLDispatch, gridDim.x)) {
+    stamp(5);
     if (!ld_volatile_int(&ctl->abort) && threadIdx.x < P)
       st_release_sys(&control_of(ctx.ws[threadIdx.x])->ll_disp_ack[me], epoch);
     if (threadIdx.x == 0) ctl->epoch[kOpLLDispatch] = epoch;
@@ -274,7 +312,7 @@ __global__ void __launch_bounds__(kLLThreads) ep_combine_ll_kernel(const __grid_
       uint8_t* base = ctx.ws[src] + bank_off;
       int4* dst = reinterpret_cast<int4*>(base + ll.ret + (size_t)rem * row_bytes);
       const int4* from = reinterpret_cast<const int4*>(reinterpret_cast<const uint8_t*>(a.x) + (size_t)r * row_bytes);
-      for (int u = lane; u < units; u += 32) dst[u] = __ldg(from + u);
+      warp_copy_row1(dst, from, units, lane);
       __threadfence_system();
       __syncwarp();
       if (lane == 0) st_release_sys(reinterpret_cast<unsigned long long*>(base + ll.ret_flag) + rem, epoch);
@@ -300,24 +338,44 @@ __global__ void __launch_bounds__(kLLThreads) ep_combine_ll_kernel(const __grid_
       if (!__shfl_sync(0xffffffffu, got, 0)) break;
       const uint8_t* rows = mine + ll.ret + (size_t)t * K * row_bytes;
       int4* out = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.out) + (size_t)t * row_bytes);
-      for (int u = lane; u < units; u += 32) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (unsigned m = valid; m; m &= m - 1) {
-          const int k = __ffs(m) - 1;
-          const int4 v = ld_cg_int4(rows + (size_t)k * row_bytes + (size_t)u * 16);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      for (int u0 = lane; u0 < units; u0 += 64) {     // two 16-byte columns per step; all slots' loads issued first
+        const bool two = u0 + 32 < units;
+        int4 v0[kMaxTopk], v1[kMaxTopk];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            // product and sum are rounded separately (no fused multiply-add), as the CPU oracle does
-            acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(w_row[k], __low2float(h[i])));
-            acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(w_row[k], __high2float(h[i])));
+        for (int k = 0; k < kMaxTopk; ++k) {
+          if (k < K && ((valid >> k) & 1u)) {
+            v0[k] = ld_cg_int4(rows + (size_t)k * row_bytes + (size_t)u0 * 16);
+            if (two) v1[k] = ld_cg_int4(rows + (size_t)k * row_bytes + (size_t)(u0 + 32) * 16);
+          }
+        }
+        float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < kMaxTopk; ++k) {
+          if (k < K && ((valid >> k) & 1u)) {
+            const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[k]);
+            const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[k]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              // product and sum are rounded separately (no fused multiply-add), as the CPU oracle does
+              a0[2 * i] = __fadd_rn(a0[2 * i], __fmul_rn(w_row[k], __low2float(h0[i])));
+              a0[2 * i + 1] = __fadd_rn(a0[2 * i + 1], __fmul_rn(w_row[k], __high2float(h0[i])));
+              if (two) {
+                a1[2 * i] = __fadd_rn(a1[2 * i], __fmul_rn(w_row[k], __low2float(h1[i])));
+                a1[2 * i + 1] = __fadd_rn(a1[2 * i + 1], __fmul_rn(w_row[k], __high2float(h1[i])));
+              }
+            }
           }
         }
         int4 o;
         __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        out[u] = o;
+        for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(a0[2 * i], a0[2 * i + 1]);
+        out[u0] = o;
+        if (two) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(a1[2 * i], a1[2 * i + 1]);
+          out[u0 + 32] = o;
+        }
       }
     }
   }

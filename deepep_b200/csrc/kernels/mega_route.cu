@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kRouteThreads) mega_route_kernel(const __grid_
           const int slot_i = i0 + src_lane, t = slot_i / K;
           const int4* from = reinterpret_cast<const int4*>(peer + in.x + (size_t)t * H);
           int4* to = reinterpret_cast<int4*>(a.a1 + row * H);
-          for (int u = lane; u < H / 16; u += 32) to[u] = ld_cg_int4(from + u);
+          { int4* one[1] = {to}; warp_copy_row<14>(one, 1, from, H / 16, lane); }
           const uint32_t* sf = reinterpret_cast<const uint32_t*>(peer + in.x_sf + (size_t)t * (H / 32));
           for (int g = lane; g < H / 128; g += 32)
             *reinterpret_cast<uint32_t*>(a.a1_sf + sf_offset(row, (long long)g * 128, H)) = __ldcg(sf + g);
