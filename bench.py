@@ -125,9 +125,9 @@ def bench_mega_moe(group, world, rank, dev, timed):
     H, I, E, K = 7168, 2048, 256, 8
     L = E // world
     g = torch.Generator(device=dev).manual_seed(5 + rank)
-    w1 = MegaWeights(torch.randint(0, 256, (L * 2 * I, H // 2), dtype=torch.uint8, device=dev, generator=g),
+    w1 = MegaWeights(torch.randint(0, 256, (L * 2 * I * (H // 128), 64), dtype=torch.uint8, device=dev, generator=g),
                      torch.full((L * 2 * I // 128 * (H // 128) * 512,), 118, dtype=torch.uint8, device=dev), L, 2 * I, H)
-    w2 = MegaWeights(torch.randint(0, 256, (L * H, I // 2), dtype=torch.uint8, device=dev, generator=g),
+    w2 = MegaWeights(torch.randint(0, 256, (L * H * (I // 128), 64), dtype=torch.uint8, device=dev, generator=g),
                      torch.full((L * H // 128 * (I // 128) * 512,), 120, dtype=torch.uint8, device=dev), L, H, I)
     out = {}
     for name, T in (("prefill", 4096), ("decode", 64)):

@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--no-profiler", action="store_true", help="skip the torch.profiler breakdown (needed under ncu)")
     args = ap.parse_args()
     from deepep_b200.models.mega_moe import MegaEngine, MegaWeights
     from deepep_b200.ops import load_native
@@ -37,9 +38,9 @@ def main():
         s.attach_peers([q.workspace for q in sessions])
     eng = MegaEngine(sessions, layout, dev, E, I)
     g = torch.Generator(device="cuda").manual_seed(0)
-    w1 = [MegaWeights(torch.randint(0, 256, (L * 2 * I, H // 2), dtype=torch.uint8, device=dev, generator=g),
+    w1 = [MegaWeights(torch.randint(0, 256, (L * 2 * I * (H // 128), 64), dtype=torch.uint8, device=dev, generator=g),
                       torch.full((L * 2 * I // 128 * (H // 128) * 512,), 118, dtype=torch.uint8, device=dev), L, 2 * I, H) for _ in range(P)]
-    w2 = [MegaWeights(torch.randint(0, 256, (L * H, I // 2), dtype=torch.uint8, device=dev, generator=g),
+    w2 = [MegaWeights(torch.randint(0, 256, (L * H * (I // 128), 64), dtype=torch.uint8, device=dev, generator=g),
                       torch.full((L * H // 128 * (I // 128) * 512,), 120, dtype=torch.uint8, device=dev), L, H, I) for _ in range(P)]
     for r in range(P):
         x, sf, ti, tw = eng.input_views(r)
@@ -65,14 +66,15 @@ def main():
     torch.cuda.synchronize()
     total_us = s.elapsed_time(e) / args.iters * 1e3
     # per-kernel breakdown from the profiler (device time)
-    from torch.profiler import ProfilerActivity, profile
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        run()
-        torch.cuda.synchronize()
     kern = {}
-    for evt in prof.events():
-        if evt.device_time > 0:
-            kern.setdefault(evt.name.split("(")[0][-40:], []).append(evt.device_time)
+    if not args.no_profiler:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            run()
+            torch.cuda.synchronize()
+        for evt in prof.events():
+            if evt.device_time > 0:
+                kern.setdefault(evt.name.split("(")[0][-40:], []).append(evt.device_time)
     rows = P * T * K
     flops = 2.0 * rows * (2 * I) * H + 2.0 * rows * H * I
     print(json.dumps({"world": P, "tokens": T, "hidden": H, "inter": I, "experts": E, "topk": K, "total_us": total_us,

@@ -11,7 +11,7 @@
 namespace dep {
 
 constexpr int kGemmBM = 128;   // token rows per tile (TMEM lanes)
-constexpr int kGemmBN = 128;   // output columns per tile
+constexpr int kGemmBN = 256;   // output columns per tile
 constexpr int kGemmBK = 128;   // K elements per pipeline stage (one 128-byte swizzle row of fp8)
 constexpr int kSfChunk = 512;  // bytes of block scales of 128 rows x 128 K-elements (ue8m0 per 32)
 
@@ -24,13 +24,13 @@ __host__ __device__ inline long long sf_offset(long long row, long long k, long 
 
 enum GemmEpilogue : int {
   kEpiStoreF32 = 0,        // C fp32 [rows, N] (tests)
-  kEpiSwigluQuant = 1,     // tile = [64 gate | 64 up] columns -> silu(gate) * up -> e4m3 + ue8m0 per 32
+  kEpiSwigluQuant = 1,     // tile = [128 gate | 128 up] columns -> silu(gate) * up -> e4m3 + ue8m0 per 32
   kEpiCombine = 2          // bf16 rows written into the source rank's combine slots over NVLink
 };
 
 struct MegaGemmParams {
   CUtensorMap tmap_a;        // activations [rows_pad, K] e4m3, box 128 x 128, 128-byte swizzle
-  CUtensorMap tmap_b;        // weights [experts * n_total, K] e2m1 (two per byte), unpacked to bytes by the copy engine
+  CUtensorMap tmap_b;        // weights, e2m1 pairs, tiled as [(rows / 128) * (K / 128) * 128, 128 values]; widened to bytes by the copy engine
   const uint8_t* sfa;        // chunked scales of A
   const uint8_t* sfb;        // chunked scales of B
   const int* mtile_expert;   // [max_mtiles] local expert of each 128-row tile
@@ -50,6 +50,7 @@ struct MegaGemmParams {
   long long comb_off;        // byte offset of the combine slots [M][topk][H] bf16 in a workspace
   int max_tokens, topk, hidden, pad2;
   int* error_flag;           // set when a pipeline wait ran out
+  long long* debug;          // optional: cycle counters of block 0 (producer wait/issue/stages, MMA wait/issue/acc wait)
 };
 cudaError_t launch_mega_gemm(const MegaGemmParams& p, int blocks, cudaStream_t stream);
 

@@ -31,22 +31,24 @@ long long getl(const py::dict& d, const char* key, long long dflt = 0) { return 
 void op_mega_gemm(const py::dict& d, py::object session, int blocks, uintptr_t stream) {
   MegaGemmParams p{};
   const long long rows_pad = getl(d, "rows_pad"), k = getl(d, "k"), b_rows = getl(d, "b_rows");
-  if (rows_pad % kGemmBM || k % kGemmBK || b_rows % kGemmBN) throw std::invalid_argument("rows, K and weight rows must be multiples of 128");
+  if (rows_pad % kGemmBM || k % kGemmBK || b_rows % kGemmBN) throw std::invalid_argument("rows and K must be multiples of 128, weight rows of 256");
   const char* err = nullptr;
   if (!encode_operand_map(&p.tmap_a, ptr<const void>(d, "a"), rows_pad, k, false, &err)) throw std::runtime_error(err);
-  if (!encode_operand_map(&p.tmap_b, ptr<const void>(d, "b"), b_rows, k, true, &err)) throw std::runtime_error(err);
+  // weights are stored tiled: every (128-row, 128-K) block is one contiguous run of 128 rows x 64 bytes
+  if (!encode_operand_map(&p.tmap_b, ptr<const void>(d, "b"), b_rows * (k / kGemmBK), kGemmBK, true, &err)) throw std::runtime_error(err);
   p.sfa = ptr<const uint8_t>(d, "sfa"); p.sfb = ptr<const uint8_t>(d, "sfb");
   p.mtile_expert = ptr<const int>(d, "mtile_expert"); p.num_mtiles = ptr<const int>(d, "num_mtiles");
   p.max_mtiles = (int)(rows_pad / kGemmBM);
   p.n_total = geti(d, "n_total"); p.n_tiles = p.n_total / kGemmBN; p.k_steps = (int)(k / kGemmBK);
-  if (p.n_total % kGemmBN) throw std::invalid_argument("output width must be a multiple of 128");
+  if (p.n_total % kGemmBN) throw std::invalid_argument("output width must be a multiple of 256");
   p.epi = geti(d, "epi");
-  p.b_tx_bytes = geti(d, "b_tx_bytes", kGemmBN * kGemmBK / 2);
+  p.b_tx_bytes = geti(d, "b_tx_bytes", 128 * kGemmBK / 2);   // bytes counted per 128-row fp4 box
   p.c = ptr<float>(d, "c"); p.ldc = geti(d, "ldc");
   p.a2 = ptr<uint8_t>(d, "a2"); p.a2_sf = ptr<uint8_t>(d, "a2_sf"); p.inter = geti(d, "inter");
   p.row_src = ptr<const int>(d, "row_src");
   p.comb_off = getl(d, "comb_off"); p.max_tokens = geti(d, "max_tokens"); p.topk = geti(d, "topk"); p.hidden = geti(d, "hidden");
   p.error_flag = ptr<int>(d, "error_flag");
+  p.debug = ptr<long long>(d, "debug");
   if (p.epi == kEpiCombine) {
     RankCtx ctx = session.cast<Session&>().ctx();
     for (int r = 0; r < ctx.world; ++r) p.ws[r] = ctx.ws[r];
@@ -94,6 +96,7 @@ void op_mega_finish(const WsLayout& lay, const std::vector<py::object>& sessions
 
 void bind_mega(py::module_& m) {
   m.attr("gemm_tile") = kGemmBM;
+  m.attr("gemm_tile_n") = kGemmBN;
   m.attr("sf_chunk") = kSfChunk;
   m.def("mega_input_offsets", [](int max_tokens, int hidden, int topk) {
     long long o[6];

@@ -39,7 +39,7 @@ def _view(ptr: int, nbytes: int, device) -> torch.Tensor:
 @dataclass
 class MegaWeights:
     """One projection of all local experts in kernel layout."""
-    packed: torch.Tensor        # [L * N, K / 2] uint8 (two e2m1 per byte, low nibble first)
+    packed: torch.Tensor        # e2m1 pairs (low nibble first), tiled: [(L * N / 128) * (K / 128) * 128, 64] uint8
     sf_chunks: torch.Tensor     # 512-byte scale chunks
     experts: int
     n: int
@@ -56,19 +56,21 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
                                    device=None) -> Tuple[MegaWeights, MegaWeights]:
     """Rearrange ``(w1 [L, 2I, H/2], w1_sf [L, 2I, H/32])`` and ``(w2 [L, H, I/2], w2_sf [L, H, I/32])`` for the kernel.
 
-    W1 rows are regrouped so every 128-row tile holds 64 gate rows followed by the 64 matching up rows
+    W1 rows are regrouped so every 256-row tile holds 128 gate rows followed by the 128 matching up rows
     (gate = first I rows, up = last I rows); scales go into the tensor-memory chunk layout.
     """
     (w1, w1_sf), (w2, w2_sf) = l1_weights, l2_weights
     L, n1, hk = w1.shape
     inter, hidden = n1 // 2, hk * 2
     assert w2.shape == (L, hidden, inter // 2), "w2 must be [L, H, I / 2]"
-    assert hidden % 128 == 0 and inter % 128 == 0, "hidden and intermediate sizes must be multiples of 128"
+    assert hidden % 256 == 0 and inter % 128 == 0, "hidden must be a multiple of 256, the intermediate size of 128"
     device = device or w1.device
-    order = torch.arange(n1).view(2, inter // 64, 64).permute(1, 0, 2).reshape(-1)     # tile j: gate[64j:64j+64], up[64j:64j+64]
-    w1t = w1.view(torch.uint8)[:, order].reshape(L * n1, hk).contiguous()
+    order = torch.arange(n1).view(2, inter // 128, 128).permute(1, 0, 2).reshape(-1)   # tile j: gate[128j:128j+128], up[128j:128j+128]
+    from ..oracle.megamoe import tile_fp4_rows
+
+    w1t = tile_fp4_rows(w1.view(torch.uint8)[:, order].reshape(L * n1, hk).contiguous())
     w1_sft = w1_sf.view(torch.uint8).reshape(L, n1, hidden // 32)[:, order].reshape(L * n1, hidden // 32)
-    w2t = w2.view(torch.uint8).reshape(L * hidden, inter // 2).contiguous()
+    w2t = tile_fp4_rows(w2.view(torch.uint8).reshape(L * hidden, inter // 2).contiguous())
     w2_sft = w2_sf.view(torch.uint8).reshape(L * hidden, inter // 32)
     return (MegaWeights(w1t.to(device), _sf_chunks(w1_sft).to(device), L, n1, hidden),
             MegaWeights(w2t.to(device), _sf_chunks(w2_sft).to(device), L, hidden, inter))
@@ -84,7 +86,7 @@ class MegaEngine:
         self.M, self.H, self.K = layout.max_tokens, layout.hidden, layout.topk
         self.E, self.I = num_experts, intermediate
         self.L = num_experts // self.world
-        assert self.H % 128 == 0 and self.I % 128 == 0 and num_experts % self.world == 0
+        assert self.H % 256 == 0 and self.I % 128 == 0 and num_experts % self.world == 0
         off = self.C.mega_input_offsets(self.M, self.H, self.K)
         self.in_off = layout.mega
         self.off_hdr, self.off_x, self.off_sf, self.off_idx, self.off_w, in_total = off

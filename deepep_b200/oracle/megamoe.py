@@ -91,5 +91,13 @@ def to_sf_chunks(sf: torch.Tensor) -> torch.Tensor:
     return v.permute(0, 3, 2, 1, 4).contiguous().view(-1)
 
 
-__all__ = ["bf16", "dequantize_mxfp8", "expert_forward", "make_weights", "mega_moe_reference", "quantize_mxfp8",
+def tile_fp4_rows(packed: torch.Tensor) -> torch.Tensor:
+    """[rows, K / 2] packed e2m1 -> [(rows / 128) * (K / 128) * 128, 64]: every (128-row, 128-K) block becomes 8 KB of
+    contiguous memory, so one tile load of the GEMM reads one contiguous block instead of 128 strided 64-byte pieces."""
+    rows, kb = packed.shape
+    assert rows % 128 == 0 and kb % 64 == 0
+    return packed.view(rows // 128, 128, kb // 64, 64).permute(0, 2, 1, 3).contiguous().view(-1, 64)
+
+
+__all__ = ["tile_fp4_rows", "bf16", "dequantize_mxfp8", "expert_forward", "make_weights", "mega_moe_reference", "quantize_mxfp8",
            "to_sf_chunks", "unpack_fp4"]

@@ -220,7 +220,7 @@ class CudaEngine:
 
     # ------------------------------------------------------------------ low latency
     def ll_blocks(self) -> int:
-        return max(1, min(32, self.sm_count // self.n))
+        return max(1, min(96, self.sm_count // self.n))   # few rows per warp: latency, not bandwidth, is the goal
 
     def ll_dispatch(self, xs: Sequence, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[torch.Tensor], num_experts: int,
                     mode: int, cpu_sync: bool = True, stream=None, outputs: Optional[list] = None):

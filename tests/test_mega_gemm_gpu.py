@@ -25,7 +25,7 @@ def _run(rows_per_expert, n_total, k, seed=0, b_tx=None):
     a_f, b_f = O.dequantize_mxfp8(a_codes, a_sf), O.unpack_fp4(packed, b_sf)
     for mt, e in enumerate(mtile_expert.tolist()):
         ref[mt * 128:(mt + 1) * 128] = a_f[mt * 128:(mt + 1) * 128] @ b_f[e * n_total:(e + 1) * n_total].t()
-    d = dict(a=a_codes.view(torch.uint8).to(dev), b=packed.to(dev), sfa=O.to_sf_chunks(a_sf).to(dev), sfb=O.to_sf_chunks(b_sf).to(dev),
+    d = dict(a=a_codes.view(torch.uint8).to(dev), b=O.tile_fp4_rows(packed).to(dev), sfa=O.to_sf_chunks(a_sf).to(dev), sfb=O.to_sf_chunks(b_sf).to(dev),
              mt=mtile_expert.to(dev), n=torch.tensor([len(mtile_expert)], dtype=torch.int32, device=dev),
              c=torch.zeros((rows_pad, n_total), dtype=torch.float32, device=dev), err=torch.zeros(1, dtype=torch.int32, device=dev))
     args = dict(a=d["a"].data_ptr(), b=d["b"].data_ptr(), sfa=d["sfa"].data_ptr(), sfb=d["sfb"].data_ptr(),
@@ -43,7 +43,7 @@ def _run(rows_per_expert, n_total, k, seed=0, b_tx=None):
 
 
 def test_single_tile():
-    _run([128], 128, 128)
+    _run([128], 256, 128)
 
 
 def test_k_loop_and_tiles():
