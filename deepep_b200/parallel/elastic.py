@@ -79,6 +79,19 @@ class EPHandle:
             raise RuntimeError("handle metadata (or its topk_idx) was modified in place after dispatch")
 
 
+def _timeout_seconds(default: float) -> float:
+    """Device wait limit: ``DEEPEP_GPU_TIMEOUT_SECONDS`` (alias ``DEEPEP_NPU_TIMEOUT_SECONDS``) overrides the constructor."""
+    import os
+
+    for name in ("DEEPEP_GPU_TIMEOUT_SECONDS", "DEEPEP_NPU_TIMEOUT_SECONDS"):
+        if name in os.environ:
+            value = float(os.environ[name])
+            if not 1 <= value <= 3600:
+                raise ValueError(f"{name} must be in [1, 3600] seconds")
+            return value
+    return default
+
+
 def _as_event(ev) -> Optional[EventHandle]:
     if ev is None:
         return None
@@ -135,7 +148,7 @@ class ElasticBuffer:
             ll = L.ll_region_bytes(self.world_size, num_max_tokens_per_rank, hidden, num_topk)
             self.layout = C.make_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, ll, 0)
             assert self.layout.total == needed, "native and Python workspace layouts disagree"
-            self.runtime = Runtime(self.control, self.layout, float(num_gpu_timeout_secs), self.device)
+            self.runtime = Runtime(self.control, self.layout, float(_timeout_seconds(num_gpu_timeout_secs)), self.device)
             self.engine = CudaEngine([self.runtime.native], self.layout, self.device, num_sms=num_sms)
         else:
             from .engine_cpu import CpuEngine
