@@ -112,7 +112,10 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
       if (threadIdx.x < P)
         st_release_sys(reinterpret_cast<unsigned long long*>(ctx.ws[threadIdx.x] + bank_off + ll.idx_flag) + me, epoch);
     }
-    for (int item = gw; item < a.T * P; item += total_warps) {
+    // with more than one block, block 0 only publishes the routing table so that it leaves as early as possible
+    const int send_first = gridDim.x > 1 ? 1 : 0;
+    const int send_warps = (gridDim.x - send_first) * nwarps;
+    for (int item = (blockIdx.x - send_first) * nwarps + warp; item < a.T * P && (int)blockIdx.x >= send_first; item += send_warps) {
       const int t = item / P, d = (me + item % P) % P;
       if (!((s_own[d][t >> 5] >> (t & 31)) & 1u)) continue;
       const int j = below8(s_own[d], t);
@@ -320,7 +323,10 @@ __global__ void __launch_bounds__(kLLThreads) ep_combine_ll_kernel(const __grid_
     // ---- weighted sum at the source, slot order, fp32
     uint8_t* mine = ctx.ws[me] + bank_off;
     const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(mine + ll.ret_flag);
-    for (int t = gw; t < a.T; t += total_warps) {
+    constexpr int kSplit = 4;                      // warps per token: each reduces a quarter of the columns
+    const int span = ((units + kSplit * 64 - 1) / (kSplit * 64)) * 64;   // columns per warp, a multiple of the 64-unit step
+    for (int item = gw; item < a.T * kSplit; item += total_warps) {
+      const int t = item / kSplit, part = item - t * kSplit;
       int idx_row[kMaxTopk];
       float w_row[kMaxTopk];
       unsigned valid = 0;
@@ -338,8 +344,9 @@ __global__ void __launch_bounds__(kLLThreads) ep_combine_ll_kernel(const __grid_
       if (!__shfl_sync(0xffffffffu, got, 0)) break;
       const uint8_t* rows = mine + ll.ret + (size_t)t * K * row_bytes;
       int4* out = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.out) + (size_t)t * row_bytes);
-      for (int u0 = lane; u0 < units; u0 += 64) {     // two 16-byte columns per step; all slots' loads issued first
-        const bool two = u0 + 32 < units;
+      const int u_end = min(units, (part + 1) * span);
+      for (int u0 = part * span + lane; u0 < u_end; u0 += 64) {     // two 16-byte columns per step; all slots' loads issued first
+        const bool two = u0 + 32 < u_end;
         int4 v0[kMaxTopk], v1[kMaxTopk];
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {
