@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--experts", type=int, default=32)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--unfused", action="store_true", help="four launches instead of the persistent kernel")
     ap.add_argument("--no-profiler", action="store_true", help="skip the torch.profiler breakdown (needed under ncu)")
     args = ap.parse_args()
     from deepep_b200.models.mega_moe import MegaEngine, MegaWeights
@@ -52,7 +53,7 @@ def main():
     ys = [torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(P)]
 
     def run():
-        eng.forward(ys, [T] * P, w1, w2)
+        eng.forward(ys, [T] * P, w1, w2, fused=not args.unfused)
 
     for _ in range(2):
         run()

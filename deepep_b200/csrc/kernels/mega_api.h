@@ -89,4 +89,14 @@ struct MegaFinishArgs {
 struct MegaFinishParams { WsLayout lay; MegaFinishArgs r[kMaxRanks]; };
 cudaError_t launch_mega_finish(const MegaFinishParams& p, int nranks, int blocks, cudaStream_t stream);
 
+// ---------------------------------------------------------------- the fused layer (one persistent kernel)
+struct MegaFusedArgs {
+  MegaGemmParams g1, g2;       // GEMM1 (SwiGLU + requant epilogue) and GEMM2 (combine epilogue)
+  MegaRouteArgs route;
+  MegaFinishArgs finish;
+  int* ready;                  // [max_mtiles] finished GEMM1 tiles per row block (zeroed by the kernel)
+};
+struct MegaFusedParams { WsLayout lay; MegaFusedArgs r[kMaxRanks]; };
+cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, cudaStream_t stream);
+
 }  // namespace dep

@@ -1,0 +1,50 @@
+// mega_moe: the whole MoE layer of one rank in ONE persistent cooperative kernel.
+//
+//   phase 1  route_phase   handshake with the peers, routing tables read from peer memory, expert tiles,
+//                          pull of the routed e4m3 rows + scales over NVLink          (grid barriers inside)
+//   phase 2  gemm_phase    GEMM1 (+SwiGLU + MXFP8 requant) and GEMM2 (+ bf16 rows stored into the source
+//                          ranks' combine slots over NVLink) as one tile list on tcgen05 / TMEM; a GEMM2
+//                          tile starts as soon as the GEMM1 tiles of its row block are done
+//   phase 3  finish_phase  handshake, y[t] = sum_k w[t, k] * row[t, k]
+// One CTA per SM stays resident for all three phases; the phases are separated by grid barriers on this
+// GPU and by flag words in peer memory across GPUs.
+//
+// Parity: mega_moe_kernel of the reference (experiments/megamoe/csrc/kernels/mega_moe/mega_moe.cpp:22-81,
+// mega_moe_arch35.hpp:852-1006): input preparation / route / cross-rank sync, expert waves of
+// dispatch + GMM1 + activation-quant + GMM2 + combine, cross-rank sync, unpermute.
+#include <cooperative_groups.h>
+
+#include "mega_gemm.cuh"
+#include "mega_route.cuh"
+
+namespace dep {
+
+__global__ void __launch_bounds__(kGemmThreads, 1) mega_moe_kernel(const __grid_constant__ MegaFusedParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  cg::grid_group grid = cg::this_grid();
+  const MegaFusedArgs& a = p.r[blockIdx.y];
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < a.route.max_mtiles; i += blockDim.x) a.ready[i] = 0;
+  route_phase(a.route, grid);
+  __threadfence();
+  grid.sync();
+  gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x);
+  __threadfence_system();
+  grid.sync();
+  finish_phase(a.finish, true);
+}
+
+cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, cudaStream_t stream) {
+  static bool configured = false;
+  const size_t smem = gemm_smem_bytes(3, true);
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mega_moe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid(blocks, nranks), block(kGemmThreads);
+  void* args[] = {const_cast<MegaFusedParams*>(&p)};
+  return cudaLaunchCooperativeKernel((const void*)mega_moe_kernel, grid, block, args, smem, stream);
+}
+
+}  // namespace dep

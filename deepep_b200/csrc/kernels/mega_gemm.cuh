@@ -1,0 +1,311 @@
+// Grouped block-scaled GEMM phase on the 5th-generation tensor cores (tcgen05 + tensor memory):
+//   C[rows of expert e, n] = sum_k A[row, k] * B[e][n, k]
+// A: e4m3 activations with one ue8m0 scale per 32 values of K; B: e2m1 weights (two per byte in
+// global memory, widened to one byte per value by the copy engine) with ue8m0 scales per 32.
+//
+// `gemm_phase` is run by a whole CTA of kGemmThreads threads, one CTA per SM, warp-specialised:
+//   warp 0     one lane issues the TMA tile loads (A, B) and bulk loads (scale chunks) of a stage
+//   warp 1     allocates tensor memory; one lane copies the scales smem -> TMEM (tcgen05.cp) and
+//              issues four tcgen05.mma (M=128, N=256, K=32) per stage; tcgen05.commit frees the stage
+//   warps 2-9  epilogue (two warps per TMEM lane quadrant, each takes half of the columns):
+//              tcgen05.ld of the fp32 accumulator (one tile row per thread), then
+//              store fp32 | SwiGLU + MXFP8 requantisation | bf16 rows pushed into the source
+//              rank's combine slots over NVLink.
+// It walks one tile list that may hold two GEMMs back to back (GEMM1 tiles, then GEMM2 tiles whose
+// A operand is GEMM1's output): a GEMM2 tile waits on a per-row-block counter that the GEMM1
+// epilogues bump, so SMs that run out of GEMM1 tiles start on GEMM2 at once.
+//
+// Tile shape: issuing one tcgen05 instruction costs the MMA thread about 50 cycles (measured), so a
+// stage of four N=128 MMAs (256 tensor cycles) was issue-bound; N=256 doubles the work per instruction.
+// A 128 x 256 fp32 accumulator takes 256 of the 512 TMEM columns and the scales need more, so there is
+// one accumulator: the next tile's loads are prefetched during the epilogue, its MMAs start after it.
+// All waits are bounded; a wait that runs out sets an error flag, the CTA stops issuing work,
+// frees its tensor memory and returns.
+//
+// Parity: the cube-core GMM1/GMM2 stages and their vector-core epilogues of the reference's MegaMoE
+// (experiments/megamoe/csrc/kernels/mega_moe/mega_moe_wave_a8w4.hpp, catlass_gmm/block_mmad_a8w4.hpp,
+// epilogue/block_epilogue_activation_mx_quant.hpp, stage/gmm2_combine.hpp).
+#pragma once
+#include "mega_api.h"
+#include "umma.cuh"
+
+namespace dep {
+
+constexpr int kGemmThreads = 320;                    // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kEpiWarps = 8;
+constexpr int kGemmMaxStages = 4;
+constexpr int kTileABytes = kGemmBM * kGemmBK;       // 16 KB
+constexpr int kTileBBytes = kGemmBN * kGemmBK;       // 32 KB in shared memory (one byte per value)
+constexpr int kStageBytes = kTileABytes + kTileBBytes;
+constexpr int kSfStageBytes = (1 + kGemmBN / 128) * kSfChunk;   // A scales + B scales of one stage
+constexpr int kEpiWarpCols = kGemmBN / 2;            // columns handled by one epilogue warp
+constexpr int kEpiStageBytes = kEpiWarps * 32 * kEpiWarpCols * 2;   // bf16 staging: each warp parks its 32 x 128 block
+constexpr int kTmemCols = 512;
+constexpr int kSfColBase = kGemmBN;                  // scale columns start after the accumulator
+constexpr int kSfColsPerStage = 4 + 4 * (kGemmBN / 128);
+
+__host__ __device__ constexpr size_t gemm_smem_bytes(int stages, bool staging) {
+  return 1024 + (size_t)stages * (kStageBytes + kSfStageBytes) + (staging ? kEpiStageBytes : 0) + 256;
+}
+
+struct GemmBarriers {
+  uint64_t full[kGemmMaxStages], empty[kGemmMaxStages], acc_full, acc_empty, epi_done;
+  uint32_t tmem_base;
+  int failed;
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ bool try_wait_now(uint64_t* bar, uint32_t parity) {   // no suspend hint: pipeline waits are short
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  for (unsigned i = 0; i < (1u << 24); ++i) {
+    if (try_wait_now(bar, parity)) return true;
+    if ((i & 63u) == 63u && *failed) return false;
+  }
+  *failed = 1;
+  return false;
+}
+// Producer-side wait for "all `need` GEMM1 tiles of this row block have been written".
+__device__ __forceinline__ bool wait_rows_ready(const int* counter, int need, volatile int* failed) {
+  for (unsigned i = 0; i < (1u << 26); ++i) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (v >= need) return true;
+    if ((i & 63u) == 63u) { if (*failed) return false; __nanosleep(100); }
+  }
+  *failed = 1;
+  return false;
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// g1: first GEMM of the list; g2: optional second GEMM (nullptr for a single GEMM).  `ready` (may be null):
+// ready[mt] counts finished g1 tiles of row block mt; g2 tiles of mt wait until it reaches g1.n_tiles.
+// `smem_raw` must provide gemm_smem_bytes(stages, staging) bytes.
+__device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaGemmParams* g2, int* ready, uint8_t* smem_raw,
+                                           int stages, int cta, int num_ctas) {
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
+  uint8_t* tiles = smem;
+  uint8_t* sf_smem = tiles + (size_t)stages * kStageBytes;
+  uint8_t* epi_smem = sf_smem + (size_t)stages * kSfStageBytes;
+  const bool staging = g1.epi == kEpiCombine || (g2 && g2->epi == kEpiCombine);
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(epi_smem + (staging ? kEpiStageBytes : 0));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGemmMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->acc_empty, kEpiWarps);
+    mbar_init(&bars->epi_done, kEpiWarps);
+    bars->failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    umma::prefetch_tensormap(&g1.tmap_a);
+    umma::prefetch_tensormap(&g1.tmap_b);
+    if (g2) { umma::prefetch_tensormap(&g2->tmap_a); umma::prefetch_tensormap(&g2->tmap_b); }
+  }
+  if (warp == 1) {
+    umma::tmem_alloc(&bars->tmem_base, kTmemCols);
+    umma::tmem_relinquish();
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* failed = &bars->failed;
+
+  const int num_mtiles = min(*g1.num_mtiles, g1.max_mtiles);
+  const int tiles1 = num_mtiles * g1.n_tiles;
+  const int total_tiles = tiles1 + (g2 ? num_mtiles * g2->n_tiles : 0);
+
+  if (warp == 0) {
+    // ============================================================ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas) {
+        const bool second = tile >= tiles1;
+        const MegaGemmParams& p = second ? *g2 : g1;
+        const int local = second ? tile - tiles1 : tile;
+        const int mt = local / p.n_tiles, nb = local - mt * p.n_tiles;
+        const int brow = p.mtile_expert[mt] * p.n_total + nb * kGemmBN;
+        if (second && ready) {
+          if (!wait_rows_ready(ready + mt, g1.n_tiles, failed)) break;
+          fence_proxy_async();          // rows written by other SMs' stores are about to be read by the copy engine
+        }
+        for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+          const int s = it % stages;
+          if (!bounded_wait(&bars->empty[s], ((it / stages) & 1u) ^ 1u, failed)) break;
+          uint8_t* a_dst = tiles + (size_t)s * kStageBytes;
+          uint8_t* sf_dst = sf_smem + (size_t)s * kSfStageBytes;
+          mbar_expect_tx(&bars->full[s], kTileABytes + (kGemmBN / 128) * p.b_tx_bytes + kSfStageBytes);
+          umma::tma_load_2d(a_dst, &p.tmap_a, ks * kGemmBK, mt * kGemmBM, &bars->full[s]);
+          bulk_g2s(sf_dst, p.sfa + ((size_t)mt * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+#pragma unroll
+          for (int h = 0; h < kGemmBN / 128; ++h) {     // 128 weight rows per box; consecutive boxes continue the same swizzled tile
+            umma::tma_load_2d(a_dst + kTileABytes + h * 128 * kGemmBK, &p.tmap_b, 0, ((brow / 128 + h) * p.k_steps + ks) * 128,
+                              &bars->full[s]);
+            bulk_g2s(sf_dst + (1 + h) * kSfChunk, p.sfb + ((size_t)(brow / 128 + h) * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, /*e4m3*/ 0, /*e2m1*/ 5);
+      uint32_t it = 0, local_tile = 0;
+      for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas, ++local_tile) {
+        const int k_steps = tile >= tiles1 ? g2->k_steps : g1.k_steps;
+        if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed)) break;
+        umma::fence_after_sync();
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % stages;
+          if (!bounded_wait(&bars->full[s], (it / stages) & 1u, failed)) break;
+          umma::fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * kStageBytes);
+          const uint32_t sf_addr = smem_u32(sf_smem + (size_t)s * kSfStageBytes);
+          const uint32_t tsfa = tmem + kSfColBase + s * kSfColsPerStage, tsfb = tsfa + 4;
+          umma::copy_sf_to_tmem(tsfa, umma::smem_desc_sf(sf_addr));
+#pragma unroll
+          for (int h = 0; h < kGemmBN / 128; ++h)
+            umma::copy_sf_to_tmem(tsfb + 4 * h, umma::smem_desc_sf(sf_addr + (1 + h) * kSfChunk));
+          const uint64_t da = umma::smem_desc_sw128(a_addr), db = umma::smem_desc_sw128(a_addr + kTileABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)   // 32 K-values = 32 bytes = 2 descriptor units per step inside the swizzle row
+            umma::mma_block_scaled(tmem, da + 2 * k, db + 2 * k, umma::with_sf_ids(idesc, k, k), tsfa, tsfb, ks > 0 || k > 0);
+          umma::commit(&bars->empty[s]);          // stage (tiles, scale columns) reusable once these MMAs finished
+        }
+        umma::commit(&bars->acc_full);             // accumulator complete
+      }
+    }
+  } else {
+    // ============================================================ epilogue (warps 2..9)
+    const int quad = warp & 3;                       // TMEM lanes [32 * quad, 32 * quad + 32)
+    const int part = (warp - 2) >> 2;                // which half of the tile's columns this warp handles
+    const int row_in_tile = quad * 32 + lane;
+    uint8_t* stage = epi_smem + (size_t)(warp - 2) * 32 * kEpiWarpCols * 2;
+    uint32_t local_tile = 0, first_done = 0;
+    for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas, ++local_tile) {
+      const bool second = tile >= tiles1;
+      const MegaGemmParams& p = second ? *g2 : g1;
+      const int local = second ? tile - tiles1 : tile;
+      const int mt = local / p.n_tiles, nb = local - mt * p.n_tiles;
+      if (!bounded_wait(&bars->acc_full, local_tile & 1u, failed)) break;
+      umma::fence_after_sync();
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+      const long long row = (long long)mt * kGemmBM + row_in_tile;
+      uint32_t v[32], u[32];
+      if (p.epi == kEpiCombine) {
+        // bf16 rows go to the source rank's combine slots.
+        // 1) drain this warp's 32 x 128 block into shared memory as bf16 and hand the accumulator back at once
+        const int code = p.row_src[row];
+        uint8_t* dst_row = nullptr;
+        if (code >= 0) {
+          const int src = code / (p.max_tokens * p.topk), rem = code - src * p.max_tokens * p.topk;
+          dst_row = p.ws[src] + p.comb_off + ((size_t)rem * p.hidden + (size_t)nb * kGemmBN) * 2;
+        }
+        uint4* mine = reinterpret_cast<uint4*>(stage + (size_t)lane * kEpiWarpCols * 2);   // 256 B per row = 16 pieces
+        __syncwarp();                                     // the previous tile's block has been written out
+        for (int c = 0; c < kEpiWarpCols; c += 32) {
+          umma::tmem_ld32(taddr + part * kEpiWarpCols + c, v);
+          umma::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w0[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+              w0[j] = *reinterpret_cast<uint32_t*>(&b0);
+            }
+            mine[(c / 8 + i) ^ (lane & 15)] = make_uint4(w0[0], w0[1], w0[2], w0[3]);   // XOR swizzle against bank conflicts
+          }
+        }
+        umma::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty);
+        // 2) write the block out: 16 lanes x 16 B cover one row's 256-byte segment, 2 rows per instruction
+#pragma unroll 4
+        for (int r0 = 0; r0 < 32; r0 += 2) {
+          const int rr = r0 + (lane >> 4), piece = lane & 15;
+          uint8_t* drow = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, (unsigned long long)dst_row, rr));
+          const uint4 val = reinterpret_cast<const uint4*>(stage + (size_t)rr * kEpiWarpCols * 2)[piece ^ (rr & 15)];
+          if (drow) reinterpret_cast<uint4*>(drow + (size_t)part * kEpiWarpCols * 2)[piece] = val;
+        }
+        continue;   // the accumulator was already released
+      }
+      if (p.epi == kEpiStoreF32) {
+        for (int c = part * (kGemmBN / 2); c < (part + 1) * (kGemmBN / 2); c += 32) {
+          umma::tmem_ld32(taddr + c, v);
+          umma::tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(p.c + row * p.ldc + nb * kGemmBN + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                             __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+        }
+      } else {
+        // SwiGLU + requantisation: columns [0, 128) are gate rows of W1, [128, 256) the matching up rows
+        for (int half = part * (kGemmBN / 128); half < (part + 1) * (kGemmBN / 128); ++half) {
+          umma::tmem_ld32(taddr + half * 32, v);
+          umma::tmem_ld32(taddr + kGemmBN / 2 + half * 32, u);
+          umma::tmem_ld_wait();
+          float h[32], amax = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float g = bf16_round(__uint_as_float(v[i])), up = bf16_round(__uint_as_float(u[i]));
+            const float act = g / (1.0f + __expf(fminf(fmaxf(-g, -80.f), 80.f))) * up;
+            h[i] = bf16_round(act);
+            amax = fmaxf(amax, fabsf(h[i]));
+          }
+          // MX scale: 2^(floor(log2(amax)) - 8), at least 2^-127; values saturate at 448
+          int e = (int)((__float_as_uint(fmaxf(amax, 1.1754944e-38f)) >> 23) & 0xff) - 127 - 8;
+          e = max(e, -127);
+          const float inv = __uint_as_float((uint32_t)(127 - e) << 23);   // 2^-e, exact (e in [-127, 120])
+          uint32_t q[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            q[i] = (uint32_t)__nv_cvt_float_to_fp8(h[4 * i] * inv, __NV_SATFINITE, __NV_E4M3) |
+                   ((uint32_t)__nv_cvt_float_to_fp8(h[4 * i + 1] * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
+                   ((uint32_t)__nv_cvt_float_to_fp8(h[4 * i + 2] * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
+                   ((uint32_t)__nv_cvt_float_to_fp8(h[4 * i + 3] * inv, __NV_SATFINITE, __NV_E4M3) << 24);
+          }
+          const long long col = (long long)nb * (kGemmBN / 2) + half * 32;
+          uint4* dst = reinterpret_cast<uint4*>(p.a2 + row * p.inter + col);
+          dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+          dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+          p.a2_sf[sf_offset(row, col, p.inter)] = (uint8_t)(e + 127);
+        }
+      }
+      umma::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty);
+      if (!second && g2 && ready) {
+        // this tile's rows of the intermediate activations are in global memory: let GEMM2 producers know
+        fence_proxy_async();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->epi_done);
+        if (warp == 2 && lane == 0 && bounded_wait(&bars->epi_done, first_done & 1u, failed)) {
+          __threadfence();
+          atomicAdd(ready + mt, 1);
+        }
+        ++first_done;
+      }
+    }
+    __threadfence_system();       // rows pushed to peers are visible before the kernel (or its next phase) signals them
+  }
+
+  umma::fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *failed && g1.error_flag) *g1.error_flag = 1;
+  if (warp == 1) {
+    umma::fence_after_sync();
+    umma::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+#endif  // __CUDACC__
+
+}  // namespace dep

@@ -28,8 +28,7 @@ long long getl(const py::dict& d, const char* key, long long dflt = 0) { return 
 
 // One grouped GEMM launch.  `d` carries operand pointers and shapes; `session` is needed only by the
 // combine epilogue (peer workspaces).
-void op_mega_gemm(const py::dict& d, py::object session, int blocks, uintptr_t stream) {
-  MegaGemmParams p{};
+void fill_gemm(MegaGemmParams& p, const py::dict& d, py::object session) {
   const long long rows_pad = getl(d, "rows_pad"), k = getl(d, "k"), b_rows = getl(d, "b_rows");
   if (rows_pad % kGemmBM || k % kGemmBK || b_rows % kGemmBN) throw std::invalid_argument("rows and K must be multiples of 128, weight rows of 256");
   const char* err = nullptr;
@@ -53,7 +52,49 @@ void op_mega_gemm(const py::dict& d, py::object session, int blocks, uintptr_t s
     RankCtx ctx = session.cast<Session&>().ctx();
     for (int r = 0; r < ctx.world; ++r) p.ws[r] = ctx.ws[r];
   }
+}
+
+void op_mega_gemm(const py::dict& d, py::object session, int blocks, uintptr_t stream) {
+  MegaGemmParams p{};
+  fill_gemm(p, d, session);
   check(launch_mega_gemm(p, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_gemm launch");
+}
+
+void fill_route(MegaRouteArgs& a, const py::dict& d, py::object session) {
+  a.ctx = session.cast<Session&>().ctx();
+  a.in_off = getl(d, "in_off"); a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K"); a.H = geti(d, "H");
+  a.max_tokens = geti(d, "max_tokens"); a.max_mtiles = geti(d, "max_mtiles");
+  a.a1 = ptr<uint8_t>(d, "a1"); a.a1_sf = ptr<uint8_t>(d, "a1_sf"); a.row_src = ptr<int>(d, "row_src");
+  a.mtile_expert = ptr<int>(d, "mtile_expert"); a.num_mtiles = ptr<int>(d, "num_mtiles");
+  a.expert_rows = ptr<int>(d, "expert_rows"); a.ticket = ptr<int>(d, "ticket");
+  if (a.H % 128 || a.E % a.ctx.world || a.E > kMaxExperts) throw std::invalid_argument("hidden % 128 == 0 and experts % world == 0 are required");
+}
+
+void fill_finish(MegaFinishArgs& a, const py::dict& d, py::object session) {
+  a.ctx = session.cast<Session&>().ctx();
+  a.in_off = getl(d, "in_off"); a.comb_off = getl(d, "comb_off");
+  a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K"); a.H = geti(d, "H"); a.max_tokens = geti(d, "max_tokens");
+  a.y = ptr<__nv_bfloat16>(d, "y");
+}
+
+// One persistent launch for the whole layer: args[i] = {"route": {...}, "gemm1": {...}, "gemm2": {...}, "finish": {...}, "ready": ptr}
+void op_mega_fused(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
+                   uintptr_t stream) {
+  static MegaFusedParams p;   // ~10 KB: kept off the stack; launches are issued by one thread at a time under the GIL
+  p = MegaFusedParams{};
+  p.lay = lay;
+  const int n = (int)args.size();
+  if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
+  for (int i = 0; i < n; ++i) {
+    const py::dict& d = args[i];
+    fill_route(p.r[i].route, d["route"].cast<py::dict>(), sessions[i]);
+    fill_finish(p.r[i].finish, d["finish"].cast<py::dict>(), sessions[i]);
+    fill_gemm(p.r[i].g1, d["gemm1"].cast<py::dict>(), sessions[i]);
+    fill_gemm(p.r[i].g2, d["gemm2"].cast<py::dict>(), sessions[i]);
+    p.r[i].ready = ptr<int>(d, "ready");
+    if (!p.r[i].ready) throw std::invalid_argument("the row-block counter array is required");
+  }
+  check(launch_mega_fused(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_moe launch");
 }
 
 void op_mega_route(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
@@ -62,17 +103,7 @@ void op_mega_route(const WsLayout& lay, const std::vector<py::object>& sessions,
   p.lay = lay;
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
-  for (int i = 0; i < n; ++i) {
-    const py::dict& d = args[i];
-    MegaRouteArgs& a = p.r[i];
-    a.ctx = sessions[i].cast<Session&>().ctx();
-    a.in_off = getl(d, "in_off"); a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K"); a.H = geti(d, "H");
-    a.max_tokens = geti(d, "max_tokens"); a.max_mtiles = geti(d, "max_mtiles");
-    a.a1 = ptr<uint8_t>(d, "a1"); a.a1_sf = ptr<uint8_t>(d, "a1_sf"); a.row_src = ptr<int>(d, "row_src");
-    a.mtile_expert = ptr<int>(d, "mtile_expert"); a.num_mtiles = ptr<int>(d, "num_mtiles");
-    a.expert_rows = ptr<int>(d, "expert_rows"); a.ticket = ptr<int>(d, "ticket");
-    if (a.H % 128 || a.E % a.ctx.world || a.E > kMaxExperts) throw std::invalid_argument("hidden % 128 == 0 and experts % world == 0 are required");
-  }
+  for (int i = 0; i < n; ++i) fill_route(p.r[i], args[i], sessions[i]);
   check(launch_mega_route(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_route launch");
 }
 
@@ -82,14 +113,7 @@ void op_mega_finish(const WsLayout& lay, const std::vector<py::object>& sessions
   p.lay = lay;
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
-  for (int i = 0; i < n; ++i) {
-    const py::dict& d = args[i];
-    MegaFinishArgs& a = p.r[i];
-    a.ctx = sessions[i].cast<Session&>().ctx();
-    a.in_off = getl(d, "in_off"); a.comb_off = getl(d, "comb_off");
-    a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K"); a.H = geti(d, "H"); a.max_tokens = geti(d, "max_tokens");
-    a.y = ptr<__nv_bfloat16>(d, "y");
-  }
+  for (int i = 0; i < n; ++i) fill_finish(p.r[i], args[i], sessions[i]);
   check(launch_mega_finish(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_finish launch");
 }
 }  // namespace
@@ -106,4 +130,5 @@ void bind_mega(py::module_& m) {
   m.def("mega_gemm", &op_mega_gemm);
   m.def("mega_route", &op_mega_route);
   m.def("mega_finish", &op_mega_finish);
+  m.def("mega_fused", &op_mega_fused);
 }

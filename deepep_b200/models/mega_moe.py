@@ -104,7 +104,8 @@ class MegaEngine:
                 a2=torch.empty((self.rows_cap, self.I), **u8), a2_sf=torch.zeros((self.max_mtiles * (self.I // 128) * 512,), **u8),
                 row_src=torch.empty((self.rows_cap,), **i32), mtile_expert=torch.zeros((self.max_mtiles,), **i32),
                 num_mtiles=torch.zeros((1,), **i32), expert_rows=torch.zeros((self.L,), **i32),
-                ticket=torch.zeros((self.L,), **i32), err=torch.zeros((1,), **i32)))
+                ticket=torch.zeros((self.L,), **i32), err=torch.zeros((1,), **i32),
+                ready=torch.zeros((self.max_mtiles,), **i32)))
 
     @staticmethod
     def mega_bytes(C, max_tokens: int, hidden: int, topk: int) -> int:
@@ -121,12 +122,14 @@ class MegaEngine:
         return x, sf, idx, w
 
     def forward(self, ys: Sequence[torch.Tensor], tokens: Sequence[int], l1: Sequence[MegaWeights], l2: Sequence[MegaWeights],
-                stream=None) -> None:
+                stream=None, fused: bool = True) -> None:
+        """Run the layer.  ``fused``: one persistent cooperative kernel (route -> GEMM1 -> GEMM2 -> finish); otherwise
+        the same phases as four launches (kept for debugging and for comparing the two schedules)."""
         C, lay = self.C, self.layout
         s = (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
-        route_args, finish_args = [], []
+        route_args, finish_args, gemm1_args, gemm2_args = [], [], [], []
         for i in range(self.n):
-            sc = self.scratch[i]
+            sc, w1, w2 = self.scratch[i], l1[i], l2[i]
             route_args.append(dict(in_off=self.in_off, T=tokens[i], E=self.E, K=self.K, H=self.H, max_tokens=self.M,
                                    max_mtiles=self.max_mtiles, a1=sc["a1"].data_ptr(), a1_sf=sc["a1_sf"].data_ptr(),
                                    row_src=sc["row_src"].data_ptr(), mtile_expert=sc["mtile_expert"].data_ptr(),
@@ -134,21 +137,26 @@ class MegaEngine:
                                    ticket=sc["ticket"].data_ptr()))
             finish_args.append(dict(in_off=self.in_off, comb_off=self.comb_off, T=tokens[i], E=self.E, K=self.K, H=self.H,
                                     max_tokens=self.M, y=ys[i].data_ptr()))
+            common = dict(mtile_expert=sc["mtile_expert"].data_ptr(), num_mtiles=sc["num_mtiles"].data_ptr(), rows_pad=self.rows_cap,
+                          error_flag=sc["err"].data_ptr())
+            gemm1_args.append(dict(common, a=sc["a1"].data_ptr(), sfa=sc["a1_sf"].data_ptr(), b=w1.packed.data_ptr(),
+                                   sfb=w1.sf_chunks.data_ptr(), k=self.H, b_rows=w1.experts * w1.n, n_total=w1.n, epi=1,
+                                   a2=sc["a2"].data_ptr(), a2_sf=sc["a2_sf"].data_ptr(), inter=self.I))
+            gemm2_args.append(dict(common, a=sc["a2"].data_ptr(), sfa=sc["a2_sf"].data_ptr(), b=w2.packed.data_ptr(),
+                                   sfb=w2.sf_chunks.data_ptr(), k=self.I, b_rows=w2.experts * w2.n, n_total=w2.n, epi=2,
+                                   row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M, topk=self.K,
+                                   hidden=self.H))
+        if fused:
+            blocks = max(1, min(self.gemm_blocks, self.sm_count // self.n))
+            C.mega_fused(lay, self.sessions, [dict(route=route_args[i], finish=finish_args[i], gemm1=gemm1_args[i],
+                                                  gemm2=gemm2_args[i], ready=self.scratch[i]["ready"].data_ptr())
+                                             for i in range(self.n)], blocks, s)
+            return
         aux_blocks = max(1, min(self.sm_count // self.n, 128))
         C.mega_route(lay, self.sessions, route_args, aux_blocks, s)
         for i in range(self.n):
-            sc, w1, w2 = self.scratch[i], l1[i], l2[i]
-            common = dict(mtile_expert=sc["mtile_expert"].data_ptr(), num_mtiles=sc["num_mtiles"].data_ptr(), rows_pad=self.rows_cap,
-                          error_flag=sc["err"].data_ptr())
-            C.mega_gemm(dict(common, a=sc["a1"].data_ptr(), sfa=sc["a1_sf"].data_ptr(), b=w1.packed.data_ptr(),
-                             sfb=w1.sf_chunks.data_ptr(), k=self.H, b_rows=w1.experts * w1.n, n_total=w1.n, epi=1,
-                             a2=sc["a2"].data_ptr(), a2_sf=sc["a2_sf"].data_ptr(), inter=self.I),
-                        self.sessions[i], self.gemm_blocks, s)
-            C.mega_gemm(dict(common, a=sc["a2"].data_ptr(), sfa=sc["a2_sf"].data_ptr(), b=w2.packed.data_ptr(),
-                             sfb=w2.sf_chunks.data_ptr(), k=self.I, b_rows=w2.experts * w2.n, n_total=w2.n, epi=2,
-                             row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M, topk=self.K,
-                             hidden=self.H),
-                        self.sessions[i], self.gemm_blocks, s)
+            C.mega_gemm(gemm1_args[i], self.sessions[i], self.gemm_blocks, s)
+            C.mega_gemm(gemm2_args[i], self.sessions[i], self.gemm_blocks, s)
         C.mega_finish(lay, self.sessions, finish_args, aux_blocks, s)
 
     def check(self) -> None:
@@ -200,7 +208,7 @@ class SymmBuffer:
 
 
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaWeights, sym_buffer: SymmBuffer, *,
-                     batch_size: Optional[int] = None, shared_weights=None, recipe=(1, 1, 32), activation: str = "swiglu",
+                     batch_size: Optional[int] = None, fused: bool = True, shared_weights=None, recipe=(1, 1, 32), activation: str = "swiglu",
                      activation_clamp=None, fast_math: bool = True, timer=None) -> torch.Tensor:
     """Fused MoE forward; overwrites ``y[:bs]`` (bf16 ``[bs, hidden]``) and returns it."""
     del fast_math, timer
@@ -219,7 +227,7 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaW
         raise ValueError("l1 weights do not match the buffer's hidden / intermediate sizes")
     if l1_weights.experts * sym_buffer.world_size != sym_buffer.num_experts:
         raise ValueError("each rank must hold num_experts / world_size experts")
-    sym_buffer.engine.forward([y], [bs], [l1_weights], [l2_weights])
+    sym_buffer.engine.forward([y], [bs], [l1_weights], [l2_weights], fused=fused)
     return y
 
 

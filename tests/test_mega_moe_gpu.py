@@ -44,18 +44,20 @@ def _case(world, tokens, H, I, E, K, seed=0):
         w = [transform_weights_for_mega_moe((l1[0][r * L:(r + 1) * L], l1[1][r * L:(r + 1) * L]),
                                             (l2[0][r * L:(r + 1) * L], l2[1][r * L:(r + 1) * L]), device=dev) for r in range(world)]
         ys = [torch.zeros((t, H), dtype=torch.bfloat16, device=dev) for t in tokens]
-        for rep in range(2):
+        for rep, fused in enumerate((True, False, True)):
             for r, t in enumerate(tokens):
                 x, sf, ti, tw = eng.input_views(r)
                 x[:t].copy_(xs[r][0]); sf[:t].copy_(xs[r][1]); ti[:t].copy_(idx[r].to(torch.int32)); tw[:t].copy_(ws[r])
-            eng.forward(ys, tokens, [a for a, _ in w], [b for _, b in w])
+            for y in ys:
+                y.zero_()
+            eng.forward(ys, tokens, [a for a, _ in w], [b for _, b in w], fused=fused)
             torch.cuda.synchronize()
             eng.check()
             for s in sessions:
                 assert s.status()["code"] == 0, s.status()
             for r in range(world):
                 ok, bad, worst = _mixed_error_ok(ys[r].cpu(), ref[r])
-                assert ok, f"rank {r}: {bad:.4f} of elements off, worst relative error {worst:.4f}"
+                assert ok, f"rank {r} (fused={fused}): {bad:.4f} of elements off, worst relative error {worst:.4f}"
     finally:
         torch.cuda.synchronize()
         for s in sessions:
