@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   __shared__ int s_T[kMaxRanks];
   __shared__ int s_rank_base[kMaxRanks + 1];
   __shared__ int s_off[kMaxExperts];
+  __shared__ int s_base[kMaxExperts];                   // scratch: totals, then per-task row bases
   __shared__ int s_rows;
 
   // ---- A: publish my routing table into every peer (after they consumed the previous one)
@@ -134,11 +135,13 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   // ---- D1: exclusive scans over tiles
   for (int i = gtid; i < P * E; i += gstride) {
     int r = i / E, e = i - r * E, run = 0, nt = (s_T[r] + kChunkTokens - 1) / kChunkTokens;
-    for (int tile = 0; tile < nt; ++tile) {
-      size_t at = ((size_t)r * NT + tile) * E + e;
-      int v = a.hist[at];
-      a.hist[at] = run;
-      run += v;
+    for (int tile0 = 0; tile0 < nt; tile0 += 8) {       // loads of a batch first, then the in-place exclusive prefix
+      int v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = tile0 + j < nt ? a.hist[((size_t)r * NT + tile0 + j) * E + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (tile0 + j < nt) { a.hist[((size_t)r * NT + tile0 + j) * E + e] = run; run += v[j]; }
     }
     a.cnt[i] = run;
   }
@@ -153,11 +156,16 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   grid.sync();
 
   // ---- D2: expert row offsets of every rank (each block keeps its own copy in shared memory)
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0;
+    for (int r = 0; r < P; ++r) tot += a.cnt[r * E + e];
+    s_base[e] = tot;                                      // total rows of expert e (all sources)
+  }
+  __syncthreads();
   if (threadIdx.x < P) {
     int d = threadIdx.x, run = 0;
     for (int l = 0; l < Lx; ++l) {
-      int e = d * Lx + l, tot = 0;
-      for (int r = 0; r < P; ++r) tot += a.cnt[r * E + e];
+      int e = d * Lx + l, tot = s_base[e];
       s_off[e] = run;
       if (d == me && blockIdx.x == 0) { a.expert_counts[l] = tot; a.expert_offsets[l] = run; }
       run += a.expand ? (tot + a.alignment - 1) / a.alignment * a.alignment : tot;
@@ -193,12 +201,20 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
     if (tile * kChunkTokens >= T_r) continue;
     const int* gidx_r = gidx + (size_t)r * Tmax * K;
     build_masks(s_m, gidx_r, tile, T_r, K, E, Lx);
+    {   // rows of expert e that precede this (source, tile): earlier sources + earlier tiles of this source
+      const int* hist_task = a.hist + (size_t)task * E;
+      for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int b = hist_task[e];
+        for (int q = 0; q < r; ++q) b += a.cnt[q * E + e];
+        s_base[e] = b;
+      }
+      __syncthreads();
+    }
     int tl = threadIdx.x, t = tile * kChunkTokens + tl;
     if (tl < kChunkTokens && t < T_r) {
       int row[kMaxTopk];
 #pragma unroll
       for (int k = 0; k < kMaxTopk; ++k) row[k] = k < K ? __ldcg(gidx_r + (size_t)t * K + k) : -1;
-      const int* hist_rt = a.hist + (size_t)task * E;
       const bool hit_me = (s_m.rank[me][tl >> 5] >> (tl & 31)) & 1u;
       if (hit_me) {
         int j = a.chunk_start[r * (NT + 1) + tile] + below(s_m.rank[me], tl);
@@ -208,9 +224,8 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
         if (a.expand) {
           for (int k = 0; k < K; ++k) {
             if (!slot_counts(row, k, E) || row[k] / Lx != me) continue;
-            int e = row[k], base = 0;
-            for (int q = 0; q < r; ++q) base += a.cnt[q * E + e];
-            int out_row = s_off[e] + base + hist_rt[e] + below(s_m.expert[e], tl);
+            int e = row[k];
+            int out_row = s_off[e] + s_base[e] + below(s_m.expert[e], tl);
             rec[2 + n++] = out_row | (k << kRowSlotShift);
             if (out_row < a.rcap) {
               a.recv_row_src[out_row] = (r * Tmax + t) * K + k;
@@ -243,9 +258,8 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
         for (int k = 0; k < K; ++k) {
           int v = -1;
           if (a.expand && slot_counts(row, k, E)) {
-            int e = row[k], base = 0;
-            for (int q = 0; q < me; ++q) base += a.cnt[q * E + e];
-            v = s_off[e] + base + hist_rt[e] + below(s_m.expert[e], tl);
+            int e = row[k];     // r == me here, so s_base already holds this rank's base
+            v = s_off[e] + s_base[e] + below(s_m.expert[e], tl);
           }
           a.slot_row[(size_t)t * K + k] = v;
         }
