@@ -34,6 +34,7 @@ struct MegaGemmParams {
   const uint8_t* sfa;        // chunked scales of A
   const uint8_t* sfb;        // chunked scales of B
   const int* mtile_expert;   // [max_mtiles] local expert of each 128-row tile
+  const int* a_ready;        // optional: rows of each tile of A in place so far; a tile's loads start at 128
   const int* num_mtiles;     // device scalar: tiles in use
   int max_mtiles, n_tiles, k_steps, n_total;
   int epi, b_tx_bytes;
@@ -71,7 +72,8 @@ struct MegaRouteArgs {
   int* mtile_expert;           // [max_mtiles]
   int* num_mtiles;             // [1]
   int* expert_rows;            // [L] rows per local expert
-  int* ticket;                 // [L] scratch: rows handed out so far
+  int* expert_list;            // [L][world * max_tokens] scratch: routed slots of each local expert
+  int* pulled;                 // optional [max_mtiles]: rows of each tile in place so far (zeroed by the caller)
 };
 struct MegaRouteParams { WsLayout lay; MegaRouteArgs r[kMaxRanks]; };
 cudaError_t launch_mega_route(const MegaRouteParams& p, int nranks, int blocks, cudaStream_t stream);

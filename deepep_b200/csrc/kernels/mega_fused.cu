@@ -19,16 +19,28 @@
 
 namespace dep {
 
-__global__ void __launch_bounds__(kGemmThreads, 1) mega_moe_kernel(const __grid_constant__ MegaFusedParams p) {
+constexpr int kPullWarps = 2;                                    // warps beside the GEMM roles that pull tokens from peers
+constexpr int kFusedThreads = kGemmThreads + kPullWarps * 32;
+
+__global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid_constant__ MegaFusedParams p) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ RouteShared sh;
   cg::grid_group grid = cg::this_grid();
   const MegaFusedArgs& a = p.r[blockIdx.y];
   if (blockIdx.x == 0)
-    for (int i = threadIdx.x; i < a.route.max_mtiles; i += blockDim.x) a.ready[i] = 0;
-  route_phase(a.route, grid);
+    for (int i = threadIdx.x; i < a.route.max_mtiles; i += blockDim.x) { a.ready[i] = 0; a.route.pulled[i] = 0; }
+  route_layout_phase(a.route, grid, sh);          // handshake, counts, tile layout (grid barriers inside)
   __threadfence();
   grid.sync();
-  gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x);
+  // The token pull overlaps the GEMMs: rows are pulled tile by tile, a GEMM1 tile starts once its rows have arrived.
+  const int warp = threadIdx.x >> 5;
+  if (warp < kGemmThreads / 32) {
+    gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x);
+  } else {
+    __syncthreads();                               // pairs with the set-up barrier inside gemm_phase
+    route_pull_phase(a.route, sh, blockIdx.x * kPullWarps + (warp - kGemmThreads / 32), gridDim.x * kPullWarps);
+    __syncthreads();                               // pairs with the tear-down barrier inside gemm_phase
+  }
   __threadfence_system();
   grid.sync();
   finish_phase(a.finish, true);
@@ -42,7 +54,7 @@ cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, 
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  dim3 grid(blocks, nranks), block(kGemmThreads);
+  dim3 grid(blocks, nranks), block(kFusedThreads);
   void* args[] = {const_cast<MegaFusedParams*>(&p)};
   return cudaLaunchCooperativeKernel((const void*)mega_moe_kernel, grid, block, args, smem, stream);
 }

@@ -135,6 +135,9 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         if (second && ready) {
           if (!wait_rows_ready(ready + mt, g1.n_tiles, failed)) break;
           fence_proxy_async();          // rows written by other SMs' stores are about to be read by the copy engine
+        } else if (!second && p.a_ready) {
+          if (!wait_rows_ready(p.a_ready + mt, kGemmBM, failed)) break;
+          fence_proxy_async();
         }
         for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
           const int s = it % stages;

@@ -4,7 +4,7 @@
 // tables straight from peer memory, counts the rows of its local experts, lays the experts out
 // as 128-row tiles, and pulls the e4m3 token rows and their ue8m0 scales from the owners'
 // symmetric input blocks into expert-major operands (scales in the tensor-memory chunk layout).
-// Row order inside an expert is arbitrary (atomic tickets): rows are independent in the GEMMs
+// Row order inside an expert is arbitrary (arrival order of an atomic counter): rows are independent in the GEMMs
 // and the final reduction is ordered by top-k slot at the source, so results stay deterministic.
 //
 // mega_finish: tells the peers that this rank's GEMM2 rows have been written, waits for the
@@ -38,18 +38,26 @@ __host__ __device__ inline MegaInput mega_input_layout(int M, int H, int K) {
 }
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void route_phase(const MegaRouteArgs& a, cg::grid_group& grid) {
+struct RouteShared {
+  int T[kMaxRanks];          // tokens of every rank
+  int base[kMaxExperts];     // first row of every local expert (multiple of 128)
+  int rows[kMaxExperts];     // rows of every local expert
+  int alive, total_rows;
+};
+
+constexpr int kPullChunk = 8;   // consecutive rows one warp pulls before it moves on
+
+// Handshake, per-expert entry lists, 128-row tile layout (tile -> expert).
+// expert_list[l * cap + j] (cap = world * max_tokens) = source * M * K + token * K + slot of the j-th routed slot of
+// local expert l, in arrival order.
+__device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::grid_group& grid, RouteShared& sh) {
   const RankCtx& ctx = a.ctx;
-  const int P = ctx.world, me = ctx.rank, K = a.K, H = a.H, E = a.E, Lx = E / P, M = a.max_tokens;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int P = ctx.world, me = ctx.rank, K = a.K, E = a.E, Lx = E / P, M = a.max_tokens;
   const int gtid = blockIdx.x * (int)blockDim.x + threadIdx.x, gstride = gridDim.x * (int)blockDim.x;
-  const int gw = blockIdx.x * ((int)blockDim.x / 32) + warp, total_warps = gridDim.x * ((int)blockDim.x / 32);
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpMega] + 1;
-  const MegaInput in = mega_input_layout(M, H, K);
-
-  __shared__ int s_T[kMaxRanks];
-  __shared__ int s_base[kMaxExperts];   // first row of every local expert (multiple of 128)
+  const MegaInput in = mega_input_layout(M, a.H, K);
+  const int cap = P * M;
 
   // ---- handshake: my inputs are in place (stream order), tell everybody, wait for everybody
   if (blockIdx.x == 0 && threadIdx.x < P) {
@@ -62,19 +70,24 @@ __device__ __forceinline__ void route_phase(const MegaRouteArgs& a, cg::grid_gro
   if (threadIdx.x < P) ok = wait_flag_ge(&ctl->mega_flag[threadIdx.x][0], epoch, ctx, kOpMega, 0, threadIdx.x);
   const int alive = __syncthreads_and(ok);
   if (threadIdx.x < kMaxRanks)
-    s_T[threadIdx.x] = (alive && threadIdx.x < P) ? __ldcg(reinterpret_cast<const int*>(ctx.ws[threadIdx.x] + a.in_off + in.hdr)) : 0;
+    sh.T[threadIdx.x] = (alive && threadIdx.x < P) ? __ldcg(reinterpret_cast<const int*>(ctx.ws[threadIdx.x] + a.in_off + in.hdr)) : 0;
+  if (threadIdx.x == 0) sh.alive = alive;
   // zero the per-expert counters
   if (blockIdx.x == 0) for (int l = threadIdx.x; l < Lx; l += (int)blockDim.x) a.expert_rows[l] = 0;
   __syncthreads();
   grid.sync();
 
-  // ---- pass 1: rows per local expert
-  for (int r = 0; r < P; ++r) {
+  // ---- pass 1: the routed slots of every local expert (own rank first, then the peers in ring order)
+  for (int r0 = 0; r0 < P; ++r0) {
+    const int r = (me + r0) % P;
     const int* idx = reinterpret_cast<const int*>(ctx.ws[r] + a.in_off + in.idx);
-    const int n = s_T[r] * K;
+    const int n = sh.T[r] * K;
     for (int i = gtid; i < n; i += gstride) {
       const int e = __ldcg(idx + i);
-      if (e >= me * Lx && e < (me + 1) * Lx) atomicAdd(&a.expert_rows[e - me * Lx], 1);
+      if (e >= me * Lx && e < (me + 1) * Lx) {
+        const int j = atomicAdd(&a.expert_rows[e - me * Lx], 1);
+        if (j < cap) a.expert_list[(size_t)(e - me * Lx) * cap + j] = r * M * K + i;
+      }
     }
   }
   __threadfence();
@@ -84,58 +97,67 @@ __device__ __forceinline__ void route_phase(const MegaRouteArgs& a, cg::grid_gro
   if (threadIdx.x == 0) {
     int run = 0;
     for (int l = 0; l < Lx; ++l) {
-      s_base[l] = run;
-      const int tiles = (a.expert_rows[l] + kGemmBM - 1) / kGemmBM;
+      const int c = min(__ldcg(a.expert_rows + l), cap);
+      sh.base[l] = run;
+      sh.rows[l] = c;
+      const int tiles = (c + kGemmBM - 1) / kGemmBM;
       if (blockIdx.x == 0)
         for (int t = 0; t < tiles && run / kGemmBM + t < a.max_mtiles; ++t) a.mtile_expert[run / kGemmBM + t] = l;
       run += tiles * kGemmBM;
     }
-    if (blockIdx.x == 0) *a.num_mtiles = min(run / kGemmBM, a.max_mtiles);
+    sh.total_rows = min(run, a.max_mtiles * kGemmBM);
+    if (blockIdx.x == 0) *a.num_mtiles = sh.total_rows / kGemmBM;
   }
   __syncthreads();
-  const int rows_cap = a.max_mtiles * kGemmBM;
-  // padding rows carry no source; their payload is never read back (tile rows are independent in the GEMMs)
-  for (int l = blockIdx.x; l < Lx; l += gridDim.x) {
-    const int c = a.expert_rows[l], end = (c + kGemmBM - 1) / kGemmBM * kGemmBM;
-    for (int rr = c + threadIdx.x; rr < end; rr += (int)blockDim.x)
-      if (s_base[l] + rr < rows_cap) a.row_src[s_base[l] + rr] = -1;
-  }
-  int* ticket = a.ticket;   // zeroed by the previous call's pass 2 epilogue (and at allocation)
-
-  // ---- pass 2: hand out rows and pull the tokens (one warp per routed slot)
-  if (alive) {
-    for (int r0 = 0; r0 < P; ++r0) {
-      const int r = (me + r0) % P;
-      const uint8_t* peer = ctx.ws[r] + a.in_off;
-      const int* idx = reinterpret_cast<const int*>(peer + in.idx);
-      const int n = s_T[r] * K;
-      for (int i0 = gw * 32; i0 < n; i0 += total_warps * 32) {
-        const int i = i0 + lane;
-        const int e = i < n ? __ldcg(idx + i) : -1;
-        const bool mine = e >= me * Lx && e < (me + 1) * Lx;
-        int my_row = -1;
-        if (mine) my_row = s_base[e - me * Lx] + atomicAdd(&ticket[e - me * Lx], 1);
-        unsigned todo = __ballot_sync(0xffffffffu, mine && my_row < rows_cap);
-        while (todo) {
-          const int src_lane = __ffs(todo) - 1;
-          todo &= todo - 1;
-          const long long row = __shfl_sync(0xffffffffu, my_row, src_lane);
-          const int slot_i = i0 + src_lane, t = slot_i / K;
-          const int4* from = reinterpret_cast<const int4*>(peer + in.x + (size_t)t * H);
-          int4* to = reinterpret_cast<int4*>(a.a1 + row * H);
-          { int4* one[1] = {to}; warp_copy_row<14>(one, 1, from, H / 16, lane); }
-          const uint32_t* sf = reinterpret_cast<const uint32_t*>(peer + in.x_sf + (size_t)t * (H / 32));
-          for (int g = lane; g < H / 128; g += 32)
-            *reinterpret_cast<uint32_t*>(a.a1_sf + sf_offset(row, (long long)g * 128, H)) = __ldcg(sf + g);
-          if (lane == 0) a.row_src[row] = (r * M + t) * K + (slot_i - t * K);
-        }
-      }
-    }
-  }
-  grid.sync();
-  if (blockIdx.x == 0) for (int l = threadIdx.x; l < Lx; l += (int)blockDim.x) ticket[l] = 0;   // ready for the next call
 }
 
+// Pulls the routed tokens from their owners in row order (tile by tile, so that the first tiles are complete first);
+// warp `gw` of `total_warps` warps.  Padding rows get row_src = -1; their payload is never read back (tile rows are
+// independent in the GEMMs).
+__device__ __forceinline__ void route_pull_phase(const MegaRouteArgs& a, const RouteShared& sh, int gw, int total_warps) {
+  const RankCtx& ctx = a.ctx;
+  const int P = ctx.world, K = a.K, H = a.H, M = a.max_tokens;
+  const int lane = threadIdx.x & 31;
+  const MegaInput in = mega_input_layout(M, H, K);
+  const int cap = P * M;
+  if (!sh.alive) return;
+  for (int row0 = gw * kPullChunk; row0 < sh.total_rows; row0 += total_warps * kPullChunk) {
+    // lane j < kPullChunk looks up row row0 + j
+    int entry = -1;
+    if (lane < kPullChunk && row0 + lane < sh.total_rows) {
+      const int row = row0 + lane, l = __ldcg(a.mtile_expert + row / kGemmBM), j = row - sh.base[l];
+      if (j < sh.rows[l]) entry = __ldcg(a.expert_list + (size_t)l * cap + j);
+      a.row_src[row] = entry;
+    }
+#pragma unroll 1
+    for (int c = 0; c < kPullChunk; ++c) {
+      const int en = __shfl_sync(0xffffffffu, entry, c);
+      if (en < 0) continue;
+      const long long row = row0 + c;
+      const int r = en / (M * K), t = (en - r * M * K) / K;
+      const uint8_t* peer = ctx.ws[r] + a.in_off;
+      const int4* from = reinterpret_cast<const int4*>(peer + in.x + (size_t)t * H);
+      int4* to = reinterpret_cast<int4*>(a.a1 + row * H);
+      { int4* one[1] = {to}; warp_copy_row<14>(one, 1, from, H / 16, lane); }
+      const uint32_t* sf = reinterpret_cast<const uint32_t*>(peer + in.x_sf + (size_t)t * (H / 32));
+      for (int g = lane; g < H / 128; g += 32)
+        *reinterpret_cast<uint32_t*>(a.a1_sf + sf_offset(row, (long long)g * 128, H)) = __ldcg(sf + g);
+    }
+    if (a.pulled) {            // tell the GEMM that these rows of the tile (payload or padding mark) are in place
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(a.pulled + row0 / kGemmBM, min(kPullChunk, sh.total_rows - row0));
+    }
+  }
+}
+
+// The whole routing step as one phase (all warps of the grid pull).
+__device__ __forceinline__ void route_phase(const MegaRouteArgs& a, cg::grid_group& grid) {
+  __shared__ RouteShared sh;
+  route_layout_phase(a, grid, sh);
+  const int warps = (int)blockDim.x / 32;
+  route_pull_phase(a, sh, blockIdx.x * warps + (threadIdx.x >> 5), gridDim.x * warps);
+}
 
 __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_epoch) {
   const RankCtx& ctx = a.ctx;

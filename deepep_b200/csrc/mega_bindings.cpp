@@ -37,6 +37,7 @@ void fill_gemm(MegaGemmParams& p, const py::dict& d, py::object session) {
   if (!encode_operand_map(&p.tmap_b, ptr<const void>(d, "b"), b_rows * (k / kGemmBK), kGemmBK, true, &err)) throw std::runtime_error(err);
   p.sfa = ptr<const uint8_t>(d, "sfa"); p.sfb = ptr<const uint8_t>(d, "sfb");
   p.mtile_expert = ptr<const int>(d, "mtile_expert"); p.num_mtiles = ptr<const int>(d, "num_mtiles");
+  p.a_ready = ptr<const int>(d, "a_ready");
   p.max_mtiles = (int)(rows_pad / kGemmBM);
   p.n_total = geti(d, "n_total"); p.n_tiles = p.n_total / kGemmBN; p.k_steps = (int)(k / kGemmBK);
   if (p.n_total % kGemmBN) throw std::invalid_argument("output width must be a multiple of 256");
@@ -66,7 +67,8 @@ void fill_route(MegaRouteArgs& a, const py::dict& d, py::object session) {
   a.max_tokens = geti(d, "max_tokens"); a.max_mtiles = geti(d, "max_mtiles");
   a.a1 = ptr<uint8_t>(d, "a1"); a.a1_sf = ptr<uint8_t>(d, "a1_sf"); a.row_src = ptr<int>(d, "row_src");
   a.mtile_expert = ptr<int>(d, "mtile_expert"); a.num_mtiles = ptr<int>(d, "num_mtiles");
-  a.expert_rows = ptr<int>(d, "expert_rows"); a.ticket = ptr<int>(d, "ticket");
+  a.expert_rows = ptr<int>(d, "expert_rows"); a.expert_list = ptr<int>(d, "expert_list");
+  a.pulled = ptr<int>(d, "pulled");
   if (a.H % 128 || a.E % a.ctx.world || a.E > kMaxExperts) throw std::invalid_argument("hidden % 128 == 0 and experts % world == 0 are required");
 }
 
@@ -92,7 +94,7 @@ void op_mega_fused(const WsLayout& lay, const std::vector<py::object>& sessions,
     fill_gemm(p.r[i].g1, d["gemm1"].cast<py::dict>(), sessions[i]);
     fill_gemm(p.r[i].g2, d["gemm2"].cast<py::dict>(), sessions[i]);
     p.r[i].ready = ptr<int>(d, "ready");
-    if (!p.r[i].ready) throw std::invalid_argument("the row-block counter array is required");
+    if (!p.r[i].ready || !p.r[i].route.pulled) throw std::invalid_argument("the fused kernel needs the ready and pulled counter arrays");
   }
   check(launch_mega_fused(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_moe launch");
 }

@@ -104,8 +104,8 @@ class MegaEngine:
                 a2=torch.empty((self.rows_cap, self.I), **u8), a2_sf=torch.zeros((self.max_mtiles * (self.I // 128) * 512,), **u8),
                 row_src=torch.empty((self.rows_cap,), **i32), mtile_expert=torch.zeros((self.max_mtiles,), **i32),
                 num_mtiles=torch.zeros((1,), **i32), expert_rows=torch.zeros((self.L,), **i32),
-                ticket=torch.zeros((self.L,), **i32), err=torch.zeros((1,), **i32),
-                ready=torch.zeros((self.max_mtiles,), **i32)))
+                expert_list=torch.empty((self.L * self.world * self.M,), **i32), err=torch.zeros((1,), **i32),
+                ready=torch.zeros((self.max_mtiles,), **i32), pulled=torch.zeros((self.max_mtiles,), **i32)))
 
     @staticmethod
     def mega_bytes(C, max_tokens: int, hidden: int, topk: int) -> int:
@@ -134,7 +134,7 @@ class MegaEngine:
                                    max_mtiles=self.max_mtiles, a1=sc["a1"].data_ptr(), a1_sf=sc["a1_sf"].data_ptr(),
                                    row_src=sc["row_src"].data_ptr(), mtile_expert=sc["mtile_expert"].data_ptr(),
                                    num_mtiles=sc["num_mtiles"].data_ptr(), expert_rows=sc["expert_rows"].data_ptr(),
-                                   ticket=sc["ticket"].data_ptr()))
+                                   expert_list=sc["expert_list"].data_ptr()))
             finish_args.append(dict(in_off=self.in_off, comb_off=self.comb_off, T=tokens[i], E=self.E, K=self.K, H=self.H,
                                     max_tokens=self.M, y=ys[i].data_ptr()))
             common = dict(mtile_expert=sc["mtile_expert"].data_ptr(), num_mtiles=sc["num_mtiles"].data_ptr(), rows_pad=self.rows_cap,
@@ -147,6 +147,10 @@ class MegaEngine:
                                    row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M, topk=self.K,
                                    hidden=self.H))
         if fused:
+            for i in range(self.n):    # the fused kernel overlaps the pull with the GEMMs through per-tile counters
+                sc = self.scratch[i]
+                route_args[i]["pulled"] = sc["pulled"].data_ptr()
+                gemm1_args[i]["a_ready"] = sc["pulled"].data_ptr()
             blocks = max(1, min(self.gemm_blocks, self.sm_count // self.n))
             C.mega_fused(lay, self.sessions, [dict(route=route_args[i], finish=finish_args[i], gemm1=gemm1_args[i],
                                                   gemm2=gemm2_args[i], ready=self.scratch[i]["ready"].data_ptr())
