@@ -160,6 +160,7 @@ void op_barrier(const std::vector<py::object>& sessions, uintptr_t stream) {
 
 void bind_low_latency(py::module_& m);
 void bind_mega(py::module_& m);
+void bind_gmm(py::module_& m);
 
 PYBIND11_MODULE(_C, m) {
   m.attr("runtime_protocol") = 1;
@@ -227,4 +228,5 @@ PYBIND11_MODULE(_C, m) {
   m.def("barrier", &op_barrier);
   bind_low_latency(m);
   bind_mega(m);
+  bind_gmm(m);
 }

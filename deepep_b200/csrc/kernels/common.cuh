@@ -29,7 +29,7 @@ constexpr int kRowMask = (1 << kRowSlotShift) - 1;
 
 enum Op : int {
   kOpBarrier = 0, kOpNotify = 1, kOpDispatch = 2, kOpCombine = 3, kOpLLDispatch = 4, kOpLLCombine = 5,
-  kOpMega = 6, kNumOps = 8
+  kOpMega = 6, kOpA2avGmm = 7, kOpGmmA2av = 8, kNumOps = 12
 };
 
 enum Status : int { kStatusOk = 0, kStatusTimeout = 1, kStatusBadArgument = 2, kStatusAborted = 3 };
@@ -62,6 +62,7 @@ struct Control {
   unsigned long long ll_disp_ack[kMaxRanks];
   unsigned long long ll_comb_ack[kMaxRanks];
   unsigned long long mega_flag[kMaxRanks][4];
+  unsigned long long gmm_flag[kMaxRanks][4];   // a2av_gmm: staged, pulled; gmm_a2av: ready, pushed
   unsigned long long disp_chunk[kMaxRanks][kMaxChunks];
   unsigned long long comb_chunk[kMaxRanks][kMaxChunks];
   // diagnostics: where a pipeline wait gave up (warp-indexed records of 4 words)
