@@ -68,6 +68,10 @@ void op(const WsLayout& lay, const std::vector<py::object>& sessions, const std:
 }  // namespace
 
 void bind_gmm(py::module_& m) {
+  m.def("gmm_region_offsets", [](long long max_rows, long long max_k, long long max_n) {
+    const GmmRegion g = gmm_region(max_rows, max_k, max_n);
+    return std::vector<long long>{g.table_a, g.table_b, g.stage, g.recv, g.total};
+  });
   m.def("gmm_region_bytes", [](long long max_rows, long long max_k, long long max_n) { return gmm_region(max_rows, max_k, max_n).total; });
   m.def("a2av_gmm", [](const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
                        uintptr_t stream) { op(lay, sessions, args, blocks, stream, true); });

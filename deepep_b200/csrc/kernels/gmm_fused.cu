@@ -30,17 +30,22 @@ namespace dep {
 
 constexpr int kGmmGemmThreads = 320;                     // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kGmmPullWarps = 2;
-constexpr int kGmmStages = 3;
+constexpr int kGmmMaxStages = 4;
 constexpr int kGmmTileA = kGmmBM * kGmmBK * 2;           // 16 KB
 constexpr int kGmmBoxB = 64 * kGmmBK * 2;                // 8 KB: 64 K-rows of 64 N-values
 constexpr int kGmmTileB = (kGmmBN / 64) * kGmmBoxB;      // 32 KB
 constexpr int kGmmStageBytes = kGmmTileA + kGmmTileB;
 constexpr int kGmmEpiBytes = 8 * 32 * (kGmmBN / 2) * 2;  // bf16 staging: each epilogue warp parks its 32 x 128 block
 constexpr int kGmmPullChunk = 8;
-constexpr size_t kGmmSmemBytes = 1024 + (size_t)kGmmStages * kGmmStageBytes + kGmmEpiBytes + 256;
+// Rows pushed to a peer are first parked in shared memory so that they leave as 256-byte segments (3 stages + staging);
+// rows stored locally go straight from registers (4 stages, no staging).
+__host__ __device__ constexpr int gmm_stages(bool push) { return push ? 3 : 4; }
+__host__ __device__ constexpr size_t gmm_smem_bytes(bool push) {
+  return 1024 + (size_t)gmm_stages(push) * kGmmStageBytes + (push ? kGmmEpiBytes : 0) + 256;
+}
 
 struct GmmBarriers {
-  uint64_t full[kGmmStages], empty[kGmmStages], acc_full[2], acc_empty[2];
+  uint64_t full[kGmmMaxStages], empty[kGmmMaxStages], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int failed;
 };
@@ -189,8 +194,9 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
                                           int cta, int num_ctas) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
+  constexpr int kGmmStages = gmm_stages(kPush);
   uint8_t* epi_smem = tiles + (size_t)kGmmStages * kGmmStageBytes;
-  GmmBarriers* bars = reinterpret_cast<GmmBarriers*>(epi_smem + kGmmEpiBytes);
+  GmmBarriers* bars = reinterpret_cast<GmmBarriers*>(epi_smem + (kPush ? kGmmEpiBytes : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int P = a.ctx.world;
 
@@ -291,6 +297,32 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
       if (!bounded_wait(&bars->acc_full[b], (local_tile >> 1) & 1u, failed)) break;
       umma::fence_after_sync();
       const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + b * kGmmBN + part * kCols;
+      if (!kPush) {
+        // each thread stores its row's columns straight from registers: 64 contiguous bytes per 32 columns
+        uint32_t v[32];
+        for (int c = 0; c < kCols; c += 32) {
+          umma::tmem_ld32(taddr + c, v);
+          umma::tmem_ld_wait();
+          const int col = nb * kGmmBN + part * kCols + c;
+          if (dst_row && col < a.N) {
+            uint4* dst = reinterpret_cast<uint4*>(dst_row + (size_t)(part * kCols + c) * 2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t w0[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                w0[j] = *reinterpret_cast<uint32_t*>(&b0);
+              }
+              dst[i] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+            }
+          }
+        }
+        umma::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
+        continue;
+      }
       // 1) drain this warp's 32 x 128 block into shared memory as bf16 and hand the accumulator back
       uint4* mine = reinterpret_cast<uint4*>(stage + (size_t)lane * kCols * 2);   // 256 B per row = 16 pieces
       __syncwarp();                                     // the previous tile's block has been written out
@@ -362,7 +394,9 @@ __global__ void __launch_bounds__(kGmmGemmThreads + kGmmPullWarps * 32, 1) a2av_
   int ok = 1;
   if (threadIdx.x < P) ok = wait_flag_ge(&ctl->gmm_flag[threadIdx.x][1], epoch - 1, ctx, kOpA2avGmm, 0, threadIdx.x);
   int alive = __syncthreads_and(ok);
-  if (alive) rank_copy(ctx.ws[me] + a.data_off, a.x, (size_t)a.rows_in * a.K * 2);
+  // x that already lives in the stage area (a view handed out by the host API) needs no copy
+  if (alive && reinterpret_cast<const uint8_t*>(a.x) != ctx.ws[me] + a.data_off)
+    rank_copy(ctx.ws[me] + a.data_off, a.x, (size_t)a.rows_in * a.K * 2);
   if (blockIdx.x == 0) {
     if (warp == 0) publish_table(a, reinterpret_cast<int*>(ctx.ws[me] + a.table_off), a.rows_in, lane);
     for (int i = threadIdx.x; i < a.max_tiles; i += (int)blockDim.x) a.pulled[i] = 0;
@@ -425,22 +459,24 @@ __global__ void __launch_bounds__(kGmmGemmThreads, 1) gmm_a2av_kernel(const __gr
   if (threadIdx.x < P) ok = wait_flag_ge(&ctl->gmm_flag[threadIdx.x][3], epoch, ctx, kOpGmmA2av, 1, threadIdx.x);
   alive = __syncthreads_and(ok) && alive;
   const int my_rows = min(__ldcg(table), a.out_rows_cap);
-  if (alive) rank_copy(a.out, ctx.ws[me] + a.data_off, (size_t)my_rows * a.N * 2);
+  // an output tensor that is a view of the receive area already holds the rows
+  if (alive && reinterpret_cast<uint8_t*>(a.out) != ctx.ws[me] + a.data_off)
+    rank_copy(a.out, ctx.ws[me] + a.data_off, (size_t)my_rows * a.N * 2);
   if (blockIdx.x == 0 && threadIdx.x == 0) ctl->epoch[kOpGmmA2av] = epoch;
 }
 
-static cudaError_t launch(const void* fn, int threads, const GmmParams& p, int nranks, int blocks, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGmmSmemBytes);
+static cudaError_t launch(const void* fn, int threads, size_t smem, const GmmParams& p, int nranks, int blocks, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid(blocks, nranks), block(threads);
   void* args[] = {const_cast<GmmParams*>(&p)};
-  return cudaLaunchCooperativeKernel(fn, grid, block, args, kGmmSmemBytes, stream);
+  return cudaLaunchCooperativeKernel(fn, grid, block, args, smem, stream);
 }
 cudaError_t launch_a2av_gmm(const GmmParams& p, int nranks, int blocks, cudaStream_t stream) {
-  return launch((const void*)a2av_gmm_kernel, kGmmGemmThreads + kGmmPullWarps * 32, p, nranks, blocks, stream);
+  return launch((const void*)a2av_gmm_kernel, kGmmGemmThreads + kGmmPullWarps * 32, gmm_smem_bytes(false), p, nranks, blocks, stream);
 }
 cudaError_t launch_gmm_a2av(const GmmParams& p, int nranks, int blocks, cudaStream_t stream) {
-  return launch((const void*)gmm_a2av_kernel, kGmmGemmThreads, p, nranks, blocks, stream);
+  return launch((const void*)gmm_a2av_kernel, kGmmGemmThreads, gmm_smem_bytes(true), p, nranks, blocks, stream);
 }
 
 bool encode_bf16_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows, const char** error) {

@@ -101,6 +101,25 @@ class GmmEngine:
     def region_bytes(C, max_rows: int, max_k: int, max_n: int) -> int:
         return int(C.gmm_region_bytes(max_rows, max_k, max_n))
 
+    def symmetric_input(self, i: int, rows: int, k: int) -> torch.Tensor:
+        """bf16 ``[rows, k]`` view of rank slot ``i``'s stage area: an ``x`` written here is read by the peers in place."""
+        from ..models.mega_moe import _view
+
+        if rows > self.max_rows or k > self.max_k:
+            raise ValueError("the view exceeds the sizes the group was initialised with")
+        off = self.layout.mega + self.C.gmm_region_offsets(self.max_rows, self.max_k, self.max_n)[2]
+        return _view(self.sessions[i].workspace + off, rows * k * 2, self.device).view(torch.bfloat16).view(rows, k)
+
+    def symmetric_output(self, i: int, rows: int, n: int) -> torch.Tensor:
+        """bf16 ``[rows, n]`` view of rank slot ``i``'s receive area: ``gmm_a2av`` into it needs no final copy.  The rows
+        are overwritten by the next ``gmm_a2av`` call of any rank."""
+        from ..models.mega_moe import _view
+
+        if rows > self.max_rows or n > self.max_n:
+            raise ValueError("the view exceeds the sizes the group was initialised with")
+        off = self.layout.mega + self.C.gmm_region_offsets(self.max_rows, self.max_k, self.max_n)[3]
+        return _view(self.sessions[i].workspace + off, rows * n * 2, self.device).view(torch.bfloat16).view(rows, n)
+
     def _gathered(self, i: int, rows: int, k: int) -> torch.Tensor:
         buf = self.scratch[i]["gathered"]
         if buf is None or buf.numel() < rows * k:
@@ -213,6 +232,24 @@ def get_config() -> GmmConfig:
 
 
 init_udma_group, destroy_udma_group, get_udma_config = init_group, destroy_group, get_config
+
+
+def symmetric_input(rows: int, k: int) -> torch.Tensor:
+    """bf16 ``[rows, k]`` view of this rank's staged-input area.  Passing it as ``x`` to :func:`alltoallv_gmm` skips
+    the staging copy (the peers read it in place).  CPU engine: an ordinary tensor."""
+    get_config()
+    if _GROUP.engine is None:
+        return torch.empty((rows, k), dtype=torch.bfloat16)
+    return _GROUP.engine.symmetric_input(0, rows, k)
+
+
+def symmetric_output(rows: int, n: int) -> torch.Tensor:
+    """bf16 ``[rows, n]`` view of this rank's returned-rows area.  Passing it as ``out`` to :func:`gmm_alltoallv` skips
+    the final copy; it stays valid until the next :func:`gmm_alltoallv` call.  CPU engine: an ordinary tensor."""
+    get_config()
+    if _GROUP.engine is None:
+        return torch.empty((rows, n), dtype=torch.bfloat16)
+    return _GROUP.engine.symmetric_output(0, rows, n)
 
 
 def load_tiling_config(path=None) -> Mapping[str, int]:
@@ -341,4 +378,4 @@ grouped_matmul_all_to_allv = gmm_alltoallv
 
 __all__ = ["GmmConfig", "GmmEngine", "all_to_allv_grouped_matmul", "alltoallv_gmm", "destroy_group", "destroy_udma_group",
            "get_config", "get_udma_config", "gmm_alltoallv", "grouped_matmul_all_to_allv", "init_group", "init_udma_group",
-           "load_tiling_config", "reference_alltoallv_gmm", "reference_gmm_alltoallv"]
+           "load_tiling_config", "reference_alltoallv_gmm", "reference_gmm_alltoallv", "symmetric_input", "symmetric_output"]

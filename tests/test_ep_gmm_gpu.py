@@ -30,7 +30,7 @@ def _close(actual, expected, what):
     assert err <= 2e-2 * scale, f"{what}: max abs error {err} against magnitude {scale}"
 
 
-def _world(world, E, K, N, max_rows, seed=0, empty_expert=None, reps=2):
+def _world(world, E, K, N, max_rows, seed=0, empty_expert=None, reps=2, zero_copy=False):
     from deepep_b200.ops import load_native
 
     C = load_native()
@@ -52,6 +52,10 @@ def _world(world, E, K, N, max_rows, seed=0, empty_expert=None, reps=2):
     try:
         eng = G.GmmEngine(sessions, layout, dev, max_rows, K, N)
         d_x = [x.to(dev) for x in xs]
+        if zero_copy:    # inputs written into the stage area are read by the peers in place
+            d_x = [eng.symmetric_input(r, x.shape[0], K) for r, x in enumerate(xs)]
+            for v, x in zip(d_x, xs):
+                v.copy_(x)
         d_w, d_w2 = [w.to(dev) for w in ws], [w.to(dev) for w in ws2]
         d_c = [torch.tensor(c, dtype=torch.int32, device=dev) for c in counts]
         for rep in range(reps):
@@ -59,6 +63,8 @@ def _world(world, E, K, N, max_rows, seed=0, empty_expert=None, reps=2):
             gath = [torch.full((r.shape[0], K), float("nan"), dtype=torch.bfloat16, device=dev) for r in ref_gathered]
             eng.a2av_gmm(d_x, d_w, d_c, outs, gath, num_experts=E)
             back = [torch.full((x.shape[0], N), float("nan"), dtype=torch.bfloat16, device=dev) for x in xs]
+            if zero_copy:
+                back = [eng.symmetric_output(r, x.shape[0], N) for r, x in enumerate(xs)]
             eng.gmm_a2av(gath, d_w2, d_c, back, num_experts=E)
             torch.cuda.synchronize()
             eng.check()
@@ -80,6 +86,10 @@ def test_single_rank_grouped_gemm():
 
 def test_two_ranks_odd_sizes():
     _world(2, 6, 192, 320, 500, seed=3, empty_expert=2)
+
+
+def test_zero_copy_views():
+    _world(2, 4, 128, 128, 400, seed=9, zero_copy=True)
 
 
 def test_four_ranks():
