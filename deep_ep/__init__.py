@@ -28,7 +28,8 @@ class _AliasFinder:
             module = importlib.import_module(real)
         except ImportError:
             return None
-        sys.modules[fullname] = module
+        # sys.modules[fullname] is set by the import system from what the loader's create_module returns; setting it
+        # here would make the import system re-run the real module's own spec
         return importlib.util.spec_from_loader(fullname, loader=_Loader(module))
 
 
