@@ -1,6 +1,8 @@
 """Fused MoE forward timing on one GPU (N virtual ranks share the device) with a per-kernel breakdown.
 
     python benchmarks/bench_mega.py --world 1 --tokens 4096 --experts 32      # one rank's share of an EP8 layer
+    python benchmarks/bench_mega.py --accuracy --world 2 --tokens 256 --hidden 1024 --inter 512 --experts 8
+                                                  # MARE / MERE / RMSE and the mixed-error gate against the cached CPU golden
 """
 import argparse
 import json
@@ -24,6 +26,8 @@ def main():
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--unfused", action="store_true", help="four launches instead of the persistent kernel")
+    ap.add_argument("--accuracy", action="store_true", help="compare with the CPU golden instead of timing")
+    ap.add_argument("--golden-dir", default=os.path.join(ROOT, "gpurun_out", "golden"))
     ap.add_argument("--no-profiler", action="store_true", help="skip the torch.profiler breakdown (needed under ncu)")
     args = ap.parse_args()
     from deepep_b200.models.mega_moe import MegaEngine, MegaWeights
@@ -32,6 +36,8 @@ def main():
     C = load_native()
     dev = torch.device("cuda")
     P, T, H, I, E, K = args.world, args.tokens, args.hidden, args.inter, args.experts, args.topk
+    if args.accuracy:
+        return accuracy(args, C, dev)
     L = E // P
     layout = C.make_mega_layout(P, T, H, K, MegaEngine.mega_bytes(C, T, H, K))
     sessions = [C.Session(r, P, layout.total, 30.0) for r in range(P)]
@@ -86,5 +92,36 @@ def main():
         s_.close()
 
 
+def accuracy(args, C, dev):
+    from deepep_b200.models import mega_tools as tools
+    from deepep_b200.models.mega_moe import MegaEngine, transform_weights_for_mega_moe
+
+    P, T, H, I, E, K = args.world, args.tokens, args.hidden, args.inter, args.experts, args.topk
+    L = E // P
+    spec = tools.contract(world=P, tokens=[T] * P, hidden=H, intermediate=I, experts=E, topk=K, seed=0)
+    xs, idx, ws, l1, l2 = tools.make_case(spec)
+    for r in range(P):
+        tools.check_routing(idx[r].tolist(), ws[r].tolist(), E, K)
+    layout = C.make_mega_layout(P, T, H, K, MegaEngine.mega_bytes(C, T, H, K))
+    sessions = [C.Session(r, P, layout.total, 30.0) for r in range(P)]
+    for s in sessions:
+        s.attach_peers([q.workspace for q in sessions])
+    eng = MegaEngine(sessions, layout, dev, E, I)
+    w = [transform_weights_for_mega_moe((l1[0][r * L:(r + 1) * L], l1[1][r * L:(r + 1) * L]),
+                                        (l2[0][r * L:(r + 1) * L], l2[1][r * L:(r + 1) * L]), device=dev) for r in range(P)]
+    for r in range(P):
+        x, sf, ti, tw = eng.input_views(r)
+        x[:T].copy_(xs[r][0]); sf[:T].copy_(xs[r][1]); ti[:T].copy_(idx[r].to(torch.int32)); tw[:T].copy_(ws[r])
+    ys = [torch.zeros((T, H), dtype=torch.bfloat16, device=dev) for _ in range(P)]
+    eng.forward(ys, [T] * P, [a for a, _ in w], [b for _, b in w], fused=not args.unfused)
+    torch.cuda.synchronize()
+    eng.check()
+    ok, rows = tools.accuracy_report(ys, spec, args.golden_dir)
+    print(json.dumps({"accuracy_ok": ok, "spec": spec, "ranks": rows}))
+    for s in sessions:
+        s.close()
+    return 0 if ok else 1
+
+
 if __name__ == "__main__":
-    main()
+    sys.exit(main() or 0)

@@ -1,7 +1,7 @@
 """``Buffer``: upstream DeepEP's V1 interface (``get_dispatch_layout`` / ``dispatch`` / ``combine``).
 
 Parity: ``deep_ep/backends/direct/buffer.py`` of the reference (``get_dispatch_layout`` :420-463,
-``dispatch`` :465-680, ``combine`` :682-751, config getters, ``capture``, ``get_comm_stream``) and
+``dispatch`` :465-680, ``combine`` :682-751, ``expand`` :753-873, ``aggregate`` :875-918, config getters, ``capture``, ``get_comm_stream``) and
 ``deep_ep/buffer.py:8-16``.  The V1 layout is the rank layout of :class:`ElasticBuffer`
 (``do_expand=False``): one received row per (source rank, token), ``recv_topk_idx`` holding local
 expert ids.  Internode and the V1 low-latency entry points belong to multi-node RDMA deployments and
@@ -135,6 +135,38 @@ class Buffer:
         return self._elastic.combine(x, handle, topk_weights=topk_weights, bias=bias, num_sms=config.num_sms if config else 0,
                                      previous_event=previous_event, async_with_compute_stream=async_finish,
                                      allocate_on_comm_stream=allocate_on_comm_stream)
+
+    def _ordered(self, fn, previous_event, async_finish: bool, tensors):
+        """Runs a local operator on the current stream after ``previous_event``; returns its results and an event."""
+        if previous_event is not None and getattr(previous_event, "event", None) is not None:
+            previous_event.current_stream_wait()
+        result = fn()
+        if async_finish and torch.cuda.is_available() and tensors(result) and tensors(result)[0].is_cuda:
+            return result, EventOverlap._from_resources(EventHandle(), tuple(t for t in tensors(result) if t is not None))
+        return result, EventOverlap()
+
+    def expand(self, x, recv_topk_idx=None, topk_weights=None, num_tokens_per_expert=None, expert_alignment=None, handle=None,
+               config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
+               allocate_on_comm_stream: bool = False):
+        """Expand rank-deduplicated dispatch rows into expert-major rows:
+        ``(expanded_x | (expanded_x, scales), expanded_topk_weights, ExpandHandle, event)``."""
+        from .ops.expand import expand as _expand
+
+        del config, allocate_on_comm_stream
+        (ex, ew, h), ev = self._ordered(lambda: _expand(x, recv_topk_idx, topk_weights, num_tokens_per_expert, expert_alignment, handle),
+                                        previous_event, async_finish,
+                                        lambda r: [*(r[0] if isinstance(r[0], tuple) else (r[0],)), r[1]])
+        return ex, ew, h, ev
+
+    def aggregate(self, x, handle, topk_weights=None, expanded_values=None, config: Optional[Config] = None, previous_event=None,
+                  async_finish: bool = False, allocate_on_comm_stream: bool = False):
+        """Reduce expert-major rows back to the rank-deduplicated layout: ``(aggregated_x, aggregated_values, event)``."""
+        from .ops.expand import aggregate as _aggregate
+
+        del config, allocate_on_comm_stream
+        (ax, av), ev = self._ordered(lambda: _aggregate(x, handle, topk_weights, expanded_values), previous_event, async_finish,
+                                     lambda r: [r[0], r[1]])
+        return ax, av, ev
 
     # ------------------------------------------------------------------ not part of this library
     def internode_dispatch(self, *a, **k): raise NotImplementedError("internode dispatch needs an RDMA fabric")

@@ -161,6 +161,7 @@ void op_barrier(const std::vector<py::object>& sessions, uintptr_t stream) {
 void bind_low_latency(py::module_& m);
 void bind_mega(py::module_& m);
 void bind_gmm(py::module_& m);
+void bind_expand(py::module_& m);
 
 PYBIND11_MODULE(_C, m) {
   m.attr("runtime_protocol") = 1;
@@ -229,4 +230,5 @@ PYBIND11_MODULE(_C, m) {
   bind_low_latency(m);
   bind_mega(m);
   bind_gmm(m);
+  bind_expand(m);
 }
