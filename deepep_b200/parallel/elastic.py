@@ -422,8 +422,12 @@ class ElasticBuffer:
 
     # ------------------------------------------------------------------ combine
     def combine(self, x, handle, topk_weights=None, bias=None, num_sms=0, num_qps=0, previous_event=None,
-                previous_event_before_epilogue=None, async_with_compute_stream=False, allocate_on_comm_stream=False):
+                previous_event_before_epilogue=None, async_with_compute_stream=False, allocate_on_comm_stream=False,
+                combine_num_sms: int = 0, reduce_num_sms: int = 0):
         """Return every expert output row to its source token and reduce.
+
+        ``combine_num_sms`` / ``reduce_num_sms`` (both or neither) set how many SMs return rows on the expert side and
+        how many reduce at the source; by default ``num_sms`` is divided 72 / 28.
 
         High-throughput handles: unweighted fp32 sum (bf16 partial per expert rank), optional ``bias`` (a tensor or a
         pair) added at the source, optional fp32 ``topk_weights`` returned per slot as an independent channel.
@@ -451,6 +455,14 @@ class ElasticBuffer:
                 raise ValueError("bias must be bf16 [tokens, hidden]")
         self._preflight("combine", (self.hidden, plan.expand, topk_weights is not None, bias is not None,
                                     handle.is_low_latency))
+        for name, v in (("combine_num_sms", combine_num_sms), ("reduce_num_sms", reduce_num_sms)):
+            if not isinstance(v, int) or isinstance(v, bool) or v < 0:
+                raise ValueError(f"{name} must be a nonnegative integer")
+        if bool(combine_num_sms) != bool(reduce_num_sms):
+            raise ValueError("pass combine_num_sms and reduce_num_sms together")
+        split = (combine_num_sms, reduce_num_sms) if combine_num_sms else None
+        if split is not None and (handle.is_low_latency or not hasattr(self.engine, "split_blocks")):
+            split = None                      # one kernel role per SM only exists on the high-throughput CUDA path
         comm = self._enter(previous_event, previous_event_before_epilogue)
         with self._on(comm if allocate_on_comm_stream else None):
             if handle.is_low_latency:
@@ -459,7 +471,8 @@ class ElasticBuffer:
                 out, out_w = self.engine.ll_combine([x], [plan], stream=comm)[0], None
             else:
                 out, out_w = self.engine.combine([x], [plan], [topk_weights], bias=None if bias is None else [tuple(biases)],
-                                                 blocks=num_sms or self.num_sms, stream=comm)[0]
+                                                 blocks=num_sms or self.num_sms, stream=comm,
+                                                 **({"split": split} if split is not None else {}))[0]
         event = self._leave(comm, async_with_compute_stream, [out, out_w, x, topk_weights] + [b for b in biases if b is not None]
                             + handle._tracked())
         return out, out_w, event

@@ -198,7 +198,8 @@ class CudaEngine:
         return outs
 
     def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[RoutingPlan], ws: Sequence[Optional[torch.Tensor]],
-                bias: Sequence = None, blocks: int = 0, stream=None):
+                bias: Sequence = None, blocks: int = 0, stream=None, split: Optional[Tuple[int, int]] = None):
+        """``split`` = (expert-side sender blocks, source-side reducer blocks) overrides the default 72 / 28 division."""
         lay, dev = self.layout, self.device
         H, K = lay.hidden, lay.topk
         outs, args = [], []
@@ -215,6 +216,11 @@ class CudaEngine:
                              meta_stride=plan.meta_stride, K=K, E=plan.num_experts, expand=int(plan.expand),
                              bias0=_ptr(b0), bias1=_ptr(b1), out=out.data_ptr(), out_w=_ptr(out_w)))
         send, recv = self.split_blocks(blocks, 0.72, self.combine_blocks)
+        if split is not None:
+            limit = max(2, self.sm_count // self.n)
+            send, recv = max(1, int(split[0])), max(1, int(split[1]))
+            if send + recv > limit:
+                raise ValueError(f"combine_num_sms + reduce_num_sms must not exceed {limit} on this device")
         self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream))
         return outs
 

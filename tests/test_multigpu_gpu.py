@@ -91,6 +91,11 @@ def test_single_gpu_public_api():
     out, _, _ = buf.combine(rx, handle)
     cref = R.combine([ref[0][0]], lays, [T], K)
     assert bits_equal(out, cref[0][0])
+    out_split, _, _ = buf.combine(rx, handle, combine_num_sms=40, reduce_num_sms=24)      # explicit sender / reducer SM split
+    assert bits_equal(out_split, cref[0][0])
+    with pytest.raises(ValueError, match="together"):
+        buf.combine(rx, handle, combine_num_sms=8)
+    # V1 local operators on the rank layout: expand to expert-major rows and reduce back
     # rank layout + aligned expanded layout
     rx2, ridx, rw2, h2, _ = buf.dispatch(xs[0].to(dev), topk_idx=idx[0].to(dev), topk_weights=ws[0].to(dev), num_experts=E)
     assert h2.is_low_latency is False or True
