@@ -97,6 +97,7 @@ struct MegaFusedArgs {
   MegaRouteArgs route;
   MegaFinishArgs finish;
   int* ready;                  // [max_mtiles] finished GEMM1 tiles per row block (zeroed by the kernel)
+  int* tile_counter;           // [1] next tile of the GEMM1 + GEMM2 tile list (zeroed by the kernel); null: static round-robin
 };
 struct MegaFusedParams { WsLayout lay; MegaFusedArgs r[kMaxRanks]; };
 cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, cudaStream_t stream);

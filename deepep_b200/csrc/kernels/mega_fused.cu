@@ -28,14 +28,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid
   cg::grid_group grid = cg::this_grid();
   const MegaFusedArgs& a = p.r[blockIdx.y];
   if (blockIdx.x == 0)
+  {
     for (int i = threadIdx.x; i < a.route.max_mtiles; i += blockDim.x) { a.ready[i] = 0; a.route.pulled[i] = 0; }
+    if (threadIdx.x == 0 && a.tile_counter) *a.tile_counter = 0;
+  }
   route_layout_phase(a.route, grid, sh);          // handshake, counts, tile layout (grid barriers inside)
   __threadfence();
   grid.sync();
   // The token pull overlaps the GEMMs: rows are pulled tile by tile, a GEMM1 tile starts once its rows have arrived.
   const int warp = threadIdx.x >> 5;
   if (warp < kGemmThreads / 32) {
-    gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x);
+    gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x, a.tile_counter);
   } else {
     __syncthreads();                               // pairs with the set-up barrier inside gemm_phase
     route_pull_phase(a.route, sh, blockIdx.x * kPullWarps + (warp - kGemmThreads / 32), gridDim.x * kPullWarps);

@@ -13,7 +13,10 @@
 //              rank's combine slots over NVLink.
 // It walks one tile list that may hold two GEMMs back to back (GEMM1 tiles, then GEMM2 tiles whose
 // A operand is GEMM1's output): a GEMM2 tile waits on a per-row-block counter that the GEMM1
-// epilogues bump, so SMs that run out of GEMM1 tiles start on GEMM2 at once.
+// epilogues bump, so SMs that run out of GEMM1 tiles start on GEMM2 at once.  In the fused layer the
+// tiles are handed out by an atomic counter (the producer warp takes the next tile and publishes its
+// id to the MMA and epilogue warps through a ring of mbarriers), which balances the long GEMM1 tiles
+// and the short GEMM2 tiles over the SMs; the stand-alone launch keeps the static round-robin.
 //
 // Tile shape: issuing one tcgen05 instruction costs the MMA thread about 50 cycles (measured), so a
 // stage of four N=128 MMAs (256 tensor cycles) was issue-bound; N=256 doubles the work per instruction.
@@ -48,8 +51,12 @@ __host__ __device__ constexpr size_t gemm_smem_bytes(int stages, bool staging) {
   return 1024 + (size_t)stages * (kStageBytes + kSfStageBytes) + (staging ? kEpiStageBytes : 0) + 256;
 }
 
+constexpr int kSchedRing = 8;   // tile ids in flight between the producer and the slowest consumer (< stages + 2)
+
 struct GemmBarriers {
   uint64_t full[kGemmMaxStages], empty[kGemmMaxStages], acc_full, acc_empty, epi_done;
+  uint64_t sched[kSchedRing];      // the producer has published tile_id[slot]
+  int tile_id[kSchedRing];
   uint32_t tmem_base;
   int failed;
 };
@@ -83,11 +90,21 @@ __device__ __forceinline__ bool wait_rows_ready(const int* counter, int need, vo
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// Next tile of this CTA: the producer publishes it to the MMA and epilogue warps through a small ring.
+__device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_tile, volatile int* failed) {
+  const uint32_t slot = local_tile % kSchedRing;
+  if (!bounded_wait(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed)) return -1;
+  return bars->tile_id[slot];
+}
+
 // g1: first GEMM of the list; g2: optional second GEMM (nullptr for a single GEMM).  `ready` (may be null):
 // ready[mt] counts finished g1 tiles of row block mt; g2 tiles of mt wait until it reaches g1.n_tiles.
+// `tile_counter` (may be null): tiles are handed out in list order by an atomic counter, whichever CTA is free takes
+// the next one (it must be zero when the first CTA arrives); null: CTA c takes tiles c, c + num_ctas, ...
+// Either way a tile is only ever taken after all tiles before it, so a GEMM2 tile's wait for its GEMM1 tiles ends.
 // `smem_raw` must provide gemm_smem_bytes(stages, staging) bytes.
 __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaGemmParams* g2, int* ready, uint8_t* smem_raw,
-                                           int stages, int cta, int num_ctas) {
+                                           int stages, int cta, int num_ctas, int* tile_counter = nullptr) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
   uint8_t* tiles = smem;
@@ -102,6 +119,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->acc_empty, kEpiWarps);
     mbar_init(&bars->epi_done, kEpiWarps);
+    for (int i = 0; i < kSchedRing; ++i) mbar_init(&bars->sched[i], 1);
     bars->failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     umma::prefetch_tensormap(&g1.tmap_a);
@@ -126,7 +144,12 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     // ============================================================ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
-      for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas) {
+      for (uint32_t local_tile = 0;; ++local_tile) {
+        int tile = tile_counter ? atomicAdd(tile_counter, 1) : cta + (int)local_tile * num_ctas;
+        if (tile >= total_tiles || *failed) tile = -1;
+        bars->tile_id[local_tile % kSchedRing] = tile;
+        mbar_arrive(&bars->sched[local_tile % kSchedRing]);      // release: the id is visible to whoever passes the wait
+        if (tile < 0) break;
         const bool second = tile >= tiles1;
         const MegaGemmParams& p = second ? *g2 : g1;
         const int local = second ? tile - tiles1 : tile;
@@ -160,8 +183,10 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     // ============================================================ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, /*e4m3*/ 0, /*e2m1*/ 5);
-      uint32_t it = 0, local_tile = 0;
-      for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas, ++local_tile) {
+      uint32_t it = 0;
+      for (uint32_t local_tile = 0;; ++local_tile) {
+        const int tile = fetch_tile(bars, local_tile, failed);
+        if (tile < 0) break;
         const int k_steps = tile >= tiles1 ? g2->k_steps : g1.k_steps;
         if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed)) break;
         umma::fence_after_sync();
@@ -191,8 +216,10 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     const int part = (warp - 2) >> 2;                // which half of the tile's columns this warp handles
     const int row_in_tile = quad * 32 + lane;
     uint8_t* stage = epi_smem + (size_t)(warp - 2) * 32 * kEpiWarpCols * 2;
-    uint32_t local_tile = 0, first_done = 0;
-    for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas, ++local_tile) {
+    uint32_t first_done = 0;
+    for (uint32_t local_tile = 0;; ++local_tile) {
+      const int tile = fetch_tile(bars, local_tile, failed);
+      if (tile < 0) break;
       const bool second = tile >= tiles1;
       const MegaGemmParams& p = second ? *g2 : g1;
       const int local = second ? tile - tiles1 : tile;

@@ -180,7 +180,14 @@ __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_
     const int* idx = reinterpret_cast<const int*>(ctx.ws[me] + a.in_off + in.idx);
     const float* w = reinterpret_cast<const float*>(ctx.ws[me] + a.in_off + in.w);
     const uint8_t* comb = ctx.ws[me] + a.comb_off;
-    for (int t = gw; t < a.T; t += total_warps) {
+    // small batches: several warps share a token, each reduces a span of columns (a multiple of the 64-piece step)
+    const int units = H / 8;
+    const int parts = max(1, min(8, total_warps / max(a.T, 1)));
+    const int span = ((units + parts * 64 - 1) / (parts * 64)) * 64;
+    for (int item = gw; item < a.T * parts; item += total_warps) {
+      const int t = item / parts, part = item - t * parts;
+      if (part * span >= units) continue;
+      const int u_end = min(units, (part + 1) * span);
       float wk[kMaxTopk];
       unsigned valid = 0;
       for (int k = 0; k < K; ++k) {
@@ -190,8 +197,8 @@ __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_
       }
       int4* out = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.y) + (size_t)t * H * 2);
       const uint8_t* rows = comb + (size_t)t * K * H * 2;
-      for (int u0 = lane; u0 < H / 8; u0 += 64) {      // two 16-byte columns per step, all slots' loads issued first
-        const bool two = u0 + 32 < H / 8;
+      for (int u0 = part * span + lane; u0 < u_end; u0 += 64) {      // two 16-byte columns per step, all slots' loads issued first
+        const bool two = u0 + 32 < u_end;
         int4 v0[kMaxTopk], v1[kMaxTopk];
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {

@@ -18,6 +18,7 @@ rows straight into the source rank's combine slots over NVLink; (4) ``mega_finis
 from __future__ import annotations
 
 from dataclasses import dataclass
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -93,6 +94,8 @@ class MegaEngine:
         self.comb_off = layout.mega + in_total
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self.gemm_blocks = num_sms or self.sm_count
+        # tiles handed out by an atomic counter (default) or statically round-robin (DEEPEP_MEGA_STATIC_TILES=1)
+        self.dynamic_tiles = os.environ.get("DEEPEP_MEGA_STATIC_TILES", "0") in ("", "0")
         rows = self.world * self.M * min(self.K, self.L) + self.L * 127
         self.max_mtiles = -(-rows // 128)
         self.rows_cap = self.max_mtiles * 128
@@ -105,7 +108,7 @@ class MegaEngine:
                 row_src=torch.empty((self.rows_cap,), **i32), mtile_expert=torch.zeros((self.max_mtiles,), **i32),
                 num_mtiles=torch.zeros((1,), **i32), expert_rows=torch.zeros((self.L,), **i32),
                 expert_list=torch.empty((self.L * self.world * self.M,), **i32), err=torch.zeros((1,), **i32),
-                ready=torch.zeros((self.max_mtiles,), **i32), pulled=torch.zeros((self.max_mtiles,), **i32)))
+                ready=torch.zeros((self.max_mtiles,), **i32), pulled=torch.zeros((self.max_mtiles,), **i32), tile_counter=torch.zeros((1,), **i32)))
 
     @staticmethod
     def mega_bytes(C, max_tokens: int, hidden: int, topk: int) -> int:
@@ -153,7 +156,8 @@ class MegaEngine:
                 gemm1_args[i]["a_ready"] = sc["pulled"].data_ptr()
             blocks = max(1, min(self.gemm_blocks, self.sm_count // self.n))
             C.mega_fused(lay, self.sessions, [dict(route=route_args[i], finish=finish_args[i], gemm1=gemm1_args[i],
-                                                  gemm2=gemm2_args[i], ready=self.scratch[i]["ready"].data_ptr())
+                                                  gemm2=gemm2_args[i], ready=self.scratch[i]["ready"].data_ptr(),
+                                                  tile_counter=self.scratch[i]["tile_counter"].data_ptr() if self.dynamic_tiles else None)
                                              for i in range(self.n)], blocks, s)
             return
         aux_blocks = max(1, min(self.sm_count // self.n, 128))

@@ -175,6 +175,16 @@ class ElasticBuffer:
     def get_logical_domain_size(self) -> Tuple[int, int]:
         return 1, self.world_size
 
+    # ------------------------------------------------------------------ device phase timing
+    def enable_profiling(self, on: bool = True) -> None:
+        """Time every kernel this buffer launches with CUDA events (also switched on by ``DEEPEP_PROFILE=1``)."""
+        if hasattr(self.engine, "enable_profiling"):
+            self.engine.enable_profiling(on)
+
+    def pop_profile(self):
+        """``[(kernel, microseconds)]`` recorded since the last call; empty on engines without device timing."""
+        return self.engine.pop_timings() if hasattr(self.engine, "pop_timings") else []
+
     def get_theoretical_num_sms(self, num_experts, num_topk, num_scaleout_topk=0, rdma_gbs=0, nvlink_gbs=0,
                                 sm_read_gbs=200, sm_write_gbs=50) -> int:
         """SMs needed to keep NVLink busy, from per-SM copy rates (bulk-copy engines move the rows)."""

@@ -13,6 +13,7 @@ single host synchronisation of a fresh dispatch
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -84,6 +85,9 @@ class CudaEngine:
         self.default_blocks = self.dispatch_blocks
         nt = -(-layout.max_tokens // self.C.chunk_tokens)
         self._nt = nt
+        # opt-in device timing of every launch (DEEPEP_PROFILE=1 or enable_profiling()): events around each kernel
+        self._profile = os.environ.get("DEEPEP_PROFILE", "0") not in ("", "0")
+        self._timings: List[Tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
         self._scratch = []
         for _ in range(self.n):
             self._scratch.append(dict(
@@ -98,6 +102,35 @@ class CudaEngine:
         *current* stream, so a caller that launches on a side stream and then makes the current stream wait for it
         needs no ``record_stream`` bookkeeping."""
         return (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
+
+    # ------------------------------------------------------------------ device phase timing
+    def enable_profiling(self, on: bool = True) -> None:
+        """Record a pair of CUDA events around every kernel launch (parity: the reference's ``DevicePhaseTiming``,
+        ``csrc/ops/device_phase_timing.hpp:13-50``, and the optional event timing of its notify op)."""
+        self._profile = bool(on)
+        self._timings.clear()
+
+    def _timed(self, name: str, stream, launch) -> None:
+        if not self._profile:
+            launch()
+            return
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(st)
+        launch()
+        end.record(st)
+        self._timings.append((name, start, end))
+        if len(self._timings) > 4096:
+            del self._timings[:2048]
+
+    def pop_timings(self) -> List[Tuple[str, float]]:
+        """``[(kernel, microseconds)]`` of the launches recorded so far (synchronises on their end events)."""
+        out = []
+        for name, start, end in self._timings:
+            end.synchronize()
+            out.append((name, start.elapsed_time(end) * 1e3))
+        self._timings.clear()
+        return out
 
     def check_status(self) -> None:
         for s in self.sessions:
@@ -158,7 +191,7 @@ class CudaEngine:
                              expert_offsets=plan.expert_offsets.data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(),
                              recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap))
         nblocks = blocks or max(1, min(64, self.sm_count // self.n))
-        C.notify(lay, self.sessions, args, nblocks, self._stream(stream))
+        self._timed("notify", stream, lambda: C.notify(lay, self.sessions, args, nblocks, self._stream(stream)))
         if cpu_sync:
             (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
             self.check_status()
@@ -194,7 +227,7 @@ class CudaEngine:
                              rank_tokens=plan.rank_tokens.data_ptr(), meta_stride=plan.meta_stride,
                              recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf)))
         send, recv = self.split_blocks(blocks, 0.25, self.dispatch_blocks)
-        self.C.dispatch(lay, self.sessions, args, send, recv, self._stream(stream))
+        self._timed("dispatch", stream, lambda: self.C.dispatch(lay, self.sessions, args, send, recv, self._stream(stream)))
         return outs
 
     def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[RoutingPlan], ws: Sequence[Optional[torch.Tensor]],
@@ -221,7 +254,7 @@ class CudaEngine:
             send, recv = max(1, int(split[0])), max(1, int(split[1]))
             if send + recv > limit:
                 raise ValueError(f"combine_num_sms + reduce_num_sms must not exceed {limit} on this device")
-        self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream))
+        self._timed("combine", stream, lambda: self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream)))
         return outs
 
     # ------------------------------------------------------------------ low latency
@@ -264,7 +297,7 @@ class CudaEngine:
                              recv_w=o["recv_w"].data_ptr(), recv_row_src=o["recv_row_src"].data_ptr(),
                              expert_counts=o["expert_counts"].data_ptr(), expert_offsets=o["expert_offsets"].data_ptr(),
                              num_rows=o["num_rows"].data_ptr(), use_mailbox=int(cpu_sync), capacity=cap))
-        self.C.ll_dispatch(lay, self.sessions, args, self.ll_blocks(), self._stream(stream))
+        self._timed("ll_dispatch", stream, lambda: self.C.ll_dispatch(lay, self.sessions, args, self.ll_blocks(), self._stream(stream)))
         if cpu_sync:
             (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
             self.check_status()
@@ -291,7 +324,7 @@ class CudaEngine:
             args.append(dict(x=xs[i].data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(), num_rows=plan.num_rows_dev.data_ptr(),
                              topk_idx=plan.topk_idx.data_ptr(), topk_w=plan.topk_w.data_ptr(), T=plan.num_tokens,
                              E=plan.num_experts, out=out.data_ptr()))
-        self.C.ll_combine(lay, self.sessions, args, self.ll_blocks(), self._stream(stream))
+        self._timed("ll_combine", stream, lambda: self.C.ll_combine(lay, self.sessions, args, self.ll_blocks(), self._stream(stream)))
         return results
 
     def barrier(self, stream=None) -> None:

@@ -91,7 +91,11 @@ def test_single_gpu_public_api():
     out, _, _ = buf.combine(rx, handle)
     cref = R.combine([ref[0][0]], lays, [T], K)
     assert bits_equal(out, cref[0][0])
+    buf.enable_profiling()
     out_split, _, _ = buf.combine(rx, handle, combine_num_sms=40, reduce_num_sms=24)      # explicit sender / reducer SM split
+    prof = buf.pop_profile()
+    assert [name for name, _ in prof] == ["combine"] and 0 < prof[0][1] < 1e6 and buf.pop_profile() == []
+    buf.enable_profiling(False)
     assert bits_equal(out_split, cref[0][0])
     with pytest.raises(ValueError, match="together"):
         buf.combine(rx, handle, combine_num_sms=8)
