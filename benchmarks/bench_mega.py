@@ -27,7 +27,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--unfused", action="store_true", help="four launches instead of the persistent kernel")
     ap.add_argument("--accuracy", action="store_true", help="compare with the CPU golden instead of timing")
-    ap.add_argument("--golden-dir", default=os.path.join(ROOT, "gpurun_out", "golden"))
+    ap.add_argument("--golden-dir", default=os.path.join(ROOT, "benchmarks", ".golden_cache"))
     ap.add_argument("--no-profiler", action="store_true", help="skip the torch.profiler breakdown (needed under ncu)")
     args = ap.parse_args()
     from deepep_b200.models.mega_moe import MegaEngine, MegaWeights
