@@ -277,16 +277,65 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
                                                              __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
         }
       } else {
-        // SwiGLU + requantisation: columns [0, 128) are gate rows of W1, [128, 256) the matching up rows
+        // SwiGLU + requantisation: columns [0, 128) are gate rows of W1, [128, 256) the matching up rows.
+        // With a staging area the bf16-rounded accumulator (the first step of the math anyway) is parked in shared
+        // memory and tensor memory is handed back before the arithmetic, so the next tile's MMAs overlap it.
+        uint4* mine = reinterpret_cast<uint4*>(stage + (size_t)lane * kEpiWarpCols * 2);   // 256 B per row = 16 pieces
+        if (staging) {
+          __syncwarp();
+#pragma unroll
+          for (int hh = 0; hh < kGemmBN / 128; ++hh) {
+            const int half = part * (kGemmBN / 128) + hh;
+            umma::tmem_ld32(taddr + half * 32, v);
+            umma::tmem_ld32(taddr + kGemmBN / 2 + half * 32, u);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t wg[4], wu[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 bg = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                __nv_bfloat162 bu = __floats2bfloat162_rn(__uint_as_float(u[8 * i + 2 * j]), __uint_as_float(u[8 * i + 2 * j + 1]));
+                wg[j] = *reinterpret_cast<uint32_t*>(&bg);
+                wu[j] = *reinterpret_cast<uint32_t*>(&bu);
+              }
+              mine[(hh * 8 + i) ^ (lane & 15)] = make_uint4(wg[0], wg[1], wg[2], wg[3]);
+              mine[(hh * 8 + 4 + i) ^ (lane & 15)] = make_uint4(wu[0], wu[1], wu[2], wu[3]);
+            }
+          }
+          umma::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->acc_empty);
+        }
         for (int half = part * (kGemmBN / 128); half < (part + 1) * (kGemmBN / 128); ++half) {
-          umma::tmem_ld32(taddr + half * 32, v);
-          umma::tmem_ld32(taddr + kGemmBN / 2 + half * 32, u);
-          umma::tmem_ld_wait();
+          float gv[32], uv[32];
+          if (staging) {
+            const int hh = half - part * (kGemmBN / 128);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 pg = mine[(hh * 8 + i) ^ (lane & 15)], pu = mine[(hh * 8 + 4 + i) ^ (lane & 15)];
+              const __nv_bfloat162* bg = reinterpret_cast<const __nv_bfloat162*>(&pg);
+              const __nv_bfloat162* bu = reinterpret_cast<const __nv_bfloat162*>(&pu);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                gv[8 * i + 2 * j] = __low2float(bg[j]); gv[8 * i + 2 * j + 1] = __high2float(bg[j]);
+                uv[8 * i + 2 * j] = __low2float(bu[j]); uv[8 * i + 2 * j + 1] = __high2float(bu[j]);
+              }
+            }
+          } else {
+            umma::tmem_ld32(taddr + half * 32, v);
+            umma::tmem_ld32(taddr + kGemmBN / 2 + half * 32, u);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { gv[i] = bf16_round(__uint_as_float(v[i])); uv[i] = bf16_round(__uint_as_float(u[i])); }
+          }
           float h[32], amax = 0.f;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float g = bf16_round(__uint_as_float(v[i])), up = bf16_round(__uint_as_float(u[i]));
-            const float act = g / (1.0f + __expf(fminf(fmaxf(-g, -80.f), 80.f))) * up;
+            const float g = gv[i], up = uv[i];
+            // div.approx: the IEEE division has a slow path for huge / non-finite operands, which padding rows (whatever
+            // the row buffer held) do contain; it made this epilogue, and with it the whole tile, measurably slower
+            const float act = __fdividef(g, 1.0f + __expf(fminf(fmaxf(-g, -80.f), 80.f))) * up;
             h[i] = bf16_round(act);
             amax = fmaxf(amax, fabsf(h[i]));
           }
@@ -309,9 +358,11 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
           p.a2_sf[sf_offset(row, col, p.inter)] = (uint8_t)(e + 127);
         }
       }
-      umma::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->acc_empty);
+      if (!(p.epi == kEpiSwigluQuant && staging)) {      // (that path released the accumulator before its arithmetic)
+        umma::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty);
+      }
       if (!second && g2 && ready) {
         // this tile's rows of the intermediate activations are in global memory: let GEMM2 producers know
         fence_proxy_async();
