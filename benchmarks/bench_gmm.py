@@ -1,7 +1,7 @@
 """alltoallv_gmm / gmm_alltoallv timing against an NCCL all-to-all-v + cuBLAS baseline.
 
 One GPU (virtual ranks share the device; the baseline is the grouped matmul alone, without a transfer):
-    python benchmarks/bench_gmm.py --world 1 --rows 32768 --k 7168 --n 4096 --experts 4
+    python benchmarks/bench_gmm.py --world 1 --rows 32768 --in-features 7168 --out-features 4096 --experts 4
 Several GPUs, one process each (public API; the baseline is all_to_all_single + one matmul per expert):
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/bench_gmm.py --rows 32768 --experts 32
 """
@@ -152,8 +152,8 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--world", type=int, default=1, help="virtual ranks on one GPU (ignored under torchrun)")
     ap.add_argument("--rows", type=int, default=32768, help="rows per rank (tokens x top-k)")
-    ap.add_argument("--k", type=int, default=7168)
-    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--in-features", dest="k", type=int, default=7168)
+    ap.add_argument("--out-features", dest="n", type=int, default=4096)
     ap.add_argument("--experts", type=int, default=4)
     ap.add_argument("--iters", type=int, default=5)
     a = ap.parse_args()
