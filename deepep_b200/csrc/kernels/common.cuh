@@ -65,6 +65,7 @@ struct Control {
   unsigned long long gmm_flag[kMaxRanks][4];   // a2av_gmm: staged, pulled; gmm_a2av: ready, pushed
   unsigned long long disp_chunk[kMaxRanks][kMaxChunks];
   unsigned long long comb_chunk[kMaxRanks][kMaxChunks];
+  unsigned int comb_parts[kMaxRanks][kMaxChunks];   // local: finished parts of a (source, chunk) in the running combine
   // diagnostics: where a pipeline wait gave up (warp-indexed records of 4 words)
   unsigned long long dbg[256];
 };

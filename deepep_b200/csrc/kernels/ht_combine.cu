@@ -4,7 +4,8 @@
 // (source token, this rank) they sum the token's rows on this rank in slot order in fp32,
 // round once to bf16 and push that single partial into the source rank's workspace over
 // NVLink (a one-row group is a pure bulk copy).  A release flag per (source, 64-token chunk)
-// follows.  Source-side blocks wait for the chunk flags of all ranks, sum the partials in
+// follows.  With few ranks there are fewer (source, chunk) pairs than SMs, so a chunk is cut into
+// up to 8 parts that different blocks take; the block that finishes a chunk's last part publishes.  Source-side blocks wait for the chunk flags of all ranks, sum the partials in
 // rank order in fp32, add the optional biases and write bf16 into the caller's tensor.
 // The optional fp32 value channel (used for dispatch-backward) is returned per slot and is
 // never multiplied into the payload.
@@ -158,9 +159,17 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpCombine] + 1;
 
+  const bool expert_side = (int)blockIdx.x < p.send_blocks;
+  // With one or two ranks a token has up to top-k rows on this rank, and a ring of ~15 whole rows cannot hold two such
+  // groups: the expert side then works on half rows, so that the next group loads while the current one is reduced.
+  const int cparts = (expert_side && P <= 2 && (row_bytes / 2) % 128 == 0) ? 2 : 1;
+  const int seg_bytes = row_bytes / cparts, seg_units = units / cparts;
   Ring ring;
-  ring.slot_bytes = (row_bytes + 127) & ~127;
-  ring.num_slots = min(kRingMaxSlots, (int)((220 << 10) / ring.slot_bytes));
+  ring.slot_bytes = (seg_bytes + 127) & ~127;
+  // the launch sizes the ring for whole rows (see launch_combine): half rows must stay inside those bytes
+  const int full_slot = (row_bytes + 127) & ~127;
+  const int ring_bytes = min(kRingMaxSlots, (int)((220 << 10) / full_slot)) * full_slot;
+  ring.num_slots = min(kRingMaxSlots, ring_bytes / ring.slot_bytes);
   ring.full = reinterpret_cast<uint64_t*>(smem);
   ring.empty = ring.full + kRingMaxSlots;
   ring.issued = reinterpret_cast<volatile unsigned*>(ring.empty + kRingMaxSlots);
@@ -175,7 +184,6 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
   }
   __syncthreads();
 
-  const bool expert_side = (int)blockIdx.x < p.send_blocks;
   int alive = 1;
   if (expert_side) {
     int ok = 1;
@@ -188,32 +196,39 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
     int max_nt = 0;
     for (int r = 0; r < P; ++r) max_nt = max(max_nt, (a.rank_tokens[r] + kChunkTokens - 1) / kChunkTokens);
     const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
+    // parts per (source, chunk): enough work items for about two rounds over the expert-side blocks
+    const int parts = max(1, min(8, (2 * p.send_blocks + max_nt * P - 1) / max(1, max_nt * P)));
+    const int num_items = max_nt * P * parts;
     unsigned k = 0;
     long long t_a = 0, t_b = 0, t_c = 0, t_d = 0, t0 = clock64(), tt;
     if (warp == 0) {
       if (lane == 0) {
         bool okp = true;
-        for (int item = blockIdx.x; item < max_nt * P && okp; item += p.send_blocks) {
-          const int c = item / P, s_rank = (me + item % P) % P;
+        for (int item = blockIdx.x; item < num_items && okp; item += p.send_blocks) {
+          const int part = item % parts, pair = item / parts;
+          const int c = pair / P, s_rank = (me + pair % P) % P;
           if (c * kChunkTokens >= a.rank_tokens[s_rank]) continue;
-          const int j0 = a.chunk_start[s_rank * (NT + 1) + c], j1 = a.chunk_start[s_rank * (NT + 1) + c + 1];
+          const int c0 = a.chunk_start[s_rank * (NT + 1) + c], cn = a.chunk_start[s_rank * (NT + 1) + c + 1] - c0;
+          const int j0 = c0 + cn * part / parts, j1 = c0 + cn * (part + 1) / parts;
           for (int j = j0; j < j1 && okp; ++j) {
             const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + j) * a.meta_stride;
             tt = clock64();
             const int n = rec[1];
             t_a += clock64() - tt;
-            if (n <= ring_rows) {
-              for (int i = 0; i < n && okp; ++i) {
-                tt = clock64();
-                const uint8_t* src = x + (size_t)(rec[2 + i] & kRowMask) * row_bytes;
-                t_a += clock64() - tt; tt = clock64();
-                okp = ring.wait(&ring.empty[k % ring.num_slots], ring.phase(k) ^ 1u);
-                t_b += clock64() - tt; tt = clock64();
-                okp = ring.push(k++, src, row_bytes);
-                t_c += clock64() - tt;
+            for (int h = 0; h < cparts && okp; ++h) {
+              if (n <= ring_rows) {
+                for (int i = 0; i < n && okp; ++i) {
+                  tt = clock64();
+                  const uint8_t* src = x + (size_t)(rec[2 + i] & kRowMask) * row_bytes + (size_t)h * seg_bytes;
+                  t_a += clock64() - tt; tt = clock64();
+                  okp = ring.wait(&ring.empty[k % ring.num_slots], ring.phase(k) ^ 1u);
+                  t_b += clock64() - tt; tt = clock64();
+                  okp = ring.push(k++, src, seg_bytes);
+                  t_c += clock64() - tt;
+                }
+              } else {
+                okp = ring.push_empty(k++);
               }
-            } else {
-              okp = ring.push_empty(k++);
             }
           }
         }
@@ -223,60 +238,68 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
       const int cw = warp - 1;
       unsigned q = 0;
       bool dead = false;
-      for (int item = blockIdx.x; item < max_nt * P; item += p.send_blocks) {
-        const int c = item / P, s_rank = (me + item % P) % P;
+      for (int item = blockIdx.x; item < num_items; item += p.send_blocks) {
+        const int part = item % parts, pair = item / parts;
+        const int c = pair / P, s_rank = (me + pair % P) % P;
         if (c * kChunkTokens >= a.rank_tokens[s_rank]) continue;
-        const int j0 = a.chunk_start[s_rank * (NT + 1) + c], j1 = a.chunk_start[s_rank * (NT + 1) + c + 1];
+        const int c0 = a.chunk_start[s_rank * (NT + 1) + c], cn = a.chunk_start[s_rank * (NT + 1) + c + 1] - c0;
+        const int j0 = c0 + cn * part / parts, j1 = c0 + cn * (part + 1) / parts;
         uint8_t* partial = ctx.ws[s_rank] + lay.partial;
         float* wret = reinterpret_cast<float*>(ctx.ws[s_rank] + lay.wret);
-        for (int j = j0; j < j1; ++j, ++q) {
+        for (int j = j0; j < j1; ++j) {
           const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + j) * a.meta_stride;
           const int t = rec[0], n = rec[1];
           const int nslots = n <= ring_rows ? n : 1;
-          if ((int)(q % kConsumerWarps) == cw && !dead) {
+          for (int h = 0; h < cparts; ++h, ++q, k += nslots) {
+            if ((int)(q % kConsumerWarps) != cw || dead) continue;
             tt = clock64();
             for (int i = 0; i < nslots && !dead; ++i) dead = !ring.wait_full(k + i);
             t_a += clock64() - tt; tt = clock64();
-            if (!dead) {
-              if (n > ring_rows) {  // rare: more rows than a group may hold in the ring
-                int4* out = reinterpret_cast<int4*>(ring.slot(k));
-                for (int u = lane; u < units; u += 32) {
-                  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                  for (int i = 0; i < n; ++i)
-                    add_bf16x8(acc, __ldg(reinterpret_cast<const int4*>(x + (size_t)(rec[2 + i] & kRowMask) * row_bytes) + u));
-                  out[u] = pack_bf16x8(acc);
-                }
-                fence_proxy_async_smem();
-              } else if (n > 1) {
-                reduce_slots(ring, k, n, units, lane, nullptr, nullptr);
-                fence_proxy_async_smem();
+            if (dead) continue;
+            if (n > ring_rows) {  // rare: more rows than a group may hold in the ring
+              int4* out = reinterpret_cast<int4*>(ring.slot(k));
+              for (int u = lane; u < seg_units; u += 32) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int i = 0; i < n; ++i)
+                  add_bf16x8(acc, __ldg(reinterpret_cast<const int4*>(x + (size_t)(rec[2 + i] & kRowMask) * row_bytes + (size_t)h * seg_bytes) + u));
+                out[u] = pack_bf16x8(acc);
               }
-              __syncwarp();
-              t_b += clock64() - tt; tt = clock64();
-              if (lane == 0) {
-                for (int i = 1; i < nslots; ++i) ring.release(k + i);
-                store_and_release(ring, k, partial + ((size_t)t * P + me) * row_bytes, row_bytes);
-              }
-              t_c += clock64() - tt;
-              if (a.w) {
-                if (a.expand) {
-                  if (lane < n) wret[(size_t)t * K + (rec[2 + lane] >> kRowSlotShift)] = a.w[rec[2 + lane] & kRowMask];
-                } else if (lane < K && ((rec[3] >> lane) & 1)) {
-                  wret[(size_t)t * K + lane] = a.w[(size_t)(rec[2] & kRowMask) * K + lane];
-                }
+              fence_proxy_async_smem();
+            } else if (n > 1) {
+              reduce_slots(ring, k, n, seg_units, lane, nullptr, nullptr);
+              fence_proxy_async_smem();
+            }
+            __syncwarp();
+            t_b += clock64() - tt; tt = clock64();
+            if (lane == 0) {
+              for (int i = 1; i < nslots; ++i) ring.release(k + i);
+              store_and_release(ring, k, partial + ((size_t)t * P + me) * row_bytes + (size_t)h * seg_bytes, seg_bytes);
+            }
+            t_c += clock64() - tt;
+            if (a.w && h == 0) {
+              if (a.expand) {
+                if (lane < n) wret[(size_t)t * K + (rec[2 + lane] >> kRowSlotShift)] = a.w[rec[2 + lane] & kRowMask];
+              } else if (lane < K && ((rec[3] >> lane) & 1)) {
+                wret[(size_t)t * K + lane] = a.w[(size_t)(rec[2] & kRowMask) * K + lane];
               }
             }
           }
-          k += nslots;
         }
-        // all partials of this (source, chunk) are complete: publish
+        // this part's partials are complete; whoever finishes the last part of the (source, chunk) publishes it
         tt = clock64();
         if (lane == 0) { bulk_wait<0>(); fence_proxy_async(); }
         __threadfence_system();
         consumer_barrier();
         t_d += clock64() - tt;
-        if (warp == 1 && lane == 0 && !ld_volatile_int(&ctl->abort))
-          st_release_sys(&control_of(ctx.ws[s_rank])->comb_chunk[me][c], epoch);
+        if (warp == 1 && lane == 0) {
+          bool last = true;
+          if (parts > 1) {
+            last = atomicAdd(&ctl->comb_parts[s_rank][c], 1u) + 1u == (unsigned)parts;
+            if (last) ctl->comb_parts[s_rank][c] = 0u;     // ready for the next call
+            __threadfence_system();
+          }
+          if (last && !ld_volatile_int(&ctl->abort)) st_release_sys(&control_of(ctx.ws[s_rank])->comb_chunk[me][c], epoch);
+        }
       }
       if (blockIdx.x < 8 && lane == 0) { unsigned long long* d = ctl->dbg + (blockIdx.x * 8 + warp) * 4; d[0] = t_a; d[1] = t_b; d[2] = t_c; d[3] = t_d; }
     }

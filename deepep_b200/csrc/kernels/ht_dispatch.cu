@@ -136,10 +136,15 @@ __global__ void __launch_bounds__(256, 1) ep_dispatch_ht_kernel(const __grid_con
     const uint8_t* stage = ctx.ws[me] + lay.stage;
     const int nsf = H / 128;
     int alive = 1;
-    for (int item = rb; item < max_nt * P && alive; item += p.recv_blocks) {
-      const int c = item / P, r = (me + item % P) % P;
+    // With few ranks there are fewer (source, chunk) pairs than receiver blocks: a chunk's rows are then cut into up
+    // to 8 parts that different blocks expand (about two rounds of work items over the blocks).
+    const int parts = max(1, min(8, (2 * p.recv_blocks + max_nt * P - 1) / max(1, max_nt * P)));
+    for (int item = rb; item < max_nt * P * parts && alive; item += p.recv_blocks) {
+      const int part = item % parts, pair = item / parts;
+      const int c = pair / P, r = (me + pair % P) % P;
       if (c * kChunkTokens >= a.rank_tokens[r]) continue;
-      const int j0 = a.chunk_start[r * (NT + 1) + c], j1 = a.chunk_start[r * (NT + 1) + c + 1];
+      const int c0 = a.chunk_start[r * (NT + 1) + c], cn = a.chunk_start[r * (NT + 1) + c + 1] - c0;
+      const int j0 = c0 + cn * part / parts, j1 = c0 + cn * (part + 1) / parts;
       if (j0 == j1) continue;
       int ok = 1;
       if (threadIdx.x == 0) ok = wait_flag_ge(&ctl->disp_chunk[r][c], epoch, ctx, kOpDispatch, 1, r);

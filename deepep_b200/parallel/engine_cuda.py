@@ -80,7 +80,11 @@ class CudaEngine:
         per_rank = max(2, self.sm_count // self.n)
         # Measured on 8 B200s: one SM moves about 30 GB/s through its copy engine, so saturating NVLink takes dozens
         # of SMs.  Defaults: dispatch 96 blocks (1/4 senders), combine nearly all SMs (3/4 on the expert side).
-        self.dispatch_blocks = min(per_rank, num_sms) if num_sms else min(per_rank, 96)
+        # With one or two ranks most of the traffic is the receive-side expansion in local memory, which scales with the
+        # number of SMs (about 30 GB/s each): use them all.
+        self.dispatch_blocks = min(per_rank, num_sms) if num_sms else min(per_rank, 96 if self.world > 2 else max(2, self.sm_count - 4))
+        # senders move one row per (token, destination rank), receivers up to top-k rows per received token
+        self.dispatch_send_fraction = 0.25 if self.world > 2 else 0.125
         self.combine_blocks = min(per_rank, num_sms) if num_sms else min(per_rank, max(2, self.sm_count - 4))
         self.default_blocks = self.dispatch_blocks
         nt = -(-layout.max_tokens // self.C.chunk_tokens)
@@ -226,7 +230,7 @@ class CudaEngine:
                              stage_meta=plan.stage_meta.data_ptr(), chunk_start=plan.chunk_start.data_ptr(),
                              rank_tokens=plan.rank_tokens.data_ptr(), meta_stride=plan.meta_stride,
                              recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf)))
-        send, recv = self.split_blocks(blocks, 0.25, self.dispatch_blocks)
+        send, recv = self.split_blocks(blocks, self.dispatch_send_fraction, self.dispatch_blocks)
         self._timed("dispatch", stream, lambda: self.C.dispatch(lay, self.sessions, args, send, recv, self._stream(stream)))
         return outs
 
