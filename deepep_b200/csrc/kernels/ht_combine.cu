@@ -10,8 +10,9 @@
 // The optional fp32 value channel (used for dispatch-backward) is returned per slot and is
 // never multiplied into the payload.
 //
-// Both sides are the same shared-memory ring pipeline: warp 0 streams whole rows into a ring
-// of row slots with bulk copies (up to ~220 KB in flight per SM), warps 1..7 each take every
+// Both sides are the same shared-memory ring pipeline: warp 0 streams rows into a ring of row
+// slots with bulk copies (up to ~220 KB in flight per SM; its lanes fill the slots of a batch of
+// groups in parallel), warps 1..7 each take every
 // 7th group, wait for the group's slots, reduce them in place from shared memory and hand the
 // result to a bulk store.  Row movement never touches registers unless a sum is needed.
 //
@@ -84,6 +85,24 @@ struct Ring {
     __threadfence_block();
     *issued = k + 1;
     return true;
+  }
+  // Lane-parallel variants: several lanes of the producer warp each fill one slot of a batch; the caller publishes the
+  // batch afterwards with publish().  Issuing the copies from several lanes overlaps the waits and the issue latency
+  // that a single producer thread pays one after the other (about 0.25 us per copy).
+  __device__ __forceinline__ bool fill(unsigned k, const void* src, uint32_t bytes) const {
+    if (!wait(&empty[k % num_slots], phase(k) ^ 1u)) return false;
+    mbar_expect_tx(&full[k % num_slots], bytes);
+    bulk_g2s(slot(k), src, bytes, &full[k % num_slots]);
+    return true;
+  }
+  __device__ __forceinline__ bool fill_empty(unsigned k) const {
+    if (!wait(&empty[k % num_slots], phase(k) ^ 1u)) return false;
+    mbar_arrive(&full[k % num_slots]);
+    return true;
+  }
+  __device__ __forceinline__ void publish(unsigned k_end) const {   // one lane, after __syncwarp()
+    __threadfence_block();
+    *issued = k_end;
   }
   __device__ __forceinline__ bool push_empty(unsigned k) const {
     if (!wait(&empty[k % num_slots], phase(k) ^ 1u)) return false;
@@ -202,37 +221,56 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
     unsigned k = 0;
     long long t_a = 0, t_b = 0, t_c = 0, t_d = 0, t0 = clock64(), tt;
     if (warp == 0) {
-      if (lane == 0) {
-        bool okp = true;
-        for (int item = blockIdx.x; item < num_items && okp; item += p.send_blocks) {
-          const int part = item % parts, pair = item / parts;
-          const int c = pair / P, s_rank = (me + pair % P) % P;
-          if (c * kChunkTokens >= a.rank_tokens[s_rank]) continue;
-          const int c0 = a.chunk_start[s_rank * (NT + 1) + c], cn = a.chunk_start[s_rank * (NT + 1) + c + 1] - c0;
-          const int j0 = c0 + cn * part / parts, j1 = c0 + cn * (part + 1) / parts;
-          for (int j = j0; j < j1 && okp; ++j) {
-            const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + j) * a.meta_stride;
-            tt = clock64();
-            const int n = rec[1];
-            t_a += clock64() - tt;
-            for (int h = 0; h < cparts && okp; ++h) {
-              if (n <= ring_rows) {
-                for (int i = 0; i < n && okp; ++i) {
-                  tt = clock64();
-                  const uint8_t* src = x + (size_t)(rec[2 + i] & kRowMask) * row_bytes + (size_t)h * seg_bytes;
-                  t_a += clock64() - tt; tt = clock64();
-                  okp = ring.wait(&ring.empty[k % ring.num_slots], ring.phase(k) ^ 1u);
-                  t_b += clock64() - tt; tt = clock64();
-                  okp = ring.push(k++, src, seg_bytes);
-                  t_c += clock64() - tt;
-                }
-              } else {
-                okp = ring.push_empty(k++);
-              }
-            }
+      // Producer: the whole warp.  A batch takes up to 8 consecutive records whose slots fit the ring; lane l fills
+      // the l-th slot of the batch (record r, column part h, row i), then lane 0 publishes the batch.
+      bool okp = true;
+      for (int item = blockIdx.x; item < num_items && okp; item += p.send_blocks) {
+        const int part = item % parts, pair = item / parts;
+        const int c = pair / P, s_rank = (me + pair % P) % P;
+        if (c * kChunkTokens >= a.rank_tokens[s_rank]) continue;
+        const int c0 = a.chunk_start[s_rank * (NT + 1) + c], cn = a.chunk_start[s_rank * (NT + 1) + c + 1] - c0;
+        const int j0 = c0 + cn * part / parts, j1 = c0 + cn * (part + 1) / parts;
+        const int cap = min(32, ring.num_slots);
+        for (int jb = j0; jb < j1 && okp;) {
+          // lanes 0..7: slots of record jb + lane
+          int my_n = 0, my_slots = 0;
+          if (lane < 8 && jb + lane < j1) {
+            my_n = a.stage_meta[((size_t)s_rank * Tmax + jb + lane) * a.meta_stride + 1];
+            my_slots = (my_n <= ring_rows ? my_n : 1) * cparts;
           }
+          int incl = my_slots;
+#pragma unroll
+          for (int d = 1; d < 8; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += o;
+          }
+          // records taken: those whose slots end within the capacity (at least the first one)
+          const unsigned fit = __ballot_sync(0xffffffffu, lane < 8 && jb + lane < j1 && (incl <= cap || lane == 0));
+          const int count = __ffs(~fit) - 1;                       // fit is a run of ones from bit 0
+          const int total = __shfl_sync(0xffffffffu, incl, count - 1);
+          // lane l -> (record r, index inside the record)
+          int r = 0, base = 0;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int e = __shfl_sync(0xffffffffu, incl, q);
+            if (q < count && lane >= e) { r = q + 1; base = e; }
+          }
+          int ok = 1;
+          if (lane < total) {
+            const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + jb + r) * a.meta_stride;
+            const int n = rec[1], nn = n <= ring_rows ? n : 1;
+            const int idx = lane - base, h = idx / nn, i = idx - h * nn;
+            if (n <= ring_rows)
+              ok = ring.fill(k + lane, x + (size_t)(rec[2 + i] & kRowMask) * row_bytes + (size_t)h * seg_bytes, seg_bytes);
+            else
+              ok = ring.fill_empty(k + lane);
+          }
+          okp = __all_sync(0xffffffffu, ok);
+          __syncwarp();
+          if (lane == 0 && okp) ring.publish(k + total);
+          k += total;
+          jb += count;
         }
-        if (blockIdx.x < 8) { unsigned long long* d = ctl->dbg + (blockIdx.x * 8 + warp) * 4; d[0] = t_a; d[1] = t_b; d[2] = t_c; d[3] = clock64() - t0; }
       }
     } else {
       const int cw = warp - 1;
@@ -320,16 +358,36 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
         if (!okp) break;
         fence_proxy_async();
         const int t1 = min(a.T, (c + 1) * kChunkTokens);
-        for (int t = c * kChunkTokens; t < t1 && okp; ++t) {
-          const int slot = lane < P ? a.send_slot[(size_t)t * P + lane] : -1;
-          unsigned mask = __ballot_sync(0xffffffffu, slot >= 0);
-          if (lane == 0) {
-            if (mask == 0 || __popc(mask) > ring_rows) { okp = ring.push_empty(k++); mask = 0; }
-            for (; mask && okp; mask &= mask - 1)
-              okp = ring.push(k++, partial + ((size_t)t * P + (__ffs(mask) - 1)) * row_bytes, row_bytes);
+        // four tokens per batch: lane = (token, rank); every partial of the batch is loaded by its own lane
+        const int cap = min(32, ring.num_slots);
+        for (int t = c * kChunkTokens; t < t1 && okp;) {
+          const int tt = lane >> 3, d = lane & 7;
+          const bool has = d < P && t + tt < t1 && a.send_slot[(size_t)(t + tt) * P + d] >= 0;
+          const unsigned m32 = __ballot_sync(0xffffffffu, has);
+          int off[5], take = 0;
+          off[0] = 0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int n = __popc((m32 >> (8 * q)) & 0xffu);
+            const int ns = (n && n <= ring_rows) ? n : 1;
+            off[q + 1] = off[q] + ns;
+            if (t + q < t1 && (off[q + 1] <= cap || q == 0) && take == q) take = q + 1;
           }
-          okp = __shfl_sync(0xffffffffu, okp, 0);
-          k = __shfl_sync(0xffffffffu, k, 0);
+          int ok = 1;
+          if (tt < take) {
+            const unsigned seg = (m32 >> (8 * tt)) & 0xffu;
+            const int n = __popc(seg);
+            if (n && n <= ring_rows) {
+              if (has) ok = ring.fill(k + off[tt] + __popc(seg & ((1u << d) - 1u)), partial + ((size_t)(t + tt) * P + d) * row_bytes, row_bytes);
+            } else if (d == 0) {
+              ok = ring.fill_empty(k + off[tt]);
+            }
+          }
+          okp = __all_sync(0xffffffffu, ok);
+          __syncwarp();
+          if (lane == 0 && okp) ring.publish(k + off[take]);
+          k += off[take];
+          t += take;
         }
       }
     } else {
