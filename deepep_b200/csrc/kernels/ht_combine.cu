@@ -24,7 +24,8 @@
 
 namespace dep {
 
-constexpr int kRingMaxSlots = 32;
+constexpr int kRingMaxSlots = 56;    // 2 x 56 barriers + the fill counter fit the 1 KB ring header
+constexpr int kStreamUnits = 7;      // 16-byte pieces per lane of a quarter row (hidden <= 7168) in the streaming reduction
 constexpr int kRingMaxRows = 8;      // larger groups are summed straight from global memory (see ring_rows)
 constexpr int kCombineThreads = 256;
 constexpr int kConsumerWarps = kCombineThreads / 32 - 1;
@@ -180,8 +181,11 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
 
   const bool expert_side = (int)blockIdx.x < p.send_blocks;
   // With one or two ranks a token has up to top-k rows on this rank, and a ring of ~15 whole rows cannot hold two such
-  // groups: the expert side then works on half rows, so that the next group loads while the current one is reduced.
-  const int cparts = (expert_side && P <= 2 && (row_bytes / 2) % 128 == 0) ? 2 : 1;
+  // groups: the expert side then works on quarter (or half) rows, so that later groups load while one is reduced.
+  // Quarter rows also let a consumer keep a group's running sum in registers and hand every slot back as soon as it
+  // has been added (`stream`), which turns the ring into a FIFO whose throughput is its size over the load latency.
+  const int cparts = !(expert_side && P <= 2) ? 1 : (row_bytes / 4) % 128 == 0 ? 4 : (row_bytes / 2) % 128 == 0 ? 2 : 1;
+  const bool stream = cparts == 4 && units / 4 <= 32 * kStreamUnits;
   const int seg_bytes = row_bytes / cparts, seg_units = units / cparts;
   Ring ring;
   ring.slot_bytes = (seg_bytes + 127) & ~127;
@@ -291,6 +295,44 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
           for (int h = 0; h < cparts; ++h, ++q, k += nslots) {
             if ((int)(q % kConsumerWarps) != cw || dead) continue;
             tt = clock64();
+            if (stream && n > 1 && n <= ring_rows) {
+              // running sum in registers (fp32, slot order); every slot but the last goes back as soon as it was added
+              float acc[kStreamUnits][8];
+#pragma unroll
+              for (int v = 0; v < kStreamUnits; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[v][e] = 0.f;
+              for (int i = 0; i < n && !dead; ++i) {
+                dead = !ring.wait_full(k + i);
+                if (dead) break;
+                const int4* row = reinterpret_cast<const int4*>(ring.slot(k + i));
+#pragma unroll
+                for (int v = 0; v < kStreamUnits; ++v)
+                  if (lane + 32 * v < seg_units) add_bf16x8(acc[v], row[lane + 32 * v]);
+                if (i + 1 < n) {
+                  __syncwarp();
+                  if (lane == 0) ring.release(k + i);
+                }
+              }
+              if (dead) continue;
+              int4* out = reinterpret_cast<int4*>(ring.slot(k + n - 1));
+#pragma unroll
+              for (int v = 0; v < kStreamUnits; ++v)
+                if (lane + 32 * v < seg_units) out[lane + 32 * v] = pack_bf16x8(acc[v]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              t_b += clock64() - tt; tt = clock64();
+              if (lane == 0) store_and_release(ring, k + n - 1, partial + ((size_t)t * P + me) * row_bytes + (size_t)h * seg_bytes, seg_bytes);
+              t_c += clock64() - tt;
+              if (a.w && h == 0) {
+                if (a.expand) {
+                  if (lane < n) wret[(size_t)t * K + (rec[2 + lane] >> kRowSlotShift)] = a.w[rec[2 + lane] & kRowMask];
+                } else if (lane < K && ((rec[3] >> lane) & 1)) {
+                  wret[(size_t)t * K + lane] = a.w[(size_t)(rec[2] & kRowMask) * K + lane];
+                }
+              }
+              continue;
+            }
             for (int i = 0; i < nslots && !dead; ++i) dead = !ring.wait_full(k + i);
             t_a += clock64() - tt; tt = clock64();
             if (dead) continue;
