@@ -121,3 +121,56 @@ def test_row_counts_that_do_not_fit_are_reported():
             eng.check()
     finally:
         s.close()
+
+
+def _real_worker(rank, world, port, results):
+    import os
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        E, K, N, max_rows = 8, 256, 320, 600
+        L = E // world
+        counts = _counts(world, E, max_rows, 21, empty_expert=3)
+        gen = torch.Generator().manual_seed(22)
+        xs = [torch.randn((sum(c), K), generator=gen).to(torch.bfloat16) for c in counts]
+        ws = [(torch.randn((L, K, N), generator=gen) / K ** 0.5).to(torch.bfloat16) for _ in range(world)]
+        ws2 = [(torch.randn((L, K, N), generator=gen) / K ** 0.5).to(torch.bfloat16) for _ in range(world)]
+        ref_out, ref_g = G.reference_alltoallv_gmm(xs, ws, counts, E)
+        ref_back = G.reference_gmm_alltoallv(ref_g, ws2, counts, E)
+        G.init_group(dist.group.WORLD, max_rows=max_rows, max_k=K, max_n=N, timeout=30.0)
+        glob = [counts[s][rank * L + l] for s in range(world) for l in range(L)]
+        for rep in range(2):
+            out, gathered = G.alltoallv_gmm(xs[rank].to(dev), ws[rank].to(dev), counts[rank], torch.tensor(glob, device=dev),
+                                            ep_size=world, expert_num=E, output_all_to_allv=True)
+            back = G.gmm_alltoallv(gathered, ws2[rank].to(dev), torch.tensor(counts[rank], device=dev), glob, ep_size=world, expert_num=E)
+            torch.cuda.synchronize()
+            assert torch.equal(gathered.cpu(), ref_g[rank])
+            _close(out, ref_out[rank], f"a2av_gmm rank {rank} rep {rep}")
+            _close(back, ref_back[rank], f"gmm_a2av rank {rank} rep {rep}")
+        results[rank] = True
+    except Exception as exc:  # surfaced by the parent
+        results[rank] = repr(exc)
+    finally:
+        G.destroy_group()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_real_ranks_public_api(world):
+    import socket
+
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    results = mp.Manager().dict()
+    mp.spawn(_real_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {r: True for r in range(world)}
