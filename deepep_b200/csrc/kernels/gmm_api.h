@@ -12,7 +12,7 @@
 
 namespace dep {
 
-constexpr int kGmmBM = 128;   // rows per tile (TMEM lanes)
+constexpr int kGmmBM = 128;   // rows per accumulator (TMEM lanes); a2av_gmm tiles hold two of them
 constexpr int kGmmBN = 256;   // output columns per tile
 constexpr int kGmmBK = 64;    // K elements per pipeline stage (one 128-byte swizzle row of bf16)
 constexpr int kGmmTableInts = 4 + kMaxExperts + 1;   // header (rows, -, -, -) + exclusive prefix of the per-expert row counts

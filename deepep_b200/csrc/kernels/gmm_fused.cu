@@ -34,14 +34,19 @@ constexpr int kGmmMaxStages = 4;
 constexpr int kGmmTileA = kGmmBM * kGmmBK * 2;           // 16 KB
 constexpr int kGmmBoxB = 64 * kGmmBK * 2;                // 8 KB: 64 K-rows of 64 N-values
 constexpr int kGmmTileB = (kGmmBN / 64) * kGmmBoxB;      // 32 KB
-constexpr int kGmmStageBytes = kGmmTileA + kGmmTileB;
 constexpr int kGmmEpiBytes = 8 * 32 * (kGmmBN / 2) * 2;  // bf16 staging: each epilogue warp parks its 32 x 128 block
 constexpr int kGmmPullChunk = 8;
-// Rows pushed to a peer are first parked in shared memory so that they leave as 256-byte segments (3 stages + staging);
-// rows stored locally go straight from registers (4 stages, no staging).
-__host__ __device__ constexpr int gmm_stages(bool push) { return push ? 3 : 4; }
+// Rows pushed to a peer are first parked in shared memory so that they leave as 256-byte segments (3 stages of 48 KB +
+// staging, 128-row tiles, the second accumulator overlaps a tile's epilogue with the next tile's MMAs); rows stored
+// locally go straight from registers (3 stages of 64 KB, 256-row tiles).
+// Rows stored locally use 256-row tiles: both 128-lane accumulators (all 512 tensor-memory columns) belong to one tile,
+// the two row halves share every B stage, and a stage moves 64 KB for twice the work (the kernel is bound by the
+// rate at which shared memory can be filled from L2, about 100 KB/us per SM, not by the tensor pipe).
+__host__ __device__ constexpr int gmm_tile_rows(bool push) { return push ? kGmmBM : 2 * kGmmBM; }
+__host__ __device__ constexpr int gmm_stage_bytes(bool push) { return (gmm_tile_rows(push) / kGmmBM) * kGmmTileA + kGmmTileB; }
+__host__ __device__ constexpr int gmm_stages(bool push) { return 3; }
 __host__ __device__ constexpr size_t gmm_smem_bytes(bool push) {
-  return 1024 + (size_t)gmm_stages(push) * kGmmStageBytes + (push ? kGmmEpiBytes : 0) + 256;
+  return 1024 + (size_t)gmm_stages(push) * gmm_stage_bytes(push) + (push ? kGmmEpiBytes : 0) + 256;
 }
 
 struct GmmBarriers {
@@ -107,7 +112,7 @@ __device__ __forceinline__ void publish_table(const GmmArgs& a, int* table, int 
 
 // Segments (local expert, source rank) of this rank's gathered order, from every rank's table.  Run by all threads
 // of every block (each block keeps its own copy in shared memory); block 0 also writes the tile list.
-__device__ __forceinline__ void build_layout(const GmmArgs& a, GmmShared& sh, int alive, int gathered_cap) {
+__device__ __forceinline__ void build_layout(const GmmArgs& a, GmmShared& sh, int alive, int gathered_cap, int tile_rows) {
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, L = a.E / P;
   int bad = 0;
@@ -128,7 +133,7 @@ __device__ __forceinline__ void build_layout(const GmmArgs& a, GmmShared& sh, in
       const int begin = run;
       for (int s = 0; s < P; ++s) { run += sh.seg_dst[l * P + s + 1]; sh.seg_dst[l * P + s + 1] = run; }
       sh.tile0[l] = tiles;
-      tiles += (run - begin + kGmmBM - 1) / kGmmBM;
+      tiles += (run - begin + tile_rows - 1) / tile_rows;
     }
     sh.tile0[L] = tiles;
     const bool fits = !bad && run <= gathered_cap && tiles <= a.max_tiles;
@@ -141,8 +146,8 @@ __device__ __forceinline__ void build_layout(const GmmArgs& a, GmmShared& sh, in
   if (blockIdx.x == 0) {
     for (int l = threadIdx.x; l < L; l += (int)blockDim.x) {
       const int begin = sh.seg_dst[l * P], rows = sh.seg_dst[(l + 1) * P] - begin;
-      for (int t = 0; sh.alive && t * kGmmBM < rows; ++t)
-        reinterpret_cast<int4*>(a.tile_info)[sh.tile0[l] + t] = make_int4(l, begin + t * kGmmBM, min(kGmmBM, rows - t * kGmmBM), 0);
+      for (int t = 0; sh.alive && t * tile_rows < rows; ++t)
+        reinterpret_cast<int4*>(a.tile_info)[sh.tile0[l] + t] = make_int4(l, begin + t * tile_rows, min(tile_rows, rows - t * tile_rows), 0);
     }
     if (threadIdx.x == 0) { a.num_tiles[0] = sh.num_tiles; a.num_tiles[1] = sh.total_rows; }
   }
@@ -169,7 +174,7 @@ __device__ __forceinline__ void pull_phase(const GmmArgs& a, const GmmShared& sh
       const int r = row0 + lane, seg = find_segment(sh, a.E, r), l = seg / P;
       src_rank = seg - l * P;
       src_row = sh.seg_src[seg] + (r - sh.seg_dst[seg]);
-      tile = sh.tile0[l] + (r - sh.seg_dst[l * P]) / kGmmBM;
+      tile = sh.tile0[l] + (r - sh.seg_dst[l * P]) / gmm_tile_rows(false);
     }
 #pragma unroll 1
     for (int c = 0; c < kGmmPullChunk; ++c) {
@@ -195,6 +200,9 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
   constexpr int kGmmStages = gmm_stages(kPush);
+  constexpr int kHalves = gmm_tile_rows(kPush) / kGmmBM;      // 128-row halves of a tile, one accumulator each
+  constexpr int kGmmStageBytes = gmm_stage_bytes(kPush);
+  constexpr int kOffB = kHalves * kGmmTileA;                  // B follows the A halves inside a stage
   uint8_t* epi_smem = tiles + (size_t)kGmmStages * kGmmStageBytes;
   GmmBarriers* bars = reinterpret_cast<GmmBarriers*>(epi_smem + (kPush ? kGmmEpiBytes : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -237,10 +245,12 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
           if (!bounded_wait(&bars->empty[s], ((it / kGmmStages) & 1u) ^ 1u, failed)) break;
           uint8_t* dst = tiles + (size_t)s * kGmmStageBytes;
           mbar_expect_tx(&bars->full[s], kGmmStageBytes);
-          umma::tma_load_2d(dst, &a.tmap_a, ks * kGmmBK, info.y, &bars->full[s]);
+#pragma unroll
+          for (int m = 0; m < kHalves; ++m)       // rows past the end of the operand are filled with zeros
+            umma::tma_load_2d(dst + m * kGmmTileA, &a.tmap_a, ks * kGmmBK, info.y + m * kGmmBM, &bars->full[s]);
 #pragma unroll
           for (int j = 0; j < kGmmBN / 64; ++j)   // a box past the last column is filled with zeros
-            umma::tma_load_2d(dst + kGmmTileA + j * kGmmBoxB, &a.tmap_b, nb * kGmmBN + j * 64, info.x * a.K + ks * kGmmBK, &bars->full[s]);
+            umma::tma_load_2d(dst + kOffB + j * kGmmBoxB, &a.tmap_b, nb * kGmmBN + j * 64, info.x * a.K + ks * kGmmBK, &bars->full[s]);
         }
       }
     }
@@ -250,19 +260,24 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
       const uint32_t idesc = instr_desc_bf16(kGmmBM, kGmmBN);
       uint32_t it = 0, local_tile = 0;
       for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas, ++local_tile) {
-        const uint32_t b = local_tile & 1u;
-        if (!bounded_wait(&bars->acc_empty[b], ((local_tile >> 1) & 1u) ^ 1u, failed)) break;
+        // one accumulator pair per tile (256-row tiles) or two alternating accumulators (128-row tiles)
+        const uint32_t b = kHalves == 2 ? 0u : (local_tile & 1u);
+        const uint32_t use = kHalves == 2 ? local_tile : (local_tile >> 1);
+        if (!bounded_wait(&bars->acc_empty[b], (use & 1u) ^ 1u, failed)) break;
         umma::fence_after_sync();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kGmmStages;
           if (!bounded_wait(&bars->full[s], (it / kGmmStages) & 1u, failed)) break;
           umma::fence_after_sync();
           const uint32_t a_addr = smem_u32(tiles + (size_t)s * kGmmStageBytes);
-          const uint64_t da = umma::smem_desc_sw128(a_addr);
-          const uint64_t db = smem_desc_mn_sw128(a_addr + kGmmTileA, kGmmBoxB);
+          const uint64_t db = smem_desc_mn_sw128(a_addr + kOffB, kGmmBoxB);
 #pragma unroll
-          for (int k = 0; k < kGmmBK / 16; ++k)   // A: 16 values = 32 bytes inside the swizzle row; B: 16 K-rows = 2048 bytes
-            mma_f16(tmem + b * kGmmBN, da + 2 * k, db + (uint64_t)(16 * 128 / 16) * k, idesc, ks > 0 || k > 0);
+          for (int m = 0; m < kHalves; ++m) {
+            const uint64_t da = umma::smem_desc_sw128(a_addr + m * kGmmTileA);
+#pragma unroll
+            for (int k = 0; k < kGmmBK / 16; ++k)   // A: 16 values = 32 bytes inside the swizzle row; B: 16 K-rows = 2048 bytes
+              mma_f16(tmem + (kHalves == 2 ? m : b) * kGmmBN, da + 2 * k, db + (uint64_t)(16 * 128 / 16) * k, idesc, ks > 0 || k > 0);
+          }
           umma::commit(&bars->empty[s]);
         }
         umma::commit(&bars->acc_full[b]);
@@ -279,42 +294,35 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
     for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas, ++local_tile) {
       const int mt = tile / n_tiles, nb = tile - mt * n_tiles;
       const int4 info = __ldcg(tile_info + mt);
-      const uint32_t b = local_tile & 1u;
-      // where this thread's row goes
-      uint8_t* dst_row = nullptr;
-      if (row_in_tile < info.z) {
-        const int g = info.y + row_in_tile;
-        if (!kPush) {
-          dst_row = reinterpret_cast<uint8_t*>(a.out) + ((size_t)g * a.N + (size_t)nb * kGmmBN) * 2;
-        } else {
-          int seg = info.x * P;
-          while (seg + 1 < (info.x + 1) * P && sh.seg_dst[seg + 1] <= g) ++seg;
-          const int s = seg - info.x * P;
-          const long long r = sh.seg_src[seg] + (g - sh.seg_dst[seg]);
-          dst_row = a.ctx.ws[s] + a.data_off + ((size_t)r * a.N + (size_t)nb * kGmmBN) * 2;
-        }
-      }
-      if (!bounded_wait(&bars->acc_full[b], (local_tile >> 1) & 1u, failed)) break;
-      umma::fence_after_sync();
-      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + b * kGmmBN + part * kCols;
+      const uint32_t b = kHalves == 2 ? 0u : (local_tile & 1u);
+      const uint32_t use = kHalves == 2 ? local_tile : (local_tile >> 1);
       if (!kPush) {
-        // each thread stores its row's columns straight from registers: 64 contiguous bytes per 32 columns
-        uint32_t v[32];
-        for (int c = 0; c < kCols; c += 32) {
-          umma::tmem_ld32(taddr + c, v);
-          umma::tmem_ld_wait();
-          const int col = nb * kGmmBN + part * kCols + c;
-          if (dst_row && col < a.N) {
-            uint4* dst = reinterpret_cast<uint4*>(dst_row + (size_t)(part * kCols + c) * 2);
+        // 256-row tile: this warp drains its 32 lanes of both accumulators (rows m * 128 + quad * 32 + lane); each
+        // thread stores its row's columns straight from registers, 64 contiguous bytes per 32 columns
+        if (!bounded_wait(&bars->acc_full[b], use & 1u, failed)) break;
+        umma::fence_after_sync();
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t w0[4];
+        for (int m = 0; m < kHalves; ++m) {
+          const int r = m * kGmmBM + row_in_tile;
+          uint8_t* dst_row = r < info.z ? reinterpret_cast<uint8_t*>(a.out) + ((size_t)(info.y + r) * a.N + (size_t)nb * kGmmBN) * 2 : nullptr;
+          const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + m * kGmmBN + part * kCols;
+          uint32_t v[32];
+          for (int c = 0; c < kCols; c += 32) {
+            umma::tmem_ld32(taddr + c, v);
+            umma::tmem_ld_wait();
+            const int col = nb * kGmmBN + part * kCols + c;
+            if (dst_row && col < a.N) {
+              uint4* dst = reinterpret_cast<uint4*>(dst_row + (size_t)(part * kCols + c) * 2);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-                w0[j] = *reinterpret_cast<uint32_t*>(&b0);
+              for (int i = 0; i < 4; ++i) {
+                uint32_t w0[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                  w0[j] = *reinterpret_cast<uint32_t*>(&b0);
+                }
+                dst[i] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
               }
-              dst[i] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
             }
           }
         }
@@ -323,6 +331,19 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
         if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
         continue;
       }
+      // where this thread's row goes: the rank it came from
+      uint8_t* dst_row = nullptr;
+      if (row_in_tile < info.z) {
+        const int g = info.y + row_in_tile;
+        int seg = info.x * P;
+        while (seg + 1 < (info.x + 1) * P && sh.seg_dst[seg + 1] <= g) ++seg;
+        const int s = seg - info.x * P;
+        const long long r = sh.seg_src[seg] + (g - sh.seg_dst[seg]);
+        dst_row = a.ctx.ws[s] + a.data_off + ((size_t)r * a.N + (size_t)nb * kGmmBN) * 2;
+      }
+      if (!bounded_wait(&bars->acc_full[b], use & 1u, failed)) break;
+      umma::fence_after_sync();
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + b * kGmmBN + part * kCols;
       // 1) drain this warp's 32 x 128 block into shared memory as bf16 and hand the accumulator back
       uint4* mine = reinterpret_cast<uint4*>(stage + (size_t)lane * kCols * 2);   // 256 B per row = 16 pieces
       __syncwarp();                                     // the previous tile's block has been written out
@@ -408,7 +429,7 @@ __global__ void __launch_bounds__(kGmmGemmThreads + kGmmPullWarps * 32, 1) a2av_
   if (threadIdx.x < P) ok = wait_flag_ge(&ctl->gmm_flag[threadIdx.x][0], epoch, ctx, kOpA2avGmm, 1, threadIdx.x);
   alive = __syncthreads_and(ok) && alive;
 
-  build_layout(a, sh, alive, min(a.gathered_cap, a.out_rows_cap));
+  build_layout(a, sh, alive, min(a.gathered_cap, a.out_rows_cap), gmm_tile_rows(false));
   __threadfence();
   grid.sync();
 
@@ -447,7 +468,7 @@ __global__ void __launch_bounds__(kGmmGemmThreads, 1) gmm_a2av_kernel(const __gr
   if (threadIdx.x < P) ok = wait_flag_ge(&ctl->gmm_flag[threadIdx.x][2], epoch, ctx, kOpGmmA2av, 0, threadIdx.x);
   int alive = __syncthreads_and(ok);
 
-  build_layout(a, sh, alive, a.rows_in);
+  build_layout(a, sh, alive, a.rows_in, gmm_tile_rows(true));
   __threadfence();
   grid.sync();
   gmm_phase<true>(a, sh, nullptr, smem_raw, blockIdx.x, gridDim.x);
