@@ -8,10 +8,12 @@
 //                     into the workspace of the rank the row came from, at its place in that rank's expert-sorted
 //                     order; after a flag handshake every rank copies its returned rows into the output tensor.
 //
-// GEMM: 128 x 256 tiles, K in steps of 64, A K-major and B (weights [K, N], N contiguous) MN-major, both moved by
-// TMA with the 128-byte swizzle, four tcgen05.mma kind::f16 (K = 16) per stage, fp32 accumulators double-buffered
-// in tensor memory (2 x 256 columns) so that a tile's epilogue overlaps the next tile's MMAs.  Expert row blocks are
-// not padded: a tile that reaches past its expert's rows computes rows that the epilogue drops.
+// GEMM: 256 x 256 tiles, K in steps of 64, A K-major and B (weights [K, N], N contiguous) MN-major, both moved by
+// TMA with the 128-byte swizzle; per stage two groups of four tcgen05.mma kind::f16 (M = 128, N = 256, K = 16), one
+// group per 128-row half of the tile, each half with its own fp32 accumulator in tensor memory (2 x 256 columns).
+// The two halves share every B stage: the kernel is bound by the rate at which one SM's shared memory is filled
+// from L2 (measured about 100 KB/us), and the shared B cuts the bytes per FLOP by a third against 128-row tiles.
+// Expert row blocks are not padded: a tile that reaches past its expert's rows computes rows that the epilogue drops.
 // Every wait is bounded; a wait that runs out sets the error flag, the CTA stops issuing work, frees its tensor
 // memory and returns.
 //
@@ -34,19 +36,15 @@ constexpr int kGmmMaxStages = 4;
 constexpr int kGmmTileA = kGmmBM * kGmmBK * 2;           // 16 KB
 constexpr int kGmmBoxB = 64 * kGmmBK * 2;                // 8 KB: 64 K-rows of 64 N-values
 constexpr int kGmmTileB = (kGmmBN / 64) * kGmmBoxB;      // 32 KB
-constexpr int kGmmEpiBytes = 8 * 32 * (kGmmBN / 2) * 2;  // bf16 staging: each epilogue warp parks its 32 x 128 block
 constexpr int kGmmPullChunk = 8;
-// Rows pushed to a peer are first parked in shared memory so that they leave as 256-byte segments (3 stages of 48 KB +
-// staging, 128-row tiles, the second accumulator overlaps a tile's epilogue with the next tile's MMAs); rows stored
-// locally go straight from registers (3 stages of 64 KB, 256-row tiles).
-// Rows stored locally use 256-row tiles: both 128-lane accumulators (all 512 tensor-memory columns) belong to one tile,
+// Tiles are 256 rows x 256 columns: both 128-lane accumulators (all 512 tensor-memory columns) belong to one tile,
 // the two row halves share every B stage, and a stage moves 64 KB for twice the work (the kernel is bound by the
 // rate at which shared memory can be filled from L2, about 100 KB/us per SM, not by the tensor pipe).
-__host__ __device__ constexpr int gmm_tile_rows(bool push) { return push ? kGmmBM : 2 * kGmmBM; }
+__host__ __device__ constexpr int gmm_tile_rows(bool) { return 2 * kGmmBM; }
 __host__ __device__ constexpr int gmm_stage_bytes(bool push) { return (gmm_tile_rows(push) / kGmmBM) * kGmmTileA + kGmmTileB; }
 __host__ __device__ constexpr int gmm_stages(bool push) { return 3; }
 __host__ __device__ constexpr size_t gmm_smem_bytes(bool push) {
-  return 1024 + (size_t)gmm_stages(push) * gmm_stage_bytes(push) + (push ? kGmmEpiBytes : 0) + 256;
+  return 1024 + (size_t)gmm_stages(push) * gmm_stage_bytes(push) + 256;
 }
 
 struct GmmBarriers {
@@ -204,7 +202,7 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
   constexpr int kGmmStageBytes = gmm_stage_bytes(kPush);
   constexpr int kOffB = kHalves * kGmmTileA;                  // B follows the A halves inside a stage
   uint8_t* epi_smem = tiles + (size_t)kGmmStages * kGmmStageBytes;
-  GmmBarriers* bars = reinterpret_cast<GmmBarriers*>(epi_smem + (kPush ? kGmmEpiBytes : 0));
+  GmmBarriers* bars = reinterpret_cast<GmmBarriers*>(epi_smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int P = a.ctx.world;
 
@@ -289,91 +287,56 @@ __device__ __forceinline__ void gmm_phase(const GmmArgs& a, const GmmShared& sh,
     const int part = (warp - 2) >> 2;                // which half of the tile's columns this warp handles
     const int row_in_tile = quad * 32 + lane;
     constexpr int kCols = kGmmBN / 2;
-    uint8_t* stage = epi_smem + (size_t)(warp - 2) * 32 * kCols * 2;
     uint32_t local_tile = 0;
     for (int tile = cta; tile < total_tiles && !*failed; tile += num_ctas, ++local_tile) {
       const int mt = tile / n_tiles, nb = tile - mt * n_tiles;
       const int4 info = __ldcg(tile_info + mt);
       const uint32_t b = kHalves == 2 ? 0u : (local_tile & 1u);
       const uint32_t use = kHalves == 2 ? local_tile : (local_tile >> 1);
-      if (!kPush) {
-        // 256-row tile: this warp drains its 32 lanes of both accumulators (rows m * 128 + quad * 32 + lane); each
-        // thread stores its row's columns straight from registers, 64 contiguous bytes per 32 columns
-        if (!bounded_wait(&bars->acc_full[b], use & 1u, failed)) break;
-        umma::fence_after_sync();
-#pragma unroll
-        for (int m = 0; m < kHalves; ++m) {
-          const int r = m * kGmmBM + row_in_tile;
-          uint8_t* dst_row = r < info.z ? reinterpret_cast<uint8_t*>(a.out) + ((size_t)(info.y + r) * a.N + (size_t)nb * kGmmBN) * 2 : nullptr;
-          const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + m * kGmmBN + part * kCols;
-          uint32_t v[32];
-          for (int c = 0; c < kCols; c += 32) {
-            umma::tmem_ld32(taddr + c, v);
-            umma::tmem_ld_wait();
-            const int col = nb * kGmmBN + part * kCols + c;
-            if (dst_row && col < a.N) {
-              uint4* dst = reinterpret_cast<uint4*>(dst_row + (size_t)(part * kCols + c) * 2);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint32_t w0[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-                  w0[j] = *reinterpret_cast<uint32_t*>(&b0);
-                }
-                dst[i] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
-              }
-            }
-          }
-        }
-        umma::fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
-        continue;
-      }
-      // where this thread's row goes: the rank it came from
-      uint8_t* dst_row = nullptr;
-      if (row_in_tile < info.z) {
-        const int g = info.y + row_in_tile;
-        int seg = info.x * P;
-        while (seg + 1 < (info.x + 1) * P && sh.seg_dst[seg + 1] <= g) ++seg;
-        const int s = seg - info.x * P;
-        const long long r = sh.seg_src[seg] + (g - sh.seg_dst[seg]);
-        dst_row = a.ctx.ws[s] + a.data_off + ((size_t)r * a.N + (size_t)nb * kGmmBN) * 2;
-      }
+      // This warp drains its 32 lanes of both accumulators (rows m * 128 + quad * 32 + lane); each thread stores its
+      // row's columns straight from registers, 64 contiguous bytes per 32 columns, to this rank's output (a2av_gmm) or
+      // into the receive area of the rank the row came from (gmm_a2av).
       if (!bounded_wait(&bars->acc_full[b], use & 1u, failed)) break;
       umma::fence_after_sync();
-      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + b * kGmmBN + part * kCols;
-      // 1) drain this warp's 32 x 128 block into shared memory as bf16 and hand the accumulator back
-      uint4* mine = reinterpret_cast<uint4*>(stage + (size_t)lane * kCols * 2);   // 256 B per row = 16 pieces
-      __syncwarp();                                     // the previous tile's block has been written out
-      uint32_t v[32];
-      for (int c = 0; c < kCols; c += 32) {
-        umma::tmem_ld32(taddr + c, v);
-        umma::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t w0[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-            w0[j] = *reinterpret_cast<uint32_t*>(&b0);
+      for (int m = 0; m < kHalves; ++m) {
+        const int r = m * kGmmBM + row_in_tile;
+        uint8_t* dst_row = nullptr;
+        if (r < info.z) {
+          const int g = info.y + r;
+          if (!kPush) {
+            dst_row = reinterpret_cast<uint8_t*>(a.out) + ((size_t)g * a.N + (size_t)nb * kGmmBN) * 2;
+          } else {
+            int seg = info.x * P;
+            while (seg + 1 < (info.x + 1) * P && sh.seg_dst[seg + 1] <= g) ++seg;
+            const long long back = sh.seg_src[seg] + (g - sh.seg_dst[seg]);
+            dst_row = a.ctx.ws[seg - info.x * P] + a.data_off + ((size_t)back * a.N + (size_t)nb * kGmmBN) * 2;
           }
-          mine[(c / 8 + i) ^ (lane & 15)] = make_uint4(w0[0], w0[1], w0[2], w0[3]);   // XOR swizzle against bank conflicts
+        }
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + m * kGmmBN + part * kCols;
+        uint32_t v[32];
+        for (int c = 0; c < kCols; c += 32) {
+          umma::tmem_ld32(taddr + c, v);
+          umma::tmem_ld_wait();
+          const int col = nb * kGmmBN + part * kCols + c;
+          if (dst_row && col < a.N) {
+            uint4* dst = reinterpret_cast<uint4*>(dst_row + (size_t)(part * kCols + c) * 2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t w0[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                w0[j] = *reinterpret_cast<uint32_t*>(&b0);
+              }
+              dst[i] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+            }
+          }
         }
       }
       umma::fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[b]);
-      // 2) write the block out: 16 lanes x 16 B cover one row's 256-byte segment, 2 rows per instruction
-      const int col0 = nb * kGmmBN + part * kCols;
-#pragma unroll 4
-      for (int r0 = 0; r0 < 32; r0 += 2) {
-        const int rr = r0 + (lane >> 4), piece = lane & 15;
-        uint8_t* drow = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, (unsigned long long)dst_row, rr));
-        const uint4 val = reinterpret_cast<const uint4*>(stage + (size_t)rr * kCols * 2)[piece ^ (rr & 15)];
-        if (drow && col0 + piece * 8 < a.N) reinterpret_cast<uint4*>(drow + (size_t)part * kCols * 2)[piece] = val;
-      }
     }
     if (kPush) __threadfence_system();   // rows pushed to peers are visible before this rank signals them
   }
