@@ -235,6 +235,28 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
         const int c0 = a.chunk_start[s_rank * (NT + 1) + c], cn = a.chunk_start[s_rank * (NT + 1) + c + 1] - c0;
         const int j0 = c0 + cn * part / parts, j1 = c0 + cn * (part + 1) / parts;
         const int cap = min(32, ring.num_slots);
+        if (stream) {
+          // streaming consumers hand slots back one by one: publish every (record, column part) on its own so that
+          // the consumers start on a group while the following ones are still being issued
+          for (int j = j0; j < j1 && okp; ++j) {
+            const int* rec = a.stage_meta + ((size_t)s_rank * Tmax + j) * a.meta_stride;
+            const int n = rec[1], nn = n <= ring_rows ? n : 1;
+            for (int h = 0; h < cparts && okp; ++h) {
+              int ok = 1;
+              if (lane < nn) {
+                if (n <= ring_rows)
+                  ok = ring.fill(k + lane, x + (size_t)(rec[2 + lane] & kRowMask) * row_bytes + (size_t)h * seg_bytes, seg_bytes);
+                else
+                  ok = ring.fill_empty(k + lane);
+              }
+              okp = __all_sync(0xffffffffu, ok);
+              __syncwarp();
+              if (lane == 0 && okp) ring.publish(k + nn);
+              k += nn;
+            }
+          }
+          continue;
+        }
         for (int jb = j0; jb < j1 && okp;) {
           // lanes 0..7: slots of record jb + lane
           int my_n = 0, my_slots = 0;
