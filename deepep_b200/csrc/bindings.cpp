@@ -198,6 +198,7 @@ PYBIND11_MODULE(_C, m) {
       .def("set_timeout", &Session::set_timeout)
       .def("clear_status", &Session::clear_status)
       .def("read_control", [](const Session& s) { return py::bytes(s.read_control()); })
+      .def("guard_intact", &Session::guard_intact)
       .def("mapped", &Session::mapped)
       .def("peer", &Session::peer)
       .def_property_readonly("workspace", &Session::workspace)

@@ -46,8 +46,9 @@ Session::Session(int rank, int world, size_t bytes, double timeout_seconds)
   instance_ = reserve_instance();
   CudaApi& api = cuda_api();
   try {
-    check(api.malloc_(reinterpret_cast<void**>(&ws_), bytes_), "workspace allocation");
+    check(api.malloc_(reinterpret_cast<void**>(&ws_), bytes_ + kGuardBytes), "workspace allocation");
     check(api.memset_(ws_, 0, bytes_), "workspace clear");
+    check(api.memset_(ws_ + bytes_, kGuardPattern, kGuardBytes), "workspace guard fill");
     check(api.host_alloc_(reinterpret_cast<void**>(&status_host_), sizeof(StatusBlock), cudaHostAllocMapped), "status block allocation");
     std::memset(status_host_, 0, sizeof(StatusBlock));
     check(api.host_dev_ptr_(reinterpret_cast<void**>(&status_dev_), status_host_, 0), "status block mapping");
@@ -118,6 +119,15 @@ void Session::clear_status() {
   std::memset(status_host_, 0, sizeof(StatusBlock));
   Control* c = control_of(ws_);
   check(cudaMemset(&c->abort, 0, sizeof(int)), "abort clear");
+}
+
+bool Session::guard_intact() const {
+  if (!ws_) throw std::runtime_error("the session is closed");
+  std::string guard(kGuardBytes, '\0');
+  check(cudaMemcpy(&guard[0], ws_ + bytes_, kGuardBytes, cudaMemcpyDeviceToHost), "workspace guard read");
+  for (unsigned char c : guard)
+    if (c != (unsigned char)kGuardPattern) return false;
+  return true;
 }
 
 std::string Session::read_control() const {

@@ -33,6 +33,8 @@ CudaApi& cuda_api();
 
 constexpr int kMaxInstances = 128;
 constexpr int kMailboxInts = 4 + kMaxExperts;
+constexpr size_t kGuardBytes = 4096;      // canary zone behind the workspace, checked by guard_intact()
+constexpr int kGuardPattern = 0xA5;
 
 class Session {
  public:
@@ -60,6 +62,8 @@ class Session {
   StatusBlock status() const { return *status_host_; }
   void clear_status();                                          // also clears the device abort word
   std::string read_control() const;                             // copy of the control block (diagnostics)
+  // The allocation carries a canary zone behind the workspace (peers map it too): true while nobody wrote past the end.
+  bool guard_intact() const;
   int* mailbox_host() const { return mailbox_host_; }
   int* mailbox_device() const { return mailbox_dev_; }
 

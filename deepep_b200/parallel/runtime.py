@@ -136,6 +136,12 @@ class Runtime:
         torch.cuda.synchronize(self.device)
         self.control.barrier()   # nobody may still be writing into a workspace that is about to be freed
         try:
+            if not self.native.guard_intact():      # the canary zone behind the workspace (peers map it as well)
+                warnings.warn("something wrote behind this rank's symmetric workspace; results of this buffer are suspect",
+                              RuntimeWarning)
+        except RuntimeError:
+            pass
+        try:
             self.native.close()
         finally:
             self.closed = True

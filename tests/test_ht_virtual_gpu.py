@@ -122,3 +122,23 @@ def test_wait_timeout_reports_status():
         s.clear_status()
         torch.cuda.synchronize()
         assert s.status()["code"] == 0
+
+
+def test_workspace_canary_detects_overrun():
+    """The allocation ends in a canary zone: intact after real work, reported once something writes behind the workspace."""
+    from deepep_b200.models.mega_moe import _view
+    from deepep_b200.ops import load_native
+
+    C = load_native()
+    layout = C.make_layout(1, 64, 256, 2, 0, 0)
+    s = C.Session(0, 1, layout.total, 5.0)
+    try:
+        assert s.guard_intact()
+        _view(s.workspace + s.bytes - 16, 16, torch.device("cuda")).fill_(7)        # last bytes of the workspace proper
+        torch.cuda.synchronize()
+        assert s.guard_intact()
+        _view(s.workspace + s.bytes, 8, torch.device("cuda")).zero_()               # first bytes of the canary zone
+        torch.cuda.synchronize()
+        assert not s.guard_intact()
+    finally:
+        s.close()
