@@ -1,0 +1,124 @@
+"""Config-driven dispatch / combine / round-trip benchmark with versioned result records.
+
+    python benchmarks/bench_ep.py --config benchmarks/configs/smoke.json
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/bench_ep.py \
+        --config benchmarks/configs/prefill_bf16.json --results-dir benchmarks/results
+Every rank times each iteration with CUDA events (host clock on the CPU engine); rank 0 gathers the samples, takes
+the per-iteration maximum over ranks and prints one JSON record (schema in deepep_b200/utils/workload.py).  The
+outputs of the first iteration are compared with the all-rank CPU oracle unless --no-check is given.
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True)
+    ap.add_argument("--results-dir", default=None, help="write the record there (existing files are never overwritten)")
+    ap.add_argument("--no-check", action="store_true")
+    args = ap.parse_args()
+
+    from deepep_b200 import ElasticBuffer
+    from deepep_b200.oracle import reference as R
+    from deepep_b200.utils import workload as W
+    from deepep_b200.utils.testing import flush_l2_cache
+
+    cfg = W.WorkloadConfig.from_json(args.config)
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world != cfg.world_size:
+        raise SystemExit(f"the configuration is for {cfg.world_size} ranks, this job has {world}")
+    cuda = torch.cuda.is_available()
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        if cuda:
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dist.init_process_group("nccl" if cuda else "gloo")
+        group = dist.group.WORLD
+    dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+
+    routes = [W.make_routes(cfg, r) for r in range(world)]           # every rank can rebuild all inputs (oracle, traffic)
+    xs = [torch.randn((cfg.tokens_per_rank[r], cfg.hidden), generator=torch.Generator().manual_seed(cfg.seed + 77 * r)).bfloat16()
+          for r in range(world)]
+    x, idx, w = xs[rank].to(dev), routes[rank][0].to(dev), (routes[rank][1].to(dev) if cfg.with_weights else None)
+    expand = cfg.layout == "expanded"
+    buf = ElasticBuffer(group, num_max_tokens_per_rank=max(max(cfg.tokens_per_rank), 257), hidden=cfg.hidden, num_topk=cfg.topk,
+                        use_fp8_dispatch=cfg.dtype == "fp8", explicitly_destroy=True)
+
+    def fresh():
+        return buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=cfg.experts, do_expand=expand,
+                            expert_alignment=cfg.alignment)
+
+    recv, _, recv_w, handle, _ = fresh()
+    rows = recv[0] if isinstance(recv, tuple) else recv
+    back = torch.randn(rows.shape, device=dev).bfloat16() if cfg.dtype == "fp8" else rows
+
+    correctness = "not_run"
+    if not args.no_check:
+        ref, lays = R.dispatch(xs, [r[0] for r in routes], [r[1] for r in routes] if cfg.with_weights else None, cfg.experts,
+                               do_expand=expand, expert_alignment=cfg.alignment)
+        good = True
+        if cfg.dtype == "bf16":
+            good = torch.equal(rows.cpu().view(torch.int16), ref[rank][0].view(torch.int16))
+            out = buf.combine(rows, handle)[0]
+            cref = R.combine([r[0] for r in ref], lays, list(cfg.tokens_per_rank), cfg.topk)
+            good = good and torch.equal(out.cpu().view(torch.int16), cref[rank][0].view(torch.int16))
+        else:
+            good = rows.shape[0] == ref[rank][0].shape[0]
+        verdicts = buf.control.all_gather_object(bool(good)) if world > 1 else [good]
+        correctness = "passed" if all(verdicts) else "failed"
+
+    ops = {"dispatch": (fresh if cfg.dispatch_mode == "fresh" else (lambda: buf.dispatch(x, handle=handle))),
+           "combine": lambda: buf.combine(back, handle)}
+
+    def roundtrip():
+        r, _, _, h, _ = fresh() if cfg.dispatch_mode == "fresh" else buf.dispatch(x, handle=handle)
+        rr = r[0] if isinstance(r, tuple) else r
+        buf.combine(back if cfg.dtype == "fp8" else rr, h)
+    ops["roundtrip"] = roundtrip
+    fn = ops[cfg.operation]
+
+    samples = []
+    for it in range(cfg.warmup + cfg.iterations):
+        buf.barrier()
+        if cuda:
+            flush_l2_cache()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            e.synchronize()
+            us = s.elapsed_time(e) * 1e3
+        else:
+            t0 = time.perf_counter_ns()
+            fn()
+            us = (time.perf_counter_ns() - t0) / 1e3
+        if it >= cfg.warmup:
+            samples.append(max(us, 1e-3))
+    gathered = buf.control.all_gather_object(samples) if world > 1 else [samples]
+    record = W.complete(W.plan(cfg), gathered, W.traffic(cfg, [r[0] for r in routes])["effective_bytes"], correctness)
+    record["engine"] = "cuda" if cuda else "cpu"
+    buf.destroy()
+    if rank == 0:
+        slim = {k: v for k, v in record.items() if k != "rank_samples_us"}
+        print(json.dumps(slim))
+        if args.results_dir:
+            print("written:", W.write_result(args.results_dir, record), file=sys.stderr)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return 0 if correctness != "failed" else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
