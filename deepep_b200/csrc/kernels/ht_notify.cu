@@ -43,7 +43,7 @@ __device__ __forceinline__ bool slot_counts(const int* row, int k, int E) {
 // One thread per token of the tile: the K ids of a row are fetched once (independent loads), duplicates
 // are resolved in registers, then the masks are updated with shared-memory atomics.
 __device__ void build_masks(TileMasks& m, const int* gidx_src, int tile, int T_r, int K, int E, int Lx) {
-  for (int i = threadIdx.x; i < kMaxExperts * 2; i += blockDim.x) (&m.expert[0][0])[i] = 0u;
+  for (int i = threadIdx.x; i < E * 2; i += blockDim.x) (&m.expert[0][0])[i] = 0u;
   if (threadIdx.x < kMaxRanks * 2) (&m.rank[0][0])[threadIdx.x] = 0u;
   __syncthreads();
   const int tl = threadIdx.x, t = tile * kChunkTokens + tl;
@@ -83,6 +83,10 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   __shared__ int s_base[kMaxExperts];                   // scratch: totals, then per-task row bases
   __shared__ int s_rows;
 
+  // phase stamps of block 0 (nanoseconds since kernel start) for diagnostics: Control::dbg[16..23]
+  const unsigned long long t_start = global_timer_ns();
+  auto stamp = [&](int i) { if (blockIdx.x == 0 && threadIdx.x == 0) ctl->dbg[16 + i] = global_timer_ns() - t_start; };
+
   // ---- A: publish my routing table into every peer (after they consumed the previous one)
   int ok = 1;
   if (threadIdx.x < P) ok = wait_flag_ge(&ctl->notify_ack[threadIdx.x], epoch - 1, ctx, kOpNotify, 0, threadIdx.x);
@@ -107,6 +111,7 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   if (alive && blockIdx.x == 0 && threadIdx.x < P)
     st_release_sys(&control_of(ctx.ws[threadIdx.x])->notify_ready[me], epoch);
 
+  stamp(0);
   // ---- B: wait for every rank's table
   ok = 1;
   if (alive && threadIdx.x < P) ok = wait_flag_ge(&ctl->notify_ready[threadIdx.x], epoch, ctx, kOpNotify, 1, threadIdx.x);
@@ -118,6 +123,7 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   __syncthreads();
   const bool has_w = alive && __ldcg(ghdr + 1) != 0 && a.recv_w != nullptr;
 
+  stamp(1);
   // ---- C: per-(source, tile) histograms
   for (int task = blockIdx.x; task < P * NT; task += gridDim.x) {
     int r = task / NT, tile = task - r * NT;
@@ -132,29 +138,57 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   }
   grid.sync();
 
+  stamp(2);
   // ---- D1: exclusive scans over tiles
-  for (int i = gtid; i < P * E; i += gstride) {
-    int r = i / E, e = i - r * E, run = 0, nt = (s_T[r] + kChunkTokens - 1) / kChunkTokens;
-    for (int tile0 = 0; tile0 < nt; tile0 += 8) {       // loads of a batch first, then the in-place exclusive prefix
-      int v[8];
+  {   // one warp per (source, expert): the lanes take 32 tiles at a time, exclusive prefix by a warp scan
+    const int lane_ = threadIdx.x & 31;
+    for (int i = gtid >> 5; i < P * E; i += gstride >> 5) {
+      const int r = i / E, e = i - r * E, nt = (s_T[r] + kChunkTokens - 1) / kChunkTokens;
+      int run = 0;
+      for (int tile0 = 0; tile0 < nt; tile0 += 32) {
+        const int tile = tile0 + lane_;
+        int* cell = a.hist + ((size_t)r * NT + tile) * E + e;
+        const int v = tile < nt ? *cell : 0;
+        int incl = v;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = tile0 + j < nt ? a.hist[((size_t)r * NT + tile0 + j) * E + e] : 0;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (tile0 + j < nt) { a.hist[((size_t)r * NT + tile0 + j) * E + e] = run; run += v[j]; }
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane_ >= d) incl += o;
+        }
+        if (tile < nt) *cell = run + incl - v;
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane_ == 0) a.cnt[i] = run;
     }
-    a.cnt[i] = run;
   }
-  if (gtid < P) {
-    int r = gtid, run = 0, nt = (s_T[r] + kChunkTokens - 1) / kChunkTokens;
-    for (int tile = 0; tile < nt; ++tile) { a.chunk_start[r * (NT + 1) + tile] = run; run += a.hits[r * NT + tile]; }
-    for (int tile = nt; tile <= NT; ++tile) a.chunk_start[r * (NT + 1) + tile] = run;
-  } else if (gtid < 2 * P) {
-    int d = gtid - P, run = 0, nt = (s_T[me] + kChunkTokens - 1) / kChunkTokens;
-    for (int tile = 0; tile < nt; ++tile) { int v = a.own_hits[tile * P + d]; a.own_hits[tile * P + d] = run; run += v; }
+  {   // staged-row starts of every (source, chunk) and my own per-destination starts: one warp each, same warp scan
+    const int w = gtid >> 5, lane_ = threadIdx.x & 31;
+    if (w < 2 * P) {
+      const bool own = w >= P;
+      const int r = own ? me : w, d = w - P, nt = (s_T[r] + kChunkTokens - 1) / kChunkTokens;
+      int run = 0;
+      for (int tile0 = 0; tile0 < nt; tile0 += 32) {
+        const int tile = tile0 + lane_;
+        const int v = tile < nt ? (own ? a.own_hits[tile * P + d] : a.hits[r * NT + tile]) : 0;
+        int incl = v;
+#pragma unroll
+        for (int q = 1; q < 32; q <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, incl, q);
+          if (lane_ >= q) incl += o;
+        }
+        if (tile < nt) {
+          if (own) a.own_hits[tile * P + d] = run + incl - v;
+          else a.chunk_start[r * (NT + 1) + tile] = run + incl - v;
+        }
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (!own)
+        for (int tile = nt + lane_; tile <= NT; tile += 32) a.chunk_start[r * (NT + 1) + tile] = run;
+    }
   }
   grid.sync();
 
+  stamp(3);
   // ---- D2: expert row offsets of every rank (each block keeps its own copy in shared memory)
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int tot = 0;
@@ -162,15 +196,26 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
     s_base[e] = tot;                                      // total rows of expert e (all sources)
   }
   __syncthreads();
-  if (threadIdx.x < P) {
-    int d = threadIdx.x, run = 0;
-    for (int l = 0; l < Lx; ++l) {
-      int e = d * Lx + l, tot = s_base[e];
-      s_off[e] = run;
-      if (d == me && blockIdx.x == 0) { a.expert_counts[l] = tot; a.expert_offsets[l] = run; }
-      run += a.expand ? (tot + a.alignment - 1) / a.alignment * a.alignment : tot;
+  if ((threadIdx.x >> 5) < P) {    // warp d: aligned exclusive prefix over the local experts of rank d
+    const int d = threadIdx.x >> 5, lane_ = threadIdx.x & 31;
+    int run = 0;
+    for (int l0 = 0; l0 < Lx; l0 += 32) {
+      const int l = l0 + lane_, e = d * Lx + l;
+      const int tot = l < Lx ? s_base[e] : 0;
+      const int al = a.expand ? (tot + a.alignment - 1) / a.alignment * a.alignment : tot;
+      int incl = al;
+#pragma unroll
+      for (int q = 1; q < 32; q <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, q);
+        if (lane_ >= q) incl += o;
+      }
+      if (l < Lx) {
+        s_off[e] = run + incl - al;
+        if (d == me && blockIdx.x == 0) { a.expert_counts[l] = tot; a.expert_offsets[l] = run + incl - al; }
+      }
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (d == me) { s_rows = run; if (blockIdx.x == 0) a.expert_offsets[Lx] = run; }
+    if (d == me && lane_ == 0) { s_rows = run; if (blockIdx.x == 0) a.expert_offsets[Lx] = run; }
   }
   if (threadIdx.x == 0) {
     int run = 0;
@@ -195,6 +240,7 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
     }
   }
 
+  stamp(4);
   // ---- E: per-token records
   for (int task = blockIdx.x; task < P * NT; task += gridDim.x) {
     int r = task / NT, tile = task - r * NT, T_r = s_T[r];
@@ -270,6 +316,7 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   __threadfence();
   grid.sync();
 
+  stamp(5);
   // ---- F: release the gathered table, publish counts to the host, advance the epoch
   if (blockIdx.x == 0) {
     if (threadIdx.x < P) st_release_sys(&control_of(ctx.ws[threadIdx.x])->notify_ack[me], epoch);

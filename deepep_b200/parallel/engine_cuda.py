@@ -194,7 +194,8 @@ class CudaEngine:
                              rank_rows=plan.rank_rows.data_ptr(), expert_counts=plan.expert_counts.data_ptr(),
                              expert_offsets=plan.expert_offsets.data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(),
                              recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap))
-        nblocks = blocks or max(1, min(64, self.sm_count // self.n))
+        # the layout pass is a chain of short phases over (source, tile) tasks: P x T / 64 of them, a few microseconds each
+        nblocks = blocks or max(1, min(128, self.sm_count // self.n))
         self._timed("notify", stream, lambda: C.notify(lay, self.sessions, args, nblocks, self._stream(stream)))
         if cpu_sync:
             (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
