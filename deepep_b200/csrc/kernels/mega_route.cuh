@@ -94,12 +94,13 @@ __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::g
   grid.sync();
 
   // ---- tile layout: every expert starts at a multiple of 128 rows
+  for (int l = threadIdx.x; l < Lx; l += (int)blockDim.x) sh.rows[l] = min(__ldcg(a.expert_rows + l), cap);   // parallel loads
+  __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
     for (int l = 0; l < Lx; ++l) {
-      const int c = min(__ldcg(a.expert_rows + l), cap);
+      const int c = sh.rows[l];
       sh.base[l] = run;
-      sh.rows[l] = c;
       const int tiles = (c + kGemmBM - 1) / kGemmBM;
       if (blockIdx.x == 0)
         for (int t = 0; t < tiles && run / kGemmBM + t < a.max_mtiles; ++t) a.mtile_expert[run / kGemmBM + t] = l;
