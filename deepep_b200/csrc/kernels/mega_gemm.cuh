@@ -94,6 +94,28 @@ __device__ __forceinline__ bool wait_rows_ready(const int* counter, int need, vo
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// Position in the fused schedule -> tile id (ids below num_mtiles * n1 are GEMM1 tiles, the rest GEMM2 tiles).
+// The schedule interleaves the two GEMMs in waves of `wave` row blocks: GEMM1 of wave 0, then for every later wave its
+// GEMM1 tiles followed by the GEMM2 tiles of the wave before, and the last wave's GEMM2 tiles at the end.  GEMM2's
+// rows leave for the source ranks over NVLink from early on instead of only after the last GEMM1 tile, and its A rows
+// are still in L2.  A GEMM2 tile still comes after all GEMM1 tiles of its row block, so its wait always ends.
+__device__ __forceinline__ int schedule_to_tile(int pos, int num_mtiles, int n1, int n2, int wave) {
+  const int waves = (num_mtiles + wave - 1) / wave;
+  for (int w = 0; w <= waves; ++w) {
+    if (w < waves) {
+      const int c1 = min(wave, num_mtiles - w * wave) * n1;
+      if (pos < c1) return w * wave * n1 + pos;
+      pos -= c1;
+    }
+    if (w >= 1) {
+      const int c2 = min(wave, num_mtiles - (w - 1) * wave) * n2;
+      if (pos < c2) return num_mtiles * n1 + (w - 1) * wave * n2 + pos;
+      pos -= c2;
+    }
+  }
+  return -1;
+}
+
 // Next tile of this CTA: the producer publishes it to the MMA and epilogue warps through a small ring.
 __device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_tile, volatile int* failed) {
   const uint32_t slot = local_tile % kSchedRing;
@@ -108,7 +130,7 @@ __device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_til
 // Either way a tile is only ever taken after all tiles before it, so a GEMM2 tile's wait for its GEMM1 tiles ends.
 // `smem_raw` must provide gemm_smem_bytes(stages, staging) bytes.
 __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaGemmParams* g2, int* ready, uint8_t* smem_raw,
-                                           int stages, int cta, int num_ctas, int* tile_counter = nullptr) {
+                                           int stages, int cta, int num_ctas, int* tile_counter = nullptr, bool interleave = false) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
   uint8_t* tiles = smem;
@@ -151,6 +173,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
       for (uint32_t local_tile = 0;; ++local_tile) {
         int tile = tile_counter ? atomicAdd(tile_counter, 1) : cta + (int)local_tile * num_ctas;
         if (tile >= total_tiles || *failed) tile = -1;
+        else if (g2 && ready && interleave) tile = schedule_to_tile(tile, num_mtiles, g1.n_tiles, g2->n_tiles, (2 * num_ctas + g1.n_tiles - 1) / g1.n_tiles);
         bars->tile_id[local_tile % kSchedRing] = tile;
         mbar_arrive(&bars->sched[local_tile % kSchedRing]);      // release: the id is visible to whoever passes the wait
         if (tile < 0) break;

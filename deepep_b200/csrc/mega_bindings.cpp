@@ -95,6 +95,7 @@ void op_mega_fused(const WsLayout& lay, const std::vector<py::object>& sessions,
     fill_gemm(p.r[i].g2, d["gemm2"].cast<py::dict>(), sessions[i]);
     p.r[i].ready = ptr<int>(d, "ready");
     p.r[i].tile_counter = ptr<int>(d, "tile_counter");
+    p.r[i].interleave = geti(d, "interleave", 1);
     if (!p.r[i].ready || !p.r[i].route.pulled) throw std::invalid_argument("the fused kernel needs the ready and pulled counter arrays");
   }
   check(launch_mega_fused(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_moe launch");
