@@ -17,7 +17,7 @@ Each op is ONE persistent cooperative CUDA kernel per rank (``csrc/kernels/gmm_f
 peer loads / stores issued from inside the kernel that runs the tcgen05 grouped GEMM.  Without a GPU the same API
 runs on a CPU engine (object all-gather + ``torch.matmul``), which is what the CPU tests exercise.
 
-``tiling=`` is accepted for signature compatibility; the kernel has one tile shape (128 x 256 x 64).
+``tiling=`` is accepted for signature compatibility; the kernel has one tile shape (256 x 256 x 64).
 """
 from __future__ import annotations
 
@@ -255,7 +255,7 @@ def symmetric_output(rows: int, n: int) -> torch.Tensor:
 def load_tiling_config(path=None) -> Mapping[str, int]:
     """The kernel has a single tile shape; returns it (the reference loads a measured search result here)."""
     del path
-    return {"m": 128, "n": 256, "k": 64}
+    return {"m": 256, "n": 256, "k": 64}
 
 
 # ------------------------------------------------------------------------------------------------ ops
