@@ -98,7 +98,8 @@ class MegaEngine:
         self.dynamic_tiles = os.environ.get("DEEPEP_MEGA_STATIC_TILES", "0") in ("", "0")
         # GEMM2 tiles scheduled right after their GEMM1 wave, or after all GEMM1 tiles.  Interleaving spreads the combine
         # rows (top-k bf16 rows per token, most of them remote from four ranks up) over the whole kernel instead of
-        # its last third; with one rank it measured 4 % slower (1630 against 1565 us), so it is on from four ranks up.
+        # its last third; with one and two ranks it measured 4-5 % slower (1630 against 1565 us, 2046 against 1951 us), so
+        # it is on only from four ranks up, where three quarters or more of those rows cross NVLink.
         # DEEPEP_MEGA_INTERLEAVE=0 / 1 overrides.
         default = "1" if self.world >= 4 else "0"
         self.interleave = os.environ.get("DEEPEP_MEGA_INTERLEAVE", default) not in ("", "0")
