@@ -40,6 +40,8 @@ def _flags(verbose: bool) -> list:
 
     flags = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-fvisibility=hidden",
              "-I", str(CSRC), "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], *ARCH_FLAGS]
+    if os.environ.get("DEEPEP_DEBUG_BOUNDS", "0") not in ("", "0"):   # index checks in the kernels (see common.cuh)
+        flags += ["-DDEEPEP_DEBUG_BOUNDS"]
     if verbose:
         flags += ["-Xptxas", "-v"]
     return flags

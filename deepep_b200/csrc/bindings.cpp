@@ -119,6 +119,7 @@ void op_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, c
     a.send_slot = ptr<const int>(d, "send_slot"); a.stage_meta = ptr<const int>(d, "stage_meta");
     a.chunk_start = ptr<const int>(d, "chunk_start"); a.rank_tokens = ptr<const int>(d, "rank_tokens");
     a.meta_stride = geti(d, "meta_stride");
+    a.recv_rows = geti(d, "recv_rows", 0);
     a.recv_x = ptr<void>(d, "recv_x"); a.recv_sf = ptr<float>(d, "recv_sf");
     if (a.mode != p.r[0].mode) throw std::invalid_argument("all ranks must use the same dispatch mode");
     if (a.mode != kDispatchBf16 && lay.hidden % 128) throw std::invalid_argument("fp8 dispatch needs hidden % 128 == 0");
@@ -142,6 +143,7 @@ void op_combine(const WsLayout& lay, const std::vector<py::object>& sessions, co
     a.rank_tokens = ptr<const int>(d, "rank_tokens"); a.send_slot = ptr<const int>(d, "send_slot");
     a.topk_idx = ptr<const long long>(d, "topk_idx");
     a.T = geti(d, "T"); a.meta_stride = geti(d, "meta_stride"); a.K = geti(d, "K"); a.E = geti(d, "E"); a.expand = geti(d, "expand", 1);
+    a.x_rows = geti(d, "x_rows", 0);
     a.bias0 = ptr<const __nv_bfloat16>(d, "bias0"); a.bias1 = ptr<const __nv_bfloat16>(d, "bias1");
     a.out = ptr<__nv_bfloat16>(d, "out"); a.out_w = ptr<float>(d, "out_w");
   }
@@ -172,6 +174,11 @@ PYBIND11_MODULE(_C, m) {
   m.attr("control_bytes") = (long long)kControlBytes;
   m.attr("row_slot_shift") = kRowSlotShift;
   m.attr("control_dbg_offset") = (long long)offsetof(Control, dbg);
+#ifdef DEEPEP_DEBUG_BOUNDS
+  m.attr("debug_bounds") = true;
+#else
+  m.attr("debug_bounds") = false;
+#endif
 
   py::class_<WsLayout>(m, "WsLayout")
       .def_readonly("gather_hdr", &WsLayout::gather_hdr).def_readonly("gather_idx", &WsLayout::gather_idx)

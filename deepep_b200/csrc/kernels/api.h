@@ -55,7 +55,7 @@ struct DispatchArgs {
   const int* stage_meta;
   const int* chunk_start;
   const int* rank_tokens;
-  int meta_stride, pad;
+  int meta_stride, recv_rows;  // recv_rows: rows of recv_x (only read by the optional index checks; 0 = unknown)
   void* recv_x;                // [R][H] 2-byte (mode 0) or e4m3 (modes 1, 2)
   float* recv_sf;              // [R][H/128] or null
 };
@@ -75,7 +75,7 @@ struct CombineArgs {
   const int* rank_tokens;
   const int* send_slot;        // [T][P]
   const long long* topk_idx;   // [T][K] of the source tokens (validity of returned weights)
-  int T, meta_stride, K, E, expand, pad;
+  int T, meta_stride, K, E, expand, x_rows;   // x_rows: rows of x (only read by the optional index checks; 0 = unknown)
   const __nv_bfloat16* bias0;  // [T][H] or null
   const __nv_bfloat16* bias1;
   __nv_bfloat16* out;          // [T][H]

@@ -135,6 +135,20 @@ __device__ __forceinline__ void report_failure(const RankCtx& ctx, int code, int
   }
 }
 
+// Optional index checking (build with DEEPEP_DEBUG_BOUNDS=1 in the environment of deepep_b200._build): an index outside its
+// range is recorded in the status block (code kStatusBadArgument, wait site 100 + site, expected = limit, seen = index),
+// the rank is aborted like after a time-out, and the access is skipped.  Without the flag the checks compile to nothing.
+#ifdef DEEPEP_DEBUG_BOUNDS
+__device__ __forceinline__ bool index_ok(const RankCtx& ctx, long long index, long long limit, int op, int site) {
+  if (index >= 0 && index < limit) return true;
+  report_failure(ctx, kStatusBadArgument, op, 100 + site, -1, (unsigned long long)limit, (unsigned long long)index);
+  return false;
+}
+#define DEP_INDEX_OK(ctx, index, limit, op, site) index_ok(ctx, index, limit, op, site)
+#else
+#define DEP_INDEX_OK(ctx, index, limit, op, site) true
+#endif
+
 // One thread spins until *flag >= expect.  Returns false when the rank has been
 // aborted or the time limit ran out (the failure is recorded for the host); the
 // caller then skips its remaining work and leaves the kernel normally.

@@ -245,7 +245,9 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
               int ok = 1;
               if (lane < nn) {
                 if (n <= ring_rows)
-                  ok = ring.fill(k + lane, x + (size_t)(rec[2 + lane] & kRowMask) * row_bytes + (size_t)h * seg_bytes, seg_bytes);
+                  ok = (a.x_rows <= 0 || DEP_INDEX_OK(ctx, rec[2 + lane] & kRowMask, a.x_rows, kOpCombine, 0))
+                           ? ring.fill(k + lane, x + (size_t)(rec[2 + lane] & kRowMask) * row_bytes + (size_t)h * seg_bytes, seg_bytes)
+                           : ring.fill_empty(k + lane);
                 else
                   ok = ring.fill_empty(k + lane);
               }
@@ -287,7 +289,9 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
             const int n = rec[1], nn = n <= ring_rows ? n : 1;
             const int idx = lane - base, h = idx / nn, i = idx - h * nn;
             if (n <= ring_rows)
-              ok = ring.fill(k + lane, x + (size_t)(rec[2 + i] & kRowMask) * row_bytes + (size_t)h * seg_bytes, seg_bytes);
+              ok = (a.x_rows <= 0 || DEP_INDEX_OK(ctx, rec[2 + i] & kRowMask, a.x_rows, kOpCombine, 0))
+                       ? ring.fill(k + lane, x + (size_t)(rec[2 + i] & kRowMask) * row_bytes + (size_t)h * seg_bytes, seg_bytes)
+                       : ring.fill_empty(k + lane);
             else
               ok = ring.fill_empty(k + lane);
           }

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(256, 1) ep_dispatch_ht_kernel(const __grid_con
         __syncwarp();
         for (int d = 0; d < P; ++d) {
           int jd = __shfl_sync(0xffffffffu, j, d);
-          if (jd >= 0 && lane == 0)
+          if (jd >= 0 && lane == 0 && DEP_INDEX_OK(ctx, jd, Tmax, kOpDispatch, 0))
             bulk_s2g(ctx.ws[d] + lay.stage + ((size_t)me * Tmax + jd) * lay.stage_row_bytes, src, moved);
         }
         if (lane == 0) bulk_commit();
@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(256, 1) ep_dispatch_ht_kernel(const __grid_con
         const uint8_t* src = slots + (size_t)s * slot_bytes;
         for (int i = 0; i < n; ++i) {
           const int row = rec[2 + i] & kRowMask;
+          if (a.recv_rows > 0 && !DEP_INDEX_OK(ctx, row, a.recv_rows, kOpDispatch, 1)) continue;
           if (lane == 0) {
             bulk_s2g(recv_x + (size_t)row * row_bytes, src, row_bytes);
             if (fp8 && sf_bulk) bulk_s2g(a.recv_sf + (size_t)row * nsf, src + H, sf_bytes);

@@ -230,7 +230,7 @@ class CudaEngine:
             args.append(dict(x=x.data_ptr(), x_sf=_ptr(sf), T=plan.num_tokens, mode=mode, send_slot=plan.send_slot.data_ptr(),
                              stage_meta=plan.stage_meta.data_ptr(), chunk_start=plan.chunk_start.data_ptr(),
                              rank_tokens=plan.rank_tokens.data_ptr(), meta_stride=plan.meta_stride,
-                             recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf)))
+                             recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf), recv_rows=recv_x.shape[0]))
         send, recv = self.split_blocks(blocks, self.dispatch_send_fraction, self.dispatch_blocks)
         self._timed("dispatch", stream, lambda: self.C.dispatch(lay, self.sessions, args, send, recv, self._stream(stream)))
         return outs
@@ -252,7 +252,7 @@ class CudaEngine:
                              chunk_start=plan.chunk_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
                              send_slot=plan.send_slot.data_ptr(), topk_idx=plan.topk_idx.data_ptr(), T=T,
                              meta_stride=plan.meta_stride, K=K, E=plan.num_experts, expand=int(plan.expand),
-                             bias0=_ptr(b0), bias1=_ptr(b1), out=out.data_ptr(), out_w=_ptr(out_w)))
+                             bias0=_ptr(b0), bias1=_ptr(b1), out=out.data_ptr(), out_w=_ptr(out_w), x_rows=xs[i].shape[0]))
         send, recv = self.split_blocks(blocks, 0.72, self.combine_blocks)
         if split is not None:
             limit = max(2, self.sm_count // self.n)

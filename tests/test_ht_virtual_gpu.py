@@ -142,3 +142,34 @@ def test_workspace_canary_detects_overrun():
         assert not s.guard_intact()
     finally:
         s.close()
+
+
+def test_index_checks_report_instead_of_reading_out_of_range():
+    """Only in a build with DEEPEP_DEBUG_BOUNDS=1: a combine whose input has fewer rows than the routing plan names is
+    reported through the status block and the rows are not read.  (The short input is a view of a full-size
+    allocation, so nothing is out of range of the allocation either way.)"""
+    from deepep_b200.ops import load_native
+    from deepep_b200.parallel.engine_cuda import CommunicationError
+    from deepep_b200.parallel.virtual import VirtualWorld
+
+    if not load_native().debug_bounds:
+        pytest.skip("needs a build with DEEPEP_DEBUG_BOUNDS=1")
+    dev = torch.device("cuda")
+    T, H, E, K = 64, 256, 4, 2
+    x = torch.randn((T, H)).bfloat16().to(dev)
+    idx = make_routes("random", T, E, K, 1, 0).to(dev)
+    vw = VirtualWorld(1, T, H, K, timeout=5.0)
+    try:
+        plans = vw.engine.notify([idx], [None], E)
+        rows = vw.engine.dispatch([x], plans, 0)[0][0]
+        short = rows[: rows.shape[0] // 2]
+        vw.engine.combine([short], plans, [None])
+        torch.cuda.synchronize()
+        with pytest.raises(CommunicationError):
+            vw.engine.check_status()
+        status = vw.sessions[0].status()
+        assert status["code"] == 2 and status["where"] == 100 and status["expected"] == short.shape[0]
+    finally:
+        torch.cuda.synchronize()
+        for s in vw.sessions:
+            s.close()
