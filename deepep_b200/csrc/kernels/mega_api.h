@@ -98,7 +98,7 @@ struct MegaFusedArgs {
   MegaFinishArgs finish;
   int* ready;                  // [max_mtiles] finished GEMM1 tiles per row block (zeroed by the kernel)
   int* tile_counter;           // [1] next tile of the GEMM1 + GEMM2 tile list (zeroed by the kernel); null: static round-robin
-  int interleave, pad;         // 1: GEMM2 tiles follow their GEMM1 wave in the schedule; 0: all GEMM1 tiles first
+  int interleave, pad;         // k > 0: GEMM2 tiles follow their GEMM1 wave (waves of 2k rounds of GEMM1 tiles); 0: all GEMM1 tiles first
 };
 struct MegaFusedParams { WsLayout lay; MegaFusedArgs r[kMaxRanks]; };
 cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, cudaStream_t stream);

@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid
   // The token pull overlaps the GEMMs: rows are pulled tile by tile, a GEMM1 tile starts once its rows have arrived.
   const int warp = threadIdx.x >> 5;
   if (warp < kGemmThreads / 32) {
-    gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x, a.tile_counter, a.interleave != 0);
+    gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x, a.tile_counter, a.interleave);
   } else {
     __syncthreads();                               // pairs with the set-up barrier inside gemm_phase
     route_pull_phase(a.route, sh, blockIdx.x * kPullWarps + (warp - kGemmThreads / 32), gridDim.x * kPullWarps);

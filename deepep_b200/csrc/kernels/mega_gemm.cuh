@@ -130,7 +130,7 @@ __device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_til
 // Either way a tile is only ever taken after all tiles before it, so a GEMM2 tile's wait for its GEMM1 tiles ends.
 // `smem_raw` must provide gemm_smem_bytes(stages, staging) bytes.
 __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaGemmParams* g2, int* ready, uint8_t* smem_raw,
-                                           int stages, int cta, int num_ctas, int* tile_counter = nullptr, bool interleave = false) {
+                                           int stages, int cta, int num_ctas, int* tile_counter = nullptr, int interleave = 0) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
   uint8_t* tiles = smem;
@@ -173,7 +173,8 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
       for (uint32_t local_tile = 0;; ++local_tile) {
         int tile = tile_counter ? atomicAdd(tile_counter, 1) : cta + (int)local_tile * num_ctas;
         if (tile >= total_tiles || *failed) tile = -1;
-        else if (g2 && ready && interleave) tile = schedule_to_tile(tile, num_mtiles, g1.n_tiles, g2->n_tiles, (2 * num_ctas + g1.n_tiles - 1) / g1.n_tiles);
+        else if (g2 && ready && interleave > 0)   // wave = row blocks whose GEMM1 tiles fill `2 * interleave` rounds of the CTAs
+          tile = schedule_to_tile(tile, num_mtiles, g1.n_tiles, g2->n_tiles, (2 * interleave * num_ctas + g1.n_tiles - 1) / g1.n_tiles);
         bars->tile_id[local_tile % kSchedRing] = tile;
         mbar_arrive(&bars->sched[local_tile % kSchedRing]);      // release: the id is visible to whoever passes the wait
         if (tile < 0) break;

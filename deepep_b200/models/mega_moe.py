@@ -97,12 +97,13 @@ class MegaEngine:
         # tiles handed out by an atomic counter (default) or statically round-robin (DEEPEP_MEGA_STATIC_TILES=1)
         self.dynamic_tiles = os.environ.get("DEEPEP_MEGA_STATIC_TILES", "0") in ("", "0")
         # GEMM2 tiles scheduled right after their GEMM1 wave, or after all GEMM1 tiles.  Interleaving spreads the combine
-        # rows (top-k bf16 rows per token, most of them remote from four ranks up) over the whole kernel instead of
-        # its last third; with one and two ranks it measured 4-5 % slower (1630 against 1565 us, 2046 against 1951 us), so
-        # it is on only from four ranks up, where three quarters or more of those rows cross NVLink.
-        # DEEPEP_MEGA_INTERLEAVE=0 / 1 overrides.
-        default = "1" if self.world >= 4 else "0"
-        self.interleave = os.environ.get("DEEPEP_MEGA_INTERLEAVE", default) not in ("", "0")
+        # rows (top-k bf16 rows per token, most of them remote from four ranks up) over the kernel instead of its last
+        # third.  The value is the wave length in units of two rounds of GEMM1 tiles over the CTAs.  One GPU, 4096
+        # tokens: 1560 us without, 1629 / 1596 / 1575 us with waves of 1 / 2 / 4 units (two GPUs, 1 unit: 2046 against
+        # 1951 us), so it is off below four ranks and uses long waves from four ranks up, where three quarters or more
+        # of those rows cross NVLink.  DEEPEP_MEGA_INTERLEAVE=<units> overrides (0 = off).
+        default = "4" if self.world >= 4 else "0"
+        self.interleave = int(os.environ.get("DEEPEP_MEGA_INTERLEAVE", default) or 0)   # wave length in units of two CTA rounds
         rows = self.world * self.M * min(self.K, self.L) + self.L * 127
         self.max_mtiles = -(-rows // 128)
         self.rows_cap = self.max_mtiles * 128
