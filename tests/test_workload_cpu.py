@@ -84,3 +84,11 @@ def test_config_driven_benchmark_runs_on_the_cpu_engine(tmp_path):
     rec = json.loads(out.stdout.strip().splitlines()[-1])
     assert rec["status"] == "measured" and rec["correctness_result"] == "passed" and rec["statistics"]["iterations"] == 3
     assert len(os.listdir(tmp_path)) == 1
+
+
+def test_reference_arm_reports_unavailable():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                          "--warmup", "1"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-1000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
