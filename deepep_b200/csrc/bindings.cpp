@@ -52,6 +52,9 @@ WsLayout make_layout(int world, int max_tokens, int hidden, int topk, long long 
   l.stage = take((long long)world * max_tokens * l.stage_row_bytes);
   l.partial = take((long long)max_tokens * world * hidden * 2);
   l.wret = take((long long)max_tokens * topk * sizeof(float));
+  const long long groups = (max_tokens + kGroupTokens - 1) / kGroupTokens;
+  l.disp_flag = take((long long)world * groups * 8);
+  l.comb_flag = take((long long)world * groups * 8);
   l.ll = take(ll_bytes);
   l.mega = take(mega_bytes);
   l.total = align_up(at, 2 << 20);
@@ -66,7 +69,7 @@ WsLayout make_mega_layout(int world, int max_tokens, int hidden, int topk, long 
   WsLayout l{};
   l.world = world; l.max_tokens = max_tokens; l.hidden = hidden; l.topk = topk;
   l.stage_row_bytes = hidden * 2;
-  l.gather_hdr = l.gather_idx = l.gather_w = l.stage = l.partial = l.wret = l.ll = kControlBytes;
+  l.gather_hdr = l.gather_idx = l.gather_w = l.stage = l.partial = l.wret = l.disp_flag = l.comb_flag = l.ll = kControlBytes;
   l.mega = kControlBytes;
   l.total = align_up(kControlBytes + mega_bytes, 2 << 20);
   return l;
@@ -90,7 +93,8 @@ void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, con
     a.expand = geti(d, "expand", 1); a.alignment = geti(d, "alignment", 1); a.meta_stride = geti(d, "meta_stride");
     a.hist = ptr<int>(d, "hist"); a.hits = ptr<int>(d, "hits"); a.own_hits = ptr<int>(d, "own_hits"); a.cnt = ptr<int>(d, "cnt");
     a.send_slot = ptr<int>(d, "send_slot"); a.slot_row = ptr<int>(d, "slot_row"); a.stage_meta = ptr<int>(d, "stage_meta");
-    a.chunk_start = ptr<int>(d, "chunk_start"); a.rank_tokens = ptr<int>(d, "rank_tokens"); a.rank_rows = ptr<int>(d, "rank_rows");
+    a.chunk_start = ptr<int>(d, "chunk_start"); a.group_start = ptr<int>(d, "group_start");
+    a.rank_tokens = ptr<int>(d, "rank_tokens"); a.rank_rows = ptr<int>(d, "rank_rows");
     a.expert_counts = ptr<int>(d, "expert_counts"); a.expert_offsets = ptr<int>(d, "expert_offsets");
     a.recv_row_src = ptr<int>(d, "recv_row_src"); a.recv_w = ptr<float>(d, "recv_w"); a.recv_idx = ptr<long long>(d, "recv_idx");
     a.mailbox = sessions[i].cast<Session&>().mailbox_device();
@@ -104,12 +108,14 @@ void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, con
 }
 
 void op_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int send_blocks,
-                 int recv_blocks, uintptr_t stream) {
+                 int recv_blocks, uintptr_t stream, bool local_direct, bool profile) {
   DispatchParams p{};
-  p.lay = lay; p.send_blocks = send_blocks; p.recv_blocks = recv_blocks;
+  p.lay = lay; p.send_blocks = send_blocks; p.recv_blocks = recv_blocks; p.local_direct = local_direct; p.profile = profile;
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
-  if (send_blocks < 1 || recv_blocks < 1) throw std::invalid_argument("sender and receiver block counts must be positive");
+  if (send_blocks < 1 || recv_blocks < 0) throw std::invalid_argument("the sender block count must be positive, the receiver count nonnegative");
+  if (recv_blocks == 0 && !(local_direct && lay.world == 1))
+    throw std::invalid_argument("receiver blocks are only optional for one rank that writes its own rows directly");
   for (int i = 0; i < n; ++i) {
     const py::dict& d = args[i];
     DispatchArgs& a = p.r[i];
@@ -117,10 +123,19 @@ void op_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, c
     a.x = ptr<const void>(d, "x"); a.x_sf = ptr<const float>(d, "x_sf");
     a.T = geti(d, "T"); a.mode = geti(d, "mode");
     a.send_slot = ptr<const int>(d, "send_slot"); a.stage_meta = ptr<const int>(d, "stage_meta");
-    a.chunk_start = ptr<const int>(d, "chunk_start"); a.rank_tokens = ptr<const int>(d, "rank_tokens");
+    a.slot_row = ptr<const int>(d, "slot_row"); a.topk_idx = ptr<const long long>(d, "topk_idx");
+    a.group_start = ptr<const int>(d, "group_start"); a.rank_tokens = ptr<const int>(d, "rank_tokens");
+    a.rank_rows = ptr<const int>(d, "rank_rows");
     a.meta_stride = geti(d, "meta_stride");
     a.recv_rows = geti(d, "recv_rows", 0);
+    a.K = geti(d, "K"); a.E = geti(d, "E"); a.expand = geti(d, "expand", 1);
     a.recv_x = ptr<void>(d, "recv_x"); a.recv_sf = ptr<float>(d, "recv_sf");
+    a.prof = ptr<unsigned long long>(d, "prof");
+    // (a rank without tokens, or without received rows, passes empty tensors whose address is null)
+    if (!a.send_slot || !a.stage_meta || !a.group_start || !a.rank_tokens || (!a.x && a.T > 0))
+      throw std::invalid_argument("dispatch: a required pointer is missing");
+    if (local_direct && (!a.slot_row || (!a.topk_idx && a.T > 0) || !a.rank_rows || a.E < a.ctx.world || a.K != lay.topk))
+      throw std::invalid_argument("dispatch: direct local rows need slot_row, topk_idx, rank_rows, E and K");
     if (a.mode != p.r[0].mode) throw std::invalid_argument("all ranks must use the same dispatch mode");
     if (a.mode != kDispatchBf16 && lay.hidden % 128) throw std::invalid_argument("fp8 dispatch needs hidden % 128 == 0");
   }
@@ -128,24 +143,30 @@ void op_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, c
 }
 
 void op_combine(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int send_blocks,
-                int recv_blocks, uintptr_t stream) {
+                int recv_blocks, uintptr_t stream, bool local_direct, bool profile) {
   CombineParams p{};
-  p.lay = lay; p.send_blocks = send_blocks; p.recv_blocks = recv_blocks;
+  p.lay = lay; p.send_blocks = send_blocks; p.recv_blocks = recv_blocks; p.local_direct = local_direct; p.profile = profile;
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
-  if (send_blocks < 1 || recv_blocks < 1) throw std::invalid_argument("sender and receiver block counts must be positive");
+  if (send_blocks < 0 || recv_blocks < 1) throw std::invalid_argument("the source-side block count must be positive, the expert-side count nonnegative");
+  if (send_blocks == 0 && !(local_direct && lay.world == 1))
+    throw std::invalid_argument("expert-side blocks are only optional for one rank that reads its own rows directly");
   for (int i = 0; i < n; ++i) {
     const py::dict& d = args[i];
     CombineArgs& a = p.r[i];
     a.ctx = ctx_of(sessions[i]);
     a.x = ptr<const __nv_bfloat16>(d, "x"); a.w = ptr<const float>(d, "w");
-    a.stage_meta = ptr<const int>(d, "stage_meta"); a.chunk_start = ptr<const int>(d, "chunk_start");
+    a.stage_meta = ptr<const int>(d, "stage_meta"); a.group_start = ptr<const int>(d, "group_start");
     a.rank_tokens = ptr<const int>(d, "rank_tokens"); a.send_slot = ptr<const int>(d, "send_slot");
     a.topk_idx = ptr<const long long>(d, "topk_idx");
     a.T = geti(d, "T"); a.meta_stride = geti(d, "meta_stride"); a.K = geti(d, "K"); a.E = geti(d, "E"); a.expand = geti(d, "expand", 1);
     a.x_rows = geti(d, "x_rows", 0);
     a.bias0 = ptr<const __nv_bfloat16>(d, "bias0"); a.bias1 = ptr<const __nv_bfloat16>(d, "bias1");
     a.out = ptr<__nv_bfloat16>(d, "out"); a.out_w = ptr<float>(d, "out_w");
+    a.prof = ptr<unsigned long long>(d, "prof");
+    if (!a.stage_meta || !a.group_start || !a.rank_tokens || !a.send_slot || ((!a.topk_idx || !a.out) && a.T > 0))
+      throw std::invalid_argument("combine: a required pointer is missing");
+    if (a.E < a.ctx.world) throw std::invalid_argument("combine: num_experts is missing");
   }
   check(launch_combine(p, n, reinterpret_cast<cudaStream_t>(stream)), "ep_combine_ht launch");
 }
@@ -184,6 +205,7 @@ PYBIND11_MODULE(_C, m) {
       .def_readonly("gather_hdr", &WsLayout::gather_hdr).def_readonly("gather_idx", &WsLayout::gather_idx)
       .def_readonly("gather_w", &WsLayout::gather_w).def_readonly("stage", &WsLayout::stage)
       .def_readonly("partial", &WsLayout::partial).def_readonly("wret", &WsLayout::wret)
+      .def_readonly("disp_flag", &WsLayout::disp_flag).def_readonly("comb_flag", &WsLayout::comb_flag)
       .def_readonly("ll", &WsLayout::ll).def_readonly("mega", &WsLayout::mega).def_readonly("total", &WsLayout::total)
       .def_readonly("max_tokens", &WsLayout::max_tokens).def_readonly("hidden", &WsLayout::hidden)
       .def_readonly("topk", &WsLayout::topk).def_readonly("world", &WsLayout::world)
@@ -232,8 +254,13 @@ PYBIND11_MODULE(_C, m) {
   m.def("live_instances", &live_instances);
 
   m.def("notify", &op_notify);
-  m.def("dispatch", &op_dispatch);
-  m.def("combine", &op_combine);
+  m.def("dispatch", &op_dispatch, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),
+        py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);
+  m.def("combine", &op_combine, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),
+        py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);
+  m.attr("group_tokens") = kGroupTokens;
+  m.attr("dispatch_prof_words") = kDispatchProfWords;
+  m.attr("combine_prof_words") = kCombineProfWords;
   m.def("barrier", &op_barrier);
   bind_low_latency(m);
   bind_mega(m);

@@ -29,6 +29,7 @@ struct NotifyArgs {
   int* slot_row;               // [T][K]  row on the destination rank (expanded layout), -1 if empty
   int* stage_meta;             // [P * Tmax][meta_stride]: token, n, n x (row | slot << 27); rank layout: token, 1, row, slot mask
   int* chunk_start;            // [P][NT + 1] staged-row index at the start of every source chunk
+  int* group_start;            // [P][NG + 1] the same per group of kGroupTokens tokens (NG = ceil(Tmax / kGroupTokens)); may be null
   int* rank_tokens;            // [P] tokens each source holds
   int* rank_rows;              // [P + 1] exclusive prefix of staged rows per source
   int* expert_counts;          // [L] unaligned rows per local expert
@@ -52,14 +53,22 @@ struct DispatchArgs {
   const float* x_sf;           // [T][H/128] (mode 1)
   int T, mode;
   const int* send_slot;        // [T][P]
+  const int* slot_row;         // [T][K] output row of every slot on its destination (expanded layout)
+  const long long* topk_idx;   // [T][K] of this rank's tokens (which slots are local)
   const int* stage_meta;
-  const int* chunk_start;
+  const int* group_start;      // [P][NG + 1]
   const int* rank_tokens;
+  const int* rank_rows;        // [P + 1] (rank layout: first output row of every source)
   int meta_stride, recv_rows;  // recv_rows: rows of recv_x (only read by the optional index checks; 0 = unknown)
+  int K, E, expand;
   void* recv_x;                // [R][H] 2-byte (mode 0) or e4m3 (modes 1, 2)
   float* recv_sf;              // [R][H/128] or null
+  unsigned long long* prof;    // profile build only: kDispatchProfWords words per block, or null
 };
-struct DispatchParams { WsLayout lay; int send_blocks, recv_blocks; DispatchArgs r[kMaxRanks]; };
+// local_direct: rows whose destination is the sending rank itself are written straight into recv_x by the sender
+// blocks (no staging, no flag); 0 sends them through the staging area like remote rows.
+struct DispatchParams { WsLayout lay; int send_blocks, recv_blocks, local_direct, profile; DispatchArgs r[kMaxRanks]; };
+constexpr int kDispatchProfWords = 8;   // per block: role, start ns, end ns, flag-wait ns (warp 0), rows moved (warp 0), 3 spare
 cudaError_t launch_dispatch(const DispatchParams& p, int nranks, cudaStream_t stream);
 
 // ---------------------------------------------------------------- high-throughput combine
@@ -71,7 +80,7 @@ struct CombineArgs {
   const __nv_bfloat16* x;      // [R][H] expert outputs
   const float* w;              // [R] (expanded) / [R][K] (rank layout) value channel, or null
   const int* stage_meta;
-  const int* chunk_start;
+  const int* group_start;      // [P][NG + 1]
   const int* rank_tokens;
   const int* send_slot;        // [T][P]
   const long long* topk_idx;   // [T][K] of the source tokens (validity of returned weights)
@@ -80,8 +89,12 @@ struct CombineArgs {
   const __nv_bfloat16* bias1;
   __nv_bfloat16* out;          // [T][H]
   float* out_w;                // [T][K] or null
+  unsigned long long* prof;    // profile build only: kCombineProfWords words per block, or null
 };
-struct CombineParams { WsLayout lay; int send_blocks, recv_blocks; CombineArgs r[kMaxRanks]; };
+// local_direct: the source side sums the rows of its own rank straight from x (same rounding: fp32 sum -> bf16 ->
+// fp32), so no local partial is written and no flag is needed for it.
+struct CombineParams { WsLayout lay; int send_blocks, recv_blocks, local_direct, profile; CombineArgs r[kMaxRanks]; };
+constexpr int kCombineProfWords = 8;    // per block: role, start ns, end ns, flag-wait ns (warp 0), rows moved (warp 0), 3 spare
 cudaError_t launch_combine(const CombineParams& p, int nranks, cudaStream_t stream);
 
 // ---------------------------------------------------------------- barrier

@@ -20,7 +20,9 @@
 namespace dep {
 
 constexpr int kMaxRanks = 8;          // one NVSwitch domain
-constexpr int kChunkTokens = 64;      // tokens per routing tile == tokens per completion flag
+constexpr int kChunkTokens = 64;      // tokens per routing tile of the layout pass
+constexpr int kGroupTokens = 4;       // tokens per completion flag of the high-throughput dispatch / combine
+constexpr int kGroupsPerChunk = kChunkTokens / kGroupTokens;
 constexpr int kMaxChunks = 256;       // => at most 16384 tokens per rank
 constexpr int kMaxTopk = 16;
 constexpr int kMaxExperts = 1024;
@@ -63,9 +65,6 @@ struct Control {
   unsigned long long ll_comb_ack[kMaxRanks];
   unsigned long long mega_flag[kMaxRanks][4];
   unsigned long long gmm_flag[kMaxRanks][4];   // a2av_gmm: staged, pulled; gmm_a2av: ready, pushed
-  unsigned long long disp_chunk[kMaxRanks][kMaxChunks];
-  unsigned long long comb_chunk[kMaxRanks][kMaxChunks];
-  unsigned int comb_parts[kMaxRanks][kMaxChunks];   // local: finished parts of a (source, chunk) in the running combine
   // diagnostics: where a pipeline wait gave up (warp-indexed records of 4 words)
   unsigned long long dbg[256];
 };
@@ -80,6 +79,8 @@ struct WsLayout {
   long long stage;         // byte  [P][Tmax][stage_row_bytes]   dispatch staging, written by sources
   long long partial;       // bf16  [Tmax][P][H]                  combine partials, written by expert ranks
   long long wret;          // float [Tmax][K]                     returned weights
+  long long disp_flag;     // u64   [P][ceil(Tmax / kGroupTokens)] dispatch: rows of (source, token group) have landed
+  long long comb_flag;     // u64   [P][ceil(Tmax / kGroupTokens)] combine: partials of (expert rank, token group) have landed
   long long ll;            // low-latency region
   long long mega;          // fused-MoE region
   long long total;

@@ -1,189 +1,259 @@
 // ep_dispatch_ht: all-to-all-v token push with rank-level dedup and receive-side expansion.
 //
-// Sender blocks read each token row once (bulk copy global -> shared), optionally quantise it
-// to e4m3 with one fp32 scale per 128 values in registers, and push it ONCE per destination
-// GPU into that GPU's staging area with bulk shared -> peer-global copies over NVLink.  After a
-// 64-token chunk the block publishes one release flag per destination.  Receiver blocks wait
-// for (source, chunk) flags and materialise every output row of a staged row (one row per
-// local expert the token routes to) with bulk copies, so a token crosses NVLink once no
-// matter how many experts of the destination it uses.
+// Every warp works on its own, there is no block-wide step inside the kernel.
+//   Sender warps take groups of kGroupTokens source tokens.  A token row is read once into registers
+//   (a quarter row per pass) and stored ONCE per destination GPU into that GPU's staging area through
+//   the peer mapping (NVLink), optionally quantised to e4m3 with one fp32 scale per 128 values on the
+//   way.  Rows whose destination is the sending rank itself are written straight into the output
+//   tensor, one copy per local expert.  After a group the warp publishes one release flag per
+//   destination: flags cover 4 tokens, so the receivers follow the senders closely and no sender ever
+//   drains a pipeline at a chunk boundary.
+//   Receiver warps take (source, group) items in the order the senders produce them, wait for the
+//   group's flag and materialise every output row of each staged row (one per local expert of the
+//   token), so a token crosses NVLink once no matter how many experts of the destination it uses.
 //
-// The reference's dispatch (csrc/kernels/dispatch/dispatch.cpp:463-590) has the same
-// three jobs (payload scatter, receiver expansion from a forward list, per-source completion
-// flags) but spreads them over 64 role-specialised vector cores and WQE queues; here the
-// copy engines of a few SMs do the moving and the roles are sender / receiver blocks.
+// Between two GPUs 32 SMs of 16-byte register stores reach the same rate as bulk shared->global copies
+// (about 0.69 TB/s per direction with both directions busy); the register form needs no staging in
+// shared memory, no proxy fences and no barriers, and lets a block keep 16 rows in flight.
+//
+// The reference's dispatch (csrc/kernels/dispatch/dispatch.cpp:463-590) has the same three jobs (payload
+// scatter, receiver expansion from a forward list, per-source completion flags) spread over 64
+// role-specialised vector cores and WQE queues.
 #include "api.h"
 
 namespace dep {
 
-constexpr int kStages = 2;
+constexpr int kHtThreads = 512;
+constexpr int kCopyUnroll = 7;    // 16-byte pieces per lane and pass: 3.5 KB in flight per warp
 
-__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long shfl_u64(unsigned long long v, int src) {
+  return __shfl_sync(0xffffffffu, v, src);
+}
 
-// bf16 row in `in` -> e4m3 bytes + fp32 scales in `out` ([H] bytes, then [H/128] floats).
-// amax over 128 values clamped to 1e-4, scale = amax / 448, q = e4m3(x * ((1 / amax) * 448)).
-__device__ __forceinline__ void quantize_row(const uint8_t* in, uint8_t* out, int H, int lane) {
-  const int nblk = H / 128;
-  float* sf = reinterpret_cast<float*>(out + H);
-  for (int b = 0; b < nblk; ++b) {
-    uint2 raw = *reinterpret_cast<const uint2*>(in + (size_t)(b * 128 + lane * 4) * 2);
-    __nv_bfloat162 p0 = *reinterpret_cast<__nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
-    float v0 = __low2float(p0), v1 = __high2float(p0), v2 = __low2float(p1), v3 = __high2float(p1);
-    float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+// Copies `units` 16-byte pieces from `src` to every destination in `mask`: lane l of the mask holds its
+// destination in `dst`.  All loads of a pass are issued before the first store.
+template <bool kPeerWritten>
+__device__ __forceinline__ void warp_fanout(const int4* src, int units, unsigned long long dst, unsigned mask, int lane) {
+  for (int u0 = 0; u0 < units; u0 += 32 * kCopyUnroll) {
+    int4 v[kCopyUnroll];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    amax = fmaxf(amax, 1e-4f);
-    float inv = __frcp_rn(amax) * 448.0f;  // reciprocal then multiply: the rounding sequence of the published recipe
-    uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(v0 * inv, __NV_SATFINITE, __NV_E4M3) |
-                 ((uint32_t)__nv_cvt_float_to_fp8(v1 * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
-                 ((uint32_t)__nv_cvt_float_to_fp8(v2 * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
-                 ((uint32_t)__nv_cvt_float_to_fp8(v3 * inv, __NV_SATFINITE, __NV_E4M3) << 24);
-    *reinterpret_cast<uint32_t*>(out + b * 128 + lane * 4) = q;
-    if (lane == 0) sf[b] = amax / 448.0f;
+    for (int i = 0; i < kCopyUnroll; ++i) {
+      const int u = u0 + i * 32 + lane;
+      if (u < units) v[i] = kPeerWritten ? __ldcg(src + u) : __ldg(src + u);
+    }
+    for (unsigned m = mask; m; m &= m - 1) {
+      int4* d = reinterpret_cast<int4*>(shfl_u64(dst, __ffs(m) - 1));
+#pragma unroll
+      for (int i = 0; i < kCopyUnroll; ++i) {
+        const int u = u0 + i * 32 + lane;
+        if (u < units) d[u] = v[i];
+      }
+    }
   }
 }
 
-__global__ void __launch_bounds__(256, 1) ep_dispatch_ht_kernel(const __grid_constant__ DispatchParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+// The same for a short run of floats (the scales of an fp8 row).
+template <bool kPeerWritten>
+__device__ __forceinline__ void warp_fanout_f32(const float* src, int n, unsigned long long dst, unsigned mask, int lane) {
+  for (int b0 = 0; b0 < n; b0 += 32) {   // the trip count is the same for every lane: all of them take part in the shuffles
+    const int b = b0 + lane;
+    float v = 0.f;
+    if (b < n) v = kPeerWritten ? __ldcg(src + b) : __ldg(src + b);
+    for (unsigned m = mask; m; m &= m - 1) {
+      float* d = reinterpret_cast<float*>(shfl_u64(dst, __ffs(m) - 1));
+      if (b < n) d[b] = v;
+    }
+  }
+}
+
+// 16 bf16 values (two 16-byte pieces) -> their absolute maximum.
+__device__ __forceinline__ float amax16(const int4& a, const int4& b, float v[16]) {
+  const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __low2float(ha[i]); v[2 * i + 1] = __high2float(ha[i]);
+    v[8 + 2 * i] = __low2float(hb[i]); v[8 + 2 * i + 1] = __high2float(hb[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
+
+// Fused quantiser: a bf16 row -> e4m3 bytes and one fp32 scale per 128 values, written to every destination.
+// amax over 128 values clamped to 1e-4, scale = amax / 448, q = e4m3(x * ((1 / amax) * 448)): reciprocal, then
+// multiply, the rounding sequence of the published recipe (deep_ep/utils/math.py:45-60 of the reference).
+// Lane l of a pass owns 16 consecutive values; 8 consecutive lanes share a scale.
+__device__ __forceinline__ void warp_quant_fanout(const int4* src, int H, unsigned long long dst, unsigned long long dst_sf,
+                                                  unsigned mask, int lane) {
+  const int units = H / 16, passes = (units + 31) / 32, nsf = H / 128;
+  float sf_keep[2] = {0.f, 0.f};   // lane l ends up with the scales of blocks l and 32 + l
+  for (int p0 = 0; p0 < passes; p0 += 2) {
+    int4 raw[2][2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int u = (p0 + q) * 32 + lane;
+      if (p0 + q < passes && u < units) { raw[q][0] = __ldg(src + 2 * u); raw[q][1] = __ldg(src + 2 * u + 1); }
+      else { raw[q][0] = make_int4(0, 0, 0, 0); raw[q][1] = make_int4(0, 0, 0, 0); }
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int p = p0 + q, u = p * 32 + lane;
+      if (p >= passes) break;
+      float v[16];
+      float amax = amax16(raw[q][0], raw[q][1], v);
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      amax = fmaxf(amax, 1e-4f);
+      const float inv = __frcp_rn(amax) * 448.0f;
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        w[i] = (uint32_t)__nv_cvt_float_to_fp8(v[4 * i] * inv, __NV_SATFINITE, __NV_E4M3) |
+               ((uint32_t)__nv_cvt_float_to_fp8(v[4 * i + 1] * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
+               ((uint32_t)__nv_cvt_float_to_fp8(v[4 * i + 2] * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
+               ((uint32_t)__nv_cvt_float_to_fp8(v[4 * i + 3] * inv, __NV_SATFINITE, __NV_E4M3) << 24);
+      const int4 out = make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
+      // block p * 4 + g lives in lanes 8g..8g+7; lane l keeps the scale of block 32 * (p / 8) + l
+      const float g = __shfl_sync(0xffffffffu, amax / 448.0f, (lane & 3) * 8);
+      if ((lane >> 2) == (p & 7)) { if ((p >> 3) == 0) sf_keep[0] = g; else sf_keep[1] = g; }
+      for (unsigned m = mask; m; m &= m - 1) {
+        int4* d = reinterpret_cast<int4*>(shfl_u64(dst, __ffs(m) - 1));
+        if (u < units) d[u] = out;
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int b = 32 * q + lane;
+    for (unsigned m = mask; m; m &= m - 1) {
+      float* d = reinterpret_cast<float*>(shfl_u64(dst_sf, __ffs(m) - 1));
+      if (b < nsf) d[b] = sf_keep[q];
+    }
+  }
+}
+
+template <bool kProfile>
+__global__ void __launch_bounds__(kHtThreads, 1) ep_dispatch_ht_kernel(const __grid_constant__ DispatchParams p) {
   const DispatchArgs& a = p.r[blockIdx.y];
   const WsLayout& lay = p.lay;
   const RankCtx& ctx = a.ctx;
-  const int P = ctx.world, me = ctx.rank, Tmax = lay.max_tokens, H = lay.hidden;
-  const int NT = (Tmax + kChunkTokens - 1) / kChunkTokens;
+  const int P = ctx.world, me = ctx.rank, Tmax = lay.max_tokens, H = lay.hidden, K = a.K;
+  const int NG = (Tmax + kGroupTokens - 1) / kGroupTokens;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpDispatch] + 1;
 
   const bool fp8 = a.mode != kDispatchBf16;
-  const int sf_bytes = fp8 ? (H / 128) * 4 : 0;
-  const int row_bytes = fp8 ? H : H * 2;                        // payload bytes of one output row
-  const int moved = fp8 ? ((H + sf_bytes + 15) & ~15) : H * 2;  // bytes of one staged row
-  const bool sf_bulk = (sf_bytes % 16) == 0;
-  const int in_bytes = a.mode == kDispatchFp8Fused ? H * 2 : moved;
-  const int out_bytes = a.mode == kDispatchFp8Fused ? moved : 0;
-  const int slot_bytes = (in_bytes + out_bytes + 127) & ~127;
+  const int nsf = fp8 ? H / 128 : 0;
+  const int row_bytes = fp8 ? H : H * 2;     // payload bytes of one output row
+  const int units = row_bytes / 16;
+  const bool sender = (int)blockIdx.x < p.send_blocks;
+  unsigned long long t_begin = 0, t_wait = 0, n_rows = 0;
+  if (kProfile) t_begin = global_timer_ns();
 
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * kStages;
-  uint8_t* slots = smem + 128 + (size_t)warp * kStages * slot_bytes;
-  if (lane == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
-    fence_barrier_init();
-  }
-  __syncthreads();
-  uint32_t parity[kStages] = {0, 0};
-
-  if ((int)blockIdx.x < p.send_blocks) {
+  if (sender) {
     // ================================================================ sender
     int ok = 1;
-    if (threadIdx.x < P) ok = wait_flag_ge(&ctl->disp_ack[threadIdx.x], epoch - 1, ctx, kOpDispatch, 0, threadIdx.x);
-    int alive = __syncthreads_and(ok);
-    const int nchunks = (a.T + kChunkTokens - 1) / kChunkTokens;
+    if (lane < P) ok = wait_flag_ge(&ctl->disp_ack[lane], epoch - 1, ctx, kOpDispatch, 0, lane);
+    bool alive = __all_sync(0xffffffffu, ok);
+    const int Lx = a.E / P, ngroups = (a.T + kGroupTokens - 1) / kGroupTokens;
     const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
     const int src_row_bytes = a.mode == kDispatchFp8Given ? H : H * 2;
-
-    auto issue_load = [&](int t, int s) {  // lane 0 only
-      uint8_t* dst = slots + (size_t)s * slot_bytes;
-      uint32_t bytes = src_row_bytes + ((a.mode == kDispatchFp8Given && sf_bulk) ? sf_bytes : 0);
-      mbar_expect_tx(&bars[s], bytes);
-      bulk_g2s(dst, x + (size_t)t * src_row_bytes, src_row_bytes, &bars[s]);
-      if (a.mode == kDispatchFp8Given && sf_bulk)
-        bulk_g2s(dst + H, reinterpret_cast<const uint8_t*>(a.x_sf) + (size_t)t * sf_bytes, sf_bytes, &bars[s]);
-    };
-
-    for (int c = blockIdx.x; c < nchunks && alive; c += p.send_blocks) {
-      const int t1 = min(a.T, (c + 1) * kChunkTokens);
-      int t = c * kChunkTokens + warp;
-      if (t < t1 && lane == 0) issue_load(t, 0);
-      for (int it = 0; t < t1; t += nwarps, ++it) {
-        const int s = it & 1, tn = t + nwarps;
-        if (lane == 0) {
-          bulk_wait_read<0>();  // the other slot's stores have left shared memory
-          if (tn < t1) issue_load(tn, s ^ 1);
+    uint8_t* recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
+    for (int gi = blockIdx.x * nwarps + warp; gi < ngroups && alive; gi += p.send_blocks * nwarps) {
+      const int t1 = min(a.T, (gi + 1) * kGroupTokens);
+      for (int t = gi * kGroupTokens; t < t1; ++t) {
+        // lanes 0..P-1: the staged row on every destination rank; lanes P..P+K-1: the output rows on this rank
+        unsigned long long dst = 0, dst_sf = 0;
+        if (lane < P) {
+          const int j = a.send_slot[(size_t)t * P + lane];
+          if (j >= 0 && !(p.local_direct && lane == me) && DEP_INDEX_OK(ctx, j, Tmax, kOpDispatch, 0)) {
+            dst = reinterpret_cast<unsigned long long>(ctx.ws[lane] + lay.stage + ((size_t)me * Tmax + j) * lay.stage_row_bytes);
+            dst_sf = dst + H;
+          }
+        } else if (p.local_direct && lane < P + K) {
+          const int k = lane - P;
+          int row = -1;
+          if (a.expand) {
+            const int r = a.slot_row[(size_t)t * K + k];
+            const long long e = a.topk_idx[(size_t)t * K + k];
+            if (r >= 0 && e >= 0 && e < a.E && (int)(e / Lx) == me) row = r;
+          } else if (k == 0) {
+            const int j = a.send_slot[(size_t)t * P + me];
+            if (j >= 0) row = a.rank_rows[me] + j;
+          }
+          if (row >= 0 && (a.recv_rows <= 0 || DEP_INDEX_OK(ctx, row, a.recv_rows, kOpDispatch, 1))) {
+            dst = reinterpret_cast<unsigned long long>(recv_x + (size_t)row * row_bytes);
+            dst_sf = reinterpret_cast<unsigned long long>(a.recv_sf + (size_t)row * nsf);
+          }
         }
-        int j = lane < P ? a.send_slot[(size_t)t * P + lane] : -1;
-        if (!mbar_wait(&bars[s], parity[s])) report_failure(ctx, kStatusTimeout, kOpDispatch, 10, me, 0, 0);
-        parity[s] ^= 1;
-        uint8_t* in = slots + (size_t)s * slot_bytes;
-        uint8_t* src = in;
+        const unsigned mask = __ballot_sync(0xffffffffu, dst != 0);
+        if (mask == 0) continue;
+        const uint8_t* src = x + (size_t)t * src_row_bytes;
         if (a.mode == kDispatchFp8Fused) {
-          src = in + in_bytes;
-          quantize_row(in, src, H, lane);
-          fence_proxy_async_smem();
-        } else if (a.mode == kDispatchFp8Given && !sf_bulk) {
-          const float* sf = a.x_sf + (size_t)t * (H / 128);
-          for (int i = lane; i < H / 128; i += 32) reinterpret_cast<float*>(in + H)[i] = sf[i];
-          fence_proxy_async_smem();
+          warp_quant_fanout(reinterpret_cast<const int4*>(src), H, dst, dst_sf, mask, lane);
+        } else {
+          warp_fanout<false>(reinterpret_cast<const int4*>(src), units, dst, mask, lane);
+          if (fp8) warp_fanout_f32<false>(a.x_sf + (size_t)t * nsf, nsf, dst_sf, mask, lane);
         }
-        __syncwarp();
-        for (int d = 0; d < P; ++d) {
-          int jd = __shfl_sync(0xffffffffu, j, d);
-          if (jd >= 0 && lane == 0 && DEP_INDEX_OK(ctx, jd, Tmax, kOpDispatch, 0))
-            bulk_s2g(ctx.ws[d] + lay.stage + ((size_t)me * Tmax + jd) * lay.stage_row_bytes, src, moved);
-        }
-        if (lane == 0) bulk_commit();
+        if (kProfile) n_rows += __popc(mask);
       }
-      if (lane == 0) { bulk_wait<0>(); fence_proxy_async(); }
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x < P) st_release_sys(&control_of(ctx.ws[threadIdx.x])->disp_chunk[me][c], epoch);
+      // publish the group: every lane's stores are ordered before the flag by the warp barrier + release
+      __syncwarp();
+      if (lane < P && !(p.local_direct && lane == me))
+        st_release_sys(reinterpret_cast<unsigned long long*>(ctx.ws[lane] + lay.disp_flag) + (size_t)me * NG + gi, epoch);
     }
   } else {
     // ================================================================ receiver
-    const int rb = blockIdx.x - p.send_blocks;
-    int max_nt = 0;
-    for (int r = 0; r < P; ++r) max_nt = max(max_nt, (a.rank_tokens[r] + kChunkTokens - 1) / kChunkTokens);
+    const int nrecv = p.recv_blocks * nwarps, w = (blockIdx.x - p.send_blocks) * nwarps + warp;
+    int max_ng = 0;
+    for (int r = 0; r < P; ++r) max_ng = max(max_ng, (a.rank_tokens[r] + kGroupTokens - 1) / kGroupTokens);
     uint8_t* recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
     const uint8_t* stage = ctx.ws[me] + lay.stage;
-    const int nsf = H / 128;
-    int alive = 1;
-    // With few ranks there are fewer (source, chunk) pairs than receiver blocks: a chunk's rows are then cut into up
-    // to 8 parts that different blocks expand (about two rounds of work items over the blocks).
-    const int parts = max(1, min(8, (2 * p.recv_blocks + max_nt * P - 1) / max(1, max_nt * P)));
-    for (int item = rb; item < max_nt * P * parts && alive; item += p.recv_blocks) {
-      const int part = item % parts, pair = item / parts;
-      const int c = pair / P, r = (me + pair % P) % P;
-      if (c * kChunkTokens >= a.rank_tokens[r]) continue;
-      const int c0 = a.chunk_start[r * (NT + 1) + c], cn = a.chunk_start[r * (NT + 1) + c + 1] - c0;
-      const int j0 = c0 + cn * part / parts, j1 = c0 + cn * (part + 1) / parts;
-      if (j0 == j1) continue;
+    const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(ctx.ws[me] + lay.disp_flag);
+    for (int item = w; item < max_ng * P; item += nrecv) {
+      const int gi = item / P, r = (me + item % P) % P;
+      if ((p.local_direct && r == me) || gi * kGroupTokens >= a.rank_tokens[r]) continue;
+      const int j0 = a.group_start[r * (NG + 1) + gi], j1 = a.group_start[r * (NG + 1) + gi + 1];
+      if (j0 >= j1) continue;
+      if (j0 < 0 || j1 - j0 > kGroupTokens || j1 > Tmax) {   // a group stages at most one row per token: the plan is damaged
+        if (lane == 0) report_failure(ctx, kStatusBadArgument, kOpDispatch, 3, r, kGroupTokens, (unsigned long long)(j1 - j0));
+        break;
+      }
       int ok = 1;
-      if (threadIdx.x == 0) ok = wait_flag_ge(&ctl->disp_chunk[r][c], epoch, ctx, kOpDispatch, 1, r);
-      alive = __syncthreads_and(ok);
-      if (!alive) break;
-      fence_proxy_async();
-
-      auto issue_load = [&](int j, int s) {  // lane 0 only
-        mbar_expect_tx(&bars[s], moved);
-        bulk_g2s(slots + (size_t)s * slot_bytes, stage + ((size_t)r * Tmax + j) * lay.stage_row_bytes, moved, &bars[s]);
-      };
-      int j = j0 + warp;
-      if (j < j1 && lane == 0) { bulk_wait_read<0>(); issue_load(j, 0); }
-      for (int it = 0; j < j1; j += nwarps, ++it) {
-        const int s = it & 1, jn = j + nwarps;
-        if (lane == 0) {
-          bulk_wait_read<0>();
-          if (jn < j1) issue_load(jn, s ^ 1);
-        }
+      if (lane == 0) {
+        unsigned long long t0 = 0;
+        if (kProfile) t0 = global_timer_ns();
+        ok = wait_flag_ge(flags + (size_t)r * NG + gi, epoch, ctx, kOpDispatch, 1, r);
+        if (kProfile) t_wait += global_timer_ns() - t0;
+      }
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      for (int j = j0; j < j1; ++j) {
+        if (!DEP_INDEX_OK(ctx, j, Tmax, kOpDispatch, 2)) continue;
         const int* rec = a.stage_meta + ((size_t)r * Tmax + j) * a.meta_stride;
-        const int n = rec[1];
-        if (!mbar_wait(&bars[s], parity[s])) report_failure(ctx, kStatusTimeout, kOpDispatch, 11, r, 0, 0);
-        parity[s] ^= 1;
-        const uint8_t* src = slots + (size_t)s * slot_bytes;
-        for (int i = 0; i < n; ++i) {
-          const int row = rec[2 + i] & kRowMask;
-          if (a.recv_rows > 0 && !DEP_INDEX_OK(ctx, row, a.recv_rows, kOpDispatch, 1)) continue;
-          if (lane == 0) {
-            bulk_s2g(recv_x + (size_t)row * row_bytes, src, row_bytes);
-            if (fp8 && sf_bulk) bulk_s2g(a.recv_sf + (size_t)row * nsf, src + H, sf_bytes);
+        const int n = min(rec[1], kMaxTopk);
+        unsigned long long dst = 0, dst_sf = 0;
+        if (lane < n) {
+          const int row = rec[2 + lane] & kRowMask;
+          if (a.recv_rows <= 0 || DEP_INDEX_OK(ctx, row, a.recv_rows, kOpDispatch, 1)) {
+            dst = reinterpret_cast<unsigned long long>(recv_x + (size_t)row * row_bytes);
+            dst_sf = reinterpret_cast<unsigned long long>(a.recv_sf + (size_t)row * nsf);
           }
-          if (fp8 && !sf_bulk)
-            for (int q = lane; q < nsf; q += 32) a.recv_sf[(size_t)row * nsf + q] = reinterpret_cast<const float*>(src + H)[q];
         }
-        __syncwarp();
-        if (lane == 0) bulk_commit();
+        const unsigned mask = __ballot_sync(0xffffffffu, dst != 0);
+        const uint8_t* src = stage + ((size_t)r * Tmax + j) * lay.stage_row_bytes;
+        warp_fanout<true>(reinterpret_cast<const int4*>(src), units, dst, mask, lane);
+        if (fp8) warp_fanout_f32<true>(reinterpret_cast<const float*>(src + H), nsf, dst_sf, mask, lane);
+        if (kProfile) n_rows += __popc(mask);
       }
     }
-    if (lane == 0) bulk_wait<0>();
+  }
+
+  if (kProfile && a.prof != nullptr && threadIdx.x == 0) {
+    unsigned long long* rec = a.prof + (size_t)blockIdx.x * kDispatchProfWords;
+    rec[0] = sender ? 0 : 1; rec[1] = t_begin; rec[2] = global_timer_ns(); rec[3] = t_wait; rec[4] = n_rows;
   }
 
   // ---- exit: the last block of this rank tells every source that its staged rows are consumed
@@ -194,27 +264,12 @@ __global__ void __launch_bounds__(256, 1) ep_dispatch_ht_kernel(const __grid_con
   }
 }
 
-static size_t dispatch_slot_bytes(const WsLayout& lay, int mode) {
-  const int H = lay.hidden;
-  const bool fp8 = mode != kDispatchBf16;
-  const int moved = fp8 ? ((H + (H / 128) * 4 + 15) & ~15) : H * 2;
-  const int in_bytes = mode == kDispatchFp8Fused ? H * 2 : moved;
-  const int out_bytes = mode == kDispatchFp8Fused ? moved : 0;
-  return (size_t)((in_bytes + out_bytes + 127) & ~127);
-}
-
 cudaError_t launch_dispatch(const DispatchParams& p, int nranks, cudaStream_t stream) {
-  const size_t slot = dispatch_slot_bytes(p.lay, p.r[0].mode);
-  const size_t budget = 220 << 10;
-  int warps = (int)(budget / (kStages * slot));
-  if (warps < 1) return cudaErrorInvalidValue;
-  if (warps > 8) warps = 8;
-  const size_t smem = 128 + (size_t)warps * kStages * slot;
-  cudaError_t e = cudaFuncSetAttribute(ep_dispatch_ht_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  dim3 grid(p.send_blocks + p.recv_blocks, nranks), block(warps * 32);
+  if (p.lay.hidden > 8192) return cudaErrorInvalidValue;   // the fused quantiser keeps at most 64 scales per row in registers
+  dim3 grid(p.send_blocks + p.recv_blocks, nranks), block(kHtThreads);
   void* args[] = {const_cast<DispatchParams*>(&p)};
-  return cudaLaunchCooperativeKernel((const void*)ep_dispatch_ht_kernel, grid, block, args, smem, stream);
+  const void* fn = p.profile ? (const void*)ep_dispatch_ht_kernel<true> : (const void*)ep_dispatch_ht_kernel<false>;
+  return cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream);
 }
 
 }  // namespace dep

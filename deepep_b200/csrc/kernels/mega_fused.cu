@@ -50,13 +50,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid
 }
 
 cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, cudaStream_t stream) {
-  static bool configured = false;
   const size_t smem = gemm_smem_bytes(3, true);
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(mega_moe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  // the attribute belongs to the current device, so it is set on every launch (a process may drive several GPUs)
+  cudaError_t e = cudaFuncSetAttribute(mega_moe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
   dim3 grid(blocks, nranks), block(kFusedThreads);
   void* args[] = {const_cast<MegaFusedParams*>(&p)};
   return cudaLaunchCooperativeKernel((const void*)mega_moe_kernel, grid, block, args, smem, stream);

@@ -9,13 +9,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mega_gemm_kernel(const __grid
 }
 
 cudaError_t launch_mega_gemm(const MegaGemmParams& p, int blocks, cudaStream_t stream) {
-  static bool configured = false;
   const size_t a = gemm_smem_bytes(4, false), b = gemm_smem_bytes(3, true);
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(mega_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(a > b ? a : b));
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  // the attribute belongs to the current device, so it is set on every launch (a process may drive several GPUs)
+  cudaError_t e = cudaFuncSetAttribute(mega_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(a > b ? a : b));
+  if (e != cudaSuccess) return e;
   void* args[] = {const_cast<MegaGemmParams*>(&p)};
   return cudaLaunchKernel((const void*)mega_gemm_kernel, dim3(blocks), dim3(kGemmThreads), args, p.epi == kEpiCombine ? b : a, stream);
 }

@@ -75,8 +75,12 @@ extern "C" __attribute__((visibility("default"))) int deepep_notify_layout_noall
   if (expert_alignment < 1) return fail("expert_alignment must be positive");
   if (!topk_idx || !send_slot || !slot_row || !stage_meta || !chunk_start || !expert_counts || !expert_offsets || !recv_row_src || !info)
     return fail("a required pointer is null");
-  if (row_capacity < (long long)num_tokens * (num_topk < num_experts ? num_topk : num_experts))
-    return fail("row_capacity is smaller than num_tokens * min(num_topk, num_experts)");
+  // rows the layout can occupy: every routed slot, plus the padding that rounds each expert's block up to the alignment
+  const long long rows_needed = (long long)num_tokens * (num_topk < num_experts ? num_topk : num_experts) +
+                                (long long)num_experts * (expert_alignment - 1);
+  if (row_capacity < rows_needed)
+    return fail("row_capacity is smaller than num_tokens * min(num_topk, num_experts) + num_experts * (expert_alignment - 1) = " +
+                std::to_string(rows_needed));
   unsigned char* scratch = nullptr;
   if (scratch_for_current_device(&scratch)) return 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -35,8 +35,11 @@ extern "C" {
 //   stage_meta     [DEEPEP_NOALLOC_MAX_TOKENS][2 + max(2, min(num_topk, num_experts))]
 //   chunk_start    [DEEPEP_NOALLOC_MAX_TOKENS / 64 + 1]
 //   expert_counts  [num_experts], expert_offsets [num_experts + 1]
-//   recv_row_src   [row_capacity]                     token * num_topk + slot of each output row
+//   recv_row_src   [row_capacity]                     token * num_topk + slot of each output row (-1: padding row)
 //   recv_weights   [row_capacity] or NULL
+//   row_capacity   must be at least num_tokens * min(num_topk, num_experts) + num_experts * (expert_alignment - 1):
+//                  with an alignment above 1 every expert's row block is padded up to a multiple of it, and the padding
+//                  rows are written too.  A smaller capacity is rejected before anything is launched.
 //   info           [4 + num_experts] int32: rows, staged rows, tokens, call number, then the counts again
 // Returns 0 on success.  The work is queued on `stream` (a cudaStream_t); outputs are ready once it drains.
 int deepep_notify_layout_noalloc(const long long* topk_idx, const float* topk_weights, int num_tokens, int num_topk,

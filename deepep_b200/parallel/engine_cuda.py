@@ -45,6 +45,7 @@ class RoutingPlan:
     slot_row: Optional[torch.Tensor]
     stage_meta: Optional[torch.Tensor]
     chunk_start: Optional[torch.Tensor]
+    group_start: Optional[torch.Tensor]
     rank_tokens: Optional[torch.Tensor]
     rank_rows: Optional[torch.Tensor]
     expert_counts: torch.Tensor
@@ -58,13 +59,19 @@ class RoutingPlan:
     topk_w: Optional[torch.Tensor] = None
 
     def tensors(self):
-        return [t for t in (self.topk_idx, self.send_slot, self.slot_row, self.stage_meta, self.chunk_start, self.rank_tokens,
+        return [t for t in (self.topk_idx, self.send_slot, self.slot_row, self.stage_meta, self.chunk_start, self.group_start,
+                            self.rank_tokens,
                             self.rank_rows, self.expert_counts, self.expert_offsets, self.recv_row_src, self.recv_w,
                             self.recv_idx) if t is not None]
 
 
 def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
+
+
+# Share of the blocks on the side that drives NVLink (dispatch: senders, combine: expert side), by world size.
+DISPATCH_SEND_FRACTION = {1: 1.0, 2: 0.5, 4: 0.4, 8: 0.35}
+COMBINE_SEND_FRACTION = {1: 0.0, 2: 0.5, 4: 0.55, 8: 0.6}
 
 
 class CudaEngine:
@@ -78,20 +85,23 @@ class CudaEngine:
         props = torch.cuda.get_device_properties(device)
         self.sm_count = props.multi_processor_count
         per_rank = max(2, self.sm_count // self.n)
-        # Measured on 8 B200s: one SM moves about 30 GB/s through its copy engine, so saturating NVLink takes dozens
-        # of SMs.  Defaults: dispatch 96 blocks (1/4 senders), combine nearly all SMs (3/4 on the expert side).
-        # With one or two ranks most of the traffic is the receive-side expansion in local memory, which scales with the
-        # number of SMs (about 30 GB/s each): use them all.
-        self.dispatch_blocks = min(per_rank, num_sms) if num_sms else min(per_rank, 96 if self.world > 2 else max(2, self.sm_count - 4))
-        # senders move one row per (token, destination rank), receivers up to top-k rows per received token
-        self.dispatch_send_fraction = 0.25 if self.world > 2 else 0.125
-        self.combine_blocks = min(per_rank, num_sms) if num_sms else min(per_rank, max(2, self.sm_count - 4))
-        self.default_blocks = self.dispatch_blocks
+        # One block per SM.  The sender side of dispatch (expert side of combine) has to keep NVLink busy, which takes
+        # 32 SMs or more; the other side moves the rows inside local memory.  With one rank every row is local and is
+        # written (read) directly by the sender (source) side, so that side gets all the blocks.
+        budget = min(per_rank, num_sms) if num_sms else min(per_rank, max(2, self.sm_count - 4))
+        self.dispatch_blocks = self.combine_blocks = self.default_blocks = budget
+        self.dispatch_send_fraction = DISPATCH_SEND_FRACTION.get(self.world, 0.35)
+        self.combine_send_fraction = COMBINE_SEND_FRACTION.get(self.world, 0.6)
+        # rows that stay on their rank bypass the staging area / the partial area (see the kernels' headers)
+        self.local_direct = os.environ.get("DEEPEP_HT_LOCAL_DIRECT", "1") not in ("", "0")
         nt = -(-layout.max_tokens // self.C.chunk_tokens)
         self._nt = nt
         # opt-in device timing of every launch (DEEPEP_PROFILE=1 or enable_profiling()): events around each kernel
         self._profile = os.environ.get("DEEPEP_PROFILE", "0") not in ("", "0")
         self._timings: List[Tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
+        # opt-in device-side records (the profile instantiation of the dispatch / combine kernels): one record per block
+        self._device_profile = False
+        self._prof: dict = {}
         self._scratch = []
         for _ in range(self.n):
             self._scratch.append(dict(
@@ -113,6 +123,40 @@ class CudaEngine:
         ``csrc/ops/device_phase_timing.hpp:13-50``, and the optional event timing of its notify op)."""
         self._profile = bool(on)
         self._timings.clear()
+
+    def enable_device_profile(self, on: bool = True) -> None:
+        """Launch the profile instantiation of the high-throughput dispatch / combine kernels (``template <bool
+        kProfile>``): every block records its role, its start and end time, the time its first warp spent waiting for
+        flags and the rows that warp moved.  The production instantiation carries none of that code.
+        Parity: the reference's ``template <bool Profile>`` kernels (``csrc/kernels/dispatch/profile.hpp``,
+        ``csrc/kernels/combine/profile.hpp``)."""
+        self._device_profile = bool(on)
+        self._prof.clear()
+
+    def _prof_buffer(self, op: str, i: int):
+        if not self._device_profile:
+            return None
+        words = self.C.dispatch_prof_words if op == "dispatch" else self.C.combine_prof_words
+        key = (op, i)
+        if key not in self._prof:
+            self._prof[key] = torch.zeros((self.sm_count, words), dtype=torch.int64, device=self.device)
+        return self._prof[key].data_ptr()
+
+    def pop_device_profile(self) -> dict:
+        """``{(op, rank index): [dict(role, start_us, end_us, flag_wait_us, rows)]}`` of the last profiled launch of each
+        op (times relative to the earliest block start of that launch)."""
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for key, buf in self._prof.items():
+            rows = [r for r in buf.cpu().tolist() if r[2] > 0]
+            if not rows:
+                continue
+            t0 = min(r[1] for r in rows)
+            side = ("sender", "receiver") if key[0] == "dispatch" else ("expert", "source")
+            out[key] = [dict(role=side[int(r[0])], start_us=(r[1] - t0) / 1e3, end_us=(r[2] - t0) / 1e3,
+                             flag_wait_us=r[3] / 1e3, rows=int(r[4])) for r in rows]
+            buf.zero_()
+        return out
 
     def _timed(self, name: str, stream, launch) -> None:
         if not self._profile:
@@ -146,7 +190,11 @@ class CudaEngine:
                     "restart the distributed job")
 
     def split_blocks(self, total: int, send_fraction: float, default: int = 0) -> Tuple[int, int]:
+        """(blocks of the NVLink side, blocks of the local side).  A fraction of 1.0 / 0.0 gives every block to one
+        side, which only a single rank with direct local rows may do."""
         total = max(2, min(total, self.sm_count // self.n) if total else (default or self.default_blocks))
+        if self.world == 1 and self.local_direct and send_fraction in (0.0, 1.0):
+            return (total, 0) if send_fraction == 1.0 else (0, total)
         send = min(total - 1, max(1, int(round(total * send_fraction))))
         return send, total - send
 
@@ -177,7 +225,8 @@ class CudaEngine:
                 num_rows=rcap, num_staged_rows=0, expert_counts_list=None, topk_idx=idx,
                 send_slot=torch.empty((max(T, 1), P), **i32), slot_row=torch.empty((max(T, 1), K), **i32),
                 stage_meta=torch.empty((P * lay.max_tokens, stride), **i32),
-                chunk_start=torch.empty((P, self._nt + 1), **i32), rank_tokens=torch.empty((P,), **i32),
+                chunk_start=torch.empty((P, self._nt + 1), **i32),
+                group_start=torch.empty((P, -(-lay.max_tokens // C.group_tokens) + 1), **i32), rank_tokens=torch.empty((P,), **i32),
                 rank_rows=torch.empty((P + 1,), **i32), expert_counts=torch.empty((local,), **i32),
                 expert_offsets=torch.empty((local + 1,), **i32), recv_row_src=torch.empty((rcap,), **i32),
                 recv_w=(torch.empty((rcap,) if expand else (rcap, K), dtype=torch.float32, device=dev)
@@ -190,7 +239,8 @@ class CudaEngine:
                              alignment=alignment, meta_stride=stride, hist=sc["hist"].data_ptr(), hits=sc["hits"].data_ptr(),
                              own_hits=sc["own_hits"].data_ptr(), cnt=sc["cnt"].data_ptr(), send_slot=plan.send_slot.data_ptr(),
                              slot_row=plan.slot_row.data_ptr(), stage_meta=plan.stage_meta.data_ptr(),
-                             chunk_start=plan.chunk_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
+                             chunk_start=plan.chunk_start.data_ptr(), group_start=plan.group_start.data_ptr(),
+                             rank_tokens=plan.rank_tokens.data_ptr(),
                              rank_rows=plan.rank_rows.data_ptr(), expert_counts=plan.expert_counts.data_ptr(),
                              expert_offsets=plan.expert_offsets.data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(),
                              recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap))
@@ -208,8 +258,10 @@ class CudaEngine:
                 plan.expert_counts_list = box[4:4 + local]
         return plans
 
-    def dispatch(self, xs: Sequence, plans: Sequence[RoutingPlan], mode: int, blocks: int = 0, stream=None):
-        """xs[i] is a tensor (modes 0, 2) or a (fp8, scales) pair (mode 1). Returns [(recv_x, recv_sf | None)]."""
+    def dispatch(self, xs: Sequence, plans: Sequence[RoutingPlan], mode: int, blocks: int = 0, stream=None,
+                 split: Optional[Tuple[int, int]] = None):
+        """xs[i] is a tensor (modes 0, 2) or a (fp8, scales) pair (mode 1). Returns [(recv_x, recv_sf | None)].
+        ``split`` = (sender blocks, receiver blocks) overrides the default division."""
         lay, dev = self.layout, self.device
         H = lay.hidden
         outs, args = [], []
@@ -228,16 +280,20 @@ class CudaEngine:
                     recv_sf.zero_()
             outs.append((recv_x, recv_sf))
             args.append(dict(x=x.data_ptr(), x_sf=_ptr(sf), T=plan.num_tokens, mode=mode, send_slot=plan.send_slot.data_ptr(),
-                             stage_meta=plan.stage_meta.data_ptr(), chunk_start=plan.chunk_start.data_ptr(),
-                             rank_tokens=plan.rank_tokens.data_ptr(), meta_stride=plan.meta_stride,
-                             recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf), recv_rows=recv_x.shape[0]))
-        send, recv = self.split_blocks(blocks, self.dispatch_send_fraction, self.dispatch_blocks)
-        self._timed("dispatch", stream, lambda: self.C.dispatch(lay, self.sessions, args, send, recv, self._stream(stream)))
+                             slot_row=plan.slot_row.data_ptr(), topk_idx=plan.topk_idx.data_ptr(),
+                             stage_meta=plan.stage_meta.data_ptr(), group_start=plan.group_start.data_ptr(),
+                             rank_tokens=plan.rank_tokens.data_ptr(), rank_rows=plan.rank_rows.data_ptr(),
+                             meta_stride=plan.meta_stride, K=plan.num_topk, E=plan.num_experts, expand=int(plan.expand),
+                             recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf), recv_rows=recv_x.shape[0],
+                             prof=self._prof_buffer("dispatch", i)))
+        send, recv = split if split is not None else self.split_blocks(blocks, self.dispatch_send_fraction, self.dispatch_blocks)
+        self._timed("dispatch", stream, lambda: self.C.dispatch(lay, self.sessions, args, send, recv, self._stream(stream),
+                                                                self.local_direct, self._device_profile))
         return outs
 
     def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[RoutingPlan], ws: Sequence[Optional[torch.Tensor]],
                 bias: Sequence = None, blocks: int = 0, stream=None, split: Optional[Tuple[int, int]] = None):
-        """``split`` = (expert-side sender blocks, source-side reducer blocks) overrides the default 72 / 28 division."""
+        """``split`` = (expert-side sender blocks, source-side reducer blocks) overrides the default division."""
         lay, dev = self.layout, self.device
         H, K = lay.hidden, lay.topk
         outs, args = [], []
@@ -249,19 +305,19 @@ class CudaEngine:
             b0, b1 = (b if isinstance(b, (tuple, list)) else (b, None)) if b is not None else (None, None)
             outs.append((out, out_w))
             args.append(dict(x=xs[i].data_ptr(), w=_ptr(ws[i]), stage_meta=plan.stage_meta.data_ptr(),
-                             chunk_start=plan.chunk_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
+                             group_start=plan.group_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
+                             prof=self._prof_buffer("combine", i),
                              send_slot=plan.send_slot.data_ptr(), topk_idx=plan.topk_idx.data_ptr(), T=T,
                              meta_stride=plan.meta_stride, K=K, E=plan.num_experts, expand=int(plan.expand),
                              bias0=_ptr(b0), bias1=_ptr(b1), out=out.data_ptr(), out_w=_ptr(out_w), x_rows=xs[i].shape[0]))
-        # one rank: the source side only copies one partial per token, 12 of 144 blocks keep up with it (measured:
-        # 271 us with the 72 / 28 division, 244 us with 132 / 12)
-        send, recv = self.split_blocks(blocks, 0.72 if self.world > 1 else 0.917, self.combine_blocks)
+        send, recv = self.split_blocks(blocks, self.combine_send_fraction, self.combine_blocks)
         if split is not None:
             limit = max(2, self.sm_count // self.n)
             send, recv = max(1, int(split[0])), max(1, int(split[1]))
             if send + recv > limit:
                 raise ValueError(f"combine_num_sms + reduce_num_sms must not exceed {limit} on this device")
-        self._timed("combine", stream, lambda: self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream)))
+        self._timed("combine", stream, lambda: self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream),
+                                                              self.local_direct, self._device_profile))
         return outs
 
     # ------------------------------------------------------------------ low latency
@@ -294,7 +350,7 @@ class CudaEngine:
                          expert_offsets=torch.empty((local + 1,), **i32), num_rows=torch.empty((1,), **i32))
             plan = RoutingPlan(num_tokens=T, num_experts=num_experts, num_topk=K, expand=True, alignment=1, meta_stride=0,
                                num_rows=cap, num_staged_rows=0, expert_counts_list=None, topk_idx=topk_idx[i], send_slot=None,
-                               slot_row=None, stage_meta=None, chunk_start=None, rank_tokens=None, rank_rows=None,
+                               slot_row=None, stage_meta=None, chunk_start=None, group_start=None, rank_tokens=None, rank_rows=None,
                                expert_counts=o["expert_counts"], expert_offsets=o["expert_offsets"],
                                recv_row_src=o["recv_row_src"], recv_w=o["recv_w"], recv_idx=None, has_weights=True)
             plan.num_rows_dev, plan.topk_w, plan.low_latency = o["num_rows"], topk_w[i], True

@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 
 
 def run_case(world, tokens, hidden, experts, topk, mode, *, expand=True, alignment=1, dmode=0, seed=0, max_tokens=None,
-             with_bias=False, repeats=1):
+             with_bias=False, repeats=1, local_direct=True):
     from deepep_b200.parallel.virtual import VirtualWorld
 
     dev = torch.device("cuda")
@@ -19,6 +19,7 @@ def run_case(world, tokens, hidden, experts, topk, mode, *, expand=True, alignme
     wts = [make_weights(t, topk, seed + r) for r, t in enumerate(tokens)]
     with VirtualWorld(world, max_tokens, hidden, topk, timeout=10.0) as vw:
         eng = vw.engine
+        eng.local_direct = local_direct   # False: rows that stay on their rank also go through staging / partial areas
         for rep in range(repeats):
             plans = eng.notify([i.to(dev) for i in idx], [w.to(dev) for w in wts], experts, expand=expand, alignment=alignment)
             if dmode == 1:
@@ -96,6 +97,18 @@ def test_fp8_given_and_fused():
     run_case(2, [128, 100], 1024, 16, 4, "random", dmode=1)
     run_case(2, [128, 100], 1024, 16, 4, "random", dmode=2)
     run_case(2, [50, 60], 384, 16, 4, "random", dmode=1)   # scale rows not 16-byte aligned
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_local_rows_through_staging(world):
+    """The same results when a rank's own rows take the staging area and the partial area like remote rows."""
+    run_case(world, [100, 77, 64, 130][:world], 512, 16 * world, 4, "invalid", local_direct=False, repeats=2)
+    run_case(world, [100, 77, 64, 130][:world], 512, 16 * world, 4, "random", expand=False, local_direct=False)
+
+
+def test_rank_layout_fp8_and_bias():
+    run_case(2, [90, 120], 1024, 16, 4, "random", expand=False, dmode=1, with_bias=True)
+    run_case(1, [200], 1024, 8, 4, "invalid", expand=False, dmode=2)
 
 
 def test_bias_and_hotspot():

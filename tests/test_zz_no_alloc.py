@@ -74,6 +74,20 @@ def test_no_alloc_entry_matches_regular_entry_twice():
         assert torch.equal(got["chunk_start"][:tiles + 1], plan.chunk_start[0, :tiles + 1])
 
 
+def test_no_alloc_entry_rejects_capacity_without_padding_rows():
+    """With an alignment above 1 the padding rows are written too: a capacity that leaves them out is refused up front."""
+    from deepep_b200.ops import native_path
+
+    lib = ctypes.CDLL(str(native_path()))
+    lib.deepep_notify_layout_noalloc.restype = ctypes.c_int
+    lib.deepep_noalloc_last_error.restype = ctypes.c_char_p
+    one = ctypes.c_void_p(256)   # never dereferenced: the call is refused before any launch
+    T, K, E, alignment = 333, 4, 16, 8
+    rc = lib.deepep_notify_layout_noalloc(one, None, T, K, E, alignment, one, one, one, one, one, one, one, None,
+                                          ctypes.c_longlong(T * K), one, None)
+    assert rc != 0 and b"expert_alignment - 1" in lib.deepep_noalloc_last_error()
+
+
 def test_no_alloc_entry_rejects_oversize():
     from deepep_b200.ops import native_path
 
