@@ -6,6 +6,11 @@
 Every rank times each iteration with CUDA events (host clock on the CPU engine); rank 0 gathers the samples, takes
 the per-iteration maximum over ranks and prints one JSON record (schema in deepep_b200/utils/workload.py).  The
 outputs of the first iteration are compared with the all-rank CPU oracle unless --no-check is given.
+
+``--sweep-blocks B... --sweep-fractions F...`` additionally times the cached dispatch and the combine of the same
+workload for every (blocks per rank, share of the blocks on the NVLink side) pair and prints one JSON line each
+(device time, maximum over ranks, and the NVLink bytes one rank sends per second); ``--device-profile`` adds the
+per-block records of the kernels' profile instantiation for the default split.
 """
 import argparse
 import json
@@ -24,6 +29,10 @@ def main() -> int:
     ap.add_argument("--config", required=True)
     ap.add_argument("--results-dir", default=None, help="write the record there (existing files are never overwritten)")
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--sweep-blocks", type=int, nargs="*", default=[], help="blocks (SMs) per rank to try")
+    ap.add_argument("--sweep-fractions", type=float, nargs="*", default=[0.3, 0.4, 0.5, 0.6],
+                    help="share of the blocks that drives NVLink (dispatch senders / combine expert side)")
+    ap.add_argument("--device-profile", action="store_true", help="per-block records of the profile kernels (CUDA engine)")
     args = ap.parse_args()
 
     from deepep_b200 import ElasticBuffer
@@ -104,6 +113,8 @@ def main() -> int:
             us = (time.perf_counter_ns() - t0) / 1e3
         if it >= cfg.warmup:
             samples.append(max(us, 1e-3))
+    if cuda and (args.sweep_blocks or args.device_profile):
+        sweep(buf, cfg, x, handle, back, routes, rank, world, args)
     gathered = buf.control.all_gather_object(samples) if world > 1 else [samples]
     record = W.complete(W.plan(cfg), gathered, W.traffic(cfg, [r[0] for r in routes])["effective_bytes"], correctness)
     record["engine"] = "cuda" if cuda else "cpu"
@@ -118,6 +129,65 @@ def main() -> int:
 
         dist.destroy_process_group()
     return 0 if correctness != "failed" else 1
+
+
+def sweep(buf, cfg, x, handle, back, routes, rank, world, args):
+    """Cached dispatch and combine under explicit SM splits (engine level: the public API only splits the combine)."""
+    import torch.distributed as dist
+
+    eng, plan = buf.engine, handle._plan
+    mode = 2 if cfg.dtype == "fp8" else 0
+    local = cfg.experts // world
+    dst = torch.where(routes[rank][0] >= 0, torch.div(routes[rank][0], local, rounding_mode="floor"), torch.full_like(routes[rank][0], -1))
+    remote_rows = sum(int((dst == d).any(dim=1).sum()) for d in range(world) if d != rank)
+    out_bytes = {"dispatch": remote_rows * (cfg.hidden * 2 if mode == 0 else cfg.hidden + cfg.hidden // 128 * 4),
+                 "combine": remote_rows * cfg.hidden * 2}
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / iters * 1e3], device=x.device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def say(**kw):
+        if rank == 0:
+            print(json.dumps(kw), flush=True)
+
+    limit = max(2, eng.sm_count)
+    for blocks in args.sweep_blocks:
+        blocks = min(blocks, limit)
+        for frac in args.sweep_fractions:
+            send = min(blocks - 1, max(1, round(blocks * frac)))
+            for op, fn in (("dispatch", lambda: eng.dispatch([x], [plan], mode, split=(send, blocks - send))),
+                           ("combine", lambda: eng.combine([back], [plan], [None], split=(send, blocks - send)))):
+                us = timed(fn)
+                say(sweep=op, blocks=blocks, nvlink_side_blocks=send, us=round(us, 1),
+                    nvlink_out_GBps=round(out_bytes[op] / (us * 1e-6) / 1e9, 1))
+    if args.device_profile:
+        eng.enable_device_profile(True)
+        eng.dispatch([x], [plan], mode)
+        eng.combine([back], [plan], [None])
+        prof = eng.pop_device_profile()
+        eng.enable_device_profile(False)
+        for (op, _), blocks in prof.items():
+            for side in sorted({b["role"] for b in blocks}):
+                sel = [b for b in blocks if b["role"] == side]
+                say(profile=op, side=side, blocks=len(sel), first_start_us=round(min(b["start_us"] for b in sel), 1),
+                    last_end_us=round(max(b["end_us"] for b in sel), 1),
+                    mean_busy_us=round(sum(b["end_us"] - b["start_us"] for b in sel) / len(sel), 1),
+                    **{k: round(sum(b[k] for b in sel) / len(sel), 1) for k in ("meta_us", "wait_us", "data_us", "publish_us")},
+                    rows=sum(b["rows"] for b in sel))
 
 
 if __name__ == "__main__":

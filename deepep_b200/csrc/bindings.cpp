@@ -260,6 +260,8 @@ PYBIND11_MODULE(_C, m) {
         py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);
   m.attr("group_tokens") = kGroupTokens;
   m.attr("dispatch_prof_words") = kDispatchProfWords;
+  m.attr("dispatch_threads") = kDispatchThreads;
+  m.attr("combine_threads") = kCombineThreads;
   m.attr("combine_prof_words") = kCombineProfWords;
   m.def("barrier", &op_barrier);
   bind_low_latency(m);

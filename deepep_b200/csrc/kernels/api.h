@@ -68,7 +68,10 @@ struct DispatchArgs {
 // local_direct: rows whose destination is the sending rank itself are written straight into recv_x by the sender
 // blocks (no staging, no flag); 0 sends them through the staging area like remote rows.
 struct DispatchParams { WsLayout lay; int send_blocks, recv_blocks, local_direct, profile; DispatchArgs r[kMaxRanks]; };
-constexpr int kDispatchProfWords = 8;   // per block: role, start ns, end ns, flag-wait ns (warp 0), rows moved (warp 0), 3 spare
+// per block: role (0 sender, 1 receiver), start ns, end ns, then summed over the block's warps: cycles spent reading
+// routing records, waiting for flags, moving rows, publishing flags; rows moved
+constexpr int kDispatchProfWords = 8;
+constexpr int kDispatchThreads = 512;   // 16 independent warps per block
 cudaError_t launch_dispatch(const DispatchParams& p, int nranks, cudaStream_t stream);
 
 // ---------------------------------------------------------------- high-throughput combine
@@ -94,7 +97,10 @@ struct CombineArgs {
 // local_direct: the source side sums the rows of its own rank straight from x (same rounding: fp32 sum -> bf16 ->
 // fp32), so no local partial is written and no flag is needed for it.
 struct CombineParams { WsLayout lay; int send_blocks, recv_blocks, local_direct, profile; CombineArgs r[kMaxRanks]; };
-constexpr int kCombineProfWords = 8;    // per block: role, start ns, end ns, flag-wait ns (warp 0), rows moved (warp 0), 3 spare
+// per block: role (0 expert side, 1 source side), start ns, end ns, then summed over the block's warps: cycles spent
+// reading routing records, waiting for flags, reducing rows, publishing flags; rows read
+constexpr int kCombineProfWords = 8;
+constexpr int kCombineThreads = 384;    // 12 warps: up to 168 registers per thread, which the source side needs for 8 partials in flight
 cudaError_t launch_combine(const CombineParams& p, int nranks, cudaStream_t stream);
 
 // ---------------------------------------------------------------- barrier

@@ -52,7 +52,7 @@ struct Control {
   // owned by this rank
   unsigned long long epoch[kNumOps];      // completed calls per op
   unsigned int blocks_done[kNumOps];      // exit counter used to find the last block
-  unsigned int ticket[kNumOps];           // dynamic work counters
+  unsigned int ticket[kNumOps][2];        // dynamic work counters: [0] items of the NVLink side, [1] items of the local side
   int abort;                              // set once a wait ran out; all later waits return at once
   int pad0[15];
   // written by peers (slot index = writer's rank)
@@ -188,6 +188,13 @@ __device__ __forceinline__ bool last_block_of_rank(Control* c, int op, unsigned 
   return s_last != 0;
 }
 
+// Next work item of a shared counter (one atomic per warp); the last block of the launch sets the counters back to zero.
+__device__ __forceinline__ int next_ticket(unsigned int* counter, int lane) {
+  unsigned int v = 0;
+  if (lane == 0) v = atomicAdd(counter, 1u);
+  return (int)__shfl_sync(0xffffffffu, v, 0);
+}
+
 // ------------------------------------------------------------------ bulk-copy (TMA 1-D) helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -230,6 +237,37 @@ template <int N> __device__ __forceinline__ void bulk_wait_read() {
 template <int N> __device__ __forceinline__ void bulk_wait() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+
+// Phase clock of the profile instantiations (template <bool kProfile>): every warp charges the cycles between two
+// marks to one of four phases; at the end of the kernel the block adds them up.  With kOn = false nothing is compiled in.
+enum ProfPhase : int { kProfMeta = 0, kProfWait = 1, kProfData = 2, kProfPublish = 3, kProfPhases = 4 };
+template <bool kOn>
+struct PhaseClock {
+  long long last = 0;
+  long long sum[kProfPhases] = {0, 0, 0, 0};
+  unsigned long long rows = 0, begin_ns = 0;
+  __device__ __forceinline__ void start() { if (kOn) { last = clock64(); begin_ns = global_timer_ns(); } }
+  __device__ __forceinline__ void mark(int phase) {
+    if (kOn) { const long long now = clock64(); sum[phase] += now - last; last = now; }
+  }
+  __device__ __forceinline__ void add_rows(int n) { if (kOn) rows += n; }
+  // all threads of the block; `out` = 8 words: role, start ns, end ns, 4 phase sums (cycles), rows
+  __device__ __forceinline__ void finish(unsigned long long* out, int role) {
+    if (!kOn) return;
+    __shared__ unsigned long long s_acc[kProfPhases + 1];
+    if (threadIdx.x <= kProfPhases) s_acc[threadIdx.x] = 0;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+      for (int i = 0; i < kProfPhases; ++i) atomicAdd(&s_acc[i], (unsigned long long)sum[i]);
+      atomicAdd(&s_acc[kProfPhases], rows);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && out != nullptr) {
+      out[0] = role; out[1] = begin_ns; out[2] = global_timer_ns();
+      for (int i = 0; i <= kProfPhases; ++i) out[3 + i] = s_acc[i];
+    }
+  }
+};
 
 __device__ __forceinline__ int4 ld_cg_int4(const void* p) { return __ldcg(reinterpret_cast<const int4*>(p)); }
 

@@ -11,6 +11,8 @@
 //   Receiver warps take (source, group) items in the order the senders produce them, wait for the
 //   group's flag and materialise every output row of each staged row (one per local expert of the
 //   token), so a token crosses NVLink once no matter how many experts of the destination it uses.
+//   Groups and items are handed out by two shared counters; sender warps turn into receivers once the
+//   last group is on its way.
 //
 // Between two GPUs 32 SMs of 16-byte register stores reach the same rate as bulk shared->global copies
 // (about 0.69 TB/s per direction with both directions busy); the register form needs no staging in
@@ -23,7 +25,6 @@
 
 namespace dep {
 
-constexpr int kHtThreads = 512;
 constexpr int kCopyUnroll = 7;    // 16-byte pieces per lane and pass: 3.5 KB in flight per warp
 
 __device__ __forceinline__ unsigned long long shfl_u64(unsigned long long v, int src) {
@@ -135,13 +136,14 @@ __device__ __forceinline__ void warp_quant_fanout(const int4* src, int H, unsign
 }
 
 template <bool kProfile>
-__global__ void __launch_bounds__(kHtThreads, 1) ep_dispatch_ht_kernel(const __grid_constant__ DispatchParams p) {
+__global__ void __launch_bounds__(kDispatchThreads, 1) ep_dispatch_ht_kernel(const __grid_constant__ DispatchParams p) {
   const DispatchArgs& a = p.r[blockIdx.y];
   const WsLayout& lay = p.lay;
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, Tmax = lay.max_tokens, H = lay.hidden, K = a.K;
   const int NG = (Tmax + kGroupTokens - 1) / kGroupTokens;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int q = lane >> 3, c = lane & 7;      // metadata of a group is fetched by lane = (token of the group) * 8 + field
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpDispatch] + 1;
 
@@ -150,40 +152,61 @@ __global__ void __launch_bounds__(kHtThreads, 1) ep_dispatch_ht_kernel(const __g
   const int row_bytes = fp8 ? H : H * 2;     // payload bytes of one output row
   const int units = row_bytes / 16;
   const bool sender = (int)blockIdx.x < p.send_blocks;
-  unsigned long long t_begin = 0, t_wait = 0, n_rows = 0;
-  if (kProfile) t_begin = global_timer_ns();
+  PhaseClock<kProfile> clk;
+  clk.start();
 
   if (sender) {
     // ================================================================ sender
     int ok = 1;
     if (lane < P) ok = wait_flag_ge(&ctl->disp_ack[lane], epoch - 1, ctx, kOpDispatch, 0, lane);
     bool alive = __all_sync(0xffffffffu, ok);
+    clk.mark(kProfWait);
     const int Lx = a.E / P, ngroups = (a.T + kGroupTokens - 1) / kGroupTokens;
     const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
     const int src_row_bytes = a.mode == kDispatchFp8Given ? H : H * 2;
     uint8_t* recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
-    for (int gi = blockIdx.x * nwarps + warp; gi < ngroups && alive; gi += p.send_blocks * nwarps) {
-      const int t1 = min(a.T, (gi + 1) * kGroupTokens);
-      for (int t = gi * kGroupTokens; t < t1; ++t) {
+    const int my_first_row = (p.local_direct && !a.expand) ? a.rank_rows[me] : 0;
+    // groups are handed out in order by a shared counter, so the warps stay busy whatever the groups' sizes
+    for (int gi = next_ticket(&ctl->ticket[kOpDispatch][0], lane); gi < ngroups && alive;
+         gi = next_ticket(&ctl->ticket[kOpDispatch][0], lane)) {
+      const int t0 = gi * kGroupTokens, count = min(a.T - t0, kGroupTokens);
+      // routing of the whole group in one round of loads: lane (q, c) holds send_slot[t0 + q][c] and the local output rows
+      // of slots c and c + 8 of token t0 + q (-1: the slot's expert lives elsewhere)
+      int ss = -1, sr0 = -1, sr1 = -1;
+      if (q < count) {
+        const int t = t0 + q;
+        if (c < P) ss = a.send_slot[(size_t)t * P + c];
+        if (p.local_direct && a.expand) {
+          if (c < K) {
+            const int r = a.slot_row[(size_t)t * K + c];
+            const long long e = a.topk_idx[(size_t)t * K + c];
+            if (r >= 0 && e >= 0 && e < a.E && (int)(e / Lx) == me) sr0 = r;
+          }
+          if (c + 8 < K) {
+            const int r = a.slot_row[(size_t)t * K + c + 8];
+            const long long e = a.topk_idx[(size_t)t * K + c + 8];
+            if (r >= 0 && e >= 0 && e < a.E && (int)(e / Lx) == me) sr1 = r;
+          }
+        }
+      }
+      clk.mark(kProfMeta);
+      for (int qq = 0; qq < count; ++qq) {
+        const int t = t0 + qq;
         // lanes 0..P-1: the staged row on every destination rank; lanes P..P+K-1: the output rows on this rank
+        const int j = __shfl_sync(0xffffffffu, ss, qq * 8 + (lane & 7));
+        const int j_me = __shfl_sync(0xffffffffu, ss, qq * 8 + me);
+        const int k = lane - P;
+        const int r0 = __shfl_sync(0xffffffffu, sr0, qq * 8 + (k & 7)), r1 = __shfl_sync(0xffffffffu, sr1, qq * 8 + (k & 7));
         unsigned long long dst = 0, dst_sf = 0;
         if (lane < P) {
-          const int j = a.send_slot[(size_t)t * P + lane];
           if (j >= 0 && !(p.local_direct && lane == me) && DEP_INDEX_OK(ctx, j, Tmax, kOpDispatch, 0)) {
             dst = reinterpret_cast<unsigned long long>(ctx.ws[lane] + lay.stage + ((size_t)me * Tmax + j) * lay.stage_row_bytes);
             dst_sf = dst + H;
           }
-        } else if (p.local_direct && lane < P + K) {
-          const int k = lane - P;
+        } else if (p.local_direct && k < K) {
           int row = -1;
-          if (a.expand) {
-            const int r = a.slot_row[(size_t)t * K + k];
-            const long long e = a.topk_idx[(size_t)t * K + k];
-            if (r >= 0 && e >= 0 && e < a.E && (int)(e / Lx) == me) row = r;
-          } else if (k == 0) {
-            const int j = a.send_slot[(size_t)t * P + me];
-            if (j >= 0) row = a.rank_rows[me] + j;
-          }
+          if (a.expand) row = k < 8 ? r0 : r1;
+          else if (k == 0 && j_me >= 0) row = my_first_row + j_me;
           if (row >= 0 && (a.recv_rows <= 0 || DEP_INDEX_OK(ctx, row, a.recv_rows, kOpDispatch, 1))) {
             dst = reinterpret_cast<unsigned long long>(recv_x + (size_t)row * row_bytes);
             dst_sf = reinterpret_cast<unsigned long long>(a.recv_sf + (size_t)row * nsf);
@@ -198,45 +221,57 @@ __global__ void __launch_bounds__(kHtThreads, 1) ep_dispatch_ht_kernel(const __g
           warp_fanout<false>(reinterpret_cast<const int4*>(src), units, dst, mask, lane);
           if (fp8) warp_fanout_f32<false>(a.x_sf + (size_t)t * nsf, nsf, dst_sf, mask, lane);
         }
-        if (kProfile) n_rows += __popc(mask);
+        clk.add_rows(__popc(mask));
       }
+      clk.mark(kProfData);
       // publish the group: every lane's stores are ordered before the flag by the warp barrier + release
       __syncwarp();
       if (lane < P && !(p.local_direct && lane == me))
         st_release_sys(reinterpret_cast<unsigned long long*>(ctx.ws[lane] + lay.disp_flag) + (size_t)me * NG + gi, epoch);
+      clk.mark(kProfPublish);
     }
-  } else {
-    // ================================================================ receiver
-    const int nrecv = p.recv_blocks * nwarps, w = (blockIdx.x - p.send_blocks) * nwarps + warp;
+  }
+  {
+    // ================================================================ receiver (sender warps join once all groups are sent)
     int max_ng = 0;
     for (int r = 0; r < P; ++r) max_ng = max(max_ng, (a.rank_tokens[r] + kGroupTokens - 1) / kGroupTokens);
     uint8_t* recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
     const uint8_t* stage = ctx.ws[me] + lay.stage;
     const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(ctx.ws[me] + lay.disp_flag);
-    for (int item = w; item < max_ng * P; item += nrecv) {
-      const int gi = item / P, r = (me + item % P) % P;
-      if ((p.local_direct && r == me) || gi * kGroupTokens >= a.rank_tokens[r]) continue;
+    // the sources whose rows pass through the staging area: all ranks, or all but this one
+    const int S = p.local_direct ? P - 1 : P, first = p.local_direct ? 1 : 0;
+    for (int item = next_ticket(&ctl->ticket[kOpDispatch][1], lane); item < max_ng * S;
+         item = next_ticket(&ctl->ticket[kOpDispatch][1], lane)) {
+      const int gi = item / S, r = (me + first + item % S) % P;
+      if (gi * kGroupTokens >= a.rank_tokens[r]) continue;
       const int j0 = a.group_start[r * (NG + 1) + gi], j1 = a.group_start[r * (NG + 1) + gi + 1];
       if (j0 >= j1) continue;
       if (j0 < 0 || j1 - j0 > kGroupTokens || j1 > Tmax) {   // a group stages at most one row per token: the plan is damaged
         if (lane == 0) report_failure(ctx, kStatusBadArgument, kOpDispatch, 3, r, kGroupTokens, (unsigned long long)(j1 - j0));
         break;
       }
-      int ok = 1;
-      if (lane == 0) {
-        unsigned long long t0 = 0;
-        if (kProfile) t0 = global_timer_ns();
-        ok = wait_flag_ge(flags + (size_t)r * NG + gi, epoch, ctx, kOpDispatch, 1, r);
-        if (kProfile) t_wait += global_timer_ns() - t0;
+      // the group's records in one round of loads (issued before the flag wait): lane (q, c) holds fields c, 8 + c, 16 + c
+      int f0 = 0, f1 = 0, f2 = 0;
+      if (q < j1 - j0) {
+        const int* rec = a.stage_meta + ((size_t)r * Tmax + j0 + q) * a.meta_stride;
+        if (c < a.meta_stride) f0 = rec[c];
+        if (8 + c < a.meta_stride) f1 = rec[8 + c];
+        if (16 + c < a.meta_stride) f2 = rec[16 + c];
       }
-      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      for (int j = j0; j < j1; ++j) {
-        if (!DEP_INDEX_OK(ctx, j, Tmax, kOpDispatch, 2)) continue;
-        const int* rec = a.stage_meta + ((size_t)r * Tmax + j) * a.meta_stride;
-        const int n = min(rec[1], kMaxTopk);
+      clk.mark(kProfMeta);
+      int ok = 1;
+      if (lane == 0) ok = wait_flag_ge(flags + (size_t)r * NG + gi, epoch, ctx, kOpDispatch, 1, r);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      clk.mark(kProfWait);
+      if (!ok) break;
+      for (int qq = 0; qq < j1 - j0; ++qq) {
+        const int j = j0 + qq;
+        const int n = min(__shfl_sync(0xffffffffu, f0, qq * 8 + 1), kMaxTopk);
+        const int fi = 2 + lane, from = qq * 8 + (fi & 7);
+        const int e0 = __shfl_sync(0xffffffffu, f0, from), e1 = __shfl_sync(0xffffffffu, f1, from), e2 = __shfl_sync(0xffffffffu, f2, from);
         unsigned long long dst = 0, dst_sf = 0;
         if (lane < n) {
-          const int row = rec[2 + lane] & kRowMask;
+          const int row = ((fi >> 3) == 0 ? e0 : (fi >> 3) == 1 ? e1 : e2) & kRowMask;
           if (a.recv_rows <= 0 || DEP_INDEX_OK(ctx, row, a.recv_rows, kOpDispatch, 1)) {
             dst = reinterpret_cast<unsigned long long>(recv_x + (size_t)row * row_bytes);
             dst_sf = reinterpret_cast<unsigned long long>(a.recv_sf + (size_t)row * nsf);
@@ -246,27 +281,25 @@ __global__ void __launch_bounds__(kHtThreads, 1) ep_dispatch_ht_kernel(const __g
         const uint8_t* src = stage + ((size_t)r * Tmax + j) * lay.stage_row_bytes;
         warp_fanout<true>(reinterpret_cast<const int4*>(src), units, dst, mask, lane);
         if (fp8) warp_fanout_f32<true>(reinterpret_cast<const float*>(src + H), nsf, dst_sf, mask, lane);
-        if (kProfile) n_rows += __popc(mask);
+        clk.add_rows(__popc(mask));
       }
+      clk.mark(kProfData);
     }
   }
 
-  if (kProfile && a.prof != nullptr && threadIdx.x == 0) {
-    unsigned long long* rec = a.prof + (size_t)blockIdx.x * kDispatchProfWords;
-    rec[0] = sender ? 0 : 1; rec[1] = t_begin; rec[2] = global_timer_ns(); rec[3] = t_wait; rec[4] = n_rows;
-  }
+  clk.finish(a.prof ? a.prof + (size_t)blockIdx.x * kDispatchProfWords : nullptr, sender ? 0 : 1);
 
   // ---- exit: the last block of this rank tells every source that its staged rows are consumed
   if (last_block_of_rank(ctl, kOpDispatch, gridDim.x)) {
     if (!ld_volatile_int(&ctl->abort) && threadIdx.x < P)
       st_release_sys(&control_of(ctx.ws[threadIdx.x])->disp_ack[me], epoch);
-    if (threadIdx.x == 0) ctl->epoch[kOpDispatch] = epoch;
+    if (threadIdx.x == 0) { ctl->ticket[kOpDispatch][0] = 0; ctl->ticket[kOpDispatch][1] = 0; ctl->epoch[kOpDispatch] = epoch; }
   }
 }
 
 cudaError_t launch_dispatch(const DispatchParams& p, int nranks, cudaStream_t stream) {
   if (p.lay.hidden > 8192) return cudaErrorInvalidValue;   // the fused quantiser keeps at most 64 scales per row in registers
-  dim3 grid(p.send_blocks + p.recv_blocks, nranks), block(kHtThreads);
+  dim3 grid(p.send_blocks + p.recv_blocks, nranks), block(kDispatchThreads);
   void* args[] = {const_cast<DispatchParams*>(&p)};
   const void* fn = p.profile ? (const void*)ep_dispatch_ht_kernel<true> : (const void*)ep_dispatch_ht_kernel<false>;
   return cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream);

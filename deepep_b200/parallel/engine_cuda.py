@@ -143,18 +143,24 @@ class CudaEngine:
         return self._prof[key].data_ptr()
 
     def pop_device_profile(self) -> dict:
-        """``{(op, rank index): [dict(role, start_us, end_us, flag_wait_us, rows)]}`` of the last profiled launch of each
-        op (times relative to the earliest block start of that launch)."""
+        """``{(op, rank index): [per-block dict]}`` of the last profiled launch of each op: ``role``, ``start_us`` /
+        ``end_us`` (relative to the earliest block start of the launch), and, averaged over the block's warps, the
+        microseconds spent reading routing records (``meta_us``), waiting for flags (``wait_us``), moving or reducing
+        rows (``data_us``) and publishing flags (``publish_us``); ``rows`` counts the rows the block handled."""
         torch.cuda.synchronize(self.device)
+        mhz = torch.cuda.get_device_properties(self.device).clock_rate / 1e3 if hasattr(
+            torch.cuda.get_device_properties(self.device), "clock_rate") else 1965.0
         out = {}
         for key, buf in self._prof.items():
+            warps = (self.C.dispatch_threads if key[0] == "dispatch" else self.C.combine_threads) / 32.0
             rows = [r for r in buf.cpu().tolist() if r[2] > 0]
             if not rows:
                 continue
             t0 = min(r[1] for r in rows)
             side = ("sender", "receiver") if key[0] == "dispatch" else ("expert", "source")
             out[key] = [dict(role=side[int(r[0])], start_us=(r[1] - t0) / 1e3, end_us=(r[2] - t0) / 1e3,
-                             flag_wait_us=r[3] / 1e3, rows=int(r[4])) for r in rows]
+                             meta_us=r[3] / mhz / warps, wait_us=r[4] / mhz / warps, data_us=r[5] / mhz / warps,
+                             publish_us=r[6] / mhz / warps, rows=int(r[7])) for r in rows]
             buf.zero_()
         return out
 

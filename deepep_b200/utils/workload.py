@@ -32,7 +32,7 @@ _CHOICES = {
     "dtype": ("bf16", "fp8"),                       # dispatch payload; fp8 = e4m3 with fp32 scales per 128, quantised in the kernel
     "layout": ("expanded", "rank"),                 # rows per (token, slot) sorted by expert, or one row per received token
     "dispatch_mode": ("fresh", "cached"),           # with or without the routing-layout pass
-    "route": ("balanced", "skew", "masked", "grouped"),
+    "route": ("balanced", "skew", "masked", "grouped", "next_rank"),
 }
 _LIMITS = {"world_size": (1, 8), "hidden": (128, 7168), "topk": (1, 16), "experts": (1, 1024), "seed": (0, 2 ** 31 - 1),
            "warmup": (0, 10000), "iterations": (1, 10000), "alignment": (1, 128)}
@@ -141,6 +141,12 @@ def make_routes(cfg: WorkloadConfig, rank: int) -> Tuple[torch.Tensor, torch.Ten
             mask = torch.zeros((T, groups), dtype=torch.bool).scatter_(1, best, True).repeat_interleave(E // groups, dim=1)
             scores = scores.masked_fill(~mask, -1.0)
         idx = scores.topk(K, dim=1).indices
+    elif cfg.route == "next_rank":    # link stress: every token goes only to experts of the next rank
+        local = E // cfg.world_size
+        base = ((rank + 1) % cfg.world_size) * local
+        idx = base + torch.rand((T, local), generator=g).topk(min(K, local), dim=1).indices
+        if idx.shape[1] < K:
+            idx = torch.cat([idx, torch.full((T, K - idx.shape[1]), -1, dtype=idx.dtype)], dim=1)
     else:                             # masked: random routes with a quarter of the slots disabled
         idx = torch.rand((T, E), generator=g).topk(K, dim=1).indices
         idx[torch.rand((T, K), generator=g) < 0.25] = -1
