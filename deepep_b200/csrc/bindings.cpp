@@ -12,6 +12,7 @@
 #include "kernels/api.h"
 #include "kernels/ll_api.h"
 #include "kernels/mega_api.h"
+#include "runtime/fake_cuda.h"
 #include "runtime/session.h"
 
 namespace py = pybind11;
@@ -215,8 +216,13 @@ PYBIND11_MODULE(_C, m) {
         py::arg("ll_bytes") = 0, py::arg("mega_bytes") = 0);
 
   py::class_<Session>(m, "Session")
-      .def(py::init<int, int, size_t, double>(), py::arg("rank"), py::arg("world"), py::arg("bytes"), py::arg("timeout"))
+      .def(py::init<int, int, size_t, double, const std::string&>(), py::arg("rank"), py::arg("world"), py::arg("bytes"),
+           py::arg("timeout"), py::arg("transport") = "auto")
+      .def_property_readonly("transport", [](const Session& s) { return std::string(s.transport()); })
       .def("ipc_handle", [](const Session& s) { return py::bytes(s.ipc_handle()); })
+      .def("export_fd", &Session::export_fd)
+      .def("open_peer_fds", &Session::open_peer_fds)
+      .def("close_peers", &Session::close_peers)
       .def("open_peers", [](Session& s, const std::vector<py::bytes>& hs) {
         std::vector<std::string> v;
         for (const auto& h : hs) v.push_back(std::string(h));
@@ -252,6 +258,16 @@ PYBIND11_MODULE(_C, m) {
         check(launch_wait_probe(s.ctx(), reinterpret_cast<cudaStream_t>(stream)), "wait probe launch");
       });
   m.def("live_instances", &live_instances);
+  m.def("vmm_supported", &vmm_supported_here);
+  // host-memory doubles of the CUDA entry points behind the session (fault-injection tests; never used by the library itself)
+  m.def("testing_install_fake_cuda", &fake::install, py::arg("vmm_supported") = true);
+  m.def("testing_restore_cuda", &fake::restore);
+  m.def("testing_fail", &fake::fail, py::arg("entry"), py::arg("nth") = 0, py::arg("code") = 1);
+  m.def("testing_log", &fake::log);
+  m.def("testing_clear", &fake::clear);
+  m.def("testing_open_allocations", &fake::open_allocations);
+  m.def("testing_poke", [](uintptr_t address, int value) { *reinterpret_cast<volatile int*>(address) = value; });
+  m.def("testing_peek", [](uintptr_t address) { return *reinterpret_cast<volatile int*>(address); });
 
   m.def("notify", &op_notify);
   m.def("dispatch", &op_dispatch, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),

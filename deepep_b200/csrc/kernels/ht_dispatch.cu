@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) ep_dispatch_ht_kernel(con
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, Tmax = lay.max_tokens, H = lay.hidden, K = a.K;
   const int NG = (Tmax + kGroupTokens - 1) / kGroupTokens;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
   const int q = lane >> 3, c = lane & 7;      // metadata of a group is fetched by lane = (token of the group) * 8 + field
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpDispatch] + 1;

@@ -5,7 +5,11 @@ and timeout validation, cross-rank agreement on the configuration vector,
 exchange of the workspace identity, creation of the communication stream and
 of the native session, ``barrier``, ``close``, poisoning after a failed
 launch, ``ResourceWarning`` for buffers that were never destroyed).
-Here the identity that ranks exchange is a CUDA IPC handle of the workspace.
+The identity that ranks exchange is either a file descriptor of a CUDA
+virtual-memory allocation, passed over Unix sockets (``vmm``), or a CUDA IPC
+memory handle that travels through the control plane (``ipc``);
+``DEEPEP_TRANSPORT=auto|vmm|ipc`` selects (``auto``: ``vmm`` when every rank's
+driver supports it).
 """
 from __future__ import annotations
 
@@ -83,6 +87,81 @@ class ControlPlane:
 _busy_runtimes = 0
 
 
+def exchange_fds(control: ControlPlane, fd: int, timeout: float = 60.0) -> List[int]:
+    """Every rank hands ``fd`` to every peer over Unix-domain sockets (SCM_RIGHTS); returns one descriptor per rank
+    (``-1`` at this rank's own index).  The caller owns the returned descriptors.
+
+    Each rank listens on an abstract socket whose name carries a token chosen by rank 0; a background thread serves
+    ``size - 1`` connections while the rank itself collects the peers' descriptors one after the other.
+    """
+    import secrets
+    import socket
+    import threading
+
+    rank, size = control.rank, control.size
+    if size == 1:
+        return [-1]
+    token = control.all_gather_object(secrets.token_hex(8) if rank == 0 else None)[0]
+    name = lambda r: f"\0deepep-{token}-{r}"
+    server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    server.bind(name(rank))
+    server.listen(size)
+    server.settimeout(timeout)
+    errors: List[str] = []
+
+    def serve():
+        try:
+            for _ in range(size - 1):
+                conn, _addr = server.accept()
+                with conn:
+                    socket.send_fds(conn, [b"fd"], [fd])
+        except Exception as exc:          # reported after the join below
+            errors.append(repr(exc))
+
+    thread = threading.Thread(target=serve, daemon=True)
+    thread.start()
+    control.barrier()                      # every listener is up
+    out = [-1] * size
+    try:
+        for step in range(1, size):
+            peer = (rank + step) % size
+            with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as client:
+                client.settimeout(timeout)
+                client.connect(name(peer))
+                _msg, fds, _flags, _addr = socket.recv_fds(client, 16, 1)
+                if len(fds) != 1:
+                    raise RuntimeError(f"rank {peer} sent no file descriptor")
+                out[peer] = fds[0]
+        thread.join(timeout)
+        if errors or thread.is_alive():
+            raise RuntimeError("handing the workspace descriptor to the peers failed: " + "; ".join(errors or ["timed out"]))
+    except Exception:
+        import os as _os
+
+        for f in out:
+            if f >= 0:
+                _os.close(f)
+        raise
+    finally:
+        server.close()
+    return out
+
+
+def shutdown_session(control: ControlPlane, native, synchronize=None) -> None:
+    """Collective teardown of one workspace.  No rank frees its workspace while a peer still maps it: every rank
+    drops its peer mappings, a barrier follows, and only then does each rank free its own allocation (freeing an
+    exported allocation that an importer still has open is undefined)."""
+    if synchronize is not None:
+        synchronize()
+    control.barrier()            # nobody is still writing into a workspace that is about to go away
+    try:
+        native.close_peers()
+    finally:
+        control.barrier()        # every peer mapping is gone
+        native.close()
+    control.barrier()
+
+
 class Runtime:
     """Owns the native session of this process for one buffer."""
 
@@ -102,11 +181,22 @@ class Runtime:
         configs = control.all_gather_object(config)
         if any(c != configs[0] for c in configs):
             raise RuntimeError(f"ranks disagree on the buffer configuration: {configs}")
-        torch.cuda.set_device(device)
+        if device.type == "cuda":          # (a CPU device only occurs in tests that swap the CUDA entry points for doubles)
+            torch.cuda.set_device(device)
+        wanted = os.environ.get("DEEPEP_TRANSPORT", "auto").lower()
+        if wanted not in ("auto", "vmm", "ipc"):
+            raise ValueError("DEEPEP_TRANSPORT must be auto, vmm or ipc")
+        # one transport for the whole job: virtual-memory allocations only when every rank can share them
+        votes = control.all_gather_object((wanted, bool(self.C.vmm_supported())))
+        if any(v[0] != wanted for v in votes):
+            raise RuntimeError(f"ranks disagree on DEEPEP_TRANSPORT: {[v[0] for v in votes]}")
+        if wanted == "vmm" and not all(v[1] for v in votes):
+            raise RuntimeError("DEEPEP_TRANSPORT=vmm, but a rank's driver cannot share virtual-memory allocations")
+        self.transport = "vmm" if wanted != "ipc" and all(v[1] for v in votes) else "ipc"
         error, handle = None, None
         try:
-            self.native = self.C.Session(self.rank, self.world, layout.total, float(timeout))
-            handle = bytes(self.native.ipc_handle()) if self.world > 1 else b""
+            self.native = self.C.Session(self.rank, self.world, layout.total, float(timeout), self.transport)
+            handle = bytes(self.native.ipc_handle()) if (self.world > 1 and self.transport == "ipc") else b""
         except Exception as exc:  # tell the peers before raising, so nobody waits for a handle
             error = repr(exc)
         replies = control.all_gather_object((error, handle))
@@ -116,10 +206,26 @@ class Runtime:
                 self.native.close()
             raise RuntimeError("workspace creation failed: " + "; ".join(errors))
         if self.world > 1:
-            self.native.open_peers([h for _, h in replies])
+            error = None
+            try:
+                if self.transport == "ipc":
+                    self.native.open_peers([h for _, h in replies])
+                else:
+                    own = self.native.export_fd()
+                    try:
+                        fds = exchange_fds(control, own)
+                    finally:
+                        os.close(own)
+                    self.native.open_peer_fds(fds)          # closes the descriptors
+            except Exception as exc:  # a rank that cannot map a peer tells the others, so that all of them raise
+                error = repr(exc)
+            errors = [f"rank {r}: {e}" for r, e in enumerate(control.all_gather_object(error)) if e]
+            if errors:
+                shutdown_session(control, self.native)
+                raise RuntimeError("mapping the peers' workspaces failed: " + "; ".join(errors))
         if not self.native.mapped():
             raise RuntimeError("a peer workspace is not mapped")
-        self.stream = torch.cuda.Stream(device=device)
+        self.stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         control.barrier()
         _busy_runtimes += 1
 
@@ -133,8 +239,9 @@ class Runtime:
         global _busy_runtimes
         if self.closed:
             return
-        torch.cuda.synchronize(self.device)
-        self.control.barrier()   # nobody may still be writing into a workspace that is about to be freed
+        sync = (lambda: torch.cuda.synchronize(self.device)) if self.device.type == "cuda" else (lambda: None)
+        sync()
+        self.control.barrier()   # every rank's kernels are done: nothing writes into this workspace any more
         try:
             if not self.native.guard_intact():      # the canary zone behind the workspace (peers map it as well)
                 warnings.warn("something wrote behind this rank's symmetric workspace; results of this buffer are suspect",
@@ -142,11 +249,10 @@ class Runtime:
         except RuntimeError:
             pass
         try:
-            self.native.close()
+            shutdown_session(self.control, self.native, sync)
         finally:
             self.closed = True
             _busy_runtimes -= 1
-        self.control.barrier()
 
     def __del__(self):
         if not getattr(self, "closed", True):
