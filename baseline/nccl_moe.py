@@ -1,16 +1,21 @@
 """The baseline the native kernels are measured against: expert-parallel MoE from library calls.
 
-* dispatch / combine: ``torch.distributed.all_to_all_single`` with per-rank split sizes (NCCL
-  all-to-all-v), one row per (token, slot) -- no rank-level dedup, the usual library formulation;
-* experts: bf16 cuBLAS GEMMs per local expert (``torch.matmul``), SwiGLU in eager PyTorch.
+* dispatch / combine: ``torch.distributed.all_to_all_single`` with per-rank split sizes (NCCL all-to-all-v) and
+  rank-level dedup: a token crosses the link once per destination rank and is expanded to that rank's experts by a
+  local gather; the way back pre-reduces a token's rows on the expert rank (fp32 accumulate, bf16 on the wire) and
+  reduces the per-rank partials at the source.  Every index tensor and split size is computed once in ``plan`` --
+  nothing inside ``dispatch`` / ``combine`` / ``moe_forward`` synchronises with the host.
+* experts: one grouped GEMM per projection over expert-major rows (``torch._grouped_mm``, bf16; ``fp8=True`` uses
+  ``torch._scaled_grouped_mm`` with row-wise scales when this PyTorch build has it for the device), SwiGLU in eager
+  PyTorch.  If the grouped kernels are missing, a per-expert ``torch.matmul`` loop over host-side counts is used.
 
-Nothing here is used by the product path.  With a world size of 1 the collectives degenerate to
-local permutations, which is still the honest single-GPU cost of this formulation.
+Nothing here is used by the product path.  With a world size of 1 the collectives degenerate to local copies,
+which is still the honest single-GPU cost of this formulation.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Tuple
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist
@@ -18,13 +23,15 @@ import torch.distributed as dist
 
 @dataclass
 class BaselinePlan:
-    order: torch.Tensor            # [T * K_valid] permutation that sorts slots by destination expert
-    token_of: torch.Tensor         # token of each sorted slot
-    slot_weight: torch.Tensor      # routing weight of each sorted slot
-    send_counts: List[int]         # rows to each rank
-    recv_counts: List[int]         # rows from each rank
-    recv_expert_counts: torch.Tensor   # [P, L] rows per (source rank, local expert)
     num_tokens: int
+    send_token: torch.Tensor           # [S] source token of every sent row, sorted by destination rank
+    send_counts: List[int]             # rows to each rank
+    recv_counts: List[int]             # rows from each rank
+    expand_from: torch.Tensor          # [R] received row that feeds every expert-major row
+    expert_offsets: torch.Tensor       # int32 [L] cumulative row ends of the local experts (grouped-GEMM offsets)
+    expert_counts: List[int]           # rows per local expert (host copy, for the fallback loop)
+    row_weight: torch.Tensor           # fp32 [R] routing weight of every expert-major row
+    num_recv: int
 
 
 class NcclExpertParallel:
@@ -34,69 +41,134 @@ class NcclExpertParallel:
         self.rank = dist.get_rank(group) if group is not None else 0
         self.num_experts, self.local = num_experts, num_experts // self.world
 
-    def plan(self, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> BaselinePlan:
-        T, K = topk_idx.shape
-        flat = topk_idx.reshape(-1)
-        valid = (flat >= 0).nonzero(as_tuple=True)[0]
-        order = valid[torch.sort(flat[valid], stable=True).indices]
-        experts = flat[order]
-        counts = torch.bincount(experts, minlength=self.num_experts).view(self.world, self.local)
-        if self.world > 1:
-            recv = torch.empty_like(counts)
-            dist.all_to_all_single(recv, counts, group=self.group)
-        else:
-            recv = counts.clone()
-        send_counts, recv_counts = counts.sum(1).tolist(), recv.sum(1).tolist()       # one host sync, like any a2a-v
-        return BaselinePlan(order, torch.div(order, K, rounding_mode="floor"), topk_weights.reshape(-1)[order], send_counts,
-                            recv_counts, recv, T)
-
-    def dispatch(self, x: torch.Tensor, plan: BaselinePlan) -> torch.Tensor:
-        send = x[plan.token_of]
+    def _a2a(self, send: torch.Tensor, send_counts: List[int], recv_counts: List[int]) -> torch.Tensor:
         if self.world == 1:
             return send
-        recv = torch.empty((sum(plan.recv_counts), x.shape[1]), dtype=x.dtype, device=x.device)
-        dist.all_to_all_single(recv, send, plan.recv_counts, plan.send_counts, group=self.group)
+        recv = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        dist.all_to_all_single(recv, send, recv_counts, send_counts, group=self.group)
         return recv
 
-    def expert_major(self, rows: torch.Tensor, plan: BaselinePlan) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        """Received rows are (source, expert)-ordered; regroup them by expert for the GEMMs."""
-        counts = plan.recv_expert_counts                      # [P, L]
-        expert_of = torch.repeat_interleave(torch.arange(self.local, device=rows.device).repeat(self.world), counts.reshape(-1))
-        perm = torch.sort(expert_of, stable=True).indices
-        return rows[perm], perm, counts.sum(0)
+    def plan(self, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> BaselinePlan:
+        """Routing metadata of one batch.  Host synchronisation happens here, once, never in the per-step calls."""
+        T, K = topk_idx.shape
+        dev = topk_idx.device
+        valid = topk_idx >= 0
+        dst = torch.where(valid, torch.div(topk_idx, self.local, rounding_mode="floor"), torch.full_like(topk_idx, -1))
+        hit = (dst.unsqueeze(-1) == torch.arange(self.world, device=dev)).any(dim=1)        # [T, P]
+        pairs = hit.t().nonzero()                                  # (rank, token), sorted by rank then token
+        send_token = pairs[:, 1].contiguous()
+        send_counts = hit.sum(0).tolist()
+        if self.world > 1:
+            counts_dev = torch.tensor(send_counts, device=dev)
+            recv_dev = torch.empty_like(counts_dev)
+            dist.all_to_all_single(recv_dev, counts_dev, group=self.group)
+            recv_counts = recv_dev.tolist()
+        else:
+            recv_counts = list(send_counts)
+        # the receivers need the routing rows of the tokens they get
+        recv_idx = self._a2a(topk_idx[send_token].contiguous(), send_counts, recv_counts)
+        recv_w = self._a2a(topk_weights[send_token].float().contiguous(), send_counts, recv_counts)
+        mine = (recv_idx >= self.rank * self.local) & (recv_idx < (self.rank + 1) * self.local)
+        rows, slots = mine.nonzero(as_tuple=True)
+        local_expert = recv_idx[rows, slots] - self.rank * self.local
+        order = torch.sort(local_expert, stable=True).indices       # expert-major, (source, token, slot) inside an expert
+        counts = torch.bincount(local_expert, minlength=self.local)
+        return BaselinePlan(T, send_token, send_counts, recv_counts, rows[order].contiguous(),
+                            torch.cumsum(counts, 0).to(torch.int32), counts.tolist(), recv_w[rows, slots][order].contiguous(),
+                            int(recv_idx.shape[0]))
+
+    def dispatch(self, x: torch.Tensor, plan: BaselinePlan) -> torch.Tensor:
+        """[T, H] -> expert-major rows [R, H] of this rank's experts."""
+        return self._a2a(x[plan.send_token], plan.send_counts, plan.recv_counts)[plan.expand_from]
 
     def combine(self, rows: torch.Tensor, plan: BaselinePlan, weighted: bool = True) -> torch.Tensor:
-        if self.world > 1:
-            back = torch.empty((sum(plan.send_counts), rows.shape[1]), dtype=rows.dtype, device=rows.device)
-            dist.all_to_all_single(back, rows, plan.send_counts, plan.recv_counts, group=self.group)
-        else:
-            back = rows
+        """Expert-major rows [R, H] -> [T, H] bf16; fp32 accumulation, one bf16 partial per (token, rank) on the wire."""
+        vals = rows.float() * plan.row_weight.unsqueeze(1) if weighted else rows.float()
+        partial = torch.zeros((plan.num_recv, rows.shape[1]), dtype=torch.float32, device=rows.device)
+        partial.index_add_(0, plan.expand_from, vals)
+        back = self._a2a(partial.to(torch.bfloat16), plan.recv_counts, plan.send_counts)
         out = torch.zeros((plan.num_tokens, rows.shape[1]), dtype=torch.float32, device=rows.device)
-        vals = back.float() * plan.slot_weight.unsqueeze(1) if weighted else back.float()
-        out.index_add_(0, plan.token_of, vals)
+        out.index_add_(0, plan.send_token, back.float())
         return out.to(torch.bfloat16)
 
 
-def expert_ffn(rows: torch.Tensor, counts: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
-    """SwiGLU experts on expert-major rows: w1 [L, 2I, H], w2 [L, H, I] bf16; one cuBLAS GEMM pair per expert."""
-    out = torch.empty((rows.shape[0], w2.shape[1]), dtype=rows.dtype, device=rows.device)
+_grouped_ok: Optional[bool] = None
+_fp8_grouped_ok: Optional[bool] = None
+
+
+def _grouped_mm(rows: torch.Tensor, weight_t: torch.Tensor, plan: BaselinePlan) -> torch.Tensor:
+    """rows [R, K] bf16 x weight_t [L, K, N] bf16 -> [R, N]; expert e owns rows offsets[e-1]..offsets[e]."""
+    global _grouped_ok
+    if _grouped_ok is not False and hasattr(torch, "_grouped_mm"):
+        try:
+            out = torch._grouped_mm(rows, weight_t, offs=plan.expert_offsets)
+            _grouped_ok = True
+            return out
+        except (RuntimeError, NotImplementedError):
+            if _grouped_ok:
+                raise
+            _grouped_ok = False
+    out = torch.empty((rows.shape[0], weight_t.shape[2]), dtype=rows.dtype, device=rows.device)
     start = 0
-    for e, c in enumerate(counts.tolist()):
-        if c == 0:
-            continue
-        h = rows[start:start + c] @ w1[e].t()
-        gate, up = h.chunk(2, dim=-1)
-        out[start:start + c] = (torch.nn.functional.silu(gate) * up) @ w2[e].t()
+    for e, c in enumerate(plan.expert_counts):
+        if c:
+            torch.matmul(rows[start:start + c], weight_t[e], out=out[start:start + c])
         start += c
     return out
 
 
-def moe_forward(ep: NcclExpertParallel, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w1: torch.Tensor,
-                w2: torch.Tensor) -> torch.Tensor:
-    plan = ep.plan(topk_idx, topk_weights)
-    rows = ep.dispatch(x, plan)
-    grouped, perm, counts = ep.expert_major(rows, plan)
-    y = expert_ffn(grouped, counts, w1, w2)
-    back = torch.empty_like(y)
-    back[perm] = y
-    return ep.combine(back, plan)
+def _rowwise_fp8(t: torch.Tensor, dim: int):
+    amax = t.float().abs().amax(dim=dim, keepdim=True).clamp(min=1e-4)
+    scale = amax / 448.0
+    return (t.float() / scale).to(torch.float8_e4m3fn), scale
+
+
+def _grouped_mm_fp8(rows: torch.Tensor, weight_q: torch.Tensor, weight_scale: torch.Tensor, plan: BaselinePlan) -> torch.Tensor:
+    """fp8 x fp8 grouped GEMM with row-wise scales (activations quantised per row on the fly, weights beforehand)."""
+    q, s = _rowwise_fp8(rows, 1)
+    return torch._scaled_grouped_mm(q, weight_q, s.squeeze(1), weight_scale, offs=plan.expert_offsets, out_dtype=torch.bfloat16,
+                                    use_fast_accum=True)
+
+
+class ExpertWeights:
+    """SwiGLU expert weights in the layouts the library GEMMs want: w1 [L, 2I, H], w2 [L, H, I] bf16."""
+
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor):
+        self.w1_t, self.w2_t = w1.transpose(1, 2), w2.transpose(1, 2)          # [L, K, N] views, K-major memory
+        self.fp8 = None
+
+    def quantize(self) -> bool:
+        """Prepare the fp8 variant; False when this PyTorch build has no fp8 grouped GEMM for the device."""
+        global _fp8_grouped_ok
+        if _fp8_grouped_ok is False or not hasattr(torch, "_scaled_grouped_mm"):
+            return False
+        try:
+            q1, s1 = _rowwise_fp8(self.w1_t.transpose(1, 2), 2)                # scales per output column: [L, N, 1]
+            q2, s2 = _rowwise_fp8(self.w2_t.transpose(1, 2), 2)
+            self.fp8 = (q1.transpose(1, 2), s1.squeeze(2), q2.transpose(1, 2), s2.squeeze(2))
+            probe = BaselinePlan(0, None, [], [], None, torch.full((q1.shape[0],), 16, dtype=torch.int32, device=q1.device).cumsum(0).to(torch.int32),
+                                 [16] * q1.shape[0], None, 0)
+            _grouped_mm_fp8(torch.zeros((16 * q1.shape[0], q1.shape[2]), dtype=torch.bfloat16, device=q1.device), self.fp8[0],
+                            self.fp8[1], probe)
+            _fp8_grouped_ok = True
+        except (RuntimeError, NotImplementedError, TypeError):
+            self.fp8, _fp8_grouped_ok = None, False
+        return self.fp8 is not None
+
+
+def expert_ffn(rows: torch.Tensor, plan: BaselinePlan, weights: ExpertWeights, fp8: bool = False) -> torch.Tensor:
+    """SwiGLU experts on expert-major rows."""
+    if fp8:
+        h = _grouped_mm_fp8(rows, weights.fp8[0], weights.fp8[1], plan)
+    else:
+        h = _grouped_mm(rows, weights.w1_t, plan)
+    gate, up = h.chunk(2, dim=-1)
+    act = torch.nn.functional.silu(gate) * up
+    if fp8:
+        return _grouped_mm_fp8(act, weights.fp8[2], weights.fp8[3], plan)
+    return _grouped_mm(act, weights.w2_t, plan)
+
+
+def moe_forward(ep: NcclExpertParallel, x: torch.Tensor, plan: BaselinePlan, weights: ExpertWeights, fp8: bool = False) -> torch.Tensor:
+    """One MoE layer from a prepared plan: dispatch -> grouped SwiGLU experts -> weighted combine."""
+    return ep.combine(expert_ffn(ep.dispatch(x, plan), plan, weights, fp8), plan, weighted=True)

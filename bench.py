@@ -12,7 +12,9 @@ docs/performance.md:21-35 times the dispatch and combine kernels and reports not
 reference's effective bandwidth (docs/performance.md:61-69): routed rows x hidden x 2 bytes, local routes included,
 for both directions, summed over all ranks, divided by the device time of the slowest rank.  The ``e2e`` entry repeats
 the measurement through a fresh dispatch (notify included) with the step's inputs copied from pinned host memory and a
-scalar of the result read back every step.  Rank 0 prints one JSON line.
+scalar of the result read back every step (the copies of the next step overlap the kernels of the current one on a
+copy stream, as a data loader would arrange it).  Before anything is timed every rank checks one dispatch + combine,
+one low-latency step and a sample of the fused MoE output (``verified`` in the JSON line).  Rank 0 prints one JSON line.
 """
 from __future__ import annotations
 
@@ -100,8 +102,11 @@ def bench_low_latency(group, world, rank, dev, timed):
     x = torch.randn((T, H), generator=gen).bfloat16().to(dev)
     idx = torch.stack([torch.randperm(E, generator=gen)[:K] for _ in range(T)]).to(torch.int64).to(dev)
     w = torch.softmax(torch.randn((T, K), generator=gen), dim=1).float().to(dev)
+    from deepep_b200.utils.verify import verify_low_latency
+
     buf = ElasticBuffer(group, num_max_tokens_per_rank=256, hidden=H, num_topk=K, use_fp8_dispatch=True, explicitly_destroy=True)
     out = {}
+    out["ll_verified"], out["ll_verify_details"] = verify_low_latency(buf, x, idx, w, E)
     (rx, rsf), _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_cpu_sync=False)
     assert handle.is_low_latency
     eo = torch.randn((rx.shape[0], H), device=dev).bfloat16()
@@ -118,26 +123,66 @@ def bench_low_latency(group, world, rank, dev, timed):
     return out
 
 
+def _expert_weights(e: int, H: int, I: int, dev):
+    """Random e2m1 weights with non-uniform ue8m0 scales of global expert ``e`` (any rank can regenerate any expert)."""
+    g = torch.Generator(device=dev).manual_seed(4242 + e)
+    out = []
+    for n, k in ((2 * I, H), (H, I)):
+        packed = torch.randint(0, 256, (1, n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        centre = 127 + int(-0.5 * torch.log2(torch.tensor(float(k))).item()) - 3
+        scales = torch.randint(centre - 1, centre + 2, (1, n, k // 32), dtype=torch.uint8, device=dev, generator=g)
+        out.append((packed, scales))
+    return out
+
+
 def bench_mega_moe(group, world, rank, dev, timed):
-    """Fused MoE forward: hidden 7168, intermediate 2048, 256 experts, top-8, e4m3 activations x e2m1 weights."""
-    from deepep_b200.models.mega_moe import MegaWeights, SymmBuffer, fp8_fp4_mega_moe
+    """Fused MoE forward: hidden 7168, intermediate 2048, 256 experts, top-8 (group-limited routing), e4m3 activations with
+    power-of-two scales per 128 values, e2m1 weights with ue8m0 scales per 32.  A sample of the output rows is checked
+    against the fp32 restatement of the layer before the timing."""
+    from deepep_b200.models.mega_moe import SymmBuffer, fp8_fp4_mega_moe, transform_weights_for_mega_moe
+    from deepep_b200.models.mega_tools import compare
+    from deepep_b200.oracle import megamoe as O
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+    from deepep_b200.utils.routing import group_limited_routes
 
     H, I, E, K = 7168, 2048, 256, 8
     L = E // world
-    g = torch.Generator(device=dev).manual_seed(5 + rank)
-    w1 = MegaWeights(torch.randint(0, 256, (L * 2 * I * (H // 128), 64), dtype=torch.uint8, device=dev, generator=g),
-                     torch.full((L * 2 * I // 128 * (H // 128) * 512,), 118, dtype=torch.uint8, device=dev), L, 2 * I, H)
-    w2 = MegaWeights(torch.randint(0, 256, (L * H * (I // 128), 64), dtype=torch.uint8, device=dev, generator=g),
-                     torch.full((L * H // 128 * (I // 128) * 512,), 120, dtype=torch.uint8, device=dev), L, H, I)
+    mine = [_expert_weights(rank * L + l, H, I, dev) for l in range(L)]
+    w1, w2 = transform_weights_for_mega_moe((torch.cat([m[0][0] for m in mine]), torch.cat([m[0][1] for m in mine])),
+                                            (torch.cat([m[1][0] for m in mine]), torch.cat([m[1][1] for m in mine])))
+    del mine
+    O.FP4_VALUES = O.FP4_VALUES.to(dev)
     out = {}
     for name, T in (("prefill", 4096), ("decode", 64)):
         buf = SymmBuffer(group, E, T, K, H, I)
-        buf.x.view(torch.uint8).copy_(torch.randint(0, 120, (T, H), dtype=torch.uint8, device=dev, generator=g))
-        buf.x_sf.fill_(127)
-        buf.topk_idx.copy_(torch.topk(torch.rand((T, E), device=dev, generator=g), K, dim=1).indices.to(torch.int32))
-        buf.topk_weights.copy_(torch.softmax(torch.randn((T, K), device=dev, generator=g), dim=1))
+        g = torch.Generator().manual_seed(31 + rank)
+        x = torch.randn((T, H), generator=g).bfloat16().to(dev)
+        idx = group_limited_routes(T, E, K, GROUPS, TOPK_GROUPS, seed=4000 + rank).to(dev)
+        w = torch.softmax(torch.randn((T, K), generator=g), dim=1).to(dev)
+        q, sf = per_token_cast_to_fp8(x, use_ue8m0=True)            # e4m3 + fp32 scales per 128 values (powers of two)
+        buf.load_inputs(q, sf, idx, w)
         y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        buf.prepare(T)
+        fp8_fp4_mega_moe(y, w1, w2, buf)
+        torch.cuda.synchronize()
+        buf.engine.check()
+        # fp32 restatement of a few tokens (their experts' weights are regenerated from the seed, wherever they live)
+        sample = list(range(0, T, max(1, T // 4)))[:4]
+        xq = q[sample].float() * sf[sample].repeat_interleave(128, dim=1)
+        ref = torch.zeros((len(sample), H), dtype=torch.float32, device=dev)
+        for i, t in enumerate(sample):
+            for k in range(K):
+                (p1, s1), (p2, s2) = _expert_weights(int(idx[t, k]), H, I, dev)
+                ref[i] += w[t, k] * O.expert_forward(xq[i:i + 1], O.unpack_fp4(p1[0], s1[0]), O.unpack_fp4(p2[0], s2[0]))[0]
+        verdict = compare(y[sample], ref.bfloat16())
+        verdicts = [verdict["ok"]]
+        if world > 1:
+            import torch.distributed as dist
+
+            gathered = [None] * world
+            dist.all_gather_object(gathered, bool(verdict["ok"]), group=group)
+            verdicts = gathered
+        out[f"mega_moe_{name}_verified"] = all(verdicts)
+        out[f"mega_moe_{name}_mare"] = verdict["mare"]
         us = timed(lambda: fp8_fp4_mega_moe(y, w1, w2, buf), 5)
         buf.engine.check()
         out[f"mega_moe_{name}_us"] = us
@@ -147,26 +192,32 @@ def bench_mega_moe(group, world, rank, dev, timed):
 
 
 def bench_baseline(group, world, rank, dev, timed, x, idx, w, E):
-    """NCCL all-to-all(v) dispatch+combine and NCCL + cuBLAS bf16 MoE layer on the same shapes (comparison only)."""
-    from baseline.nccl_moe import NcclExpertParallel, moe_forward
+    """NCCL all-to-all(v) dispatch+combine (rank-level dedup, plan built once) and the NCCL + grouped-GEMM MoE layer on the
+    same shapes, bf16 and (when this PyTorch has the kernel) fp8 (comparison only)."""
+    from baseline.nccl_moe import ExpertWeights, NcclExpertParallel, moe_forward
 
     out = {}
     ep = NcclExpertParallel(group, E)
-    plan = ep.plan(idx, w)
+    plan = ep.plan(idx, w)                       # outside every timed region
 
     def a2a():
-        rows = ep.dispatch(x, plan)
-        return ep.combine(rows, plan, weighted=False)
+        return ep.combine(ep.dispatch(x, plan), plan, weighted=False)
 
     out["baseline_nccl_dispatch_combine_us"] = timed(a2a, 5)
     H, I = x.shape[1], 2048
     L = E // world
-    w1 = torch.randn((L, 2 * I, H), device=dev, dtype=torch.bfloat16) * 0.02
-    w2 = torch.randn((L, H, I), device=dev, dtype=torch.bfloat16) * 0.02
+    weights = ExpertWeights(torch.randn((L, 2 * I, H), device=dev, dtype=torch.bfloat16) * 0.02,
+                            torch.randn((L, H, I), device=dev, dtype=torch.bfloat16) * 0.02)
+    has_fp8 = weights.quantize()
+    out["baseline_fp8_grouped_gemm"] = bool(has_fp8)
     for name, T in (("prefill", x.shape[0]), ("decode", 64)):
-        us = timed(lambda: moe_forward(ep, x[:T], idx[:T], w[:T], w1, w2), 3)
+        p = plan if T == x.shape[0] else ep.plan(idx[:T], w[:T])
+        us = timed(lambda: moe_forward(ep, x[:T], p, weights), 3)
         out[f"baseline_nccl_cublas_moe_{name}_us"] = us
         out[f"baseline_nccl_cublas_moe_{name}_tokens_per_s"] = world * T / (us * 1e-6)
+        if has_fp8:
+            us8 = timed(lambda: moe_forward(ep, x[:T], p, weights, fp8=True), 3)
+            out[f"baseline_nccl_fp8_moe_{name}_us"] = us8
     return out
 
 
@@ -179,8 +230,8 @@ def main():
     from deepep_b200 import ElasticBuffer
     from deepep_b200.utils.math import per_token_cast_to_fp8
 
-    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests"))
-    from helpers import group_limited_routes
+    from deepep_b200.utils.routing import group_limited_routes
+    from deepep_b200.utils.verify import verify_dispatch_combine
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -213,6 +264,8 @@ def main():
     x, idx, w = x_host.to(dev), idx_host.to(dev), w_host.to(dev)
 
     buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True, num_sms=args.num_sms)
+    # every rank checks one dispatch + combine of this very workload (structure, payload checksums, reduction bit for bit)
+    verified, verify_details = verify_dispatch_combine(buf, x, idx, w, E)
     recv_x, _, recv_w, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
     rows = recv_x.shape[0]
     expert_out = recv_x  # identity experts: the dispatch output is the combine input
@@ -288,33 +341,68 @@ def main():
             extras.update(bench_baseline(group, world, rank, dev, timed, x, idx, w, E))
         except Exception as exc:
             extras["baseline_error"] = repr(exc)[:200]
+        for name in ("prefill", "decode"):
+            ours, theirs = extras.get(f"mega_moe_{name}_us"), extras.get(f"baseline_nccl_cublas_moe_{name}_us")
+            best = min(v for v in (theirs, extras.get(f"baseline_nccl_fp8_moe_{name}_us")) if v) if theirs else None
+            if ours and best:
+                extras[f"mega_moe_{name}_speedup_vs_best_baseline"] = best / ours
 
-    # end to end through the public API: pinned host inputs in, a scalar of the result out, every step
-    xd, idxd, wd = torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)
+    # End to end through the public API: every step copies its inputs from pinned host memory, runs a fresh dispatch
+    # (routing layout included) and a combine, and reads a scalar of the result back.  Like a data loader would, the
+    # copies of step i + 1 run on a copy stream while step i computes (two input buffers), and the scalar of step i is
+    # read by the host after step i + 1 has been queued; the timed region covers all copies and read-backs.
+    copy_stream = torch.cuda.Stream(device=dev)
+    slots = [(torch.empty_like(x), torch.empty_like(idx), torch.empty_like(w)) for _ in range(2)]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]       # input slot filled
+    consumed = [torch.cuda.Event(), torch.cuda.Event()]    # input slot no longer read by the kernels
+    result_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    result_done = [torch.cuda.Event(), torch.cuda.Event()]
+    main_stream = torch.cuda.current_stream(dev)
 
-    def e2e_step():
-        xd.copy_(x_host, non_blocking=True)
-        idxd.copy_(idx_host, non_blocking=True)
-        wd.copy_(w_host, non_blocking=True)
-        rx, _, rw, h, _ = buf.dispatch(xd, topk_idx=idxd, topk_weights=wd, num_experts=E, do_expand=True)
-        combined, _, _ = buf.combine(rx, h)
-        return float(combined[:, :8].float().sum().item())
+    def prefetch(i):
+        xd, idxd, wd = slots[i % 2]
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            xd.copy_(x_host, non_blocking=True)
+            idxd.copy_(idx_host, non_blocking=True)
+            wd.copy_(w_host, non_blocking=True)
+            ready[i % 2].record(copy_stream)
 
-    for _ in range(3):
-        e2e_step()
+    def e2e_loop(n):
+        total = 0.0
+        for ev in consumed:
+            ev.record(main_stream)
+        prefetch(0)
+        for i in range(n):
+            if i + 1 < n:
+                prefetch(i + 1)
+            xd, idxd, wd = slots[i % 2]
+            main_stream.wait_event(ready[i % 2])
+            rx, _, rw, h, _ = buf.dispatch(xd, topk_idx=idxd, topk_weights=wd, num_experts=E, do_expand=True)
+            combined, _, _ = buf.combine(rx, h)
+            consumed[i % 2].record(main_stream)
+            result_host[i % 2].copy_(combined[:, :8].float().sum().reshape(1), non_blocking=True)
+            result_done[i % 2].record(main_stream)
+            if i > 0:                                     # the previous step's scalar: its copy has long finished
+                result_done[(i - 1) % 2].synchronize()
+                total += float(result_host[(i - 1) % 2][0])
+        result_done[(n - 1) % 2].synchronize()
+        return total + float(result_host[(n - 1) % 2][0])
+
+    e2e_loop(3)
     sync_all()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_iters = max(3, args.steps // 2)
     s.record()
-    for _ in range(e2e_iters):
-        e2e_step()
+    e2e_loop(e2e_iters)
     e.record()
     sync_all()
     e2e_ms = max_over_ranks(s.elapsed_time(e) / e2e_iters)
     h2d = x_host.numel() * 2 + idx_host.numel() * 8 + w_host.numel() * 4
     e2e = {"value": bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-           "what": "H2D of x/topk_idx/topk_weights from pinned memory + notify + dispatch + combine + D2H of a checksum"}
+           "what": "H2D of x/topk_idx/topk_weights from pinned memory (copy stream, double-buffered) + notify + dispatch + "
+                   "combine + D2H of a checksum, every step"}
 
     buf.destroy()
     if rank == 0:
@@ -328,6 +416,9 @@ def main():
                        "l2": "working set per step (>= 0.9 GB) is larger than the 126 MB L2; no explicit flush",
                        "effective_bytes_per_step": bytes_per_step, "rows_per_rank": rows},
             "per_gpu_value": value / world, "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps,
+            "verified": bool(verified and extras.get("ll_verified", True) and extras.get("mega_moe_prefill_verified", True)
+                             and extras.get("mega_moe_decode_verified", True)),
+            "verify_details": verify_details,
             "kernels": extras,
         }
         print(json.dumps(line), flush=True)

@@ -60,6 +60,19 @@ def _digest(src: Path, flags: list) -> str:
     return h.hexdigest()
 
 
+CAPABILITIES = ["ep_notify", "ep_dispatch_ht", "ep_combine_ht", "ep_dispatch_ll", "ep_combine_ll", "ep_barrier", "ep_expand",
+                "ep_aggregate", "mega_moe", "a2av_gmm", "gmm_a2av", "transport:vmm", "transport:ipc"]
+
+
+def write_build_info(binary: Path, nvcc: str) -> None:
+    """Provenance of the binary next to it: what was compiled, with what, and the binary's hash (checked by the loader)."""
+    info = {"arch": "sm_100a", "nvcc": subprocess.run([nvcc, "--version"], capture_output=True, text=True).stdout.strip().splitlines()[-1],
+            "sources": [s.relative_to(ROOT).as_posix() for s in sources()], "runtime_protocol": 1,
+            "debug_bounds": os.environ.get("DEEPEP_DEBUG_BOUNDS", "0") not in ("", "0"), "capabilities": CAPABILITIES,
+            "binary": binary.name, "binary_sha256": hashlib.sha256(binary.read_bytes()).hexdigest()}
+    (ROOT / "_build_info.json").write_text(json.dumps(info, indent=1))
+
+
 def build(verbose: bool = False, force: bool = False) -> Path:
     BUILD.mkdir(parents=True, exist_ok=True)
     nvcc, flags = _nvcc(), _flags(verbose)
@@ -90,14 +103,12 @@ def build(verbose: bool = False, force: bool = False) -> Path:
                 stamps[name] = digest
         stamp_file.write_text(json.dumps(stamps, indent=0))
     out = target_path()
-    if jobs or not out.exists():
+    if jobs or not out.exists() or not (ROOT / "_build_info.json").exists():
         cmd = [nvcc, "-shared", *ARCH_FLAGS, "-o", str(out), *map(str, objects)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-        info = {"arch": "sm_100a", "nvcc": subprocess.run([nvcc, "--version"], capture_output=True, text=True).stdout.strip().splitlines()[-1],
-                "sources": [s.relative_to(ROOT).as_posix() for s in sources()], "runtime_protocol": 1}
-        (ROOT / "_build_info.json").write_text(json.dumps(info, indent=1))
+        write_build_info(out, nvcc)
     return out
 
 

@@ -211,6 +211,33 @@ class SymmBuffer:
         self.batch_size = batch_size
         return self
 
+    def load_inputs(self, x: torch.Tensor, x_sf: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> "SymmBuffer":
+        """Copy one batch into the symmetric input block and ``prepare`` it.
+
+        ``x`` is e4m3 ``[bs, hidden]``.  ``x_sf`` is either ue8m0 codes, uint8 ``[bs, hidden / 32]`` (the kernel's
+        native form), or fp32 ``[bs, hidden / 128]`` block scales that are powers of two (what
+        ``per_token_cast_to_fp8(x, use_ue8m0=True)`` produces): those are exact in ue8m0 and each is used for its four
+        32-value blocks.  Other fp32 scales would have to be rounded, which changes the numbers, so they are refused.
+        """
+        bs = x.shape[0]
+        if x.dtype != torch.float8_e4m3fn or tuple(x.shape) != (bs, self.hidden) or bs > self.num_max_tokens_per_rank:
+            raise ValueError(f"x must be e4m3 [batch <= {self.num_max_tokens_per_rank}, {self.hidden}]")
+        if x_sf.dtype == torch.uint8 and tuple(x_sf.shape) == (bs, self.hidden // 32):
+            codes = x_sf
+        elif x_sf.dtype == torch.float32 and tuple(x_sf.shape) == (bs, self.hidden // 128):
+            mantissa, exponent = torch.frexp(x_sf)            # x_sf = mantissa * 2^exponent, mantissa in [0.5, 1)
+            if not bool((mantissa == 0.5).all()) or not bool(((exponent >= -126) & (exponent <= 128)).all()):
+                raise ValueError("fp32 block scales must be powers of two (per_token_cast_to_fp8(x, use_ue8m0=True)); "
+                                 "other scales cannot be carried by the ue8m0 scale format without rounding")
+            codes = (exponent - 1 + 127).to(torch.uint8).repeat_interleave(4, dim=1)
+        else:
+            raise ValueError("x_sf must be uint8 [batch, hidden / 32] (ue8m0) or fp32 [batch, hidden / 128] (powers of two)")
+        self.x.view(torch.uint8)[:bs].copy_(x.view(torch.uint8))
+        self.x_sf[:bs].copy_(codes)
+        self.topk_idx[:bs].copy_(topk_idx.to(torch.int32))
+        self.topk_weights[:bs].copy_(topk_weights.float())
+        return self.prepare(bs)
+
     def validate_inputs(self, batch_size: int) -> None:
         idx = self.topk_idx[:batch_size]
         if bool(((idx >= self.num_experts)).any()):

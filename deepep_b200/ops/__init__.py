@@ -38,11 +38,26 @@ def load_native(build_if_missing: bool = False):
         from .._build import build
 
         build()
+    _verify_binary()
     mod = importlib.import_module("deepep_b200._C")
     if getattr(mod, "runtime_protocol", None) != RUNTIME_PROTOCOL:
         raise NativeUnavailable("native extension speaks another runtime protocol; rebuild it")
     _native = mod
     return mod
+
+
+def _verify_binary() -> None:
+    """When the build left its provenance file, the binary on disk must be the one it describes (a stale or foreign
+    ``_C*.so`` is refused instead of being loaded into the process)."""
+    info = build_info()
+    digest = info.get("binary_sha256")
+    if not digest:
+        return
+    import hashlib
+
+    if info.get("binary") != native_path().name or hashlib.sha256(native_path().read_bytes()).hexdigest() != digest:
+        raise NativeUnavailable("the native extension on disk is not the one _build_info.json describes; "
+                                "run `python -m deepep_b200._build`")
 
 
 def require_native(operation: str):

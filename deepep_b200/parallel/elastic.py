@@ -271,16 +271,23 @@ class ElasticBuffer:
             comm.wait_stream(cur)
         return comm
 
-    def _leave(self, comm, async_with_compute_stream: bool, resources: Sequence[Any]) -> EventOverlap:
+    def _leave(self, comm, async_with_compute_stream: bool, resources: Sequence[Any],
+               allocated_on_comm: bool = False) -> EventOverlap:
         """Sync mode: the current stream waits for the call.  Async mode: the caller waits on the returned event."""
         if comm is None:
             return EventOverlap()
         cur = torch.cuda.current_stream(self.device)
         if async_with_compute_stream:
             return EventOverlap._from_resources(EventHandle(comm), tuple(resources))
-        # outputs were allocated on the current stream and the current stream now waits for the call:
-        # stream-ordered reuse of their memory is already safe, no record_stream needed
         cur.wait_stream(comm)
+        if allocated_on_comm:
+            # The outputs belong to the communication stream's memory pool but will be used on the current stream: tell
+            # the allocator, or it could hand a dropped block to the next communication kernel while compute still reads it.
+            for t in resources:
+                if isinstance(t, torch.Tensor) and t.is_cuda:
+                    t.record_stream(cur)
+        # otherwise outputs were allocated on the current stream, which now waits for the call: stream-ordered reuse of
+        # their memory is already safe
         return EventOverlap()
 
     def _check(self) -> None:
@@ -355,7 +362,7 @@ class ElasticBuffer:
             with self._on(comm if allocate_on_comm_stream else None):
                 if low_latency and hasattr(self.engine, "ll_dispatch"):
                     return self._dispatch_low_latency(x_data, x_sf, topk_idx, topk_weights, num_experts, mode, cpu_sync,
-                                                      comm, async_with_compute_stream)
+                                                      comm, async_with_compute_stream, allocate_on_comm_stream)
                 plan = self.engine.notify([topk_idx], [topk_weights], num_experts, expand=expand, alignment=alignment,
                                           cpu_sync=cpu_sync, stream=comm)[0]
                 recv_x, recv_sf = self.engine.dispatch([x if x_sf is not None else x_data], [plan], mode,
@@ -376,7 +383,7 @@ class ElasticBuffer:
             recv_sf = _col_major(recv_sf)
         out_x = recv_x if recv_sf is None else (recv_x, recv_sf)
         event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, recv_w, recv_idx, x_data, x_sf, topk_idx,
-                                                               topk_weights] + h._tracked())
+                                                               topk_weights] + h._tracked(), allocate_on_comm_stream)
         return out_x, recv_idx, recv_w, h, event
 
     def _note_failure(self, exc: Exception) -> None:
@@ -403,11 +410,12 @@ class ElasticBuffer:
                 recv_x, recv_sf = self.engine.dispatch([x_data if x_sf is None else (x_data, x_sf)], [handle._plan], mode,
                                                        blocks=num_sms or self.num_sms, stream=comm)[0]
         out_x = recv_x if recv_sf is None else (recv_x, recv_sf)
-        event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, x_data, x_sf] + handle._tracked())
+        event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, x_data, x_sf] + handle._tracked(),
+                            allocate_on_comm_stream)
         return out_x, None, None, handle, event
 
     def _dispatch_low_latency(self, x_data, x_sf, topk_idx, topk_weights, num_experts, mode, cpu_sync, comm,
-                              async_with_compute_stream):
+                              async_with_compute_stream, allocated_on_comm=False):
         plan, recv_x, recv_sf = self.engine.ll_dispatch([x_data if x_sf is None else (x_data, x_sf)], [topk_idx],
                                                         [topk_weights], num_experts, mode, cpu_sync=cpu_sync, stream=comm)[0]
         rows = plan.num_rows
@@ -416,7 +424,7 @@ class ElasticBuffer:
         recv_w = plan.recv_w[:rows]
         out_x = recv_x if recv_sf is None else (recv_x, recv_sf)
         event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, recv_w, x_data, x_sf, topk_idx, topk_weights]
-                            + h._tracked())
+                            + h._tracked(), allocated_on_comm)
         return out_x, None, recv_w, h, event
 
     def _make_handle(self, plan, expand, num_experts, alignment, num_sms, topk_idx, tokens, low_latency) -> EPHandle:
@@ -484,7 +492,7 @@ class ElasticBuffer:
                                                  blocks=num_sms or self.num_sms, stream=comm,
                                                  **({"split": split} if split is not None else {}))[0]
         event = self._leave(comm, async_with_compute_stream, [out, out_w, x, topk_weights] + [b for b in biases if b is not None]
-                            + handle._tracked())
+                            + handle._tracked(), allocate_on_comm_stream)
         return out, out_w, event
 
     # ------------------------------------------------------------------ validation helpers

@@ -1,5 +1,6 @@
 """Host-side behaviour: API surface, aliases, layout mirror, store collectives, utils, failure paths without a GPU."""
 import inspect
+import os
 import threading
 
 import pytest
@@ -205,3 +206,26 @@ def test_timeout_environment_override(monkeypatch):
     monkeypatch.setenv("DEEPEP_GPU_TIMEOUT_SECONDS", "0")
     with pytest.raises(ValueError):
         _timeout_seconds(100)
+
+
+def test_installation_validator_reports_a_healthy_package():
+    """``python -m deepep_b200.validate``: lazy import, binary matches its provenance file, CPU smoke run passes."""
+    import json
+    import subprocess
+    import sys
+
+    from deepep_b200.ops import load_native
+
+    load_native(build_if_missing=True)
+    res = subprocess.run([sys.executable, "-m", "deepep_b200.validate"], capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(__file__)))
+    report = json.loads(res.stdout)
+    assert res.returncode == 0 and report["ok"] and report["package"]["import_is_lazy"] and report["smoke"]["ok"]
+
+
+def test_loader_refuses_a_binary_that_is_not_the_recorded_one(tmp_path, monkeypatch):
+    import deepep_b200.ops as ops
+
+    monkeypatch.setattr(ops, "_native", None)
+    monkeypatch.setattr(ops, "build_info", lambda: {"binary": ops.native_path().name, "binary_sha256": "0" * 64})
+    with pytest.raises(ops.NativeUnavailable, match="not the one"):
+        ops.load_native()
