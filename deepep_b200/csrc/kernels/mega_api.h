@@ -59,12 +59,20 @@ cudaError_t launch_mega_gemm(const MegaGemmParams& p, int blocks, cudaStream_t s
 // fp4 = true: elements are packed e2m1 pairs that the copy engine widens to one byte each in shared memory.
 bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, bool fp4, const char** error);
 
+// Phase stamps of the fused kernel, one record per CTA (globaltimer nanoseconds): kernel start, inputs quantised and
+// handshake done, routing layout done, token pull done (pull warps), GEMM tile loop done, finish handshake done, end.
+constexpr int kMegaTimerWords = 8;
+enum MegaTimerSlot : int { kTimStart = 0, kTimHandshake = 1, kTimLayout = 2, kTimPull = 3, kTimGemm = 4, kTimFinishSync = 5, kTimEnd = 6 };
+
 // ---------------------------------------------------------------- routing + token pull
 struct MegaRouteArgs {
   RankCtx ctx;
   long long in_off;            // byte offset of the input block (x, x_sf, topk_idx, topk_w) in a workspace
   int T, E, K, H;              // tokens of this rank, experts, top-k, hidden
   int max_tokens, max_mtiles;
+  int S, pad;                  // shared experts of this rank: local experts E / world .. E / world + S - 1, fed with all of its own tokens
+  const __nv_bfloat16* x_bf16; // optional [T, H]: quantised to MXFP8 into the input block at the start of the kernel
+  unsigned long long* timer;   // optional [blocks][kMegaTimerWords] phase stamps in nanoseconds (see mega_tools.parse_timer)
   // outputs
   uint8_t* a1;                 // [rows_pad, H] e4m3
   uint8_t* a1_sf;              // chunked scales
@@ -85,7 +93,8 @@ void mega_input_offsets(int max_tokens, int hidden, int topk, long long* out6);
 struct MegaFinishArgs {
   RankCtx ctx;
   long long in_off, comb_off;
-  int T, E, K, H, max_tokens, pad;
+  int T, E, K, H, max_tokens, S;   // S shared experts: combine slots K .. K + S - 1 of a token carry their rows (weight 1)
+  unsigned long long* timer;
   __nv_bfloat16* y;            // [T, H]
 };
 struct MegaFinishParams { WsLayout lay; MegaFinishArgs r[kMaxRanks]; };

@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid
     route_pull_phase(a.route, sh, blockIdx.x * kPullWarps + (warp - kGemmThreads / 32), gridDim.x * kPullWarps);
     __syncthreads();                               // pairs with the tear-down barrier inside gemm_phase
   }
+  mega_stamp(a.route.timer, kTimGemm);             // this CTA ran out of tiles (or of rows to pull)
   __threadfence_system();
   grid.sync();
   finish_phase(a.finish, true);

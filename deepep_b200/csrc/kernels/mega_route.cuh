@@ -47,9 +47,58 @@ struct RouteShared {
 
 constexpr int kPullChunk = 8;   // consecutive rows one warp pulls before it moves on
 
+__device__ __forceinline__ void mega_stamp(unsigned long long* timer, int slot) {
+  if (timer != nullptr && threadIdx.x == 0) timer[(size_t)blockIdx.x * kMegaTimerWords + slot] = global_timer_ns();
+}
+
+// bf16 [T, H] -> e4m3 codes and one ue8m0 exponent per 32 values, written into this rank's symmetric input block.
+// Block scale 2^(floor(log2(amax)) - 8) (amax clamped to 2^-119, exponent to -127), values clamped to +-448: the
+// quantiser of the reference's token-quant stage (stage/mega_moe_token_quant.hpp; oracle: reference.py:44-54).
+// One lane per 32-value block.
+__device__ __forceinline__ void quantize_inputs_phase(const MegaRouteArgs& a, uint8_t* x_out, uint8_t* sf_out) {
+  const int blocks_per_row = a.H / 32;
+  const long long total = (long long)a.T * blocks_per_row;
+  for (long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x; b < total; b += (long long)gridDim.x * blockDim.x) {
+    const int4* src = reinterpret_cast<const int4*>(a.x_bf16) + b * 4;
+    int4 raw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) raw[i] = __ldg(src + i);
+    float v[32];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[8 * i + 2 * j] = __low2float(h[j]); v[8 * i + 2 * j + 1] = __high2float(h[j]);
+        amax = fmaxf(amax, fmaxf(fabsf(v[8 * i + 2 * j]), fabsf(v[8 * i + 2 * j + 1])));
+      }
+    }
+    amax = fmaxf(amax, __uint_as_float((127u - 119u) << 23));                       // 2^-119
+    const int exponent = max((int)((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 8, -127);
+    const float inv = __uint_as_float((unsigned)(127 - exponent) << 23);          // 2^-exponent, exact
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float scaled = fminf(fmaxf(v[4 * i + j] * inv, -448.f), 448.f);
+        word |= (uint32_t)__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+      }
+      w[i] = word;
+    }
+    int4* dst = reinterpret_cast<int4*>(x_out) + b * 2;
+    dst[0] = make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
+    dst[1] = make_int4((int)w[4], (int)w[5], (int)w[6], (int)w[7]);
+    sf_out[b] = (uint8_t)(exponent + 127);
+  }
+}
+
 // Handshake, per-expert entry lists, 128-row tile layout (tile -> expert).
-// expert_list[l * cap + j] (cap = world * max_tokens) = source * M * K + token * K + slot of the j-th routed slot of
-// local expert l, in arrival order.
+// expert_list[l * cap + j] (cap = world * max_tokens) = (source * M + token) * (K + S) + slot of the j-th routed slot of
+// local expert l, in arrival order; the S shared experts follow the routed ones and take every token of this rank
+// (slot K + s).
 __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::grid_group& grid, RouteShared& sh) {
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, K = a.K, E = a.E, Lx = E / P, M = a.max_tokens;
@@ -57,9 +106,13 @@ __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::g
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpMega] + 1;
   const MegaInput in = mega_input_layout(M, a.H, K);
-  const int cap = P * M;
+  const int cap = P * M, S = a.S, Kp = K + S;     // Kp: combine slots per token (top-k slots, then one per shared expert)
 
-  // ---- handshake: my inputs are in place (stream order), tell everybody, wait for everybody
+  mega_stamp(a.timer, kTimStart);
+  if (a.x_bf16 != nullptr)   // the caller passed bf16 activations: quantise them into the symmetric input block first
+    quantize_inputs_phase(a, ctx.ws[me] + a.in_off + in.x, ctx.ws[me] + a.in_off + in.x_sf);
+  // ---- handshake: my inputs are in place (stream order, or just written above), tell everybody, wait for everybody
+  __threadfence_system();
   if (blockIdx.x == 0 && threadIdx.x < P) {
     if (threadIdx.x == 0) reinterpret_cast<int*>(ctx.ws[me] + a.in_off + in.hdr)[0] = a.T;
     __threadfence_system();
@@ -73,9 +126,10 @@ __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::g
     sh.T[threadIdx.x] = (alive && threadIdx.x < P) ? __ldcg(reinterpret_cast<const int*>(ctx.ws[threadIdx.x] + a.in_off + in.hdr)) : 0;
   if (threadIdx.x == 0) sh.alive = alive;
   // zero the per-expert counters
-  if (blockIdx.x == 0) for (int l = threadIdx.x; l < Lx; l += (int)blockDim.x) a.expert_rows[l] = 0;
+  if (blockIdx.x == 0) for (int l = threadIdx.x; l < Lx + S; l += (int)blockDim.x) a.expert_rows[l] = 0;
   __syncthreads();
   grid.sync();
+  mega_stamp(a.timer, kTimHandshake);
 
   // ---- pass 1: the routed slots of every local expert (own rank first, then the peers in ring order)
   for (int r0 = 0; r0 < P; ++r0) {
@@ -86,19 +140,24 @@ __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::g
       const int e = __ldcg(idx + i);
       if (e >= me * Lx && e < (me + 1) * Lx) {
         const int j = atomicAdd(&a.expert_rows[e - me * Lx], 1);
-        if (j < cap) a.expert_list[(size_t)(e - me * Lx) * cap + j] = r * M * K + i;
+        if (j < cap) a.expert_list[(size_t)(e - me * Lx) * cap + j] = (r * M + i / K) * Kp + i % K;
       }
     }
+  }
+  // shared experts: every token of this rank, in order, into combine slot K + s
+  for (int s = 0; s < S; ++s) {
+    for (int t = gtid; t < a.T; t += gstride) a.expert_list[(size_t)(Lx + s) * cap + t] = (me * M + t) * Kp + K + s;
+    if (gtid == 0) a.expert_rows[Lx + s] = a.T;
   }
   __threadfence();
   grid.sync();
 
   // ---- tile layout: every expert starts at a multiple of 128 rows
-  for (int l = threadIdx.x; l < Lx; l += (int)blockDim.x) sh.rows[l] = min(__ldcg(a.expert_rows + l), cap);   // parallel loads
+  for (int l = threadIdx.x; l < Lx + S; l += (int)blockDim.x) sh.rows[l] = min(__ldcg(a.expert_rows + l), cap);   // parallel loads
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
-    for (int l = 0; l < Lx; ++l) {
+    for (int l = 0; l < Lx + S; ++l) {
       const int c = sh.rows[l];
       sh.base[l] = run;
       const int tiles = (c + kGemmBM - 1) / kGemmBM;
@@ -110,6 +169,7 @@ __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::g
     if (blockIdx.x == 0) *a.num_mtiles = sh.total_rows / kGemmBM;
   }
   __syncthreads();
+  mega_stamp(a.timer, kTimLayout);
 }
 
 // Pulls the routed tokens from their owners in row order (tile by tile, so that the first tiles are complete first);
@@ -120,7 +180,7 @@ __device__ __forceinline__ void route_pull_phase(const MegaRouteArgs& a, const R
   const int P = ctx.world, K = a.K, H = a.H, M = a.max_tokens;
   const int lane = threadIdx.x & 31;
   const MegaInput in = mega_input_layout(M, H, K);
-  const int cap = P * M;
+  const int cap = P * M, Kp = K + a.S;
   if (!sh.alive) return;
   for (int row0 = gw * kPullChunk; row0 < sh.total_rows; row0 += total_warps * kPullChunk) {
     // lane j < kPullChunk looks up row row0 + j
@@ -135,7 +195,7 @@ __device__ __forceinline__ void route_pull_phase(const MegaRouteArgs& a, const R
       const int en = __shfl_sync(0xffffffffu, entry, c);
       if (en < 0) continue;
       const long long row = row0 + c;
-      const int r = en / (M * K), t = (en - r * M * K) / K;
+      const int r = en / (M * Kp), t = (en - r * M * Kp) / Kp;
       const uint8_t* peer = ctx.ws[r] + a.in_off;
       const int4* from = reinterpret_cast<const int4*>(peer + in.x + (size_t)t * H);
       int4* to = reinterpret_cast<int4*>(a.a1 + row * H);
@@ -150,6 +210,8 @@ __device__ __forceinline__ void route_pull_phase(const MegaRouteArgs& a, const R
       if (lane == 0) atomicAdd(a.pulled + row0 / kGemmBM, min(kPullChunk, sh.total_rows - row0));
     }
   }
+  if (a.timer != nullptr && lane == 0)     // the CTA's pull warps all write this word; the last one to finish wins
+    a.timer[(size_t)blockIdx.x * kMegaTimerWords + kTimPull] = global_timer_ns();
 }
 
 // The whole routing step as one phase (all warps of the grid pull).
@@ -162,7 +224,7 @@ __device__ __forceinline__ void route_phase(const MegaRouteArgs& a, cg::grid_gro
 
 __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_epoch) {
   const RankCtx& ctx = a.ctx;
-  const int P = ctx.world, me = ctx.rank, K = a.K, H = a.H, M = a.max_tokens;
+  const int P = ctx.world, me = ctx.rank, K = a.K, H = a.H, M = a.max_tokens, Kp = a.K + a.S;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gw = blockIdx.x * ((int)blockDim.x / 32) + warp, total_warps = gridDim.x * ((int)blockDim.x / 32);
   Control* ctl = control_of(ctx.ws[me]);
@@ -177,6 +239,7 @@ __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_
   int ok = 1;
   if (threadIdx.x < P) ok = wait_flag_ge(&ctl->mega_flag[threadIdx.x][1], epoch, ctx, kOpMega, 1, threadIdx.x);
   const int alive = __syncthreads_and(ok);
+  mega_stamp(a.timer, kTimFinishSync);
   if (alive) {
     const int* idx = reinterpret_cast<const int*>(ctx.ws[me] + a.in_off + in.idx);
     const float* w = reinterpret_cast<const float*>(ctx.ws[me] + a.in_off + in.w);
@@ -196,14 +259,15 @@ __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_
         wk[k] = w[(size_t)t * K + k];
         if (e >= 0 && e < a.E) valid |= 1u << k;
       }
+      for (int k = K; k < Kp; ++k) { wk[k] = 1.f; valid |= 1u << k; }     // shared experts: every token, weight one
       int4* out = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.y) + (size_t)t * H * 2);
-      const uint8_t* rows = comb + (size_t)t * K * H * 2;
+      const uint8_t* rows = comb + (size_t)t * Kp * H * 2;
       for (int u0 = part * span + lane; u0 < u_end; u0 += 64) {      // two 16-byte columns per step, all slots' loads issued first
         const bool two = u0 + 32 < u_end;
         int4 v0[kMaxTopk], v1[kMaxTopk];
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {
-          if (k < K && ((valid >> k) & 1u)) {
+          if (k < Kp && ((valid >> k) & 1u)) {
             v0[k] = ld_cg_int4(rows + (size_t)k * H * 2 + (size_t)u0 * 16);
             if (two) v1[k] = ld_cg_int4(rows + (size_t)k * H * 2 + (size_t)(u0 + 32) * 16);
           }
@@ -211,7 +275,7 @@ __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_
         float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {
-          if (k < K && ((valid >> k) & 1u)) {
+          if (k < Kp && ((valid >> k) & 1u)) {
             const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[k]);
             const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[k]);
 #pragma unroll
@@ -238,6 +302,7 @@ __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_
       }
     }
   }
+  mega_stamp(a.timer, kTimEnd);
   if (bump_epoch && last_block_of_rank(ctl, kOpMega, gridDim.x)) {
     if (threadIdx.x == 0) ctl->epoch[kOpMega] = epoch;
   }

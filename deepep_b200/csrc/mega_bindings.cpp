@@ -69,6 +69,11 @@ void fill_route(MegaRouteArgs& a, const py::dict& d, py::object session) {
   a.mtile_expert = ptr<int>(d, "mtile_expert"); a.num_mtiles = ptr<int>(d, "num_mtiles");
   a.expert_rows = ptr<int>(d, "expert_rows"); a.expert_list = ptr<int>(d, "expert_list");
   a.pulled = ptr<int>(d, "pulled");
+  a.S = geti(d, "S", 0);
+  a.x_bf16 = ptr<const __nv_bfloat16>(d, "x_bf16");
+  a.timer = ptr<unsigned long long>(d, "timer");
+  if (a.S < 0 || a.K + a.S > kMaxTopk || a.E / a.ctx.world + a.S > kMaxExperts)
+    throw std::invalid_argument("top-k plus shared experts must not exceed 16, local plus shared experts 1024");
   if (a.H % 128 || a.E % a.ctx.world || a.E > kMaxExperts) throw std::invalid_argument("hidden % 128 == 0 and experts % world == 0 are required");
 }
 
@@ -77,6 +82,8 @@ void fill_finish(MegaFinishArgs& a, const py::dict& d, py::object session) {
   a.in_off = getl(d, "in_off"); a.comb_off = getl(d, "comb_off");
   a.T = geti(d, "T"); a.E = geti(d, "E"); a.K = geti(d, "K"); a.H = geti(d, "H"); a.max_tokens = geti(d, "max_tokens");
   a.y = ptr<__nv_bfloat16>(d, "y");
+  a.S = geti(d, "S", 0);
+  a.timer = ptr<unsigned long long>(d, "timer");
 }
 
 // One persistent launch for the whole layer: args[i] = {"route": {...}, "gemm1": {...}, "gemm2": {...}, "finish": {...}, "ready": ptr}
@@ -126,6 +133,7 @@ void bind_mega(py::module_& m) {
   m.attr("gemm_tile") = kGemmBM;
   m.attr("gemm_tile_n") = kGemmBN;
   m.attr("sf_chunk") = kSfChunk;
+  m.attr("mega_timer_words") = kMegaTimerWords;
   m.def("mega_input_offsets", [](int max_tokens, int hidden, int topk) {
     long long o[6];
     mega_input_offsets(max_tokens, hidden, topk, o);

@@ -80,18 +80,21 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
 class MegaEngine:
     """Runs the four kernels for one rank, or for several virtual ranks that share a GPU."""
 
-    def __init__(self, sessions: Sequence, layout, device, num_experts: int, intermediate: int, num_sms: int = 0):
+    def __init__(self, sessions: Sequence, layout, device, num_experts: int, intermediate: int, num_sms: int = 0,
+                 num_shared_experts: int = 0):
         self.C = require_native("MegaMoE")
         self.sessions, self.layout, self.device = list(sessions), layout, device
         self.n, self.world = len(self.sessions), layout.world
         self.M, self.H, self.K = layout.max_tokens, layout.hidden, layout.topk
         self.E, self.I = num_experts, intermediate
         self.L = num_experts // self.world
+        self.S = int(num_shared_experts)              # shared experts: extra local experts that take all of this rank's tokens
         assert self.H % 256 == 0 and self.I % 128 == 0 and num_experts % self.world == 0
+        assert self.S >= 0 and self.K + self.S <= 16, "top-k plus shared experts must not exceed 16"
         off = self.C.mega_input_offsets(self.M, self.H, self.K)
         self.in_off = layout.mega
         self.off_hdr, self.off_x, self.off_sf, self.off_idx, self.off_w, in_total = off
-        self.comb_off = layout.mega + in_total
+        self.comb_off = layout.mega + in_total        # combine slots [M][K + S][H] bf16
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self.gemm_blocks = num_sms or self.sm_count
         # tiles handed out by an atomic counter (default) or statically round-robin (DEEPEP_MEGA_STATIC_TILES=1)
@@ -104,7 +107,7 @@ class MegaEngine:
         # of those rows cross NVLink.  DEEPEP_MEGA_INTERLEAVE=<units> overrides (0 = off).
         default = "4" if self.world >= 4 else "0"
         self.interleave = int(os.environ.get("DEEPEP_MEGA_INTERLEAVE", default) or 0)   # wave length in units of two CTA rounds
-        rows = self.world * self.M * min(self.K, self.L) + self.L * 127
+        rows = self.world * self.M * min(self.K, self.L) + self.S * self.M + (self.L + self.S) * 127
         self.max_mtiles = -(-rows // 128)
         self.rows_cap = self.max_mtiles * 128
         u8, i32 = dict(dtype=torch.uint8, device=device), dict(dtype=torch.int32, device=device)
@@ -114,13 +117,13 @@ class MegaEngine:
                 a1=torch.empty((self.rows_cap, self.H), **u8), a1_sf=torch.zeros((self.max_mtiles * (self.H // 128) * 512,), **u8),
                 a2=torch.empty((self.rows_cap, self.I), **u8), a2_sf=torch.zeros((self.max_mtiles * (self.I // 128) * 512,), **u8),
                 row_src=torch.empty((self.rows_cap,), **i32), mtile_expert=torch.zeros((self.max_mtiles,), **i32),
-                num_mtiles=torch.zeros((1,), **i32), expert_rows=torch.zeros((self.L,), **i32),
-                expert_list=torch.empty((self.L * self.world * self.M,), **i32), err=torch.zeros((1,), **i32),
+                num_mtiles=torch.zeros((1,), **i32), expert_rows=torch.zeros((self.L + self.S,), **i32),
+                expert_list=torch.empty(((self.L + self.S) * self.world * self.M,), **i32), err=torch.zeros((1,), **i32),
                 ready=torch.zeros((self.max_mtiles,), **i32), pulled=torch.zeros((self.max_mtiles,), **i32), tile_counter=torch.zeros((1,), **i32)))
 
     @staticmethod
-    def mega_bytes(C, max_tokens: int, hidden: int, topk: int) -> int:
-        return C.mega_input_offsets(max_tokens, hidden, topk)[5] + max_tokens * topk * hidden * 2 + 1024
+    def mega_bytes(C, max_tokens: int, hidden: int, topk: int, num_shared_experts: int = 0) -> int:
+        return C.mega_input_offsets(max_tokens, hidden, topk)[5] + max_tokens * (topk + num_shared_experts) * hidden * 2 + 1024
 
     def input_views(self, i: int):
         """(x e4m3 [M, H], x_sf uint8 [M, H/32], topk_idx int32 [M, K], topk_weights fp32 [M, K]) of rank slot i."""
@@ -133,21 +136,28 @@ class MegaEngine:
         return x, sf, idx, w
 
     def forward(self, ys: Sequence[torch.Tensor], tokens: Sequence[int], l1: Sequence[MegaWeights], l2: Sequence[MegaWeights],
-                stream=None, fused: bool = True) -> None:
+                stream=None, fused: bool = True, x_bf16: Optional[Sequence[Optional[torch.Tensor]]] = None,
+                timer: Optional[torch.Tensor] = None) -> None:
         """Run the layer.  ``fused``: one persistent cooperative kernel (route -> GEMM1 -> GEMM2 -> finish); otherwise
-        the same phases as four launches (kept for debugging and for comparing the two schedules)."""
+        the same phases as four launches (kept for debugging and for comparing the two schedules).
+        ``l1`` / ``l2`` hold the routed experts followed by the shared ones when the engine has shared experts.
+        ``x_bf16[i]``: bf16 activations quantised to MXFP8 inside the kernel instead of pre-quantised inputs.
+        ``timer``: int64 ``[SMs, mega_timer_words]`` that receives one record of phase stamps per CTA (fused, one rank)."""
         C, lay = self.C, self.layout
         s = (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
         route_args, finish_args, gemm1_args, gemm2_args = [], [], [], []
         for i in range(self.n):
             sc, w1, w2 = self.scratch[i], l1[i], l2[i]
             route_args.append(dict(in_off=self.in_off, T=tokens[i], E=self.E, K=self.K, H=self.H, max_tokens=self.M,
+                                   S=self.S, x_bf16=None if x_bf16 is None or x_bf16[i] is None else x_bf16[i].data_ptr(),
+                                   timer=None if timer is None else timer.data_ptr(),
                                    max_mtiles=self.max_mtiles, a1=sc["a1"].data_ptr(), a1_sf=sc["a1_sf"].data_ptr(),
                                    row_src=sc["row_src"].data_ptr(), mtile_expert=sc["mtile_expert"].data_ptr(),
                                    num_mtiles=sc["num_mtiles"].data_ptr(), expert_rows=sc["expert_rows"].data_ptr(),
                                    expert_list=sc["expert_list"].data_ptr()))
             finish_args.append(dict(in_off=self.in_off, comb_off=self.comb_off, T=tokens[i], E=self.E, K=self.K, H=self.H,
-                                    max_tokens=self.M, y=ys[i].data_ptr()))
+                                    max_tokens=self.M, y=ys[i].data_ptr(), S=self.S,
+                                    timer=None if timer is None else timer.data_ptr()))
             common = dict(mtile_expert=sc["mtile_expert"].data_ptr(), num_mtiles=sc["num_mtiles"].data_ptr(), rows_pad=self.rows_cap,
                           error_flag=sc["err"].data_ptr())
             gemm1_args.append(dict(common, a=sc["a1"].data_ptr(), sfa=sc["a1_sf"].data_ptr(), b=w1.packed.data_ptr(),
@@ -155,8 +165,8 @@ class MegaEngine:
                                    a2=sc["a2"].data_ptr(), a2_sf=sc["a2_sf"].data_ptr(), inter=self.I))
             gemm2_args.append(dict(common, a=sc["a2"].data_ptr(), sfa=sc["a2_sf"].data_ptr(), b=w2.packed.data_ptr(),
                                    sfb=w2.sf_chunks.data_ptr(), k=self.I, b_rows=w2.experts * w2.n, n_total=w2.n, epi=2,
-                                   row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M, topk=self.K,
-                                   hidden=self.H))
+                                   row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M,
+                                   topk=self.K + self.S, hidden=self.H))
         if fused:
             for i in range(self.n):    # the fused kernel overlaps the pull with the GEMMs through per-tile counters
                 sc = self.scratch[i]
@@ -186,8 +196,14 @@ class SymmBuffer:
     """Symmetric input/output block of the fused MoE forward; construction is collective."""
 
     def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
-                 intermediate_hidden: int, *, rank: Optional[int] = None, world_size: Optional[int] = None, device=None,
+                 intermediate_hidden: int, *, num_shared_experts: int = 0, mma_type: str = "fp8xfp4", activation: str = "swiglu",
+                 rank: Optional[int] = None, world_size: Optional[int] = None, device=None,
                  num_gpu_timeout_secs: float = 100, num_sms: int = 0):
+        if mma_type != "fp8xfp4":
+            raise NotImplementedError("only e4m3 activations x e2m1 weights (mma_type='fp8xfp4') are implemented; "
+                                      "'fp8xfp8' weights are not")
+        if activation != "swiglu":
+            raise NotImplementedError("only SwiGLU is implemented")
         from ..parallel.runtime import ControlPlane, Runtime
 
         C = require_native("MegaMoE SymmBuffer")
@@ -196,11 +212,14 @@ class SymmBuffer:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.num_experts, self.num_topk, self.hidden, self.intermediate_hidden = num_experts, num_topk, hidden, intermediate_hidden
         self.num_max_tokens_per_rank = num_max_tokens_per_rank
-        mega = MegaEngine.mega_bytes(C, num_max_tokens_per_rank, hidden, num_topk)
+        self.num_shared_experts, self.mma_type = int(num_shared_experts), mma_type
+        mega = MegaEngine.mega_bytes(C, num_max_tokens_per_rank, hidden, num_topk, self.num_shared_experts)
         # the generic regions are sized for one token: this buffer only uses the fused-MoE region
         self.layout = C.make_mega_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, mega)
         self.runtime = Runtime(self.control, self.layout, float(num_gpu_timeout_secs), self.device)
-        self.engine = MegaEngine([self.runtime.native], self.layout, self.device, num_experts, intermediate_hidden, num_sms)
+        self.engine = MegaEngine([self.runtime.native], self.layout, self.device, num_experts, intermediate_hidden, num_sms,
+                                 self.num_shared_experts)
+        self._joined: dict = {}          # routed + shared weights joined once per weight set
         self.x, self.x_sf, self.topk_idx, self.topk_weights = self.engine.input_views(0)
         self.batch_size = 0
         self._destroyed = False
@@ -238,6 +257,25 @@ class SymmBuffer:
         self.topk_weights[:bs].copy_(topk_weights.float())
         return self.prepare(bs)
 
+    def allocate_timer(self) -> torch.Tensor:
+        """A zeroed int64 ``[SMs, words]`` tensor for ``fp8_fp4_mega_moe(..., timer=...)``: the kernel writes one record
+        of phase stamps per CTA; ``mega_tools.parse_timer`` turns it into a per-phase breakdown.
+        Parity: ``SymmBuffer.allocate_timer`` (``api.py:226-233`` of the reference)."""
+        C = require_native("MegaMoE timer")
+        return torch.zeros((self.engine.sm_count, C.mega_timer_words), dtype=torch.int64, device=self.device)
+
+    def joined_weights(self, routed: MegaWeights, shared: Optional[MegaWeights]) -> MegaWeights:
+        """Routed experts followed by the shared ones in one operand (the kernel sees them as extra local experts)."""
+        if shared is None:
+            return routed
+        key = (routed.packed.data_ptr(), shared.packed.data_ptr())
+        if key not in self._joined:
+            if (shared.n, shared.k) != (routed.n, routed.k):
+                raise ValueError("shared experts must have the shapes of the routed experts")
+            self._joined[key] = MegaWeights(torch.cat([routed.packed, shared.packed]), torch.cat([routed.sf_chunks, shared.sf_chunks]),
+                                            routed.experts + shared.experts, routed.n, routed.k)
+        return self._joined[key]
+
     def validate_inputs(self, batch_size: int) -> None:
         idx = self.topk_idx[:batch_size]
         if bool(((idx >= self.num_experts)).any()):
@@ -251,41 +289,82 @@ class SymmBuffer:
             self.runtime.close()
 
 
-def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaWeights, sym_buffer: SymmBuffer, *,
-                     batch_size: Optional[int] = None, fused: bool = True, shared_weights=None, recipe=(1, 1, 32), activation: str = "swiglu",
-                     activation_clamp=None, fast_math: bool = True, timer=None) -> torch.Tensor:
-    """Fused MoE forward; overwrites ``y[:bs]`` (bf16 ``[bs, hidden]``) and returns it."""
-    del fast_math, timer
-    if shared_weights is not None:
-        raise NotImplementedError("shared-expert weights are not fused; run the shared expert as a separate dense layer")
+def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaWeights, sym_buffer: SymmBuffer,
+                     shared_l1_weights: Optional[MegaWeights] = None, shared_l2_weights: Optional[MegaWeights] = None,
+                     cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None, recipe=(1, 1, 32),
+                     activation: str = "swiglu", activation_clamp=None, fast_math: bool = True, *, x: Optional[torch.Tensor] = None,
+                     timer: Optional[torch.Tensor] = None, fused: bool = True, check: bool = False) -> None:
+    """Fused MoE forward; overwrites ``y`` (bf16 ``[bs, hidden]``, ``bs = y.shape[0]``) in place and returns ``None``.
+
+    The positional parameters follow the reference (``api.py:520-535``).  Inputs are read from ``sym_buffer.x`` /
+    ``x_sf`` / ``topk_idx`` / ``topk_weights`` unless ``x`` (bf16 ``[bs, hidden]``) is given, which the kernel quantises
+    to MXFP8 itself.  ``shared_l1_weights`` / ``shared_l2_weights`` (both or neither; transformed like the routed
+    weights) are the rank's shared experts: every token passes through them with weight one.
+    ``cumulative_local_expert_recv_stats`` (int32 ``[experts per rank]``) is incremented by the rows every routed
+    local expert received.  ``timer``: see ``SymmBuffer.allocate_timer``.  ``check=True`` synchronises and raises if a
+    wait inside the kernel ran out.
+    """
     if tuple(recipe) != (1, 1, 32):
         raise NotImplementedError("the tensor-core path consumes one ue8m0 scale per 32 values: recipe must be (1, 1, 32)")
-    if activation != "swiglu" or activation_clamp is not None:
-        raise NotImplementedError("only unclamped SwiGLU is implemented")
+    if activation != "swiglu" or activation_clamp is not None or fast_math is not True:
+        raise NotImplementedError("only unclamped SwiGLU with the default math is implemented")
+    if not isinstance(sym_buffer, SymmBuffer):
+        raise TypeError("sym_buffer must be a SymmBuffer of this library")
     if not isinstance(l1_weights, MegaWeights) or not isinstance(l2_weights, MegaWeights):
         raise TypeError("pass the weights through transform_weights_for_mega_moe first")
-    bs = sym_buffer.batch_size if batch_size is None else batch_size
-    if y.dtype != torch.bfloat16 or y.dim() != 2 or y.shape[1] != sym_buffer.hidden or y.shape[0] < bs or not y.is_contiguous():
-        raise ValueError("y must be a contiguous bf16 [>= batch, hidden] tensor")
+    if (shared_l1_weights is None) != (shared_l2_weights is None):
+        raise ValueError("supply both shared weight pairs, or neither")
+    shared = 0 if shared_l1_weights is None else shared_l1_weights.experts
+    if shared != sym_buffer.num_shared_experts:
+        raise ValueError("the shared expert count does not match the buffer's num_shared_experts")
+    if y.dtype != torch.bfloat16 or y.dim() != 2 or y.shape[1] != sym_buffer.hidden or not y.is_contiguous():
+        raise ValueError("y must be a contiguous bf16 [batch, hidden] tensor")
+    bs = y.shape[0]
+    if not 0 < bs <= sym_buffer.num_max_tokens_per_rank:
+        raise ValueError("the batch must be non-empty and fit the buffer")
+    if x is not None and (x.dtype != torch.bfloat16 or tuple(x.shape) != (bs, sym_buffer.hidden) or not x.is_contiguous()):
+        raise ValueError("the x override must be contiguous bf16 [batch, hidden]; omit x for buffered fp8 input")
     if l1_weights.k != sym_buffer.hidden or l1_weights.n != 2 * sym_buffer.intermediate_hidden:
         raise ValueError("l1 weights do not match the buffer's hidden / intermediate sizes")
     if l1_weights.experts * sym_buffer.world_size != sym_buffer.num_experts:
         raise ValueError("each rank must hold num_experts / world_size experts")
-    sym_buffer.engine.forward([y], [bs], [l1_weights], [l2_weights], fused=fused)
-    return y
+    stats = cumulative_local_expert_recv_stats
+    local = sym_buffer.num_experts // sym_buffer.world_size
+    if stats is not None and (stats.dtype != torch.int32 or tuple(stats.shape) != (local,) or stats.device != y.device
+                              or not stats.is_contiguous()):
+        raise ValueError("cumulative stats must be contiguous int32 [experts per rank] on the buffer's device")
+    if timer is not None and (not fused or timer.dtype != torch.int64 or not timer.is_contiguous()):
+        raise ValueError("timer must come from SymmBuffer.allocate_timer() and needs the fused kernel")
+    engine = sym_buffer.engine
+    engine.forward([y], [bs], [sym_buffer.joined_weights(l1_weights, shared_l1_weights)],
+                   [sym_buffer.joined_weights(l2_weights, shared_l2_weights)], fused=fused,
+                   x_bf16=None if x is None else [x], timer=timer)
+    if stats is not None:
+        stats.add_(engine.scratch[0]["expert_rows"][:local])
+    if check:
+        torch.cuda.synchronize(sym_buffer.device)
+        engine.check()
+    return None
 
 
-def mega_moe(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, l1_weights: MegaWeights,
-             l2_weights: MegaWeights, sym_buffer: SymmBuffer) -> torch.Tensor:
-    """Convenience wrapper: quantise bf16 ``x`` to MXFP8, fill the symmetric inputs, run the fused forward."""
-    bs = x.shape[0]
-    codes, sf = quantize_mxfp8_cuda(x)
+def mega_moe(x, topk_idx: torch.Tensor, topk_weights: torch.Tensor, l1_weights: MegaWeights,
+             l2_weights: MegaWeights, sym_buffer: SymmBuffer, *, shared_l1_weights: Optional[MegaWeights] = None,
+             shared_l2_weights: Optional[MegaWeights] = None, out: Optional[torch.Tensor] = None,
+             timer: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Explicit-input convenience API (parity: ``mega_moe``, ``api.py:380-412``): ``x`` is bf16 ``[bs, hidden]`` (quantised
+    to MXFP8 here) or an ``(e4m3, ue8m0)`` pair that is copied as is; fills the symmetric inputs and runs the fused forward."""
+    if isinstance(x, (tuple, list)):
+        codes, sf = x
+    else:
+        codes, sf = quantize_mxfp8_cuda(x)
+    bs = codes.shape[0]
     sym_buffer.x[:bs].copy_(codes)
     sym_buffer.x_sf[:bs].copy_(sf)
     sym_buffer.topk_idx[:bs].copy_(topk_idx.to(torch.int32))
     sym_buffer.topk_weights[:bs].copy_(topk_weights.float())
-    y = torch.empty((bs, sym_buffer.hidden), dtype=torch.bfloat16, device=x.device)
-    return fp8_fp4_mega_moe(y, l1_weights, l2_weights, sym_buffer.prepare(bs))
+    y = torch.empty((bs, sym_buffer.hidden), dtype=torch.bfloat16, device=codes.device) if out is None else out
+    fp8_fp4_mega_moe(y, l1_weights, l2_weights, sym_buffer.prepare(bs), shared_l1_weights, shared_l2_weights, timer=timer)
+    return y
 
 
 def quantize_mxfp8_cuda(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -92,6 +92,35 @@ def compare(actual: torch.Tensor, expected: torch.Tensor, *, diff_thd: float = 0
     return m
 
 
+# ------------------------------------------------------------------------------------------------ device timer
+TIMER_SLOTS = ("start", "handshake", "layout", "pull", "gemm", "finish_sync", "end")
+
+
+def parse_timer(timer: torch.Tensor) -> Dict[str, float]:
+    """Per-phase breakdown of one fused-kernel launch from the records of ``SymmBuffer.allocate_timer()``.
+
+    Every CTA stamps ``%globaltimer`` at: kernel start, inputs quantised + handshake done, routing layout done, its pull
+    warps done, its GEMM tile loop done, finish handshake done, end.  The result holds, in microseconds, the time
+    from the earliest start to the latest stamp of each boundary (so the phases add up to ``total_us``), plus the
+    spread of the CTAs' GEMM end (``gemm_tail_us``: how long the slowest CTA worked after the fastest was done).
+    Parity: the reference's timer tooling (``timer/protocol.py``, ``timer/parse_timer_csv.py``, ``timer/breakdown.py``).
+    """
+    rec = timer.detach().cpu().to(torch.int64)
+    rec = rec[rec[:, 0] > 0]
+    if rec.numel() == 0:
+        return dict(ctas=0, total_us=0.0)
+    t0 = int(rec[:, 0].min())
+    last = {name: (int(rec[:, i][rec[:, i] > 0].max()) - t0) / 1e3 if bool((rec[:, i] > 0).any()) else 0.0
+            for i, name in enumerate(TIMER_SLOTS)}
+    gemm_ends = rec[:, 4][rec[:, 4] > 0]
+    out = dict(ctas=int(rec.shape[0]), total_us=last["end"],
+               handshake_us=last["handshake"], layout_us=max(0.0, last["layout"] - last["handshake"]),
+               pull_done_us=last["pull"], gemm_us=max(0.0, last["gemm"] - last["layout"]),
+               finish_sync_us=max(0.0, last["finish_sync"] - last["gemm"]), reduce_us=max(0.0, last["end"] - last["finish_sync"]),
+               gemm_tail_us=(int(gemm_ends.max()) - int(gemm_ends.min())) / 1e3 if gemm_ends.numel() else 0.0)
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ goldens
 def contract(*, world: int, tokens: Sequence[int], hidden: int, intermediate: int, experts: int, topk: int, seed: int,
              routing: str = "random") -> Dict:

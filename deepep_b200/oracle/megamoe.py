@@ -63,10 +63,14 @@ def expert_forward(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch
 
 
 def mega_moe_reference(xs: Sequence[Tuple[torch.Tensor, torch.Tensor]], topk_idx: Sequence[torch.Tensor],
-                       topk_w: Sequence[torch.Tensor], l1, l2, num_experts: int) -> List[torch.Tensor]:
-    """All-rank forward.  xs[r] = (e4m3 [T, H], ue8m0 [T, H / 32]); l1/l2 = (packed, scales) for all experts."""
+                       topk_w: Sequence[torch.Tensor], l1, l2, num_experts: int, shared_l1=None, shared_l2=None) -> List[torch.Tensor]:
+    """All-rank forward.  xs[r] = (e4m3 [T, H], ue8m0 [T, H / 32]); l1/l2 = (packed, scales) for all experts.
+    ``shared_l1`` / ``shared_l2``: weights of the shared experts (the same on every rank); every token passes through
+    each of them with weight one, after its routed experts (``golden.py:160-165`` of the reference)."""
     w1 = unpack_fp4(*l1)
     w2 = unpack_fp4(*l2)
+    s1 = None if shared_l1 is None else unpack_fp4(*shared_l1)
+    s2 = None if shared_l2 is None else unpack_fp4(*shared_l2)
     outs = []
     for (codes, sf), idx, w in zip(xs, topk_idx, topk_w):
         x = dequantize_mxfp8(codes, sf)
@@ -77,6 +81,9 @@ def mega_moe_reference(xs: Sequence[Tuple[torch.Tensor, torch.Tensor]], topk_idx
                     continue
                 tok = (idx[:, k] == e).nonzero(as_tuple=True)[0]
                 y[tok] += w[tok, k].float().unsqueeze(1) * expert_forward(x[tok], w1[e], w2[e])
+        if s1 is not None and x.shape[0]:
+            for e in range(s1.shape[0]):
+                y += expert_forward(x, s1[e], s2[e])
         outs.append(y.bfloat16())
     return outs
 
