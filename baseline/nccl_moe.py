@@ -5,9 +5,10 @@
   local gather; the way back pre-reduces a token's rows on the expert rank (fp32 accumulate, bf16 on the wire) and
   reduces the per-rank partials at the source.  Every index tensor and split size is computed once in ``plan`` --
   nothing inside ``dispatch`` / ``combine`` / ``moe_forward`` synchronises with the host.
-* experts: one grouped GEMM per projection over expert-major rows (``torch._grouped_mm``, bf16; ``fp8=True`` uses
-  ``torch._scaled_grouped_mm`` with row-wise scales when this PyTorch build has it for the device), SwiGLU in eager
-  PyTorch.  If the grouped kernels are missing, a per-expert ``torch.matmul`` loop over host-side counts is used.
+* experts: one grouped GEMM per projection over expert-major rows (``torch._grouped_mm``, bf16), SwiGLU in eager
+  PyTorch.  If the grouped kernel is missing or does not run on this device (``select_gemm`` probes it in a child
+  process), a per-expert ``torch.matmul`` (cuBLAS) loop over host-side counts is used.  There is no fp8 variant: the
+  row-wise scaled grouped GEMM of this PyTorch build is compiled for another architecture and aborts on sm_100.
 
 Nothing here is used by the product path.  With a world size of 1 the collectives degenerate to local copies,
 which is still the honest single-GPU cost of this formulation.
@@ -92,22 +93,13 @@ class NcclExpertParallel:
         return out.to(torch.bfloat16)
 
 
-_grouped_ok: Optional[bool] = None
-_fp8_grouped_ok: Optional[bool] = None
+_grouped_ok: Optional[bool] = False      # set by select_gemm(); the per-expert loop until then
 
 
 def _grouped_mm(rows: torch.Tensor, weight_t: torch.Tensor, plan: BaselinePlan) -> torch.Tensor:
     """rows [R, K] bf16 x weight_t [L, K, N] bf16 -> [R, N]; expert e owns rows offsets[e-1]..offsets[e]."""
-    global _grouped_ok
-    if _grouped_ok is not False and hasattr(torch, "_grouped_mm"):
-        try:
-            out = torch._grouped_mm(rows, weight_t, offs=plan.expert_offsets)
-            _grouped_ok = True
-            return out
-        except (RuntimeError, NotImplementedError):
-            if _grouped_ok:
-                raise
-            _grouped_ok = False
+    if _grouped_ok:
+        return torch._grouped_mm(rows, weight_t, offs=plan.expert_offsets)
     out = torch.empty((rows.shape[0], weight_t.shape[2]), dtype=rows.dtype, device=rows.device)
     start = 0
     for e, c in enumerate(plan.expert_counts):
@@ -117,58 +109,47 @@ def _grouped_mm(rows: torch.Tensor, weight_t: torch.Tensor, plan: BaselinePlan) 
     return out
 
 
-def _rowwise_fp8(t: torch.Tensor, dim: int):
-    amax = t.float().abs().amax(dim=dim, keepdim=True).clamp(min=1e-4)
-    scale = amax / 448.0
-    return (t.float() / scale).to(torch.float8_e4m3fn), scale
-
-
-def _grouped_mm_fp8(rows: torch.Tensor, weight_q: torch.Tensor, weight_scale: torch.Tensor, plan: BaselinePlan) -> torch.Tensor:
-    """fp8 x fp8 grouped GEMM with row-wise scales (activations quantised per row on the fly, weights beforehand)."""
-    q, s = _rowwise_fp8(rows, 1)
-    return torch._scaled_grouped_mm(q, weight_q, s.squeeze(1), weight_scale, offs=plan.expert_offsets, out_dtype=torch.bfloat16,
-                                    use_fast_accum=True)
-
-
 class ExpertWeights:
     """SwiGLU expert weights in the layouts the library GEMMs want: w1 [L, 2I, H], w2 [L, H, I] bf16."""
 
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor):
         self.w1_t, self.w2_t = w1.transpose(1, 2), w2.transpose(1, 2)          # [L, K, N] views, K-major memory
-        self.fp8 = None
-
-    def quantize(self) -> bool:
-        """Prepare the fp8 variant; False when this PyTorch build has no fp8 grouped GEMM for the device."""
-        global _fp8_grouped_ok
-        if _fp8_grouped_ok is False or not hasattr(torch, "_scaled_grouped_mm"):
-            return False
-        try:
-            q1, s1 = _rowwise_fp8(self.w1_t.transpose(1, 2), 2)                # scales per output column: [L, N, 1]
-            q2, s2 = _rowwise_fp8(self.w2_t.transpose(1, 2), 2)
-            self.fp8 = (q1.transpose(1, 2), s1.squeeze(2), q2.transpose(1, 2), s2.squeeze(2))
-            probe = BaselinePlan(0, None, [], [], None, torch.full((q1.shape[0],), 16, dtype=torch.int32, device=q1.device).cumsum(0).to(torch.int32),
-                                 [16] * q1.shape[0], None, 0)
-            _grouped_mm_fp8(torch.zeros((16 * q1.shape[0], q1.shape[2]), dtype=torch.bfloat16, device=q1.device), self.fp8[0],
-                            self.fp8[1], probe)
-            _fp8_grouped_ok = True
-        except (RuntimeError, NotImplementedError, TypeError):
-            self.fp8, _fp8_grouped_ok = None, False
-        return self.fp8 is not None
 
 
-def expert_ffn(rows: torch.Tensor, plan: BaselinePlan, weights: ExpertWeights, fp8: bool = False) -> torch.Tensor:
+def expert_ffn(rows: torch.Tensor, plan: BaselinePlan, weights: ExpertWeights) -> torch.Tensor:
     """SwiGLU experts on expert-major rows."""
-    if fp8:
-        h = _grouped_mm_fp8(rows, weights.fp8[0], weights.fp8[1], plan)
-    else:
-        h = _grouped_mm(rows, weights.w1_t, plan)
-    gate, up = h.chunk(2, dim=-1)
-    act = torch.nn.functional.silu(gate) * up
-    if fp8:
-        return _grouped_mm_fp8(act, weights.fp8[2], weights.fp8[3], plan)
-    return _grouped_mm(act, weights.w2_t, plan)
+    gate, up = _grouped_mm(rows, weights.w1_t, plan).chunk(2, dim=-1)
+    return _grouped_mm(torch.nn.functional.silu(gate) * up, weights.w2_t, plan)
 
 
-def moe_forward(ep: NcclExpertParallel, x: torch.Tensor, plan: BaselinePlan, weights: ExpertWeights, fp8: bool = False) -> torch.Tensor:
+def moe_forward(ep: NcclExpertParallel, x: torch.Tensor, plan: BaselinePlan, weights: ExpertWeights) -> torch.Tensor:
     """One MoE layer from a prepared plan: dispatch -> grouped SwiGLU experts -> weighted combine."""
-    return ep.combine(expert_ffn(ep.dispatch(x, plan), plan, weights, fp8), plan, weighted=True)
+    return ep.combine(expert_ffn(ep.dispatch(x, plan), plan, weights), plan, weighted=True)
+
+
+_PROBE = """
+import torch
+a = torch.randn(96, 64, device='cuda', dtype=torch.bfloat16)
+b = torch.randn(3, 64, 32, device='cuda', dtype=torch.bfloat16)
+offs = torch.tensor([32, 32, 96], device='cuda', dtype=torch.int32)
+out = torch._grouped_mm(a, b, offs=offs)
+torch.cuda.synchronize()
+ref = torch.cat([a[:32] @ b[0], a[32:32] @ b[1], a[32:] @ b[2]])
+assert torch.allclose(out.float(), ref.float(), rtol=0.05, atol=0.5)
+"""
+
+
+def select_gemm(use_grouped: Optional[bool] = None) -> bool:
+    """Chooses between the library's grouped GEMM and the per-expert loop; returns whether the grouped one is used.
+
+    ``None`` probes ``torch._grouped_mm`` in a child process (a library kernel built for another architecture aborts the
+    process that launches it, which must not be the benchmark itself); the caller passes the result to the other ranks."""
+    global _grouped_ok
+    if use_grouped is None:
+        import subprocess
+        import sys
+
+        use_grouped = hasattr(torch, "_grouped_mm") and torch.cuda.is_available() and \
+            subprocess.run([sys.executable, "-c", _PROBE], capture_output=True, timeout=300).returncode == 0
+    _grouped_ok = bool(use_grouped)
+    return _grouped_ok
