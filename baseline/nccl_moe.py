@@ -127,29 +127,13 @@ def moe_forward(ep: NcclExpertParallel, x: torch.Tensor, plan: BaselinePlan, wei
     return ep.combine(expert_ffn(ep.dispatch(x, plan), plan, weights), plan, weighted=True)
 
 
-_PROBE = """
-import torch
-a = torch.randn(96, 64, device='cuda', dtype=torch.bfloat16)
-b = torch.randn(3, 64, 32, device='cuda', dtype=torch.bfloat16)
-offs = torch.tensor([32, 32, 96], device='cuda', dtype=torch.int32)
-out = torch._grouped_mm(a, b, offs=offs)
-torch.cuda.synchronize()
-ref = torch.cat([a[:32] @ b[0], a[32:32] @ b[1], a[32:] @ b[2]])
-assert torch.allclose(out.float(), ref.float(), rtol=0.05, atol=0.5)
-"""
-
-
 def select_gemm(use_grouped: Optional[bool] = None) -> bool:
     """Chooses between the library's grouped GEMM and the per-expert loop; returns whether the grouped one is used.
 
     ``None`` probes ``torch._grouped_mm`` in a child process (a library kernel built for another architecture aborts the
     process that launches it, which must not be the benchmark itself); the caller passes the result to the other ranks."""
     global _grouped_ok
-    if use_grouped is None:
-        import subprocess
-        import sys
+    from deepep_b200.utils.grouped_mm import grouped_mm_usable
 
-        use_grouped = hasattr(torch, "_grouped_mm") and torch.cuda.is_available() and \
-            subprocess.run([sys.executable, "-c", _PROBE], capture_output=True, timeout=300).returncode == 0
-    _grouped_ok = bool(use_grouped)
+    _grouped_ok = grouped_mm_usable(use_grouped)
     return _grouped_ok

@@ -191,6 +191,40 @@ def bench_mega_moe(group, world, rank, dev, timed):
     return out
 
 
+def bench_training(group, world, rank, dev, timed):
+    """MoE layer training step (forward + backward by handle reversal), all bf16: 8192 tokens per rank, hidden 4096,
+    64 experts, top-6, SwiGLU experts with intermediate size 1536 (Kaiming-uniform init)."""
+    from deepep_b200 import ElasticBuffer
+    from deepep_b200.models.moe_layer import ExpertParallelMoE
+    from deepep_b200.utils.grouped_mm import grouped_mm_usable
+
+    T, H, E, K, I = 8192, 4096, 64, 6, 1536
+    usable = [grouped_mm_usable() if rank == 0 else None]
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.broadcast_object_list(usable, src=0, group=group)
+        grouped_mm_usable(usable[0])
+    g = torch.Generator().manual_seed(900 + rank)
+    x = torch.randn((T, H), generator=g).bfloat16().to(dev).requires_grad_()
+    idx = torch.rand((T, E), generator=g).topk(K, dim=1).indices.to(torch.int64).to(dev)
+    w = torch.softmax(torch.randn((T, K), generator=g), dim=1).to(dev).requires_grad_()
+    grad = torch.randn((T, H), generator=g).bfloat16().to(dev)
+    buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True)
+    layer = ExpertParallelMoE(buf, E, H, I, device=dev)
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        x.grad = w.grad = None
+        layer(x, idx, w).backward(grad)
+
+    out = {"moe_train_fwd_bwd_us": timed(step, 3), "moe_train_grouped_gemm": bool(usable[0])}
+    out["moe_train_tokens_per_s"] = world * T / (out["moe_train_fwd_bwd_us"] * 1e-6)
+    out["moe_train_grads_finite"] = bool(torch.isfinite(x.grad.float()).all() and torch.isfinite(w.grad).all())
+    buf.destroy()
+    return out
+
+
 def bench_baseline(group, world, rank, dev, timed, x, idx, w, E):
     """NCCL all-to-all(v) dispatch+combine (rank-level dedup, plan built once) and the NCCL + grouped-GEMM MoE layer on the
     same shapes in bf16 (comparison only)."""
@@ -339,6 +373,10 @@ def main():
             extras.update(bench_mega_moe(group, world, rank, dev, timed))
         except Exception as exc:
             extras["mega_moe_error"] = repr(exc)[:200]
+        try:
+            extras.update(bench_training(group, world, rank, dev, timed))
+        except Exception as exc:
+            extras["training_error"] = repr(exc)[:200]
         try:
             extras.update(bench_baseline(group, world, rank, dev, timed, x, idx, w, E))
         except Exception as exc:

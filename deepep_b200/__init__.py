@@ -3,7 +3,7 @@
 Importing the package loads neither torch nor the native extension; the public
 names resolve on first use (parity: ``deep_ep/__init__.py:11-25`` of the reference).
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 __all__ = ["Buffer", "ElasticBuffer", "EPHandle", "Config", "EventHandle", "EventOverlap"]
 
@@ -15,6 +15,10 @@ _LAZY = {
     "EventHandle": ("deepep_b200.utils.event", "EventHandle"),
     "EventOverlap": ("deepep_b200.utils.event", "EventOverlap"),
     "topk_idx_t": ("deepep_b200.buffer", "topk_idx_t"),
+    "Handle": ("deepep_b200.resources", "Handle"),
+    "Slot": ("deepep_b200.resources", "Slot"),
+    "SlotState": ("deepep_b200.resources", "SlotState"),
+    "ExpandHandle": ("deepep_b200.ops.expand", "ExpandHandle"),
 }
 
 

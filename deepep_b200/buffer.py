@@ -1,11 +1,13 @@
 """``Buffer``: upstream DeepEP's V1 interface (``get_dispatch_layout`` / ``dispatch`` / ``combine``).
 
 Parity: ``deep_ep/backends/direct/buffer.py`` of the reference (``get_dispatch_layout`` :420-463,
-``dispatch`` :465-680, ``combine`` :682-751, ``expand`` :753-873, ``aggregate`` :875-918, config getters, ``capture``, ``get_comm_stream``) and
-``deep_ep/buffer.py:8-16``.  The V1 layout is the rank layout of :class:`ElasticBuffer`
-(``do_expand=False``): one received row per (source rank, token), ``recv_topk_idx`` holding local
-expert ids.  Internode and the V1 low-latency entry points belong to multi-node RDMA deployments and
-raise ``NotImplementedError``; decode-size batches use ``ElasticBuffer``'s low-latency path.
+``dispatch`` :465-680 with the six-tensor handle, ``num_worst_tokens`` and the graph-capture guard :496-515,
+``combine`` :682-751, ``expand`` :753-873, ``aggregate`` :875-918, config getters, ``capture``, ``get_comm_stream``),
+``deep_ep/backends/direct/resources.py`` (slot life cycle, generation-checked handle) and ``deep_ep/buffer.py:8-16``.
+The V1 layout is the rank layout of :class:`ElasticBuffer` (``do_expand=False``): one received row per (source rank,
+token), ``recv_topk_idx`` holding local expert ids.  ``get_dispatch_layout`` is its own small kernel (``ep_layout``).
+Internode and the V1 low-latency entry points belong to multi-node RDMA deployments and raise
+``NotImplementedError``; decode-size batches use ``ElasticBuffer``'s low-latency path.
 """
 from __future__ import annotations
 
@@ -15,6 +17,7 @@ import torch
 
 from .config import Config
 from .parallel.elastic import ElasticBuffer
+from .resources import Handle, SlotPool, SlotState
 from .utils.event import EventHandle, EventOverlap
 
 topk_idx_t = torch.int64
@@ -37,6 +40,7 @@ class Buffer:
         self.group, self.num_nvl_bytes, self.explicitly_destroy = group, num_nvl_bytes, explicitly_destroy
         self._shape = (num_max_tokens_per_rank, hidden, num_topk)
         self._elastic: Optional[ElasticBuffer] = None
+        self._slots = SlotPool()
         if all(self._shape):
             self._ensure(*self._shape)
 
@@ -90,51 +94,118 @@ class Buffer:
     # ------------------------------------------------------------------ V1 operations
     def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: int, previous_event=None, async_finish: bool = False,
                             allocate_on_comm_stream: bool = False):
-        """(num_tokens_per_rank, num_tokens_per_rdma_rank=None, num_tokens_per_expert, is_token_in_rank, event)."""
+        """(num_tokens_per_rank, num_tokens_per_rdma_rank=None, num_tokens_per_expert, is_token_in_rank, event).
+
+        On a GPU this is the ``ep_layout`` kernel; on CPU tensors the same counts in torch."""
         del allocate_on_comm_stream
         world = 1 if self.group is None else torch.distributed.get_world_size(self.group)
-        if previous_event is not None and previous_event.event is not None:
+        if topk_idx.dim() != 2 or topk_idx.dtype != torch.int64 or not topk_idx.is_contiguous():
+            raise ValueError("topk_idx must be contiguous int64 [tokens, top-k]")
+        if num_experts <= 0 or num_experts % world or num_experts > 1024:
+            raise ValueError("num_experts must be a positive multiple of the world size, at most 1024")
+        if previous_event is not None and getattr(previous_event, "event", None) is not None:
             previous_event.current_stream_wait()
+        T, K = topk_idx.shape
+        if topk_idx.is_cuda:
+            from .ops import require_native
+
+            C = require_native("Buffer.get_dispatch_layout")
+            dev = topk_idx.device
+            per_rank = torch.zeros((world,), dtype=torch.int32, device=dev)
+            per_expert = torch.zeros((num_experts,), dtype=torch.int32, device=dev)
+            in_rank = torch.empty((T, world), dtype=torch.bool, device=dev)
+            C.layout(topk_idx.data_ptr(), T, K, num_experts, world, per_rank.data_ptr(), per_expert.data_ptr(), in_rank.data_ptr(),
+                     torch.cuda.current_stream(dev).cuda_stream)
+            event = EventOverlap._from_resources(EventHandle(), (per_rank, per_expert, in_rank, topk_idx)) if async_finish \
+                else EventOverlap()
+            return per_rank, None, per_expert, in_rank, event
         local = num_experts // world
         valid = (topk_idx >= 0) & (topk_idx < num_experts)
         dst = torch.where(valid, torch.div(topk_idx, local, rounding_mode="floor"), torch.full_like(topk_idx, -1))
         in_rank = torch.stack([(dst == r).any(dim=1) for r in range(world)], dim=1)
         per_expert = torch.bincount(topk_idx[valid], minlength=num_experts).to(torch.int32)
-        event = EventOverlap(EventHandle()) if async_finish else EventOverlap()
-        return in_rank.sum(0).to(torch.int32), None, per_expert, in_rank, event
+        return in_rank.sum(0).to(torch.int32), None, per_expert, in_rank, EventOverlap()
+
+    def _v1_handle(self, eh, in_rank: Optional[torch.Tensor], tokens: int) -> Handle:
+        """Upstream's six handle tensors from the routing plan of the dispatch, bound to a slot."""
+        plan = eh._plan
+        tmax, K = self._elastic.num_max_tokens_per_rank, self._elastic.num_topk
+        rank_prefix = torch.cumsum(plan.rank_matrix.to(torch.int64), dim=0).to(torch.int32)
+        recv_src_idx = (torch.div(plan.recv_row_src[:plan.num_rows], K, rounding_mode="floor") % tmax).to(torch.int32)
+        send_head = plan.send_slot[:tokens]
+        if in_rank is None:
+            in_rank = send_head >= 0
+        slot = self._slots.acquire()
+        slot.move(SlotState.DISPATCH_IN_FLIGHT)
+        slot.move(SlotState.DISPATCH_READY)
+        return Handle((rank_prefix, plan.send_chunk_prefix, plan.chunk_start, recv_src_idx, in_rank, send_head), slot, eh)
 
     def dispatch(self, x, handle=None, num_tokens_per_rank=None, num_tokens_per_rdma_rank=None, is_token_in_rank=None,
                  num_tokens_per_expert=None, topk_idx=None, topk_weights=None, expert_alignment: int = 1, num_worst_tokens: int = 0,
                  config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
                  allocate_on_comm_stream: bool = False):
-        """(recv_x, recv_topk_idx, recv_topk_weights, num_recv_tokens_per_expert_list, handle, event)."""
-        del num_tokens_per_rank, num_tokens_per_rdma_rank, is_token_in_rank
-        if expert_alignment != 1:
-            raise NotImplementedError("expert_alignment applies to the expanded layout: use ElasticBuffer(do_expand=True)")
+        """(recv_x, recv_topk_idx, recv_topk_weights, num_recv_tokens_per_expert_list, handle, event).
+
+        ``expert_alignment`` rounds the per-expert counts of the returned list up (the rows themselves keep the rank
+        layout).  ``num_worst_tokens > 0`` gives outputs of exactly that many rows without any host synchronisation
+        (the list is empty then); it must equal ``group size x num_max_tokens_per_rank`` and is required while the
+        current stream is being captured into a CUDA graph."""
+        del num_tokens_per_rank, num_tokens_per_rdma_rank
+        if expert_alignment < 1:
+            raise ValueError("expert_alignment must be positive")
         data = x[0] if isinstance(x, (tuple, list)) else x
         sms = config.num_sms if config is not None else 0
+        capturing = data.is_cuda and torch.cuda.is_current_stream_capturing()
         if handle is not None:
+            if not isinstance(handle, Handle):
+                raise TypeError("handle must come from Buffer.dispatch")
+            handle.check_live()
             eb = self._ensure(data.shape[0], data.shape[1], handle.topk_idx.shape[1])
-            rx, _, _, h, ev = eb.dispatch(x, handle=handle, num_sms=sms, previous_event=previous_event,
+            handle.slot.move(SlotState.DISPATCH_IN_FLIGHT)
+            rx, _, _, _, ev = eb.dispatch(x, handle=handle.elastic, num_sms=sms, previous_event=previous_event,
                                           async_with_compute_stream=async_finish, allocate_on_comm_stream=allocate_on_comm_stream)
-            return rx, None, None, None, h, ev
+            handle.slot.move(SlotState.DISPATCH_READY)
+            return rx, None, None, None, handle, ev
         if topk_idx is None or num_tokens_per_expert is None:
             raise ValueError("a fresh V1 dispatch needs topk_idx and num_tokens_per_expert (from get_dispatch_layout)")
         eb = self._ensure(data.shape[0], data.shape[1], topk_idx.shape[1])
+        if capturing and num_worst_tokens == 0:
+            raise RuntimeError("a fresh dispatch inside a CUDA graph capture cannot read the row count back: pass num_worst_tokens")
+        if num_worst_tokens and num_worst_tokens != eb.world_size * eb.num_max_tokens_per_rank:
+            raise ValueError(f"num_worst_tokens must be group size x num_max_tokens_per_rank = "
+                             f"{eb.world_size * eb.num_max_tokens_per_rank}")
         rx, ridx, rw, h, ev = eb.dispatch(x, topk_idx=topk_idx, topk_weights=topk_weights, num_experts=num_tokens_per_expert.numel(),
                                           num_sms=sms, previous_event=previous_event, async_with_compute_stream=async_finish,
                                           allocate_on_comm_stream=allocate_on_comm_stream, do_expand=False,
-                                          do_cpu_sync=(num_worst_tokens == 0), num_max_tokens_per_rank=10 ** 9)
-        return rx, ridx, rw, h.num_recv_tokens_per_expert_list, h, ev
+                                          do_cpu_sync=(num_worst_tokens == 0), num_max_tokens_per_rank=10 ** 9, _rank_matrix=True)
+        counts = h.num_recv_tokens_per_expert_list
+        if counts is not None and expert_alignment > 1:
+            counts = [-(-c // expert_alignment) * expert_alignment for c in counts]
+        return rx, ridx, rw, ([] if counts is None else counts), self._v1_handle(h, is_token_in_rank, data.shape[0]), ev
 
     def combine(self, x, handle, topk_weights=None, bias=None, config: Optional[Config] = None, previous_event=None,
                 async_finish: bool = False, allocate_on_comm_stream: bool = False):
         """(combined_x, combined_topk_weights, event)."""
         if self._elastic is None:
             raise RuntimeError("combine needs the buffer that produced the handle")
-        return self._elastic.combine(x, handle, topk_weights=topk_weights, bias=bias, num_sms=config.num_sms if config else 0,
-                                     previous_event=previous_event, async_with_compute_stream=async_finish,
-                                     allocate_on_comm_stream=allocate_on_comm_stream)
+        if not isinstance(handle, Handle):
+            raise TypeError("handle must come from Buffer.dispatch")
+        handle.check_live()
+        handle.slot.move(SlotState.COMBINE_IN_FLIGHT)
+        try:
+            out = self._elastic.combine(x, handle.elastic, topk_weights=topk_weights, bias=bias,
+                                        num_sms=config.num_sms if config else 0, previous_event=previous_event,
+                                        async_with_compute_stream=async_finish, allocate_on_comm_stream=allocate_on_comm_stream)
+        except Exception:
+            handle.slot.move(SlotState.DISPATCH_READY)
+            raise
+        handle.slot.move(SlotState.RELEASABLE)       # still usable (backward passes) until a later dispatch needs the slot
+        return out
+
+    def release(self, handle: Handle) -> None:
+        """Give the handle's slot back now instead of waiting for a later dispatch to recycle it."""
+        if isinstance(handle, Handle) and handle.slot is not None and handle.slot.generation == handle.generation:
+            self._slots.release(handle.slot)
 
     def _ordered(self, fn, previous_event, async_finish: bool, tensors):
         """Runs a local operator on the current stream after ``previous_event``; returns its results and an event."""
@@ -177,4 +248,4 @@ class Buffer:
     def get_next_low_latency_combine_buffer(self, *a, **k): raise NotImplementedError("V1 low-latency mode: use ElasticBuffer")
 
 
-__all__ = ["Buffer", "topk_idx_t"]
+__all__ = ["Buffer", "Handle", "topk_idx_t"]

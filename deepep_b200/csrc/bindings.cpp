@@ -98,6 +98,7 @@ void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, con
     a.rank_tokens = ptr<int>(d, "rank_tokens"); a.rank_rows = ptr<int>(d, "rank_rows");
     a.expert_counts = ptr<int>(d, "expert_counts"); a.expert_offsets = ptr<int>(d, "expert_offsets");
     a.recv_row_src = ptr<int>(d, "recv_row_src"); a.recv_w = ptr<float>(d, "recv_w"); a.recv_idx = ptr<long long>(d, "recv_idx");
+    a.rank_matrix = ptr<int>(d, "rank_matrix");
     a.mailbox = sessions[i].cast<Session&>().mailbox_device();
     a.rcap = getl(d, "rcap");
     if (a.T < 0 || a.T > lay.max_tokens) throw std::invalid_argument("token count exceeds num_max_tokens_per_rank");
@@ -269,6 +270,12 @@ PYBIND11_MODULE(_C, m) {
   m.def("testing_poke", [](uintptr_t address, int value) { *reinterpret_cast<volatile int*>(address) = value; });
   m.def("testing_peek", [](uintptr_t address) { return *reinterpret_cast<volatile int*>(address); });
 
+  m.def("layout", [](uintptr_t topk_idx, int T, int K, int E, int P, uintptr_t per_rank, uintptr_t per_expert, uintptr_t in_rank,
+                     uintptr_t stream) {
+    check(launch_layout(reinterpret_cast<const long long*>(topk_idx), T, K, E, P, reinterpret_cast<int*>(per_rank),
+                        reinterpret_cast<int*>(per_expert), reinterpret_cast<bool*>(in_rank), reinterpret_cast<cudaStream_t>(stream)),
+          "ep_layout launch");
+  });
   m.def("notify", &op_notify);
   m.def("dispatch", &op_dispatch, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),
         py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);

@@ -37,6 +37,7 @@ struct NotifyArgs {
   int* recv_row_src;           // [rcap] (source * Tmax + token) * K + slot of every output row, -1 for padding
   float* recv_w;               // [rcap] (expanded) or [rcap][K] (rank layout); may be null
   long long* recv_idx;         // [rcap][K] destination-local expert ids (rank layout) or null
+  int* rank_matrix;            // optional [P][P], zeroed by the caller: tokens that source i sends to rank j (every rank computes all of it)
   int* mailbox;                // mapped host memory: [0] rows, [1] staged rows, [2] max tokens, [3] epoch, [4..] counts
   long long rcap;
 };
@@ -102,6 +103,10 @@ struct CombineParams { WsLayout lay; int send_blocks, recv_blocks, local_direct,
 constexpr int kCombineProfWords = 8;
 constexpr int kCombineThreads = 384;    // 12 warps: up to 168 registers per thread, which the source side needs for 8 partials in flight
 cudaError_t launch_combine(const CombineParams& p, int nranks, cudaStream_t stream);
+
+// ---------------------------------------------------------------- V1 routing summary (get_dispatch_layout)
+cudaError_t launch_layout(const long long* topk_idx, int T, int K, int E, int P, int* tokens_per_rank, int* tokens_per_expert,
+                          bool* is_token_in_rank, cudaStream_t stream);
 
 // ---------------------------------------------------------------- barrier
 struct BarrierParams { RankCtx r[kMaxRanks]; };

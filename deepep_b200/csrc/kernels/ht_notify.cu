@@ -133,6 +133,8 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
     for (int e = threadIdx.x; e < E; e += blockDim.x)
       a.hist[(size_t)task * E + e] = __popc(s_m.expert[e][0]) + __popc(s_m.expert[e][1]);
     if (threadIdx.x == 0) a.hits[task] = __popc(s_m.rank[me][0]) + __popc(s_m.rank[me][1]);
+    if (a.rank_matrix && threadIdx.x < P)
+      atomicAdd(&a.rank_matrix[r * P + threadIdx.x], __popc(s_m.rank[threadIdx.x][0]) + __popc(s_m.rank[threadIdx.x][1]));
     if (r == me && threadIdx.x < P)
       a.own_hits[tile * P + threadIdx.x] = __popc(s_m.rank[threadIdx.x][0]) + __popc(s_m.rank[threadIdx.x][1]);
     __syncthreads();

@@ -62,9 +62,23 @@ class ExpertParallelMoE(torch.nn.Module):
             for e in range(self.local):
                 torch.nn.init.kaiming_uniform_(w[e], a=5 ** 0.5)
         self.w1, self.w2 = torch.nn.Parameter(w1), torch.nn.Parameter(w2)
+        self.use_grouped_mm = None        # decided at the first GPU forward (set it to False to force the per-expert loop)
 
-    def experts(self, rows: torch.Tensor, psum: torch.Tensor) -> torch.Tensor:
-        bounds = [0] + psum.tolist()
+    def experts(self, rows: torch.Tensor, psum: torch.Tensor, counts=None) -> torch.Tensor:
+        """SwiGLU experts on expert-major rows.  On a GPU with a usable library grouped GEMM both projections are one
+        ``torch._grouped_mm`` each (row ranges from the handle's cumulative counts, which stay on the device);
+        otherwise a loop over the experts with the host-side counts of the handle (no device synchronisation)."""
+        if rows.is_cuda and self.use_grouped_mm is None:
+            from ..utils.grouped_mm import grouped_mm_usable
+
+            self.use_grouped_mm = grouped_mm_usable()
+        if rows.is_cuda and self.use_grouped_mm and rows.shape[0] > 0:
+            offs = psum.to(torch.int32)
+            gate, up = torch._grouped_mm(rows, self.w1.transpose(1, 2), offs=offs).chunk(2, dim=-1)
+            return torch._grouped_mm(torch.nn.functional.silu(gate) * up, self.w2.transpose(1, 2), offs=offs)
+        bounds = [0]
+        for c in (counts if counts is not None else torch.diff(psum, prepend=psum.new_zeros(1)).tolist()):
+            bounds.append(bounds[-1] + int(c))
         outs = []
         for e in range(self.local):
             seg = rows[bounds[e]:bounds[e + 1]]
@@ -75,7 +89,7 @@ class ExpertParallelMoE(torch.nn.Module):
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         holder = {}
         recv_x, recv_w, psum = _Dispatch.apply(self.buffer, x, topk_idx, topk_weights, self.num_experts, holder)
-        y = self.experts(recv_x, psum) * recv_w.unsqueeze(1).to(recv_x.dtype)
+        y = self.experts(recv_x, psum, holder["handle"].num_recv_tokens_per_expert_list) * recv_w.unsqueeze(1).to(recv_x.dtype)
         return _Combine.apply(self.buffer, y.contiguous(), holder["handle"])
 
 

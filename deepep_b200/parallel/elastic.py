@@ -325,7 +325,7 @@ class ElasticBuffer:
                  num_max_tokens_per_rank=None, expert_alignment=None, num_sms=0, num_qps=0, previous_event=None,
                  previous_event_before_epilogue=None, async_with_compute_stream=False, allocate_on_comm_stream=False,
                  handle=None, do_handle_copy=True, do_cpu_sync=None, do_expand=False, do_zero_padding=False,
-                 use_tma_aligned_col_major_sf=False):
+                 use_tma_aligned_col_major_sf=False, _rank_matrix=False):
         """Send every token to the ranks that own its experts.
 
         Returns ``(recv_x | (recv_x, recv_x_sf), recv_topk_idx, recv_topk_weights, handle, event)``.
@@ -364,7 +364,7 @@ class ElasticBuffer:
                     return self._dispatch_low_latency(x_data, x_sf, topk_idx, topk_weights, num_experts, mode, cpu_sync,
                                                       comm, async_with_compute_stream, allocate_on_comm_stream)
                 plan = self.engine.notify([topk_idx], [topk_weights], num_experts, expand=expand, alignment=alignment,
-                                          cpu_sync=cpu_sync, stream=comm)[0]
+                                          cpu_sync=cpu_sync, stream=comm, **({"rank_matrix": True} if _rank_matrix else {}))[0]
                 recv_x, recv_sf = self.engine.dispatch([x if x_sf is not None else x_data], [plan], mode,
                                                        blocks=num_sms or self.num_sms, stream=comm)[0]
                 if stats is not None:

@@ -43,6 +43,8 @@ class CpuPlan:
     chunk_start: Optional[torch.Tensor] = None
     has_weights: bool = False
     low_latency: bool = False
+    rank_matrix: Optional[torch.Tensor] = None
+    send_chunk_prefix: Optional[torch.Tensor] = None
 
     def tensors(self):
         return [t for t in (self.topk_idx, self.expert_counts, self.expert_offsets, self.recv_row_src, self.recv_w,
@@ -62,7 +64,8 @@ class CpuEngine:
         return self.control.all_gather_object(obj)
 
     def notify(self, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[Optional[torch.Tensor]], num_experts: int,
-               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0, stream=None) -> List[CpuPlan]:
+               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0, stream=None,
+               rank_matrix: bool = False) -> List[CpuPlan]:
         del cpu_sync, blocks, stream
         idx = topk_idx[0].cpu().long()
         w = None if topk_w[0] is None else topk_w[0].cpu().float()
@@ -82,10 +85,34 @@ class CpuEngine:
             recv_w = outs[self.rank][2]
         rank_rows = torch.zeros(self.world + 1, dtype=torch.int32)
         rank_rows[1:] = torch.cumsum(lay.rank_rows, 0).int()
-        return [CpuPlan(idx.shape[0], num_experts, k, expand, alignment, lay.num_rows, int(rank_rows[-1]),
-                        lay.expert_counts.tolist(), topk_idx[0], layouts, [i.shape[0] for i in all_idx], all_idx, all_w,
-                        lay.expert_counts.int(), lay.expert_offsets.int(), rank_rows, src, recv_w,
-                        lay.recv_topk_idx, has_weights=all_w is not None)]
+        plan = CpuPlan(idx.shape[0], num_experts, k, expand, alignment, lay.num_rows, int(rank_rows[-1]),
+                       lay.expert_counts.tolist(), topk_idx[0], layouts, [i.shape[0] for i in all_idx], all_idx, all_w,
+                       lay.expert_counts.int(), lay.expert_offsets.int(), rank_rows, src, recv_w,
+                       lay.recv_topk_idx, has_weights=all_w is not None)
+        if rank_matrix:     # what the V1 handle is built from (the CUDA engine gets these from the layout kernel)
+            local, chunk = num_experts // self.world, 64
+            hits = []
+            for i in all_idx:
+                ok = (i >= 0) & (i < num_experts)
+                dst = torch.where(ok, torch.div(i.clamp(min=0), local, rounding_mode="floor"), torch.full_like(i, -1))
+                hits.append(torch.stack([(dst == d).any(dim=1) for d in range(self.world)], dim=1))      # [T_r, P]
+            plan.rank_matrix = torch.stack([h.sum(0) for h in hits]).int()
+            mine = hits[self.rank]
+            pos = torch.cumsum(mine.int(), 0) - 1
+            plan.send_slot = torch.where(mine, pos, torch.full_like(pos, -1)).int()
+            tiles = max(1, -(-idx.shape[0] // chunk))
+            pad = torch.zeros((tiles * chunk, self.world), dtype=torch.int64)
+            pad[:mine.shape[0]] = mine
+            per_chunk = pad.view(tiles, chunk, self.world).sum(1)                                        # [tiles, P]
+            plan.send_chunk_prefix = (torch.cumsum(per_chunk, 0) - per_chunk).t().contiguous().int()     # exclusive, [P, tiles]
+            nt = -(-self.max_tokens // chunk)
+            starts = torch.zeros((self.world, nt + 1), dtype=torch.int32)
+            for r, h in enumerate(hits):
+                col = torch.zeros(nt * chunk, dtype=torch.int64)
+                col[:h.shape[0]] = h[:, self.rank]
+                starts[r, 1:] = torch.cumsum(col.view(nt, chunk).sum(1), 0).int()
+            plan.chunk_start = starts
+        return [plan]
 
     def dispatch(self, xs: Sequence, plans: Sequence[CpuPlan], mode: int, blocks: int = 0, stream=None):
         del blocks, stream

@@ -12,6 +12,7 @@ single host synchronisation of a fresh dispatch
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass, field
 import os
 from typing import List, Optional, Sequence, Tuple
@@ -57,6 +58,8 @@ class RoutingPlan:
     low_latency: bool = False
     num_rows_dev: Optional[torch.Tensor] = None
     topk_w: Optional[torch.Tensor] = None
+    rank_matrix: Optional[torch.Tensor] = None
+    send_chunk_prefix: Optional[torch.Tensor] = None
 
     def tensors(self):
         return [t for t in (self.topk_idx, self.send_slot, self.slot_row, self.stage_meta, self.chunk_start, self.group_start,
@@ -215,7 +218,11 @@ class CudaEngine:
 
     # ------------------------------------------------------------------ ops
     def notify(self, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[Optional[torch.Tensor]], num_experts: int,
-               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0, stream=None) -> List[RoutingPlan]:
+               expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0, stream=None,
+               rank_matrix: bool = False) -> List[RoutingPlan]:
+        """``rank_matrix``: also count, on every rank, the tokens each source sends to each rank (``plan.rank_matrix
+        [P, P]``, what the V1 handle's ``rank_prefix_matrix`` is built from) and keep this rank's per-chunk send
+        prefixes (``plan.send_chunk_prefix [P, chunks]``)."""
         C, lay, dev = self.C, self.layout, self.device
         P, K = self.world, lay.topk
         local = num_experts // P
@@ -239,6 +246,7 @@ class CudaEngine:
                         if topk_w[i] is not None else None),
                 recv_idx=None if expand else torch.empty((rcap, K), dtype=torch.int64, device=dev),
                 has_weights=topk_w[i] is not None)
+            plan.rank_matrix = torch.zeros((P, P), **i32) if rank_matrix else None
             plans.append(plan)
             sc = self._scratch[i]
             args.append(dict(topk_idx=idx.data_ptr(), topk_w=_ptr(topk_w[i]), T=T, E=num_experts, K=K, expand=int(expand),
@@ -249,10 +257,16 @@ class CudaEngine:
                              rank_tokens=plan.rank_tokens.data_ptr(),
                              rank_rows=plan.rank_rows.data_ptr(), expert_counts=plan.expert_counts.data_ptr(),
                              expert_offsets=plan.expert_offsets.data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(),
-                             recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap))
+                             recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap,
+                             rank_matrix=_ptr(plan.rank_matrix)))
         # the layout pass is a chain of short phases over (source, tile) tasks: P x T / 64 of them, a few microseconds each
         nblocks = blocks or max(1, min(128, self.sm_count // self.n))
         self._timed("notify", stream, lambda: C.notify(lay, self.sessions, args, nblocks, self._stream(stream)))
+        if rank_matrix:       # the scratch is reused by the next call: keep this rank's per-chunk send prefixes with the plan
+            for plan, sc in zip(plans, self._scratch):
+                tiles = -(-max(plan.num_tokens, 1) // C.chunk_tokens)
+                with torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext():
+                    plan.send_chunk_prefix = sc["own_hits"][:tiles * P].view(tiles, P).t().contiguous()
         if cpu_sync:
             (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
             self.check_status()

@@ -107,3 +107,38 @@ def test_single_gpu_public_api():
     ref3, lays3 = R.dispatch(xs, idx, None, E, do_expand=True, expert_alignment=16)
     assert bits_equal(rx3, ref3[0][0])
     buf.destroy()
+
+
+def test_v1_buffer_on_one_gpu():
+    """Upstream V1 interface on the GPU: the layout kernel against torch, dispatch with the six-tensor handle, combine,
+    fixed-size outputs (num_worst_tokens) and a cached dispatch."""
+    import deepep_b200 as deep_ep
+    from helpers import make_routes
+
+    dev = torch.device("cuda")
+    T, H, E, K = 333, 512, 16, 4
+    x = torch.randn((T, H), generator=torch.Generator().manual_seed(4)).bfloat16().to(dev)
+    idx = make_routes("invalid", T, E, K, 1, 9).to(dev)
+    w = make_weights(T, K, 2).to(dev)
+    buf = deep_ep.Buffer(None, num_max_tokens_per_rank=512, hidden=H, num_topk=K)
+    per_rank, _, per_expert, in_rank, ev = buf.get_dispatch_layout(idx, E, async_finish=True)
+    ev.current_stream_wait()
+    valid = idx >= 0
+    assert per_expert.tolist() == torch.bincount(idx[valid], minlength=E).tolist()
+    assert torch.equal(in_rank[:, 0], valid.any(1)) and per_rank.tolist() == [int(valid.any(1).sum())]
+    rx, ridx, rw, counts, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_rank=per_rank,
+                                                   is_token_in_rank=in_rank, num_tokens_per_expert=per_expert)
+    rank_prefix, chan_prefix, recv_chan_prefix, recv_src_idx, in_rank2, send_head = handle
+    assert rank_prefix.tolist() == [[rx.shape[0]]] and counts == per_expert.tolist()
+    assert torch.equal(rx, x[recv_src_idx.long()]) and torch.equal(send_head[:, 0] >= 0, in_rank[:, 0])
+    assert int(chan_prefix[0, 1]) == int(in_rank[:64].sum()) == int(recv_chan_prefix[0, 1])
+    out, ow, _ = buf.combine(rx, handle, topk_weights=rw)
+    assert bits_equal(out, (x.float() * in_rank.float()).bfloat16())
+    assert torch.equal(ow, torch.where(valid, w, torch.zeros_like(w)))
+    rx2 = buf.dispatch(out, handle=handle)[0]
+    assert rx2.shape == rx.shape
+    worst = 512
+    rx3, ridx3, _, counts3, h3, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_expert=per_expert, num_worst_tokens=worst)
+    torch.cuda.synchronize()
+    assert rx3.shape[0] == worst and counts3 == [] and torch.equal(rx3[:rx.shape[0]], rx)
+    buf.destroy()
