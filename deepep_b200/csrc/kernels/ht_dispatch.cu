@@ -83,8 +83,9 @@ __device__ __forceinline__ float amax16(const int4& a, const int4& b, float v[16
 }
 
 // Fused quantiser: a bf16 row -> e4m3 bytes and one fp32 scale per 128 values, written to every destination.
-// amax over 128 values clamped to 1e-4, scale = amax / 448, q = e4m3(x * (448 / amax)): the rounding sequence of the
-// published recipe (deep_ep/utils/math.py:45-60 of the reference), so results equal it bit for bit.
+// amax over 128 values clamped to 1e-4, scale = amax / 448, q = e4m3(x * ((1 / amax) * 448)): reciprocal, then
+// multiply, which is how torch evaluates the recipe's `448.0 / amax` (deep_ep/utils/math.py:45-60 of the reference),
+// so results equal the recipe bit for bit.
 // Lane l of a pass owns 16 consecutive values; 8 consecutive lanes share a scale.
 __device__ __forceinline__ void warp_quant_fanout(const int4* src, int H, unsigned long long dst, unsigned long long dst_sf,
                                                   unsigned mask, int lane) {
@@ -107,7 +108,7 @@ __device__ __forceinline__ void warp_quant_fanout(const int4* src, int H, unsign
 #pragma unroll
       for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       amax = fmaxf(amax, 1e-4f);
-      const float inv = __fdiv_rn(448.0f, amax);   // one rounding, like the published recipe (x * (448 / amax))
+      const float inv = __frcp_rn(amax) * 448.0f;   // torch evaluates `448 / amax` (scalar / tensor) as reciprocal, then multiply
       uint32_t w[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)

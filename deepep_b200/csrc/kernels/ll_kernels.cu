@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             amax = fmaxf(amax, 1e-4f);
-            const float inv = __fdiv_rn(448.0f, amax);   // one rounding, like the published recipe (x * (448 / amax))
+            const float inv = __frcp_rn(amax) * 448.0f;   // torch evaluates `448 / amax` (scalar / tensor) as reciprocal, then multiply
             uint32_t q[2] = {0u, 0u};
 #pragma unroll
             for (int j = 0; j < 8; ++j)

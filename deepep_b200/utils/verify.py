@@ -105,9 +105,13 @@ def verify_low_latency(buf, x: torch.Tensor, topk_idx: torch.Tensor, topk_weight
     src = handle.recv_src_metadata[:rows].cpu().long()
     s, t, k = src // (tmax * K), (src // K) % tmax, src % K
     src_rows = _lookup([f[0] for f in facts], s, t)
+    mismatch = {}
     if fp8:
-        q, sf = per_token_cast_to_fp8(src_rows.to(x.device))
-        ok_payload = bool(torch.equal(recv_x.view(torch.int8), q.view(torch.int8))) and bool(torch.equal(out_x[1], sf))
+        q, sf = per_token_cast_to_fp8(src_rows)          # the recipe, evaluated on the host like the oracle does
+        bad_q = int((recv_x.cpu().view(torch.int8) != q.view(torch.int8)).sum())
+        bad_sf = int((out_x[1].cpu() != sf).sum())
+        ok_payload = bad_q == 0 and bad_sf == 0
+        mismatch = dict(code_mismatches=bad_q, scale_mismatches=bad_sf)
     else:
         ok_payload = bool(torch.equal(recv_x.cpu().view(torch.int16), src_rows.view(torch.int16)))
     named = _lookup([f[1] for f in facts], s, t).gather(1, k.unsqueeze(1)).squeeze(1)
@@ -122,7 +126,7 @@ def verify_low_latency(buf, x: torch.Tensor, topk_idx: torch.Tensor, topk_weight
         term = topk_weights[:, slot:slot + 1].float() * xf
         acc = torch.where(first[:, slot:slot + 1], acc + term, acc)
     ok_combine = bool(torch.equal(combined.view(torch.int16), acc.bfloat16().view(torch.int16)))
-    details = dict(rows=rows, payload_ok=ok_payload, experts_ok=ok_expert, combine_ok=ok_combine, fp8=fp8)
+    details = dict(rows=rows, payload_ok=ok_payload, experts_ok=ok_expert, combine_ok=ok_combine, fp8=fp8, **mismatch)
     return _agree(buf, ok_payload and ok_expert and ok_combine), details
 
 
