@@ -12,6 +12,7 @@
 #include "kernels/api.h"
 #include "kernels/ll_api.h"
 #include "kernels/mega_api.h"
+#include "kernels/ws_layout.h"
 #include "runtime/fake_cuda.h"
 #include "runtime/session.h"
 
@@ -35,47 +36,6 @@ int geti(const py::dict& d, const char* key, int dflt = 0) { return d.contains(k
 long long getl(const py::dict& d, const char* key, long long dflt = 0) { return d.contains(key) ? d[key].cast<long long>() : dflt; }
 float getf(const py::dict& d, const char* key, float dflt = 0.f) { return d.contains(key) ? d[key].cast<float>() : dflt; }
 
-constexpr long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
-
-WsLayout make_layout(int world, int max_tokens, int hidden, int topk, long long ll_bytes, long long mega_bytes) {
-  if (world < 1 || world > kMaxRanks) throw std::invalid_argument("world size must be in [1, 8]");
-  if (max_tokens < 1 || max_tokens > kChunkTokens * kMaxChunks) throw std::invalid_argument("num_max_tokens_per_rank must be in [1, 16384]");
-  if (topk < 1 || topk > kMaxTopk) throw std::invalid_argument("num_topk must be in [1, 16]");
-  if (hidden < 8 || hidden % 8) throw std::invalid_argument("hidden must be a positive multiple of 8");
-  WsLayout l{};
-  l.world = world; l.max_tokens = max_tokens; l.hidden = hidden; l.topk = topk;
-  l.stage_row_bytes = (int)align_up((long long)hidden * 2, 128);
-  long long at = kControlBytes;
-  auto take = [&](long long bytes) { long long o = at; at = align_up(at + bytes, 1024); return o; };
-  l.gather_hdr = take((long long)world * 4 * sizeof(int));
-  l.gather_idx = take((long long)world * max_tokens * topk * sizeof(int));
-  l.gather_w = take((long long)world * max_tokens * topk * sizeof(float));
-  l.stage = take((long long)world * max_tokens * l.stage_row_bytes);
-  l.partial = take((long long)max_tokens * world * hidden * 2);
-  l.wret = take((long long)max_tokens * topk * sizeof(float));
-  const long long groups = (max_tokens + kGroupTokens - 1) / kGroupTokens;
-  l.disp_flag = take((long long)world * groups * 8);
-  l.comb_flag = take((long long)world * groups * 8);
-  l.ll = take(ll_bytes);
-  l.mega = take(mega_bytes);
-  l.total = align_up(at, 2 << 20);
-  return l;
-}
-
-// Workspace that only carries the control block and the fused-MoE region (dispatch/combine regions are empty).
-WsLayout make_mega_layout(int world, int max_tokens, int hidden, int topk, long long mega_bytes) {
-  if (world < 1 || world > kMaxRanks) throw std::invalid_argument("world size must be in [1, 8]");
-  if (topk < 1 || topk > kMaxTopk) throw std::invalid_argument("num_topk must be in [1, 16]");
-  if (hidden < 128 || hidden % 128) throw std::invalid_argument("hidden must be a positive multiple of 128");
-  WsLayout l{};
-  l.world = world; l.max_tokens = max_tokens; l.hidden = hidden; l.topk = topk;
-  l.stage_row_bytes = hidden * 2;
-  l.gather_hdr = l.gather_idx = l.gather_w = l.stage = l.partial = l.wret = l.disp_flag = l.comb_flag = l.ll = kControlBytes;
-  l.mega = kControlBytes;
-  l.total = align_up(kControlBytes + mega_bytes, 2 << 20);
-  return l;
-}
-
 RankCtx ctx_of(const py::handle& session) { return session.cast<Session&>().ctx(); }
 
 void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
@@ -94,8 +54,7 @@ void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, con
     a.expand = geti(d, "expand", 1); a.alignment = geti(d, "alignment", 1); a.meta_stride = geti(d, "meta_stride");
     a.hist = ptr<int>(d, "hist"); a.hits = ptr<int>(d, "hits"); a.own_hits = ptr<int>(d, "own_hits"); a.cnt = ptr<int>(d, "cnt");
     a.send_slot = ptr<int>(d, "send_slot"); a.slot_row = ptr<int>(d, "slot_row"); a.stage_meta = ptr<int>(d, "stage_meta");
-    a.chunk_start = ptr<int>(d, "chunk_start"); a.group_start = ptr<int>(d, "group_start");
-    a.rank_tokens = ptr<int>(d, "rank_tokens"); a.rank_rows = ptr<int>(d, "rank_rows");
+    a.chunk_start = ptr<int>(d, "chunk_start"); a.rank_tokens = ptr<int>(d, "rank_tokens"); a.rank_rows = ptr<int>(d, "rank_rows");
     a.expert_counts = ptr<int>(d, "expert_counts"); a.expert_offsets = ptr<int>(d, "expert_offsets");
     a.recv_row_src = ptr<int>(d, "recv_row_src"); a.recv_w = ptr<float>(d, "recv_w"); a.recv_idx = ptr<long long>(d, "recv_idx");
     a.rank_matrix = ptr<int>(d, "rank_matrix");
@@ -126,18 +85,17 @@ void op_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, c
     a.T = geti(d, "T"); a.mode = geti(d, "mode");
     a.send_slot = ptr<const int>(d, "send_slot"); a.stage_meta = ptr<const int>(d, "stage_meta");
     a.slot_row = ptr<const int>(d, "slot_row"); a.topk_idx = ptr<const long long>(d, "topk_idx");
-    a.group_start = ptr<const int>(d, "group_start"); a.rank_tokens = ptr<const int>(d, "rank_tokens");
-    a.rank_rows = ptr<const int>(d, "rank_rows");
+    a.rank_tokens = ptr<const int>(d, "rank_tokens"); a.rank_rows = ptr<const int>(d, "rank_rows");
     a.meta_stride = geti(d, "meta_stride");
     a.recv_rows = geti(d, "recv_rows", 0);
     a.K = geti(d, "K"); a.E = geti(d, "E"); a.expand = geti(d, "expand", 1);
     a.recv_x = ptr<void>(d, "recv_x"); a.recv_sf = ptr<float>(d, "recv_sf");
     a.prof = ptr<unsigned long long>(d, "prof");
     // (a rank without tokens, or without received rows, passes empty tensors whose address is null)
-    if (!a.send_slot || !a.stage_meta || !a.group_start || !a.rank_tokens || (!a.x && a.T > 0))
+    if (!a.send_slot || !a.stage_meta || !a.rank_tokens || !a.rank_rows || (!a.x && a.T > 0))
       throw std::invalid_argument("dispatch: a required pointer is missing");
-    if (local_direct && (!a.slot_row || (!a.topk_idx && a.T > 0) || !a.rank_rows || a.E < a.ctx.world || a.K != lay.topk))
-      throw std::invalid_argument("dispatch: direct local rows need slot_row, topk_idx, rank_rows, E and K");
+    if (local_direct && (!a.slot_row || (!a.topk_idx && a.T > 0) || a.E < a.ctx.world || a.K != lay.topk))
+      throw std::invalid_argument("dispatch: direct local rows need slot_row, topk_idx, E and K");
     if (a.mode != p.r[0].mode) throw std::invalid_argument("all ranks must use the same dispatch mode");
     if (a.mode != kDispatchBf16 && lay.hidden % 128) throw std::invalid_argument("fp8 dispatch needs hidden % 128 == 0");
   }
@@ -158,7 +116,7 @@ void op_combine(const WsLayout& lay, const std::vector<py::object>& sessions, co
     CombineArgs& a = p.r[i];
     a.ctx = ctx_of(sessions[i]);
     a.x = ptr<const __nv_bfloat16>(d, "x"); a.w = ptr<const float>(d, "w");
-    a.stage_meta = ptr<const int>(d, "stage_meta"); a.group_start = ptr<const int>(d, "group_start");
+    a.stage_meta = ptr<const int>(d, "stage_meta"); a.rank_rows = ptr<const int>(d, "rank_rows");
     a.rank_tokens = ptr<const int>(d, "rank_tokens"); a.send_slot = ptr<const int>(d, "send_slot");
     a.topk_idx = ptr<const long long>(d, "topk_idx");
     a.T = geti(d, "T"); a.meta_stride = geti(d, "meta_stride"); a.K = geti(d, "K"); a.E = geti(d, "E"); a.expand = geti(d, "expand", 1);
@@ -166,7 +124,7 @@ void op_combine(const WsLayout& lay, const std::vector<py::object>& sessions, co
     a.bias0 = ptr<const __nv_bfloat16>(d, "bias0"); a.bias1 = ptr<const __nv_bfloat16>(d, "bias1");
     a.out = ptr<__nv_bfloat16>(d, "out"); a.out_w = ptr<float>(d, "out_w");
     a.prof = ptr<unsigned long long>(d, "prof");
-    if (!a.stage_meta || !a.group_start || !a.rank_tokens || !a.send_slot || ((!a.topk_idx || !a.out) && a.T > 0))
+    if (!a.stage_meta || !a.rank_rows || !a.rank_tokens || !a.send_slot || ((!a.topk_idx || !a.out) && a.T > 0))
       throw std::invalid_argument("combine: a required pointer is missing");
     if (a.E < a.ctx.world) throw std::invalid_argument("combine: num_experts is missing");
   }
@@ -282,6 +240,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("combine", &op_combine, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),
         py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);
   m.attr("group_tokens") = kGroupTokens;
+  m.attr("row_block") = kRowBlock;
   m.attr("dispatch_prof_words") = kDispatchProfWords;
   m.attr("dispatch_threads") = kDispatchThreads;
   m.attr("combine_threads") = kCombineThreads;

@@ -29,7 +29,6 @@ struct NotifyArgs {
   int* slot_row;               // [T][K]  row on the destination rank (expanded layout), -1 if empty
   int* stage_meta;             // [P * Tmax][meta_stride]: token, n, n x (row | slot << 27); rank layout: token, 1, row, slot mask
   int* chunk_start;            // [P][NT + 1] staged-row index at the start of every source chunk
-  int* group_start;            // [P][NG + 1] the same per group of kGroupTokens tokens (NG = ceil(Tmax / kGroupTokens)); may be null
   int* rank_tokens;            // [P] tokens each source holds
   int* rank_rows;              // [P + 1] exclusive prefix of staged rows per source
   int* expert_counts;          // [L] unaligned rows per local expert
@@ -57,9 +56,8 @@ struct DispatchArgs {
   const int* slot_row;         // [T][K] output row of every slot on its destination (expanded layout)
   const long long* topk_idx;   // [T][K] of this rank's tokens (which slots are local)
   const int* stage_meta;
-  const int* group_start;      // [P][NG + 1]
   const int* rank_tokens;
-  const int* rank_rows;        // [P + 1] (rank layout: first output row of every source)
+  const int* rank_rows;        // [P + 1] exclusive prefix of the staged rows per source (rank layout: first output row of a source)
   int meta_stride, recv_rows;  // recv_rows: rows of recv_x (only read by the optional index checks; 0 = unknown)
   int K, E, expand;
   void* recv_x;                // [R][H] 2-byte (mode 0) or e4m3 (modes 1, 2)
@@ -84,8 +82,8 @@ struct CombineArgs {
   const __nv_bfloat16* x;      // [R][H] expert outputs
   const float* w;              // [R] (expanded) / [R][K] (rank layout) value channel, or null
   const int* stage_meta;
-  const int* group_start;      // [P][NG + 1]
   const int* rank_tokens;
+  const int* rank_rows;        // [P + 1] exclusive prefix of the staged rows per source
   const int* send_slot;        // [T][P]
   const long long* topk_idx;   // [T][K] of the source tokens (validity of returned weights)
   int T, meta_stride, K, E, expand, x_rows;   // x_rows: rows of x (only read by the optional index checks; 0 = unknown)

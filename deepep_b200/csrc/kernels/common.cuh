@@ -21,8 +21,8 @@ namespace dep {
 
 constexpr int kMaxRanks = 8;          // one NVSwitch domain
 constexpr int kChunkTokens = 64;      // tokens per routing tile of the layout pass
-constexpr int kGroupTokens = 4;       // tokens per completion flag of the high-throughput dispatch / combine
-constexpr int kGroupsPerChunk = kChunkTokens / kGroupTokens;
+constexpr int kGroupTokens = 2;       // source tokens per completion flag of the high-throughput dispatch
+constexpr int kRowBlock = 4;          // staged rows per work item of the local sides, and per completion flag of the combine
 constexpr int kMaxChunks = 256;       // => at most 16384 tokens per rank
 constexpr int kMaxTopk = 16;
 constexpr int kMaxExperts = 1024;
@@ -79,8 +79,8 @@ struct WsLayout {
   long long stage;         // byte  [P][Tmax][stage_row_bytes]   dispatch staging, written by sources
   long long partial;       // bf16  [Tmax][P][H]                  combine partials, written by expert ranks
   long long wret;          // float [Tmax][K]                     returned weights
-  long long disp_flag;     // u64   [P][ceil(Tmax / kGroupTokens)] dispatch: rows of (source, token group) have landed
-  long long comb_flag;     // u64   [P][ceil(Tmax / kGroupTokens)] combine: partials of (expert rank, token group) have landed
+  long long disp_flag;     // u64   [P][ceil(Tmax / kGroupTokens)] dispatch: the rows of (source, token group) have landed
+  long long comb_flag;     // u64   [P][ceil(Tmax / kRowBlock)]    combine: the partials of (expert rank, block of its staged rows) have landed
   long long ll;            // low-latency region
   long long mega;          // fused-MoE region
   long long total;

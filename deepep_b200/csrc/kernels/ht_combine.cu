@@ -1,13 +1,13 @@
 // ep_combine_ht: all-to-all-v return of expert outputs fused with the top-k reduction.
 //
 // Every warp works on its own, there is no block-wide step inside the kernel.
-//   Expert-side warps walk the staged-row records that dispatch used, (source, group of kGroupTokens
-//   tokens) by (source, group): for one (source token, this rank) they sum the token's rows on this
+//   Expert-side warps walk the staged-row records that dispatch used, a block of kRowBlock records
+//   of one source at a time: for one (source token, this rank) they sum the token's rows on this
 //   rank in slot order in fp32, round once to bf16 and store that single partial into the source
-//   rank's workspace through the peer mapping (NVLink); a release flag per (source, group) follows.
-//   Source-side warps take one token each: they wait for the group flags of the ranks the token was
-//   sent to, sum the partials in rank order in fp32, add the optional biases and write bf16 into the
-//   caller's tensor.  The rows that stayed on the source rank itself are summed straight from the
+//   rank's workspace through the peer mapping (NVLink); a release flag per (source, block) follows.
+//   Source-side warps take one token each: they wait for the flags of the blocks that hold the
+//   token's staged row on the ranks it was sent to (the send-slot table names the row), sum the
+//   partials in rank order in fp32, add the optional biases and write bf16 into the caller's tensor.  The rows that stayed on the source rank itself are summed straight from the
 //   expert output (same rounding: fp32 sum -> bf16 -> fp32), so the local share never takes the detour
 //   through a partial.
 // The optional fp32 value channel (used for dispatch-backward) is returned per slot and is never
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
   const WsLayout& lay = p.lay;
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, Tmax = lay.max_tokens, H = lay.hidden, K = a.K;
-  const int NG = (Tmax + kGroupTokens - 1) / kGroupTokens;
+  const int NB = (Tmax + kRowBlock - 1) / kRowBlock;   // completion flags per expert rank
   const int lane = threadIdx.x & 31;
   const int q = lane >> 3, c = lane & 7;      // metadata of a group is fetched by lane = (record of the group) * 8 + field
   const int row_bytes = H * 2, units = H / 8;  // 16-byte units per row
@@ -138,24 +138,23 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
     if (lane < P) ok = wait_flag_ge(&ctl->comb_ack[lane], epoch - 1, ctx, kOpCombine, 0, lane);
     const bool alive = __all_sync(0xffffffffu, ok);
     clk.mark(kProfWait);
-    int max_ng = 0;
-    for (int r = 0; r < P; ++r) max_ng = max(max_ng, (a.rank_tokens[r] + kGroupTokens - 1) / kGroupTokens);
     // the sources whose rows are returned through a partial: all ranks, or all but this one
     const int S = p.local_direct ? P - 1 : P, first = p.local_direct ? 1 : 0;
-    // (source, group) items are handed out in order by a shared counter
-    for (int item = next_ticket(&ctl->ticket[kOpCombine][0], lane); item < max_ng * S && alive;
+    int max_nb = 0;
+    for (int s = 0; s < S; ++s) {
+      const int r = (me + first + s) % P;
+      max_nb = max(max_nb, (a.rank_rows[r + 1] - a.rank_rows[r] + kRowBlock - 1) / kRowBlock);
+    }
+    // items are blocks of kRowBlock staged-row records of one source, handed out in order by a shared counter
+    for (int item = next_ticket(&ctl->ticket[kOpCombine][0], lane); item < max_nb * S && alive;
          item = next_ticket(&ctl->ticket[kOpCombine][0], lane)) {
-      const int gi = item / S, r = (me + first + item % S) % P;
-      if (gi * kGroupTokens >= a.rank_tokens[r]) continue;
-      const int j0 = a.group_start[r * (NG + 1) + gi], j1 = a.group_start[r * (NG + 1) + gi + 1];
-      if (j0 >= j1) continue;
-      if (j0 < 0 || j1 - j0 > kGroupTokens || j1 > Tmax) {   // a group stages at most one row per token: the plan is damaged
-        if (lane == 0) report_failure(ctx, kStatusBadArgument, kOpCombine, 3, r, kGroupTokens, (unsigned long long)(j1 - j0));
-        break;
-      }
-      // the group's records in one round of loads: lane (q, c) holds fields c, 8 + c, 16 + c of record j0 + q
+      const int r = (me + first + item % S) % P, jb = item / S, j0 = jb * kRowBlock;
+      const int rows_r = min(a.rank_rows[r + 1] - a.rank_rows[r], Tmax);
+      if (j0 >= rows_r) continue;
+      const int cnt = min(kRowBlock, rows_r - j0);
+      // the block's records in one round of loads: lane (q, c) holds fields c, 8 + c, 16 + c of record j0 + q
       int f0 = 0, f1 = 0, f2 = 0;
-      if (q < j1 - j0) {
+      if (q < cnt) {
         const int* rec = a.stage_meta + ((size_t)r * Tmax + j0 + q) * a.meta_stride;
         if (c < a.meta_stride) f0 = rec[c];
         if (8 + c < a.meta_stride) f1 = rec[8 + c];
@@ -164,7 +163,7 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
       uint8_t* partial = ctx.ws[r] + lay.partial;
       float* wret = reinterpret_cast<float*>(ctx.ws[r] + lay.wret);
       clk.mark(kProfMeta);
-      for (int qq = 0; qq < j1 - j0; ++qq) {
+      for (int qq = 0; qq < cnt; ++qq) {
         const int t = __shfl_sync(0xffffffffu, f0, qq * 8), n = min(__shfl_sync(0xffffffffu, f0, qq * 8 + 1), kMaxTopk);
         const int rec3 = __shfl_sync(0xffffffffu, f0, qq * 8 + 3);
         const int fi = 2 + lane, from = qq * 8 + (fi & 7);
@@ -202,10 +201,10 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
         clk.add_rows(n);
       }
       clk.mark(kProfData);
-      // publish the group: every lane's stores are ordered before the flag by the warp barrier + release
+      // publish the block: every lane's stores are ordered before the flag by the warp barrier + release
       __syncwarp();
       if (lane == 0)
-        st_release_sys(reinterpret_cast<unsigned long long*>(ctx.ws[r] + lay.comb_flag) + (size_t)me * NG + gi, epoch);
+        st_release_sys(reinterpret_cast<unsigned long long*>(ctx.ws[r] + lay.comb_flag) + (size_t)me * NB + jb, epoch);
       clk.mark(kProfPublish);
     }
   }
@@ -226,8 +225,8 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
       if (local && j_me < Tmax && lane < a.meta_stride) f = a.stage_meta[((size_t)me * Tmax + j_me) * a.meta_stride + lane];
       clk.mark(kProfMeta);
       int ok = 1;
-      if (((dmask >> lane) & 1u) && !(local && lane == me))
-        ok = wait_flag_ge(flags + (size_t)lane * NG + t / kGroupTokens, epoch, ctx, kOpCombine, 1, lane);
+      if (((dmask >> lane) & 1u) && !(local && lane == me))   // the partial of rank `lane` belongs to the block of its staged row
+        ok = wait_flag_ge(flags + (size_t)lane * NB + min(ss, Tmax - 1) / kRowBlock, epoch, ctx, kOpCombine, 1, lane);
       ok = __all_sync(0xffffffffu, ok);
       clk.mark(kProfWait);
       if (!ok) break;

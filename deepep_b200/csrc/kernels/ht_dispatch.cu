@@ -6,13 +6,15 @@
 //   the peer mapping (NVLink), optionally quantised to e4m3 with one fp32 scale per 128 values on the
 //   way.  Rows whose destination is the sending rank itself are written straight into the output
 //   tensor, one copy per local expert.  After a group the warp publishes one release flag per
-//   destination: flags cover 4 tokens, so the receivers follow the senders closely and no sender ever
-//   drains a pipeline at a chunk boundary.
-//   Receiver warps take (source, group) items in the order the senders produce them, wait for the
-//   group's flag and materialise every output row of each staged row (one per local expert of the
-//   token), so a token crosses NVLink once no matter how many experts of the destination it uses.
-//   Groups and items are handed out by two shared counters; sender warps turn into receivers once the
-//   last group is on its way.
+//   destination: flags cover two tokens, so the receivers follow the senders closely, no sender ever
+//   drains a pipeline at a chunk boundary, and there are several groups per sender warp, which keeps
+//   the last wave of groups short.
+//   Receiver warps take blocks of kRowBlock staged rows of one source, in the order the senders
+//   produce them.  Each record names its source token; the warp waits for that token's flag and
+//   materialises every output row of the staged row (one per local expert of the token), so a token
+//   crosses NVLink once no matter how many experts of the destination it uses.
+//   Groups and blocks are handed out by two shared counters; sender warps turn into receivers once
+//   the last group is on its way.
 //
 // Between two GPUs 32 SMs of 16-byte register stores reach the same rate as bulk shared->global copies
 // (about 0.69 TB/s per direction with both directions busy); the register form needs no staging in
@@ -234,39 +236,51 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) ep_dispatch_ht_kernel(con
   }
   {
     // ================================================================ receiver (sender warps join once all groups are sent)
-    int max_ng = 0;
-    for (int r = 0; r < P; ++r) max_ng = max(max_ng, (a.rank_tokens[r] + kGroupTokens - 1) / kGroupTokens);
     uint8_t* recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
     const uint8_t* stage = ctx.ws[me] + lay.stage;
     const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(ctx.ws[me] + lay.disp_flag);
     // the sources whose rows pass through the staging area: all ranks, or all but this one
     const int S = p.local_direct ? P - 1 : P, first = p.local_direct ? 1 : 0;
-    for (int item = next_ticket(&ctl->ticket[kOpDispatch][1], lane); item < max_ng * S;
+    int max_nb = 0;
+    for (int s = 0; s < S; ++s) {
+      const int r = (me + first + s) % P;
+      max_nb = max(max_nb, (a.rank_rows[r + 1] - a.rank_rows[r] + kRowBlock - 1) / kRowBlock);
+    }
+    // items are blocks of kRowBlock staged rows, block b of every source before block b + 1 of any: the order in which
+    // the senders, which all walk their tokens front to back, complete them
+    for (int item = next_ticket(&ctl->ticket[kOpDispatch][1], lane); item < max_nb * S;
          item = next_ticket(&ctl->ticket[kOpDispatch][1], lane)) {
-      const int gi = item / S, r = (me + first + item % S) % P;
-      if (gi * kGroupTokens >= a.rank_tokens[r]) continue;
-      const int j0 = a.group_start[r * (NG + 1) + gi], j1 = a.group_start[r * (NG + 1) + gi + 1];
-      if (j0 >= j1) continue;
-      if (j0 < 0 || j1 - j0 > kGroupTokens || j1 > Tmax) {   // a group stages at most one row per token: the plan is damaged
-        if (lane == 0) report_failure(ctx, kStatusBadArgument, kOpDispatch, 3, r, kGroupTokens, (unsigned long long)(j1 - j0));
-        break;
-      }
-      // the group's records in one round of loads (issued before the flag wait): lane (q, c) holds fields c, 8 + c, 16 + c
+      const int r = (me + first + item % S) % P, j0 = (item / S) * kRowBlock;
+      const int rows_r = min(a.rank_rows[r + 1] - a.rank_rows[r], Tmax), T_r = a.rank_tokens[r];
+      if (j0 >= rows_r) continue;
+      const int cnt = min(kRowBlock, rows_r - j0);
+      // the block's records in one round of loads: lane (q, c) holds fields c, 8 + c, 16 + c of record j0 + q
       int f0 = 0, f1 = 0, f2 = 0;
-      if (q < j1 - j0) {
+      if (q < cnt) {
         const int* rec = a.stage_meta + ((size_t)r * Tmax + j0 + q) * a.meta_stride;
         if (c < a.meta_stride) f0 = rec[c];
         if (8 + c < a.meta_stride) f1 = rec[8 + c];
         if (16 + c < a.meta_stride) f2 = rec[16 + c];
       }
       clk.mark(kProfMeta);
-      int ok = 1;
-      if (lane == 0) ok = wait_flag_ge(flags + (size_t)r * NG + gi, epoch, ctx, kOpDispatch, 1, r);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      clk.mark(kProfWait);
-      if (!ok) break;
-      for (int qq = 0; qq < j1 - j0; ++qq) {
+      int waited = -1;
+      bool alive = true;
+      for (int qq = 0; qq < cnt && alive; ++qq) {
         const int j = j0 + qq;
+        const int t = __shfl_sync(0xffffffffu, f0, qq * 8);
+        if (t < 0 || t >= T_r) {   // a record names the source token whose flag covers it: the plan is damaged
+          if (lane == 0) report_failure(ctx, kStatusBadArgument, kOpDispatch, 3, r, T_r, (unsigned long long)(unsigned)t);
+          alive = false;
+          break;
+        }
+        if (t / kGroupTokens != waited) {
+          waited = t / kGroupTokens;
+          int ok = 1;
+          if (lane == 0) ok = wait_flag_ge(flags + (size_t)r * NG + waited, epoch, ctx, kOpDispatch, 1, r);
+          alive = __shfl_sync(0xffffffffu, ok, 0) != 0;
+          clk.mark(kProfWait);
+          if (!alive) break;
+        }
         const int n = min(__shfl_sync(0xffffffffu, f0, qq * 8 + 1), kMaxTopk);
         const int fi = 2 + lane, from = qq * 8 + (fi & 7);
         const int e0 = __shfl_sync(0xffffffffu, f0, from), e1 = __shfl_sync(0xffffffffu, f1, from), e2 = __shfl_sync(0xffffffffu, f2, from);
@@ -283,8 +297,9 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) ep_dispatch_ht_kernel(con
         warp_fanout<true>(reinterpret_cast<const int4*>(src), units, dst, mask, lane);
         if (fp8) warp_fanout_f32<true>(reinterpret_cast<const float*>(src + H), nsf, dst_sf, mask, lane);
         clk.add_rows(__popc(mask));
+        clk.mark(kProfData);
       }
-      clk.mark(kProfData);
+      if (!alive) break;
     }
   }
 

@@ -71,7 +71,6 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, K = a.K, E = a.E, Lx = E / P, Tmax = lay.max_tokens;
   const int NT = (Tmax + kChunkTokens - 1) / kChunkTokens;
-  const int NG = (Tmax + kGroupTokens - 1) / kGroupTokens;
   uint8_t* ws = ctx.ws[me];
   Control* ctl = control_of(ws);
   const unsigned long long epoch = ctl->epoch[kOpNotify] + 1;
@@ -260,13 +259,6 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
       __syncthreads();
     }
     int tl = threadIdx.x, t = tile * kChunkTokens + tl;
-    if (a.group_start && tl <= kGroupsPerChunk && tile * kGroupsPerChunk + tl <= NG) {
-      // staged-row index at the start of every token group of this tile (the entry behind the last group is the start
-      // of the next tile, which that tile's task writes again with the same value)
-      const int first = tl * kGroupTokens;
-      const int before = first >= kChunkTokens ? __popc(s_m.rank[me][0]) + __popc(s_m.rank[me][1]) : below(s_m.rank[me], first);
-      a.group_start[(size_t)r * (NG + 1) + tile * kGroupsPerChunk + tl] = a.chunk_start[r * (NT + 1) + tile] + before;
-    }
     if (tl < kChunkTokens && t < T_r) {
       int row[kMaxTopk];
 #pragma unroll

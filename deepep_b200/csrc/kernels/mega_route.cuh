@@ -12,12 +12,12 @@
 //
 // Parity: stage/route_compact, stage/token_dispatch, CrossRankSync and stage/unpermute of the
 // reference's MegaMoE kernel (experiments/megamoe/csrc/kernels/mega_moe/mega_moe_arch35.hpp:852-1006).
-#include <cooperative_groups.h>
-
 #pragma once
-#include "mega_api.h"
-
+#ifdef __CUDACC__
+#include <cooperative_groups.h>
 namespace cg = cooperative_groups;
+#endif
+#include "mega_api.h"
 
 namespace dep {
 

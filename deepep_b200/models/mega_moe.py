@@ -99,13 +99,11 @@ class MegaEngine:
         self.gemm_blocks = num_sms or self.sm_count
         # tiles handed out by an atomic counter (default) or statically round-robin (DEEPEP_MEGA_STATIC_TILES=1)
         self.dynamic_tiles = os.environ.get("DEEPEP_MEGA_STATIC_TILES", "0") in ("", "0")
-        # GEMM2 tiles scheduled right after their GEMM1 wave, or after all GEMM1 tiles.  Interleaving spreads the combine
-        # rows (top-k bf16 rows per token, most of them remote from four ranks up) over the kernel instead of its last
-        # third.  The value is the wave length in units of two rounds of GEMM1 tiles over the CTAs.  One GPU, 4096
-        # tokens: 1560 us without, 1629 / 1596 / 1575 us with waves of 1 / 2 / 4 units (two GPUs, 1 unit: 2046 against
-        # 1951 us), so it is off below four ranks and uses long waves from four ranks up, where three quarters or more
-        # of those rows cross NVLink.  DEEPEP_MEGA_INTERLEAVE=<units> overrides (0 = off).
-        default = "4" if self.world >= 4 else "0"
+        # GEMM2 tiles scheduled after all GEMM1 tiles (0, the default) or right after their GEMM1 wave, which spreads the
+        # combine rows over the kernel instead of its last third.  The value is the wave length in units of two rounds of
+        # GEMM1 tiles over the CTAs.  Measured with 4096 tokens per rank, off against on: 1560 against 1575-1629 us on one
+        # GPU, 1951 against 2046 us on two, 2372 against 2399 us on four, so it stays an option (DEEPEP_MEGA_INTERLEAVE=<units>).
+        default = "0"
         self.interleave = int(os.environ.get("DEEPEP_MEGA_INTERLEAVE", default) or 0)   # wave length in units of two CTA rounds
         rows = self.world * self.M * min(self.K, self.L) + self.S * self.M + (self.L + self.S) * 127
         self.max_mtiles = -(-rows // 128)

@@ -46,7 +46,6 @@ class RoutingPlan:
     slot_row: Optional[torch.Tensor]
     stage_meta: Optional[torch.Tensor]
     chunk_start: Optional[torch.Tensor]
-    group_start: Optional[torch.Tensor]
     rank_tokens: Optional[torch.Tensor]
     rank_rows: Optional[torch.Tensor]
     expert_counts: torch.Tensor
@@ -62,8 +61,7 @@ class RoutingPlan:
     send_chunk_prefix: Optional[torch.Tensor] = None
 
     def tensors(self):
-        return [t for t in (self.topk_idx, self.send_slot, self.slot_row, self.stage_meta, self.chunk_start, self.group_start,
-                            self.rank_tokens,
+        return [t for t in (self.topk_idx, self.send_slot, self.slot_row, self.stage_meta, self.chunk_start, self.rank_tokens,
                             self.rank_rows, self.expert_counts, self.expert_offsets, self.recv_row_src, self.recv_w,
                             self.recv_idx) if t is not None]
 
@@ -238,8 +236,7 @@ class CudaEngine:
                 num_rows=rcap, num_staged_rows=0, expert_counts_list=None, topk_idx=idx,
                 send_slot=torch.empty((max(T, 1), P), **i32), slot_row=torch.empty((max(T, 1), K), **i32),
                 stage_meta=torch.empty((P * lay.max_tokens, stride), **i32),
-                chunk_start=torch.empty((P, self._nt + 1), **i32),
-                group_start=torch.empty((P, -(-lay.max_tokens // C.group_tokens) + 1), **i32), rank_tokens=torch.empty((P,), **i32),
+                chunk_start=torch.empty((P, self._nt + 1), **i32), rank_tokens=torch.empty((P,), **i32),
                 rank_rows=torch.empty((P + 1,), **i32), expert_counts=torch.empty((local,), **i32),
                 expert_offsets=torch.empty((local + 1,), **i32), recv_row_src=torch.empty((rcap,), **i32),
                 recv_w=(torch.empty((rcap,) if expand else (rcap, K), dtype=torch.float32, device=dev)
@@ -253,8 +250,7 @@ class CudaEngine:
                              alignment=alignment, meta_stride=stride, hist=sc["hist"].data_ptr(), hits=sc["hits"].data_ptr(),
                              own_hits=sc["own_hits"].data_ptr(), cnt=sc["cnt"].data_ptr(), send_slot=plan.send_slot.data_ptr(),
                              slot_row=plan.slot_row.data_ptr(), stage_meta=plan.stage_meta.data_ptr(),
-                             chunk_start=plan.chunk_start.data_ptr(), group_start=plan.group_start.data_ptr(),
-                             rank_tokens=plan.rank_tokens.data_ptr(),
+                             chunk_start=plan.chunk_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
                              rank_rows=plan.rank_rows.data_ptr(), expert_counts=plan.expert_counts.data_ptr(),
                              expert_offsets=plan.expert_offsets.data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(),
                              recv_w=_ptr(plan.recv_w), recv_idx=_ptr(plan.recv_idx), rcap=rcap,
@@ -301,7 +297,7 @@ class CudaEngine:
             outs.append((recv_x, recv_sf))
             args.append(dict(x=x.data_ptr(), x_sf=_ptr(sf), T=plan.num_tokens, mode=mode, send_slot=plan.send_slot.data_ptr(),
                              slot_row=plan.slot_row.data_ptr(), topk_idx=plan.topk_idx.data_ptr(),
-                             stage_meta=plan.stage_meta.data_ptr(), group_start=plan.group_start.data_ptr(),
+                             stage_meta=plan.stage_meta.data_ptr(),
                              rank_tokens=plan.rank_tokens.data_ptr(), rank_rows=plan.rank_rows.data_ptr(),
                              meta_stride=plan.meta_stride, K=plan.num_topk, E=plan.num_experts, expand=int(plan.expand),
                              recv_x=recv_x.data_ptr(), recv_sf=_ptr(recv_sf), recv_rows=recv_x.shape[0],
@@ -325,7 +321,7 @@ class CudaEngine:
             b0, b1 = (b if isinstance(b, (tuple, list)) else (b, None)) if b is not None else (None, None)
             outs.append((out, out_w))
             args.append(dict(x=xs[i].data_ptr(), w=_ptr(ws[i]), stage_meta=plan.stage_meta.data_ptr(),
-                             group_start=plan.group_start.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
+                             rank_rows=plan.rank_rows.data_ptr(), rank_tokens=plan.rank_tokens.data_ptr(),
                              prof=self._prof_buffer("combine", i),
                              send_slot=plan.send_slot.data_ptr(), topk_idx=plan.topk_idx.data_ptr(), T=T,
                              meta_stride=plan.meta_stride, K=K, E=plan.num_experts, expand=int(plan.expand),
@@ -370,7 +366,7 @@ class CudaEngine:
                          expert_offsets=torch.empty((local + 1,), **i32), num_rows=torch.empty((1,), **i32))
             plan = RoutingPlan(num_tokens=T, num_experts=num_experts, num_topk=K, expand=True, alignment=1, meta_stride=0,
                                num_rows=cap, num_staged_rows=0, expert_counts_list=None, topk_idx=topk_idx[i], send_slot=None,
-                               slot_row=None, stage_meta=None, chunk_start=None, group_start=None, rank_tokens=None, rank_rows=None,
+                               slot_row=None, stage_meta=None, chunk_start=None, rank_tokens=None, rank_rows=None,
                                expert_counts=o["expert_counts"], expert_offsets=o["expert_offsets"],
                                recv_row_src=o["recv_row_src"], recv_w=o["recv_w"], recv_idx=None, has_weights=True)
             plan.num_rows_dev, plan.topk_w, plan.low_latency = o["num_rows"], topk_w[i], True

@@ -5,8 +5,9 @@ Parity: ``deep_ep/backends/mesh_clos/_elastic_layout.py`` of the reference
 :164-173).  The region list differs because the transport differs: a routing
 gather area, a dispatch staging area (one row per source token and
 destination rank), a combine partial area (one row per token and expert
-rank), the returned-weight area, one completion flag per (rank, group of four
-tokens) for dispatch and for combine, and the low-latency region.
+rank), the returned-weight area, the completion flags of dispatch (one per rank
+and pair of source tokens) and of combine (one per rank and block of four
+staged rows), and the low-latency region.
 """
 from __future__ import annotations
 
@@ -18,7 +19,8 @@ LL_MAX_TOKENS = 256
 LL_SIZE_HINT = 8 << 30
 ALIGN = 2 << 20
 CONTROL_BYTES = 64 << 10
-GROUP_TOKENS = 4           # tokens per completion flag of the high-throughput kernels (kGroupTokens in common.cuh)
+GROUP_TOKENS = 2           # source tokens per completion flag of the high-throughput dispatch (kGroupTokens in common.cuh)
+ROW_BLOCK = 4              # staged rows per completion flag of the high-throughput combine (kRowBlock in common.cuh)
 
 
 def align_up(value: int, alignment: int) -> int:
@@ -54,10 +56,10 @@ def workspace_bytes(world: int, max_tokens: int, hidden: int, topk: int, ll_byte
     """Python mirror of the native ``make_layout`` (checked against it in the tests)."""
     at = CONTROL_BYTES
     stage_row = align_up(hidden * 2, 128)
-    groups = -(-max_tokens // GROUP_TOKENS)
+    groups, row_blocks = -(-max_tokens // GROUP_TOKENS), -(-max_tokens // ROW_BLOCK)
     for size in (world * 4 * 4, world * max_tokens * topk * 4, world * max_tokens * topk * 4,
                  world * max_tokens * stage_row, max_tokens * world * hidden * 2, max_tokens * topk * 4,
-                 world * groups * 8, world * groups * 8, ll_bytes, mega_bytes):
+                 world * groups * 8, world * row_blocks * 8, ll_bytes, mega_bytes):
         at = align_up(at + size, 1024)
     return align_up(at, ALIGN)
 

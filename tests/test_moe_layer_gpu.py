@@ -71,11 +71,11 @@ def _run(rank, world, group, dev, grouped):
     torch.cuda.synchronize()
     ref, g1, g2 = _dense([i[0] for i in ins], [i[1] for i in ins], [i[2] for i in ins], full_w1, full_w2, grads, dev)
     ry, rdx, rdw = ref[rank]
-    checks = dict(y=torch.allclose(y.float(), ry, rtol=0.05, atol=0.05),
-                  dx=torch.allclose(x.grad.float(), rdx, rtol=0.05, atol=0.05),
-                  dw=torch.allclose(w.grad, rdw, rtol=0.05, atol=0.1),
-                  dw1=torch.allclose(layer.w1.grad.float(), g1[rank * L:(rank + 1) * L], rtol=0.05, atol=0.1),
-                  dw2=torch.allclose(layer.w2.grad.float(), g2[rank * L:(rank + 1) * L], rtol=0.05, atol=0.1),
+    def close(a, b):   # bf16 rounding of the products scales with the tensor, not with each element
+        return bool((a.float() - b).abs().max() <= 0.02 * b.abs().max())
+
+    checks = dict(y=close(y, ry), dx=close(x.grad, rdx), dw=close(w.grad, rdw),
+                  dw1=close(layer.w1.grad, g1[rank * L:(rank + 1) * L]), dw2=close(layer.w2.grad, g2[rank * L:(rank + 1) * L]),
                   dtypes=x.grad.dtype == torch.bfloat16 and w.grad.dtype == torch.float32)
     buf.destroy()
     return checks
