@@ -34,14 +34,14 @@ template <class T> T* ptr(const py::dict& d, const char* key) {
 }
 int geti(const py::dict& d, const char* key, int dflt = 0) { return d.contains(key) ? d[key].cast<int>() : dflt; }
 long long getl(const py::dict& d, const char* key, long long dflt = 0) { return d.contains(key) ? d[key].cast<long long>() : dflt; }
-float getf(const py::dict& d, const char* key, float dflt = 0.f) { return d.contains(key) ? d[key].cast<float>() : dflt; }
 
 RankCtx ctx_of(const py::handle& session) { return session.cast<Session&>().ctx(); }
 
 void op_notify(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
-               uintptr_t stream) {
+               uintptr_t stream, bool profile) {
   NotifyParams p{};
   p.lay = lay;
+  p.profile = profile ? 1 : 0;
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
   for (int i = 0; i < n; ++i) {
@@ -234,7 +234,8 @@ PYBIND11_MODULE(_C, m) {
                         reinterpret_cast<int*>(per_expert), reinterpret_cast<bool*>(in_rank), reinterpret_cast<cudaStream_t>(stream)),
           "ep_layout launch");
   });
-  m.def("notify", &op_notify);
+  m.def("notify", &op_notify, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("blocks"), py::arg("stream"),
+        py::arg("profile") = false);
   m.def("dispatch", &op_dispatch, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),
         py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);
   m.def("combine", &op_combine, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),

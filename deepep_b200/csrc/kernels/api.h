@@ -40,7 +40,7 @@ struct NotifyArgs {
   int* mailbox;                // mapped host memory: [0] rows, [1] staged rows, [2] max tokens, [3] epoch, [4..] counts
   long long rcap;
 };
-struct NotifyParams { WsLayout lay; NotifyArgs r[kMaxRanks]; };
+struct NotifyParams { WsLayout lay; int profile, pad; NotifyArgs r[kMaxRanks]; };   // profile: block 0 stamps its phases into Control::dbg[16..23]
 cudaError_t launch_notify(const NotifyParams& p, int nranks, int blocks, cudaStream_t stream);
 
 // ---------------------------------------------------------------- high-throughput dispatch

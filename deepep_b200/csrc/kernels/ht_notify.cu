@@ -64,6 +64,7 @@ __device__ void build_masks(TileMasks& m, const int* gidx_src, int tile, int T_r
   __syncthreads();
 }
 
+template <bool kProfile>
 __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_constant__ NotifyParams p) {
   cg::grid_group grid = cg::this_grid();
   const NotifyArgs& a = p.r[blockIdx.y];
@@ -83,9 +84,13 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
   __shared__ int s_base[kMaxExperts];                   // scratch: totals, then per-task row bases
   __shared__ int s_rows;
 
-  // phase stamps of block 0 (nanoseconds since kernel start) for diagnostics: Control::dbg[16..23]
-  const unsigned long long t_start = global_timer_ns();
-  auto stamp = [&](int i) { if (blockIdx.x == 0 && threadIdx.x == 0) ctl->dbg[16 + i] = global_timer_ns() - t_start; };
+  // profile instantiation only: phase stamps of block 0 (nanoseconds since kernel start) in Control::dbg[16..23]
+  unsigned long long t_start = 0;
+  if constexpr (kProfile) t_start = global_timer_ns();
+  auto stamp = [&](int i) {
+    if constexpr (kProfile)
+      if (blockIdx.x == 0 && threadIdx.x == 0) ctl->dbg[16 + i] = global_timer_ns() - t_start;
+  };
 
   // ---- A: publish my routing table into every peer (after they consumed the previous one)
   int ok = 1;
@@ -344,7 +349,8 @@ __global__ void __launch_bounds__(kNotifyThreads) ep_notify_kernel(const __grid_
 cudaError_t launch_notify(const NotifyParams& p, int nranks, int blocks, cudaStream_t stream) {
   dim3 grid(blocks, nranks), block(kNotifyThreads);
   void* args[] = {const_cast<NotifyParams*>(&p)};
-  return cudaLaunchCooperativeKernel((const void*)ep_notify_kernel, grid, block, args, 0, stream);
+  const void* fn = p.profile ? (const void*)ep_notify_kernel<true> : (const void*)ep_notify_kernel<false>;
+  return cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream);
 }
 
 }  // namespace dep

@@ -9,15 +9,17 @@
 
 namespace dep {
 
+constexpr int kLLParts = 4;   // column parts of a row, each with its own completion flag
+
 // Offsets inside the low-latency region of a workspace (relative to WsLayout::ll), for one bank.
 struct LLLayout {
   long long gather_hdr;   // int   [P][4]
   long long gather_idx;   // int   [P][M][K]
   long long gather_w;     // float [P][M][K]
   long long idx_flag;     // u64   [P]        routing table of source r has landed
-  long long row_flag;     // u64   [P][M]     staged row j of source r has landed
+  long long row_flag;     // u64   [P][M][kLLParts]  part p of staged row j of source r has landed
   long long stage;        // byte  [P][M][msg_bytes]
-  long long ret_flag;     // u64   [M][K]     returned row of (token, slot) has landed
+  long long ret_flag;     // u64   [M][K][kLLParts]  part p of the returned row of (token, slot) has landed
   long long ret;          // bf16  [M][K][H]
   long long bank_bytes;   // size of one bank; bank b starts at b * bank_bytes
   int msg_bytes, pad;
@@ -33,9 +35,9 @@ __host__ __device__ inline LLLayout make_ll_layout(int P, int M, int K, int H) {
   l.gather_idx = at; at = ll_align(at + (long long)P * M * K * 4);
   l.gather_w = at;   at = ll_align(at + (long long)P * M * K * 4);
   l.idx_flag = at;   at = ll_align(at + (long long)P * 8);
-  l.row_flag = at;   at = ll_align(at + (long long)P * M * 8);
+  l.row_flag = at;   at = ll_align(at + (long long)P * M * kLLParts * 8);
   l.stage = at;      at = ll_align(at + (long long)P * M * l.msg_bytes);
-  l.ret_flag = at;   at = ll_align(at + (long long)M * K * 8);
+  l.ret_flag = at;   at = ll_align(at + (long long)M * K * kLLParts * 8);
   l.ret = at;        at = ll_align(at + (long long)M * K * H * 2);
   l.bank_bytes = at;
   return l;
@@ -59,7 +61,7 @@ struct LLDispatchArgs {
   int* mailbox;                // mapped host memory (may be null): [0] rows, [3] epoch, [4..] counts
   long long capacity;          // rows available in recv_x
 };
-struct LLDispatchParams { WsLayout lay; LLDispatchArgs r[kMaxRanks]; };
+struct LLDispatchParams { WsLayout lay; int profile, pad; LLDispatchArgs r[kMaxRanks]; };   // profile: block 0 stamps its phases into Control::dbg[0..7]
 cudaError_t launch_ll_dispatch(const LLDispatchParams& p, int nranks, int blocks, cudaStream_t stream);
 
 struct LLCombineArgs {
@@ -72,7 +74,7 @@ struct LLCombineArgs {
   int T, E;
   __nv_bfloat16* out;          // [T][H]
 };
-struct LLCombineParams { WsLayout lay; LLCombineArgs r[kMaxRanks]; };
+struct LLCombineParams { WsLayout lay; int profile, pad; LLCombineArgs r[kMaxRanks]; };     // profile: the same into Control::dbg[8..15]
 cudaError_t launch_ll_combine(const LLCombineParams& p, int nranks, int blocks, cudaStream_t stream);
 
 }  // namespace dep

@@ -31,10 +31,11 @@ void check_ll_shape(const WsLayout& lay) {
 }
 
 void op_ll_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
-                    uintptr_t stream) {
+                    uintptr_t stream, bool profile) {
   check_ll_shape(lay);
   LLDispatchParams p{};
   p.lay = lay;
+  p.profile = profile ? 1 : 0;
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
   for (int i = 0; i < n; ++i) {
@@ -58,10 +59,11 @@ void op_ll_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions
 }
 
 void op_ll_combine(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int blocks,
-                   uintptr_t stream) {
+                   uintptr_t stream, bool profile) {
   check_ll_shape(lay);
   LLCombineParams p{};
   p.lay = lay;
+  p.profile = profile ? 1 : 0;
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
   for (int i = 0; i < n; ++i) {
@@ -79,6 +81,8 @@ void op_ll_combine(const WsLayout& lay, const std::vector<py::object>& sessions,
 
 void bind_low_latency(py::module_& m) {
   m.def("ll_region_bytes", &ll_region_bytes, py::arg("world"), py::arg("max_tokens"), py::arg("topk"), py::arg("hidden"));
-  m.def("ll_dispatch", &op_ll_dispatch);
-  m.def("ll_combine", &op_ll_combine);
+  m.def("ll_dispatch", &op_ll_dispatch, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("blocks"), py::arg("stream"),
+        py::arg("profile") = false);
+  m.def("ll_combine", &op_ll_combine, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("blocks"), py::arg("stream"),
+        py::arg("profile") = false);
 }

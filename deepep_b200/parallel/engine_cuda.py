@@ -126,13 +126,29 @@ class CudaEngine:
         self._timings.clear()
 
     def enable_device_profile(self, on: bool = True) -> None:
-        """Launch the profile instantiation of the high-throughput dispatch / combine kernels (``template <bool
-        kProfile>``): every block records its role, its start and end time, the time its first warp spent waiting for
+        """Launch the profile instantiation of the kernels (``template <bool kProfile>``).  Notify and the low-latency
+        kernels stamp the phases of their block 0 (read with ``phase_stamps``); in the high-throughput dispatch /
+        combine every block records its role, its start and end time, the time its first warp spent waiting for
         flags and the rows that warp moved.  The production instantiation carries none of that code.
         Parity: the reference's ``template <bool Profile>`` kernels (``csrc/kernels/dispatch/profile.hpp``,
         ``csrc/kernels/combine/profile.hpp``)."""
         self._device_profile = bool(on)
         self._prof.clear()
+
+    PHASE_STAMPS = {"ll_dispatch": (0, ("routes_read", "rows_sent", "tables_in", "layout_done", "rows_out", "last_block", "table_sent",
+                                        "first_row_stored")),
+                    "ll_combine": (8, ("entered", "rows_returned", "reduced", "last_block")),
+                    "notify": (16, ("table_sent", "tables_in", "histograms", "scans", "records", "done"))}
+
+    def phase_stamps(self, op: str, i: int = 0) -> dict:
+        """Phase stamps of block 0 of the last profiled launch of ``op`` (``"notify"``, ``"ll_dispatch"`` or
+        ``"ll_combine"``) on rank index ``i``: microseconds since the kernel started at which each phase was complete.
+        Only the profile instantiations of these kernels write stamps (``enable_device_profile``)."""
+        first, names = self.PHASE_STAMPS[op]
+        torch.cuda.synchronize(self.device)
+        words = torch.frombuffer(bytearray(self.sessions[i].read_control()), dtype=torch.int64)
+        at = self.C.control_dbg_offset // 8 + first
+        return {name: int(words[at + k]) / 1e3 for k, name in enumerate(names)}
 
     def _prof_buffer(self, op: str, i: int):
         if not self._device_profile:
@@ -257,7 +273,7 @@ class CudaEngine:
                              rank_matrix=_ptr(plan.rank_matrix)))
         # the layout pass is a chain of short phases over (source, tile) tasks: P x T / 64 of them, a few microseconds each
         nblocks = blocks or max(1, min(128, self.sm_count // self.n))
-        self._timed("notify", stream, lambda: C.notify(lay, self.sessions, args, nblocks, self._stream(stream)))
+        self._timed("notify", stream, lambda: C.notify(lay, self.sessions, args, nblocks, self._stream(stream), self._device_profile))
         if rank_matrix:       # the scratch is reused by the next call: keep this rank's per-chunk send prefixes with the plan
             for plan, sc in zip(plans, self._scratch):
                 tiles = -(-max(plan.num_tokens, 1) // C.chunk_tokens)
@@ -338,7 +354,7 @@ class CudaEngine:
 
     # ------------------------------------------------------------------ low latency
     def ll_blocks(self) -> int:
-        return max(1, min(96, self.sm_count // self.n))   # few rows per warp: latency, not bandwidth, is the goal
+        return max(1, min(128, self.sm_count // self.n))   # at most a part of a row or two per warp: latency is the goal
 
     def ll_dispatch(self, xs: Sequence, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[torch.Tensor], num_experts: int,
                     mode: int, cpu_sync: bool = True, stream=None, outputs: Optional[list] = None):
@@ -376,7 +392,8 @@ class CudaEngine:
                              recv_w=o["recv_w"].data_ptr(), recv_row_src=o["recv_row_src"].data_ptr(),
                              expert_counts=o["expert_counts"].data_ptr(), expert_offsets=o["expert_offsets"].data_ptr(),
                              num_rows=o["num_rows"].data_ptr(), use_mailbox=int(cpu_sync), capacity=cap))
-        self._timed("ll_dispatch", stream, lambda: self.C.ll_dispatch(lay, self.sessions, args, self.ll_blocks(), self._stream(stream)))
+        self._timed("ll_dispatch", stream, lambda: self.C.ll_dispatch(lay, self.sessions, args, self.ll_blocks(), self._stream(stream),
+                                                                             self._device_profile))
         if cpu_sync:
             (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
             self.check_status()
@@ -403,7 +420,8 @@ class CudaEngine:
             args.append(dict(x=xs[i].data_ptr(), recv_row_src=plan.recv_row_src.data_ptr(), num_rows=plan.num_rows_dev.data_ptr(),
                              topk_idx=plan.topk_idx.data_ptr(), topk_w=plan.topk_w.data_ptr(), T=plan.num_tokens,
                              E=plan.num_experts, out=out.data_ptr()))
-        self._timed("ll_combine", stream, lambda: self.C.ll_combine(lay, self.sessions, args, self.ll_blocks(), self._stream(stream)))
+        self._timed("ll_combine", stream, lambda: self.C.ll_combine(lay, self.sessions, args, self.ll_blocks(), self._stream(stream),
+                                                                           self._device_profile))
         return results
 
     def barrier(self, stream=None) -> None:

@@ -20,6 +20,7 @@ LL_SIZE_HINT = 8 << 30
 ALIGN = 2 << 20
 CONTROL_BYTES = 64 << 10
 GROUP_TOKENS = 2           # source tokens per completion flag of the high-throughput dispatch (kGroupTokens in common.cuh)
+LL_PARTS = 4               # column parts of a low-latency row, each with its own flag (kLLParts in ll_api.h)
 ROW_BLOCK = 4              # staged rows per completion flag of the high-throughput combine (kRowBlock in common.cuh)
 
 
@@ -39,15 +40,16 @@ def validate_hidden(hidden: int, fp8: bool = False) -> None:
 def ll_region_bytes(world: int, max_tokens: int, hidden: int, topk: int) -> int:
     """Bytes of the low-latency region (two banks); 0 when the buffer is too large for that path.
 
-    Mirror of ``make_ll_layout`` in ``csrc/kernels/ll_api.h``: routing gather tables, per-row flags,
-    one staging slot per (source rank, token), one return slot per (token, top-k slot).
+    Mirror of ``make_ll_layout`` in ``csrc/kernels/ll_api.h``: routing gather tables, one flag per column part of a
+    row, one staging slot per (source rank, token), one return slot per (token, top-k slot).
     """
     if max_tokens > LL_MAX_TOKENS or max_tokens <= 0:
         return 0
     msg = align_up(hidden * 2, 128)
     at = 0
-    for size in (world * 16, world * max_tokens * topk * 4, world * max_tokens * topk * 4, world * 8, world * max_tokens * 8,
-                 world * max_tokens * msg, max_tokens * topk * 8, max_tokens * topk * hidden * 2):
+    for size in (world * 16, world * max_tokens * topk * 4, world * max_tokens * topk * 4, world * 8,
+                 world * max_tokens * LL_PARTS * 8, world * max_tokens * msg, max_tokens * topk * LL_PARTS * 8,
+                 max_tokens * topk * hidden * 2):
         at = align_up(at + size, 1024)
     return 2 * at
 

@@ -142,3 +142,49 @@ def test_v1_buffer_on_one_gpu():
     torch.cuda.synchronize()
     assert rx3.shape[0] == worst and counts3 == [] and torch.equal(rx3[:rx.shape[0]], rx)
     buf.destroy()
+
+
+def test_high_throughput_without_host_sync_in_a_graph():
+    """``do_cpu_sync=False`` on the high-throughput path: nothing waits on the host, outputs have the worst-case row
+    count (valid rows first, per the handle's device-side cumulative counts), and the whole fresh dispatch + combine
+    replays from a CUDA graph with new inputs."""
+    from deepep_b200 import ElasticBuffer
+
+    dev = torch.device("cuda")
+    T, H, E, K = 200, 512, 8, 4
+    buf = ElasticBuffer(None, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True)
+    x = torch.zeros((T, H), dtype=torch.bfloat16, device=dev)
+    idx = torch.zeros((T, K), dtype=torch.int64, device=dev)
+    w = torch.zeros((T, K), dtype=torch.float32, device=dev)
+
+    def fill(seed):
+        xs, ii, ws = _inputs(1, T, H, E, K) if seed == 0 else (None, None, None)
+        g = torch.Generator().manual_seed(seed)
+        x.copy_(torch.randn((T, H), generator=g).bfloat16() if xs is None else xs[0])
+        idx.copy_(torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]) if ii is None else ii[0])
+        w.copy_(torch.rand((T, K), generator=g) if ws is None else ws[0])
+
+    def step():
+        rx, _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True, do_cpu_sync=False)
+        assert not handle.is_low_latency and handle.num_recv_tokens_per_expert_list is None
+        out, _, _ = buf.combine(rx, handle)
+        return rx, rw, handle.psum_num_recv_tokens_per_expert, out
+
+    fill(0)
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        rx, rw, psum, out = step()
+    assert rx.shape[0] == T * min(K, E)                       # worst case: every token on every one of its experts
+    for seed in (3, 4):
+        fill(seed)
+        graph.replay()
+        torch.cuda.synchronize()
+        ref, lays = R.dispatch([x.cpu()], [idx.cpu()], [w.cpu()], E, do_expand=True)
+        rows = int(psum[-1])
+        assert rows == ref[0][0].shape[0] and bits_equal(rx[:rows], ref[0][0]) and torch.equal(rw[:rows].cpu(), ref[0][2])
+        cref = R.combine([ref[0][0]], lays, [T], K)
+        assert bits_equal(out, cref[0][0])
+    buf.destroy()
