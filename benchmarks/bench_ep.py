@@ -114,7 +114,7 @@ def main() -> int:
         if it >= cfg.warmup:
             samples.append(max(us, 1e-3))
     if cuda and (args.sweep_blocks or args.device_profile):
-        sweep(buf, cfg, x, handle, back, routes, rank, world, args)
+        sweep(buf, cfg, x, handle, back, routes, rank, world, args, fresh)
     gathered = buf.control.all_gather_object(samples) if world > 1 else [samples]
     record = W.complete(W.plan(cfg), gathered, W.traffic(cfg, [r[0] for r in routes])["effective_bytes"], correctness)
     record["engine"] = "cuda" if cuda else "cpu"
@@ -131,7 +131,7 @@ def main() -> int:
     return 0 if correctness != "failed" else 1
 
 
-def sweep(buf, cfg, x, handle, back, routes, rank, world, args):
+def sweep(buf, cfg, x, handle, back, routes, rank, world, args, fresh):
     """Cached dispatch and combine under explicit SM splits (engine level: the public API only splits the combine)."""
     import torch.distributed as dist
 
@@ -176,6 +176,8 @@ def sweep(buf, cfg, x, handle, back, routes, rank, world, args):
                     nvlink_out_GBps=round(out_bytes[op] / (us * 1e-6) / 1e9, 1))
     if args.device_profile:
         eng.enable_device_profile(True)
+        fresh()                                   # the routing layout pass stamps its phases
+        say(profile="notify", phases_us={k: round(v, 1) for k, v in eng.phase_stamps("notify").items()})
         eng.dispatch([x], [plan], mode)
         eng.combine([back], [plan], [None])
         prof = eng.pop_device_profile()

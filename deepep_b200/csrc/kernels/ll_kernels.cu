@@ -82,7 +82,8 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, M = lay.max_tokens, K = lay.topk, H = lay.hidden, E = a.E, Lx = E / P;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
-  const int gw = blockIdx.x * nwarps + warp, total_warps = gridDim.x * nwarps;
+  // consecutive work items go to different SMs, so a short list of items spreads over the whole GPU
+  const int gw = warp * gridDim.x + blockIdx.x, total_warps = gridDim.x * nwarps;
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpLLDispatch] + 1;
   const LLLayout ll = make_ll_layout(P, M, K, H);
@@ -368,7 +369,8 @@ __global__ void __launch_bounds__(kLLThreads) ep_combine_ll_kernel(const __grid_
   const RankCtx& ctx = a.ctx;
   const int P = ctx.world, me = ctx.rank, M = lay.max_tokens, K = lay.topk, H = lay.hidden;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kLLThreads / 32;
-  const int gw = blockIdx.x * nwarps + warp, total_warps = gridDim.x * nwarps;
+  // consecutive work items go to different SMs, so a short list of items spreads over the whole GPU
+  const int gw = warp * gridDim.x + blockIdx.x, total_warps = gridDim.x * nwarps;
   Control* ctl = control_of(ctx.ws[me]);
   const unsigned long long epoch = ctl->epoch[kOpLLCombine] + 1;
   const LLLayout ll = make_ll_layout(P, M, K, H);

@@ -30,7 +30,8 @@ enum GemmEpilogue : int {
 
 struct MegaGemmParams {
   CUtensorMap tmap_a;        // activations [rows_pad, K] e4m3, box 128 x 128, 128-byte swizzle
-  CUtensorMap tmap_b;        // weights, e2m1 pairs, tiled as [(rows / 128) * (K / 128) * 128, 128 values]; widened to bytes by the copy engine
+  CUtensorMap tmap_b;        // weights, tiled as [(rows / 128) * (K / 128) * 128, 128 values]: e2m1 pairs that the copy engine widens
+                             // to one byte per value, or e4m3 bytes (b_fp8)
   const uint8_t* sfa;        // chunked scales of A
   const uint8_t* sfb;        // chunked scales of B
   const int* mtile_expert;   // [max_mtiles] local expert of each 128-row tile
@@ -40,7 +41,7 @@ struct MegaGemmParams {
   int epi, b_tx_bytes;
   // kEpiStoreF32
   float* c;
-  int ldc, pad0;
+  int ldc, b_fp8;            // b_fp8: the weights are e4m3 (A8W8) instead of e2m1 (A8W4)
   // kEpiSwigluQuant
   uint8_t* a2;               // [rows_pad, inter] e4m3
   uint8_t* a2_sf;            // chunked scales of a2

@@ -1,7 +1,8 @@
 // Grouped block-scaled GEMM phase on the 5th-generation tensor cores (tcgen05 + tensor memory):
 //   C[rows of expert e, n] = sum_k A[row, k] * B[e][n, k]
 // A: e4m3 activations with one ue8m0 scale per 32 values of K; B: e2m1 weights (two per byte in
-// global memory, widened to one byte per value by the copy engine) with ue8m0 scales per 32.
+// global memory, widened to one byte per value by the copy engine) or e4m3 weights, with ue8m0
+// scales per 32.
 //
 // `gemm_phase` is run by a whole CTA of kGemmThreads threads, one CTA per SM, warp-specialised:
 //   warp 0     one lane issues the TMA tile loads (A, B) and bulk loads (scale chunks) of a stage
@@ -210,12 +211,15 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
   } else if (warp == 1) {
     // ============================================================ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, /*e4m3*/ 0, /*e2m1*/ 5);
+      // A is e4m3 (format 0); B is e2m1 (5) or e4m3 (0), per GEMM
+      const uint32_t idesc1 = umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, 0, g1.b_fp8 ? 0 : 5);
+      const uint32_t idesc2 = g2 ? umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, 0, g2->b_fp8 ? 0 : 5) : idesc1;
       uint32_t it = 0;
       for (uint32_t local_tile = 0;; ++local_tile) {
         const int tile = fetch_tile(bars, local_tile, failed);
         if (tile < 0) break;
         const int k_steps = tile >= tiles1 ? g2->k_steps : g1.k_steps;
+        const uint32_t idesc = tile >= tiles1 ? idesc2 : idesc1;
         if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed)) break;
         umma::fence_after_sync();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {

@@ -33,8 +33,9 @@ void fill_gemm(MegaGemmParams& p, const py::dict& d, py::object session) {
   if (rows_pad % kGemmBM || k % kGemmBK || b_rows % kGemmBN) throw std::invalid_argument("rows and K must be multiples of 128, weight rows of 256");
   const char* err = nullptr;
   if (!encode_operand_map(&p.tmap_a, ptr<const void>(d, "a"), rows_pad, k, false, &err)) throw std::runtime_error(err);
-  // weights are stored tiled: every (128-row, 128-K) block is one contiguous run of 128 rows x 64 bytes
-  if (!encode_operand_map(&p.tmap_b, ptr<const void>(d, "b"), b_rows * (k / kGemmBK), kGemmBK, true, &err)) throw std::runtime_error(err);
+  // weights are stored tiled: every (128-row, 128-K) block is one contiguous run of 128 rows x 64 (e2m1) or 128 (e4m3) bytes
+  p.b_fp8 = geti(d, "b_fp8", 0) ? 1 : 0;
+  if (!encode_operand_map(&p.tmap_b, ptr<const void>(d, "b"), b_rows * (k / kGemmBK), kGemmBK, !p.b_fp8, &err)) throw std::runtime_error(err);
   p.sfa = ptr<const uint8_t>(d, "sfa"); p.sfb = ptr<const uint8_t>(d, "sfb");
   p.mtile_expert = ptr<const int>(d, "mtile_expert"); p.num_mtiles = ptr<const int>(d, "num_mtiles");
   p.a_ready = ptr<const int>(d, "a_ready");
@@ -42,7 +43,7 @@ void fill_gemm(MegaGemmParams& p, const py::dict& d, py::object session) {
   p.n_total = geti(d, "n_total"); p.n_tiles = p.n_total / kGemmBN; p.k_steps = (int)(k / kGemmBK);
   if (p.n_total % kGemmBN) throw std::invalid_argument("output width must be a multiple of 256");
   p.epi = geti(d, "epi");
-  p.b_tx_bytes = geti(d, "b_tx_bytes", 128 * kGemmBK / 2);   // bytes counted per 128-row fp4 box
+  p.b_tx_bytes = geti(d, "b_tx_bytes", p.b_fp8 ? 128 * kGemmBK : 128 * kGemmBK / 2);   // bytes counted per 128-row box of weights
   p.c = ptr<float>(d, "c"); p.ldc = geti(d, "ldc");
   p.a2 = ptr<uint8_t>(d, "a2"); p.a2_sf = ptr<uint8_t>(d, "a2_sf"); p.inter = geti(d, "inter");
   p.row_src = ptr<const int>(d, "row_src");

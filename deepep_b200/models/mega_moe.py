@@ -40,11 +40,12 @@ def _view(ptr: int, nbytes: int, device) -> torch.Tensor:
 @dataclass
 class MegaWeights:
     """One projection of all local experts in kernel layout."""
-    packed: torch.Tensor        # e2m1 pairs (low nibble first), tiled: [(L * N / 128) * (K / 128) * 128, 64] uint8
+    packed: torch.Tensor        # tiled uint8 [(L * N / 128) * (K / 128) * 128, 64 | 128]: e2m1 pairs (low nibble first) or e4m3
     sf_chunks: torch.Tensor     # 512-byte scale chunks
     experts: int
     n: int
     k: int
+    fp8: bool = False           # e4m3 weights (mma_type "fp8xfp8") instead of e2m1 ("fp8xfp4")
 
 
 def _sf_chunks(sf: torch.Tensor) -> torch.Tensor:
@@ -57,24 +58,31 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
                                    device=None) -> Tuple[MegaWeights, MegaWeights]:
     """Rearrange ``(w1 [L, 2I, H/2], w1_sf [L, 2I, H/32])`` and ``(w2 [L, H, I/2], w2_sf [L, H, I/32])`` for the kernel.
 
+    Weights are packed e2m1 pairs (uint8, two values per byte: ``mma_type="fp8xfp4"``) or, for ``mma_type="fp8xfp8"``,
+    e4m3 tensors ``w1 [L, 2I, H]`` / ``w2 [L, H, I]``; the scales are ue8m0 per 32 values either way.
     W1 rows are regrouped so every 256-row tile holds 128 gate rows followed by the 128 matching up rows
     (gate = first I rows, up = last I rows); scales go into the tensor-memory chunk layout.
     """
     (w1, w1_sf), (w2, w2_sf) = l1_weights, l2_weights
+    fp8 = w1.dtype == torch.float8_e4m3fn
+    if (w2.dtype == torch.float8_e4m3fn) != fp8:
+        raise ValueError("both projections must hold the same kind of weights")
+    per_byte = 1 if fp8 else 2
     L, n1, hk = w1.shape
-    inter, hidden = n1 // 2, hk * 2
-    assert w2.shape == (L, hidden, inter // 2), "w2 must be [L, H, I / 2]"
+    inter, hidden = n1 // 2, hk * per_byte
+    assert w2.shape == (L, hidden, inter // per_byte), "w2 must be [L, H, I / 2] (e2m1 pairs) or [L, H, I] (e4m3)"
     assert hidden % 256 == 0 and inter % 128 == 0, "hidden must be a multiple of 256, the intermediate size of 128"
     device = device or w1.device
     order = torch.arange(n1).view(2, inter // 128, 128).permute(1, 0, 2).reshape(-1)   # tile j: gate[128j:128j+128], up[128j:128j+128]
-    from ..oracle.megamoe import tile_fp4_rows
+    from ..oracle.megamoe import tile_rows
 
-    w1t = tile_fp4_rows(w1.view(torch.uint8)[:, order].reshape(L * n1, hk).contiguous())
+    width = 128 // per_byte       # bytes of 128 K-values
+    w1t = tile_rows(w1.view(torch.uint8)[:, order].reshape(L * n1, hk).contiguous(), width)
     w1_sft = w1_sf.view(torch.uint8).reshape(L, n1, hidden // 32)[:, order].reshape(L * n1, hidden // 32)
-    w2t = tile_fp4_rows(w2.view(torch.uint8).reshape(L * hidden, inter // 2).contiguous())
+    w2t = tile_rows(w2.view(torch.uint8).reshape(L * hidden, inter // per_byte).contiguous(), width)
     w2_sft = w2_sf.view(torch.uint8).reshape(L * hidden, inter // 32)
-    return (MegaWeights(w1t.to(device), _sf_chunks(w1_sft).to(device), L, n1, hidden),
-            MegaWeights(w2t.to(device), _sf_chunks(w2_sft).to(device), L, hidden, inter))
+    return (MegaWeights(w1t.to(device), _sf_chunks(w1_sft).to(device), L, n1, hidden, fp8),
+            MegaWeights(w2t.to(device), _sf_chunks(w2_sft).to(device), L, hidden, inter, fp8))
 
 
 class MegaEngine:
@@ -160,9 +168,11 @@ class MegaEngine:
                           error_flag=sc["err"].data_ptr())
             gemm1_args.append(dict(common, a=sc["a1"].data_ptr(), sfa=sc["a1_sf"].data_ptr(), b=w1.packed.data_ptr(),
                                    sfb=w1.sf_chunks.data_ptr(), k=self.H, b_rows=w1.experts * w1.n, n_total=w1.n, epi=1,
+                                   b_fp8=int(w1.fp8),
                                    a2=sc["a2"].data_ptr(), a2_sf=sc["a2_sf"].data_ptr(), inter=self.I))
             gemm2_args.append(dict(common, a=sc["a2"].data_ptr(), sfa=sc["a2_sf"].data_ptr(), b=w2.packed.data_ptr(),
                                    sfb=w2.sf_chunks.data_ptr(), k=self.I, b_rows=w2.experts * w2.n, n_total=w2.n, epi=2,
+                                   b_fp8=int(w2.fp8),
                                    row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M,
                                    topk=self.K + self.S, hidden=self.H))
         if fused:
@@ -197,9 +207,8 @@ class SymmBuffer:
                  intermediate_hidden: int, *, num_shared_experts: int = 0, mma_type: str = "fp8xfp4", activation: str = "swiglu",
                  rank: Optional[int] = None, world_size: Optional[int] = None, device=None,
                  num_gpu_timeout_secs: float = 100, num_sms: int = 0):
-        if mma_type != "fp8xfp4":
-            raise NotImplementedError("only e4m3 activations x e2m1 weights (mma_type='fp8xfp4') are implemented; "
-                                      "'fp8xfp8' weights are not")
+        if mma_type not in ("fp8xfp4", "fp8xfp8"):
+            raise ValueError("mma_type must be 'fp8xfp4' (e2m1 weights) or 'fp8xfp8' (e4m3 weights)")
         if activation != "swiglu":
             raise NotImplementedError("only SwiGLU is implemented")
         from ..parallel.runtime import ControlPlane, Runtime
@@ -268,10 +277,10 @@ class SymmBuffer:
             return routed
         key = (routed.packed.data_ptr(), shared.packed.data_ptr())
         if key not in self._joined:
-            if (shared.n, shared.k) != (routed.n, routed.k):
-                raise ValueError("shared experts must have the shapes of the routed experts")
+            if (shared.n, shared.k, shared.fp8) != (routed.n, routed.k, routed.fp8):
+                raise ValueError("shared experts must have the shapes and the weight type of the routed experts")
             self._joined[key] = MegaWeights(torch.cat([routed.packed, shared.packed]), torch.cat([routed.sf_chunks, shared.sf_chunks]),
-                                            routed.experts + shared.experts, routed.n, routed.k)
+                                            routed.experts + shared.experts, routed.n, routed.k, routed.fp8)
         return self._joined[key]
 
     def validate_inputs(self, batch_size: int) -> None:
@@ -322,6 +331,8 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaW
         raise ValueError("the batch must be non-empty and fit the buffer")
     if x is not None and (x.dtype != torch.bfloat16 or tuple(x.shape) != (bs, sym_buffer.hidden) or not x.is_contiguous()):
         raise ValueError("the x override must be contiguous bf16 [batch, hidden]; omit x for buffered fp8 input")
+    if l1_weights.fp8 != (sym_buffer.mma_type == "fp8xfp8") or l2_weights.fp8 != l1_weights.fp8:
+        raise ValueError(f"the buffer was built for mma_type={sym_buffer.mma_type!r}; the weights are of the other kind")
     if l1_weights.k != sym_buffer.hidden or l1_weights.n != 2 * sym_buffer.intermediate_hidden:
         raise ValueError("l1 weights do not match the buffer's hidden / intermediate sizes")
     if l1_weights.experts * sym_buffer.world_size != sym_buffer.num_experts:

@@ -17,7 +17,8 @@ Each op is ONE persistent cooperative CUDA kernel per rank (``csrc/kernels/gmm_f
 peer loads / stores issued from inside the kernel that runs the tcgen05 grouped GEMM.  Without a GPU the same API
 runs on a CPU engine (object all-gather + ``torch.matmul``), which is what the CPU tests exercise.
 
-``tiling=`` is accepted for signature compatibility; the kernel has one tile shape (256 x 256 x 64).
+``tiling=`` names the tile shape to run; the kernel is built for one (256 x 256 x 64, see ``load_tiling_config``), so
+any other request is rejected instead of being ignored.
 """
 from __future__ import annotations
 
@@ -252,10 +253,32 @@ def symmetric_output(rows: int, n: int) -> torch.Tensor:
     return _GROUP.engine.symmetric_output(0, rows, n)
 
 
+TILE_SHAPE = {"m": 256, "n": 256, "k": 64}
+
+
 def load_tiling_config(path=None) -> Mapping[str, int]:
-    """The kernel has a single tile shape; returns it (the reference loads a measured search result here)."""
-    del path
-    return {"m": 256, "n": 256, "k": 64}
+    """The kernel has a single tile shape; returns it (the reference loads a measured search result here).  A JSON file
+    at ``path`` is read and checked against that shape, so a configuration written for another build fails early."""
+    if path is not None:
+        import json
+
+        with open(path) as fh:
+            _check_tiling(json.load(fh))
+    return dict(TILE_SHAPE)
+
+
+def _check_tiling(tiling: Optional[Mapping[str, int]]) -> None:
+    """``tiling`` may name the tile shape (keys ``m``, ``n``, ``k``; any subset): only the built shape is available."""
+    if tiling is None:
+        return
+    if not isinstance(tiling, Mapping):
+        raise TypeError("tiling must be a mapping with the keys m, n, k")
+    unknown = set(tiling) - set(TILE_SHAPE)
+    if unknown:
+        raise ValueError(f"unknown tiling keys {sorted(unknown)}; expected a subset of {sorted(TILE_SHAPE)}")
+    for key, value in tiling.items():
+        if int(value) != TILE_SHAPE[key]:
+            raise ValueError(f"tiling {key}={value} is not available: the kernel is built for {TILE_SHAPE}")
 
 
 # ------------------------------------------------------------------------------------------------ ops
@@ -300,7 +323,7 @@ def alltoallv_gmm(x: torch.Tensor, weight: torch.Tensor, local_tokens_per_expert
                   received_rows: Optional[int] = None, out: Optional[torch.Tensor] = None, output_all_to_allv: bool = False,
                   all_to_allv_out: Optional[torch.Tensor] = None, tiling: Optional[Mapping[str, int]] = None):
     """Dispatch rows to their experts' ranks and apply the destination rank's grouped matmuls (one kernel)."""
-    del tiling
+    _check_tiling(tiling)
     g = _GROUP
     cfg = get_config()
     _check_operands(x, weight, ep_size, expert_num, cfg)
@@ -345,7 +368,7 @@ def gmm_alltoallv(x: torch.Tensor, weight: torch.Tensor, local_tokens_per_expert
                   global_tokens_per_local_expert: RouteInput, *, ep_size: int, expert_num: int,
                   out: Optional[torch.Tensor] = None, tiling: Optional[Mapping[str, int]] = None) -> torch.Tensor:
     """Apply this rank's grouped matmuls and return the products to the ranks their rows came from (one kernel)."""
-    del tiling
+    _check_tiling(tiling)
     g = _GROUP
     cfg = get_config()
     _check_operands(x, weight, ep_size, expert_num, cfg)

@@ -42,6 +42,30 @@ def unpack_fp4(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     return values * torch.exp2(scales.reshape(*values.shape[:-1], -1).float() - 127).repeat_interleave(32, dim=-1)
 
 
+def unpack_weights(w: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """Weights of either kind -> fp32: packed e2m1 pairs (uint8 [..., K / 2]) or e4m3 ([..., K]), ue8m0 scales per 32."""
+    if w.dtype == torch.float8_e4m3fn:
+        return dequantize_mxfp8(w, scales.reshape(*w.shape[:-1], -1))
+    return unpack_fp4(w, scales)
+
+
+def make_fp8_weights(experts: int, hidden: int, intermediate: int, seed: int):
+    """Random e4m3 weights with ue8m0 scales per 32 (A8W8): ((w1 [E, 2I, H], w1_sf [E, 2I, H / 32]), (w2, w2_sf))."""
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for n, k in ((2 * intermediate, hidden), (hidden, intermediate)):
+        w = torch.randn((experts, n, k), generator=g) * (k ** -0.5)
+        out.append(quantize_mxfp8(w))
+    return tuple(out)
+
+
+def tile_rows(rows: torch.Tensor, width: int) -> torch.Tensor:
+    """[rows, bytes per row] uint8 -> every (128-row, `width`-byte) block contiguous (width = bytes of 128 K-values)."""
+    n, kb = rows.shape
+    assert n % 128 == 0 and kb % width == 0
+    return rows.view(n // 128, 128, kb // width, width).permute(0, 2, 1, 3).contiguous().view(-1, width)
+
+
 def make_weights(experts: int, hidden: int, intermediate: int, seed: int):
     """Random packed e2m1 weights with non-uniform ue8m0 scales: ((w1, w1_sf), (w2, w2_sf))."""
     g = torch.Generator().manual_seed(seed)
@@ -67,10 +91,10 @@ def mega_moe_reference(xs: Sequence[Tuple[torch.Tensor, torch.Tensor]], topk_idx
     """All-rank forward.  xs[r] = (e4m3 [T, H], ue8m0 [T, H / 32]); l1/l2 = (packed, scales) for all experts.
     ``shared_l1`` / ``shared_l2``: weights of the shared experts (the same on every rank); every token passes through
     each of them with weight one, after its routed experts (``golden.py:160-165`` of the reference)."""
-    w1 = unpack_fp4(*l1)
-    w2 = unpack_fp4(*l2)
-    s1 = None if shared_l1 is None else unpack_fp4(*shared_l1)
-    s2 = None if shared_l2 is None else unpack_fp4(*shared_l2)
+    w1 = unpack_weights(*l1)
+    w2 = unpack_weights(*l2)
+    s1 = None if shared_l1 is None else unpack_weights(*shared_l1)
+    s2 = None if shared_l2 is None else unpack_weights(*shared_l2)
     outs = []
     for (codes, sf), idx, w in zip(xs, topk_idx, topk_w):
         x = dequantize_mxfp8(codes, sf)
@@ -101,10 +125,8 @@ def to_sf_chunks(sf: torch.Tensor) -> torch.Tensor:
 def tile_fp4_rows(packed: torch.Tensor) -> torch.Tensor:
     """[rows, K / 2] packed e2m1 -> [(rows / 128) * (K / 128) * 128, 64]: every (128-row, 128-K) block becomes 8 KB of
     contiguous memory, so one tile load of the GEMM reads one contiguous block instead of 128 strided 64-byte pieces."""
-    rows, kb = packed.shape
-    assert rows % 128 == 0 and kb % 64 == 0
-    return packed.view(rows // 128, 128, kb // 64, 64).permute(0, 2, 1, 3).contiguous().view(-1, 64)
+    return tile_rows(packed, 64)
 
 
-__all__ = ["tile_fp4_rows", "bf16", "dequantize_mxfp8", "expert_forward", "make_weights", "mega_moe_reference", "quantize_mxfp8",
+__all__ = ["tile_fp4_rows", "tile_rows", "unpack_weights", "make_fp8_weights", "bf16", "dequantize_mxfp8", "expert_forward", "make_weights", "mega_moe_reference", "quantize_mxfp8",
            "to_sf_chunks", "unpack_fp4"]

@@ -65,3 +65,27 @@ def test_public_api_on_two_gloo_ranks():
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
     assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def test_tiling_argument_is_checked(tmp_path):
+    """``tiling=`` is honoured: the built tile shape passes, anything else is rejected (never silently ignored)."""
+    import json
+
+    from deepep_b200.ops import ep_gmm_fused as G
+
+    shape = G.load_tiling_config()
+    assert shape == {"m": 256, "n": 256, "k": 64}
+    G._check_tiling(None)
+    G._check_tiling({"m": 256})
+    with pytest.raises(ValueError, match="not available"):
+        G._check_tiling({"m": 128, "n": 256})
+    with pytest.raises(ValueError, match="unknown tiling keys"):
+        G._check_tiling({"rows": 256})
+    with pytest.raises(TypeError):
+        G._check_tiling([256, 256, 64])
+    good, bad = tmp_path / "good.json", tmp_path / "bad.json"
+    good.write_text(json.dumps(shape))
+    bad.write_text(json.dumps({"k": 128}))
+    assert G.load_tiling_config(good) == shape
+    with pytest.raises(ValueError):
+        G.load_tiling_config(bad)

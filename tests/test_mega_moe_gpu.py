@@ -170,3 +170,33 @@ def test_shared_experts_on_two_virtual_ranks():
         torch.cuda.synchronize()
         for s in sessions:
             s.close()
+
+
+def test_fp8_weights_public_api():
+    """``mma_type="fp8xfp8"``: e4m3 weights with ue8m0 scales per 32 (routed and shared) through the same fused kernel."""
+    from deepep_b200.models.mega_moe import SymmBuffer, fp8_fp4_mega_moe, transform_weights_for_mega_moe
+
+    dev = torch.device("cuda")
+    T, H, I, E, K, S = 160, 512, 256, 4, 2, 1
+    l1, l2 = O.make_fp8_weights(E, H, I, 21)
+    sl1, sl2 = O.make_fp8_weights(S, H, I, 22)
+    x = torch.randn((T, H), generator=torch.Generator().manual_seed(5)).bfloat16()
+    idx, w = make_routes("random", T, E, K, 1, 9), make_weights(T, K, 4)
+    ref = O.mega_moe_reference([O.quantize_mxfp8(x)], [idx], [w], l1, l2, E, sl1, sl2)[0]
+    buf = SymmBuffer(None, E, 256, K, H, I, num_shared_experts=S, mma_type="fp8xfp8")
+    try:
+        w1, w2 = transform_weights_for_mega_moe(l1, l2, device=dev)
+        sw1, sw2 = transform_weights_for_mega_moe(sl1, sl2, device=dev)
+        assert w1.fp8 and w2.fp8 and w1.packed.shape[1] == 128
+        buf.topk_idx[:T].copy_(idx.to(torch.int32)); buf.topk_weights[:T].copy_(w)
+        y = torch.zeros((T, H), dtype=torch.bfloat16, device=dev)
+        for fused in (True, False):
+            y.zero_()
+            fp8_fp4_mega_moe(y, w1, w2, buf, sw1, sw2, x=x.to(dev), fused=fused, check=True)
+            ok, bad, worst = _mixed_error_ok(y.cpu(), ref)
+            assert ok, f"fused={fused}: {bad:.4f} of elements off, worst relative error {worst:.4f}"
+        e2m1 = transform_weights_for_mega_moe(*O.make_weights(E, H, I, 3), device=dev)
+        with pytest.raises(ValueError, match="mma_type"):
+            fp8_fp4_mega_moe(y, e2m1[0], e2m1[1], buf, sw1, sw2)          # e2m1 weights on an fp8xfp8 buffer
+    finally:
+        buf.destroy()
