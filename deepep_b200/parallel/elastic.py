@@ -112,8 +112,9 @@ class ElasticBuffer:
         global _next_buffer_id
         del num_cpu_bytes, allow_hybrid_mode, allow_multiple_reduction, prefer_overlap_with_compute, sl_idx
         del num_allocated_qps, use_1g_huge_pages, rootinfo_path, combine_only
-        if machine_type not in ("auto", None, "nvswitch", "b200"):
-            raise ValueError("machine_type must be 'auto' or 'nvswitch': one NVLink/NVSwitch domain is the only topology")
+        if machine_type not in ("auto", None, "nvswitch", "b200", "single", "cpu"):
+            raise ValueError("machine_type must be 'auto', 'nvswitch', 'single' or 'cpu': one NVLink/NVSwitch domain is the "
+                             "only multi-GPU topology")
         if bootstrap not in ("default", "auto", "group", "store"):
             raise ValueError("bootstrap must be 'default', 'group' or 'store'")
         if num_max_tokens_per_rank <= 0 or hidden <= 0 or num_topk <= 0:
@@ -139,6 +140,13 @@ class ElasticBuffer:
         self.on_cuda = torch.cuda.is_available() and (
             self.control.backend() != "gloo" or (device is not None and torch.device(device).type == "cuda"))
         self.runtime: Optional[Runtime] = None
+        # what the ranks run on: detected on every rank, exchanged and checked by all of them before memory is shared
+        from . import topology
+
+        cuda_device = None
+        if self.on_cuda:
+            cuda_device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.machine_type = topology.agree(self.control, cuda_device, machine_type)
         if self.on_cuda:
             from ..ops import require_native
             from .engine_cuda import CudaEngine
