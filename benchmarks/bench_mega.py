@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--accuracy", action="store_true", help="compare with the CPU golden instead of timing")
     ap.add_argument("--golden-dir", default=os.path.join(ROOT, "benchmarks", ".golden_cache"))
     ap.add_argument("--no-profiler", action="store_true", help="skip the torch.profiler breakdown (needed under ncu)")
+    ap.add_argument("--pairs", choices=["auto", "0", "1"], default=None, help="CTA pairs in the fused kernel (default: the engine's rule)")
+    ap.add_argument("--phases", action="store_true", help="one extra launch with the per-CTA phase timer; prints the breakdown")
     args = ap.parse_args()
     from deepep_b200.models.mega_moe import MegaEngine, MegaWeights
     from deepep_b200.ops import load_native
@@ -44,6 +46,8 @@ def main():
     for s in sessions:
         s.attach_peers([q.workspace for q in sessions])
     eng = MegaEngine(sessions, layout, dev, E, I)
+    if args.pairs is not None:
+        eng.pairs = args.pairs
     g = torch.Generator(device="cuda").manual_seed(0)
     w1 = [MegaWeights(torch.randint(0, 256, (L * 2 * I * (H // 128), 64), dtype=torch.uint8, device=dev, generator=g),
                       torch.full((L * 2 * I // 128 * (H // 128) * 512,), 118, dtype=torch.uint8, device=dev), L, 2 * I, H) for _ in range(P)]
@@ -82,11 +86,19 @@ def main():
         for evt in prof.events():
             if evt.device_time > 0:
                 kern.setdefault(evt.name.split("(")[0][-40:], []).append(evt.device_time)
+    phases = None
+    if args.phases and not args.unfused:
+        from deepep_b200.models.mega_tools import parse_timer
+
+        timer = torch.zeros((eng.sm_count, C.mega_timer_words), dtype=torch.int64, device=dev)
+        eng.forward(ys, [T] * P, w1, w2, fused=True, timer=timer)
+        torch.cuda.synchronize()
+        phases = {k: round(v, 1) if isinstance(v, float) else v for k, v in parse_timer(timer).items()}
     rows = P * T * K
     flops = 2.0 * rows * (2 * I) * H + 2.0 * rows * H * I
     print(json.dumps({"world": P, "tokens": T, "hidden": H, "inter": I, "experts": E, "topk": K, "total_us": total_us,
-                      "tokens_per_s": P * T / (total_us * 1e-6), "tflops": flops / (total_us * 1e-6) / 1e12,
-                      "kernels_us": {k: v for k, v in kern.items()}}))
+                      "tokens_per_s": P * T / (total_us * 1e-6), "tflops": flops / (total_us * 1e-6) / 1e12, "cta_pairs": bool(eng.use_pairs([T] * P)) and not args.unfused,
+                      "kernels_us": {k: v for k, v in kern.items()}, **({"phases_us": phases} if phases else {})}))
     torch.cuda.synchronize()
     for s_ in sessions:
         s_.close()

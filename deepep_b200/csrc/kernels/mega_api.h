@@ -32,6 +32,7 @@ struct MegaGemmParams {
   CUtensorMap tmap_a;        // activations [rows_pad, K] e4m3, box 128 x 128, 128-byte swizzle
   CUtensorMap tmap_b;        // weights, tiled as [(rows / 128) * (K / 128) * 128, 128 values]: e2m1 pairs that the copy engine widens
                              // to one byte per value, or e4m3 bytes (b_fp8)
+  CUtensorMap tmap_sfa, tmap_sfb;   // the chunked scales as [chunks][512 B] (CTA pairs load them through the copy engine's tile path)
   const uint8_t* sfa;        // chunked scales of A
   const uint8_t* sfb;        // chunked scales of B
   const int* mtile_expert;   // [max_mtiles] local expert of each 128-row tile
@@ -39,6 +40,7 @@ struct MegaGemmParams {
   const int* num_mtiles;     // device scalar: tiles in use
   int max_mtiles, n_tiles, k_steps, n_total;
   int epi, b_tx_bytes;
+  int pair, pad3;            // stand-alone launch only: run as CTA pairs (the tile list must pair row blocks 2j, 2j + 1 of one expert)
   // kEpiStoreF32
   float* c;
   int ldc, b_fp8;            // b_fp8: the weights are e4m3 (A8W8) instead of e2m1 (A8W4)
@@ -59,6 +61,8 @@ cudaError_t launch_mega_gemm(const MegaGemmParams& p, int blocks, cudaStream_t s
 // Encodes a 2-D tensor map with a {128 (K), 128 (rows)} box and the 128-byte swizzle.
 // fp4 = true: elements are packed e2m1 pairs that the copy engine widens to one byte each in shared memory.
 bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, bool fp4, const char** error);
+// Encodes an array of 512-byte scale chunks as a 2-D map {128 x uint32, chunks} with a one-chunk box, no swizzle.
+bool encode_sf_map(CUtensorMap* map, const void* base, long long chunks, const char** error);
 
 // Phase stamps of the fused kernel, one record per CTA (globaltimer nanoseconds): kernel start, inputs quantised and
 // handshake done, routing layout done, token pull done (pull warps), GEMM tile loop done, finish handshake done, end.
@@ -71,7 +75,8 @@ struct MegaRouteArgs {
   long long in_off;            // byte offset of the input block (x, x_sf, topk_idx, topk_w) in a workspace
   int T, E, K, H;              // tokens of this rank, experts, top-k, hidden
   int max_tokens, max_mtiles;
-  int S, pad;                  // shared experts of this rank: local experts E / world .. E / world + S - 1, fed with all of its own tokens
+  int S, tile_pairs;           // tile_pairs: every expert's rows start at a multiple of 256 (pairs of 128-row tiles of one expert)
+                               // S: shared experts of this rank: local experts E / world .. E / world + S - 1, fed with all of its own tokens
   const __nv_bfloat16* x_bf16; // optional [T, H]: quantised to MXFP8 into the input block at the start of the kernel
   unsigned long long* timer;   // optional [blocks][kMegaTimerWords] phase stamps in nanoseconds (see mega_tools.parse_timer)
   // outputs
@@ -108,7 +113,8 @@ struct MegaFusedArgs {
   MegaFinishArgs finish;
   int* ready;                  // [max_mtiles] finished GEMM1 tiles per row block (zeroed by the kernel)
   int* tile_counter;           // [1] next tile of the GEMM1 + GEMM2 tile list (zeroed by the kernel); null: static round-robin
-  int interleave, pad;         // k > 0: GEMM2 tiles follow their GEMM1 wave (waves of 2k rounds of GEMM1 tiles); 0: all GEMM1 tiles first
+  int interleave, pair;        // pair: CTA pairs share the weights tile (cluster of two; needs route.tile_pairs)
+                               // interleave k > 0: GEMM2 tiles follow their GEMM1 wave (waves of 2k rounds of GEMM1 tiles); 0: all GEMM1 tiles first
 };
 struct MegaFusedParams { WsLayout lay; MegaFusedArgs r[kMaxRanks]; };
 cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, cudaStream_t stream);

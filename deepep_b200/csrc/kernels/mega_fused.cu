@@ -22,6 +22,7 @@ namespace dep {
 constexpr int kPullWarps = 2;                                    // warps beside the GEMM roles that pull tokens from peers
 constexpr int kFusedThreads = kGemmThreads + kPullWarps * 32;
 
+template <bool kPair>
 __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid_constant__ MegaFusedParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ RouteShared sh;
@@ -38,11 +39,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid
   // The token pull overlaps the GEMMs: rows are pulled tile by tile, a GEMM1 tile starts once its rows have arrived.
   const int warp = threadIdx.x >> 5;
   if (warp < kGemmThreads / 32) {
-    gemm_phase(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x, a.tile_counter, a.interleave);
+    if constexpr (kPair) gemm_phase<true>(a.g1, &a.g2, a.ready, smem_raw, 4, blockIdx.x / 2, gridDim.x / 2, a.tile_counter, a.interleave);
+    else gemm_phase<false>(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x, a.tile_counter, a.interleave);
   } else {
-    __syncthreads();                               // pairs with the set-up barrier inside gemm_phase
+    // the pull warps take part in the block (and, for CTA pairs, cluster) barriers of gemm_phase's set-up and tear-down
+    if constexpr (kPair) { __syncthreads(); umma::cluster_sync_all(); }
+    __syncthreads();
     route_pull_phase(a.route, sh, blockIdx.x * kPullWarps + (warp - kGemmThreads / 32), gridDim.x * kPullWarps);
-    __syncthreads();                               // pairs with the tear-down barrier inside gemm_phase
+    __syncthreads();
+    if constexpr (kPair) umma::cluster_sync_all();
   }
   mega_stamp(a.route.timer, kTimGemm);             // this CTA ran out of tiles (or of rows to pull)
   __threadfence_system();
@@ -52,12 +57,27 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid
 
 cudaError_t launch_mega_fused(const MegaFusedParams& p, int nranks, int blocks, cudaStream_t stream) {
   const size_t smem = gemm_smem_bytes(3, true);
+  bool pair = p.r[0].pair != 0;
+  for (int i = 0; i < nranks; ++i)
+    if ((p.r[i].pair != 0) != pair || (p.r[i].route.tile_pairs != 0) != pair) return cudaErrorInvalidValue;
+  const void* fn = pair ? (const void*)mega_moe_kernel<true> : (const void*)mega_moe_kernel<false>;
   // the attribute belongs to the current device, so it is set on every launch (a process may drive several GPUs)
-  cudaError_t e = cudaFuncSetAttribute(mega_moe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  dim3 grid(blocks, nranks), block(kFusedThreads);
   void* args[] = {const_cast<MegaFusedParams*>(&p)};
-  return cudaLaunchCooperativeKernel((const void*)mega_moe_kernel, grid, block, args, smem, stream);
+  if (!pair) return cudaLaunchCooperativeKernel(fn, dim3(blocks, nranks), dim3(kFusedThreads), args, smem, stream);
+  // CTA pairs: a cooperative launch of clusters of two CTAs (an even number of CTAs per rank)
+  if (blocks < 2) return cudaErrorInvalidValue;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks / 2 * 2, nranks); cfg.blockDim = dim3(kFusedThreads);
+  cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
+  cfg.attrs = attr; cfg.numAttrs = 2;
+  return cudaLaunchKernelExC(&cfg, fn, args);
 }
 
 }  // namespace dep

@@ -56,10 +56,18 @@ __host__ __device__ constexpr size_t gemm_smem_bytes(int stages, bool staging) {
   return 1024 + (size_t)stages * (kStageBytes + kSfStageBytes) + (staging ? kEpiStageBytes : 0) + 256;
 }
 
+// The MMA thread releases pipeline stages in groups of kCommitEvery (one tcgen05.commit per group); a stage is reloaded
+// once the commit of its group has arrived.  One stage per commit is the fastest setting measured: releasing two stages
+// per commit made the fused layer slower (4096 tokens, 32 local experts: GEMM phases 1641 against 1361 us), because a
+// stage then waits up to one more stage time before it is reloaded.
+constexpr int kCommitEvery = 1;
+constexpr int kGroupRing = 4;   // group barriers in rotation; more than the groups a producer can be ahead of the MMAs
 constexpr int kSchedRing = 8;   // tile ids in flight between the producer and the slowest consumer (< stages + 2)
 
 struct GemmBarriers {
   uint64_t full[kGemmMaxStages], empty[kGemmMaxStages], acc_full, acc_empty, epi_done;
+  uint64_t peer_acc_empty;         // CTA pairs: the odd CTA's acc_empty, forwarded to the even CTA
+  uint64_t released[kGroupRing];   // the MMAs of a group of kCommitEvery stages have completed
   uint64_t sched[kSchedRing];      // the producer has published tile_id[slot]
   int tile_id[kSchedRing];
   uint32_t tmem_base;
@@ -73,6 +81,21 @@ __device__ __forceinline__ bool try_wait_now(uint64_t* bar, uint32_t parity) {  
       "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
+}
+__device__ __forceinline__ bool try_wait_cluster(uint64_t* bar, uint32_t parity) {   // acquires what the peer CTA released
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool bounded_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  for (unsigned i = 0; i < (1u << 24); ++i) {
+    if (try_wait_cluster(bar, parity)) return true;
+    if ((i & 63u) == 63u && *failed) return false;
+  }
+  *failed = 1;
+  return false;
 }
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
   for (unsigned i = 0; i < (1u << 24); ++i) {
@@ -118,10 +141,11 @@ __device__ __forceinline__ int schedule_to_tile(int pos, int num_mtiles, int n1,
 }
 
 // Next tile of this CTA: the producer publishes it to the MMA and epilogue warps through a small ring.
-__device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_tile, volatile int* failed) {
+__device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_tile, volatile int* failed, bool from_peer = false) {
   const uint32_t slot = local_tile % kSchedRing;
-  if (!bounded_wait(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed)) return -1;
-  return bars->tile_id[slot];
+  const bool ok = from_peer ? bounded_wait_cluster(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed)
+                            : bounded_wait(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed);
+  return ok ? *reinterpret_cast<volatile int*>(&bars->tile_id[slot]) : -1;
 }
 
 // g1: first GEMM of the list; g2: optional second GEMM (nullptr for a single GEMM).  `ready` (may be null):
@@ -130,12 +154,24 @@ __device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_til
 // the next one (it must be zero when the first CTA arrives); null: CTA c takes tiles c, c + num_ctas, ...
 // Either way a tile is only ever taken after all tiles before it, so a GEMM2 tile's wait for its GEMM1 tiles ends.
 // `smem_raw` must provide gemm_smem_bytes(stages, staging) bytes.
+//
+// kPair: the CTAs of a cluster of two work on one 256-row tile pair (row blocks 2j and 2j + 1, which the routing layout
+// gives to the same expert).  Each CTA loads its own 128 rows of A and HALF of the 256 weight rows of B; the even CTA
+// issues tcgen05.mma.cta_group::2 (M = 256), which reads both halves of B from the two CTAs' shared memory, so a stage
+// fills 32 KB per CTA instead of 48 KB for the same tensor work.  Both CTAs' loads count their bytes on the even CTA's
+// "stage full" barrier; the odd CTA's MMA warp forwards its "accumulator drained" barrier; the even CTA's commits arrive
+// on both CTAs' barriers.  `cta` / `num_ctas` count pairs then, `stages` may be 4, and all threads of both CTAs must
+// make this call (cluster barriers).
+template <bool kPair>
 __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaGemmParams* g2, int* ready, uint8_t* smem_raw,
                                            int stages, int cta, int num_ctas, int* tile_counter = nullptr, int interleave = 0) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
   uint8_t* tiles = smem;
-  uint8_t* sf_smem = tiles + (size_t)stages * kStageBytes;
+  constexpr int kBBoxes = kPair ? 1 : kGemmBN / 128;                  // 128-row boxes of B this CTA loads per stage
+  constexpr int kStage = kTileABytes + kBBoxes * 128 * kGemmBK;       // bytes of A and B per stage in this CTA
+  const uint32_t crank = kPair ? umma::cluster_ctarank() : 0u;        // 0: issues the MMAs
+  uint8_t* sf_smem = tiles + (size_t)stages * kStage;
   uint8_t* epi_smem = sf_smem + (size_t)stages * kSfStageBytes;
   const bool staging = g1.epi == kEpiCombine || (g2 && g2->epi == kEpiCombine);
   GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(epi_smem + (staging ? kEpiStageBytes : 0));
@@ -147,15 +183,21 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     mbar_init(&bars->acc_empty, kEpiWarps);
     mbar_init(&bars->epi_done, kEpiWarps);
     for (int i = 0; i < kSchedRing; ++i) mbar_init(&bars->sched[i], 1);
+    mbar_init(&bars->peer_acc_empty, 1);
+    for (int i = 0; i < kGroupRing; ++i) mbar_init(&bars->released[i], 1);
     bars->failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     umma::prefetch_tensormap(&g1.tmap_a);
     umma::prefetch_tensormap(&g1.tmap_b);
     if (g2) { umma::prefetch_tensormap(&g2->tmap_a); umma::prefetch_tensormap(&g2->tmap_b); }
   }
+  if constexpr (kPair) {      // the peer's barriers exist before anything arrives on them, and both CTAs allocate together
+    __syncthreads();
+    umma::cluster_sync_all();
+  }
   if (warp == 1) {
-    umma::tmem_alloc(&bars->tmem_base, kTmemCols);
-    umma::tmem_relinquish();
+    if constexpr (kPair) { umma::tmem_alloc_pair(&bars->tmem_base, kTmemCols); umma::tmem_relinquish_pair(); }
+    else { umma::tmem_alloc(&bars->tmem_base, kTmemCols); umma::tmem_relinquish(); }
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -163,7 +205,8 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
   const uint32_t tmem = bars->tmem_base;
   volatile int* failed = &bars->failed;
 
-  const int num_mtiles = min(*g1.num_mtiles, g1.max_mtiles);
+  // row blocks in the tile list: 128-row tiles, or pairs of them (the routing layout keeps a pair inside one expert)
+  const int num_mtiles = kPair ? (min(*g1.num_mtiles, g1.max_mtiles) + 1) / 2 : min(*g1.num_mtiles, g1.max_mtiles);
   const int tiles1 = num_mtiles * g1.n_tiles;
   const int total_tiles = tiles1 + (g2 ? num_mtiles * g2->n_tiles : 0);
 
@@ -172,18 +215,28 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     if (lane == 0) {
       uint32_t it = 0;
       for (uint32_t local_tile = 0;; ++local_tile) {
-        int tile = tile_counter ? atomicAdd(tile_counter, 1) : cta + (int)local_tile * num_ctas;
-        if (tile >= total_tiles || *failed) tile = -1;
-        else if (g2 && ready && interleave > 0)   // wave = row blocks whose GEMM1 tiles fill `2 * interleave` rounds of the CTAs
-          tile = schedule_to_tile(tile, num_mtiles, g1.n_tiles, g2->n_tiles, (2 * interleave * num_ctas + g1.n_tiles - 1) / g1.n_tiles);
-        bars->tile_id[local_tile % kSchedRing] = tile;
-        mbar_arrive(&bars->sched[local_tile % kSchedRing]);      // release: the id is visible to whoever passes the wait
+        int tile;
+        if (kPair && crank != 0) {
+          tile = fetch_tile(bars, local_tile, failed, true);      // the even CTA hands out the pair's tiles
+        } else {
+          tile = tile_counter ? atomicAdd(tile_counter, 1) : cta + (int)local_tile * num_ctas;
+          if (tile >= total_tiles || *failed) tile = -1;
+          else if (g2 && ready && interleave > 0)   // wave = row blocks whose GEMM1 tiles fill `2 * interleave` rounds of the CTAs
+            tile = schedule_to_tile(tile, num_mtiles, g1.n_tiles, g2->n_tiles, (2 * interleave * num_ctas + g1.n_tiles - 1) / g1.n_tiles);
+          const uint32_t slot = local_tile % kSchedRing;
+          bars->tile_id[slot] = tile;
+          mbar_arrive(&bars->sched[slot]);      // release: the id is visible to whoever passes the wait
+          if constexpr (kPair) {
+            umma::remote_store_u32(umma::map_to_cta(smem_u32(&bars->tile_id[slot]), 1), (uint32_t)tile);
+            umma::remote_arrive(umma::map_to_cta(smem_u32(&bars->sched[slot]), 1));
+          }
+        }
         if (tile < 0) break;
         const bool second = tile >= tiles1;
         const MegaGemmParams& p = second ? *g2 : g1;
         const int local = second ? tile - tiles1 : tile;
-        const int mt = local / p.n_tiles, nb = local - mt * p.n_tiles;
-        const int brow = p.mtile_expert[mt] * p.n_total + nb * kGemmBN;
+        const int mt = kPair ? 2 * (local / p.n_tiles) + (int)crank : local / p.n_tiles, nb = local % p.n_tiles;
+        const int brow = p.mtile_expert[mt] * p.n_total + nb * kGemmBN;        // first of the tile's 256 weight rows
         if (second && ready) {
           if (!wait_rows_ready(ready + mt, g1.n_tiles, failed)) break;
           fence_proxy_async();          // rows written by other SMs' stores are about to be read by the copy engine
@@ -193,27 +246,53 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         }
         for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
           const int s = it % stages;
-          if (!bounded_wait(&bars->empty[s], ((it / stages) & 1u) ^ 1u, failed)) break;
-          uint8_t* a_dst = tiles + (size_t)s * kStageBytes;
+          if (it >= (uint32_t)stages) {     // the stage's previous contents have been consumed: their group was released
+            const uint32_t grp = (it - (uint32_t)stages) / kCommitEvery;
+            if (!bounded_wait(&bars->released[grp % kGroupRing], (grp / kGroupRing) & 1u, failed)) break;
+          }
+          uint8_t* a_dst = tiles + (size_t)s * kStage;
           uint8_t* sf_dst = sf_smem + (size_t)s * kSfStageBytes;
-          mbar_expect_tx(&bars->full[s], kTileABytes + (kGemmBN / 128) * p.b_tx_bytes + kSfStageBytes);
-          umma::tma_load_2d(a_dst, &p.tmap_a, ks * kGemmBK, mt * kGemmBM, &bars->full[s]);
-          bulk_g2s(sf_dst, p.sfa + ((size_t)mt * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+          if constexpr (kPair) {
+            // both CTAs' bytes are counted on the even CTA's barrier, which the MMA thread waits on
+            const uint32_t bar = umma::map_to_cta(smem_u32(&bars->full[s]), 0);
+            if (crank == 0) mbar_expect_tx(&bars->full[s], 2 * (kTileABytes + p.b_tx_bytes + kSfStageBytes));
+            umma::tma_load_2d_pair(a_dst, &p.tmap_a, ks * kGemmBK, mt * kGemmBM, bar);
+            umma::tma_load_2d_pair(sf_dst, &p.tmap_sfa, 0, mt * p.k_steps + ks, bar);
+            // this CTA's half of the 256 weight rows, and the scales of all of them (each CTA of a pair needs them all)
+            umma::tma_load_2d_pair(a_dst + kTileABytes, &p.tmap_b, 0, ((brow / 128 + (int)crank) * p.k_steps + ks) * 128, bar);
 #pragma unroll
-          for (int h = 0; h < kGemmBN / 128; ++h) {     // 128 weight rows per box; consecutive boxes continue the same swizzled tile
-            umma::tma_load_2d(a_dst + kTileABytes + h * 128 * kGemmBK, &p.tmap_b, 0, ((brow / 128 + h) * p.k_steps + ks) * 128,
-                              &bars->full[s]);
-            bulk_g2s(sf_dst + (1 + h) * kSfChunk, p.sfb + ((size_t)(brow / 128 + h) * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+            for (int h = 0; h < kGemmBN / 128; ++h)
+              umma::tma_load_2d_pair(sf_dst + (1 + h) * kSfChunk, &p.tmap_sfb, 0, (brow / 128 + h) * p.k_steps + ks, bar);
+          } else {
+            mbar_expect_tx(&bars->full[s], kTileABytes + kBBoxes * p.b_tx_bytes + kSfStageBytes);
+            umma::tma_load_2d(a_dst, &p.tmap_a, ks * kGemmBK, mt * kGemmBM, &bars->full[s]);
+            bulk_g2s(sf_dst, p.sfa + ((size_t)mt * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+#pragma unroll
+            for (int h = 0; h < kGemmBN / 128; ++h) {     // 128 weight rows per box; consecutive boxes continue the same swizzled tile
+              umma::tma_load_2d(a_dst + kTileABytes + h * 128 * kGemmBK, &p.tmap_b, 0, ((brow / 128 + h) * p.k_steps + ks) * 128,
+                                &bars->full[s]);
+              bulk_g2s(sf_dst + (1 + h) * kSfChunk, p.sfb + ((size_t)(brow / 128 + h) * p.k_steps + ks) * kSfChunk, kSfChunk, &bars->full[s]);
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ============================================================ MMA issuer
-    if (lane == 0) {
-      // A is e4m3 (format 0); B is e2m1 (5) or e4m3 (0), per GEMM
-      const uint32_t idesc1 = umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, 0, g1.b_fp8 ? 0 : 5);
-      const uint32_t idesc2 = g2 ? umma::instr_desc_mxf8f6f4(kGemmBM, kGemmBN, 0, g2->b_fp8 ? 0 : 5) : idesc1;
+    if (lane == 0 && crank == 0) {
+      // A is e4m3 (format 0); B is e2m1 (5) or e4m3 (0), per GEMM.  A pair issues M = 256: 128 rows in each CTA.
+      constexpr int kInstrM = kPair ? 2 * kGemmBM : kGemmBM;
+      const uint32_t idesc1 = umma::instr_desc_mxf8f6f4(kInstrM, kGemmBN, 0, g1.b_fp8 ? 0 : 5);
+      const uint32_t idesc2 = g2 ? umma::instr_desc_mxf8f6f4(kInstrM, kGemmBN, 0, g2->b_fp8 ? 0 : 5) : idesc1;
+      // commits of a pair arrive on the barrier of both CTAs
+      auto commit_both = [&](uint64_t* bar) {
+        if constexpr (kPair) {
+          umma::commit_pair(smem_u32(bar));
+          umma::commit_pair(umma::map_to_cta(smem_u32(bar), 1));
+        } else {
+          umma::commit(bar);
+        }
+      };
       uint32_t it = 0;
       for (uint32_t local_tile = 0;; ++local_tile) {
         const int tile = fetch_tile(bars, local_tile, failed);
@@ -221,25 +300,48 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         const int k_steps = tile >= tiles1 ? g2->k_steps : g1.k_steps;
         const uint32_t idesc = tile >= tiles1 ? idesc2 : idesc1;
         if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed)) break;
+        if constexpr (kPair)      // the odd CTA forwards one arrival per tile, the first as soon as it starts
+          if (!bounded_wait_cluster(&bars->peer_acc_empty, local_tile & 1u, failed)) break;
         umma::fence_after_sync();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % stages;
           if (!bounded_wait(&bars->full[s], (it / stages) & 1u, failed)) break;
           umma::fence_after_sync();
-          const uint32_t a_addr = smem_u32(tiles + (size_t)s * kStageBytes);
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * kStage);
           const uint32_t sf_addr = smem_u32(sf_smem + (size_t)s * kSfStageBytes);
           const uint32_t tsfa = tmem + kSfColBase + s * kSfColsPerStage, tsfb = tsfa + 4;
-          umma::copy_sf_to_tmem(tsfa, umma::smem_desc_sf(sf_addr));
+          if constexpr (kPair) {
+            umma::copy_sf_to_tmem_pair(tsfa, umma::smem_desc_sf(sf_addr));
 #pragma unroll
-          for (int h = 0; h < kGemmBN / 128; ++h)
-            umma::copy_sf_to_tmem(tsfb + 4 * h, umma::smem_desc_sf(sf_addr + (1 + h) * kSfChunk));
+            for (int h = 0; h < kGemmBN / 128; ++h)
+              umma::copy_sf_to_tmem_pair(tsfb + 4 * h, umma::smem_desc_sf(sf_addr + (1 + h) * kSfChunk));
+          } else {
+            umma::copy_sf_to_tmem(tsfa, umma::smem_desc_sf(sf_addr));
+#pragma unroll
+            for (int h = 0; h < kGemmBN / 128; ++h)
+              umma::copy_sf_to_tmem(tsfb + 4 * h, umma::smem_desc_sf(sf_addr + (1 + h) * kSfChunk));
+          }
           const uint64_t da = umma::smem_desc_sw128(a_addr), db = umma::smem_desc_sw128(a_addr + kTileABytes);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)   // 32 K-values = 32 bytes = 2 descriptor units per step inside the swizzle row
-            umma::mma_block_scaled(tmem, da + 2 * k, db + 2 * k, umma::with_sf_ids(idesc, k, k), tsfa, tsfb, ks > 0 || k > 0);
-          umma::commit(&bars->empty[s]);          // stage (tiles, scale columns) reusable once these MMAs finished
+          for (int k = 0; k < 4; ++k) {   // 32 K-values = 32 bytes = 2 descriptor units per step inside the swizzle row
+            if constexpr (kPair)
+              umma::mma_block_scaled_pair(tmem, da + 2 * k, db + 2 * k, umma::with_sf_ids(idesc, k, k), tsfa, tsfb, ks > 0 || k > 0);
+            else
+              umma::mma_block_scaled(tmem, da + 2 * k, db + 2 * k, umma::with_sf_ids(idesc, k, k), tsfa, tsfb, ks > 0 || k > 0);
+          }
+          if (it % kCommitEvery == kCommitEvery - 1)      // stages (tiles, scale columns) reusable once these MMAs finished
+            commit_both(&bars->released[(it / kCommitEvery) % kGroupRing]);
         }
-        umma::commit(&bars->acc_full);             // accumulator complete
+        commit_both(&bars->acc_full);              // accumulator complete
+      }
+    } else if (kPair && lane == 0) {
+      // ---- odd CTA of a pair: no MMAs to issue; forward "accumulator drained" to the even CTA, once per tile
+      const uint32_t acc_fwd = umma::map_to_cta(smem_u32(&bars->peer_acc_empty), 0);
+      for (uint32_t local_tile = 0;; ++local_tile) {
+        const int tile = fetch_tile(bars, local_tile, failed, true);
+        if (tile < 0) break;
+        if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed)) break;
+        umma::remote_arrive(acc_fwd);
       }
     }
   } else {
@@ -250,12 +352,12 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     uint8_t* stage = epi_smem + (size_t)(warp - 2) * 32 * kEpiWarpCols * 2;
     uint32_t first_done = 0;
     for (uint32_t local_tile = 0;; ++local_tile) {
-      const int tile = fetch_tile(bars, local_tile, failed);
+      const int tile = fetch_tile(bars, local_tile, failed, kPair && crank != 0);
       if (tile < 0) break;
       const bool second = tile >= tiles1;
       const MegaGemmParams& p = second ? *g2 : g1;
       const int local = second ? tile - tiles1 : tile;
-      const int mt = local / p.n_tiles, nb = local - mt * p.n_tiles;
+      const int mt = kPair ? 2 * (local / p.n_tiles) + (int)crank : local / p.n_tiles, nb = local % p.n_tiles;
       if (!bounded_wait(&bars->acc_full, local_tile & 1u, failed)) break;
       umma::fence_after_sync();
       const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
@@ -414,9 +516,11 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
   umma::fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0 && *failed && g1.error_flag) *g1.error_flag = 1;
+  if constexpr (kPair) umma::cluster_sync_all();    // both CTAs are done with each other's shared and tensor memory
   if (warp == 1) {
     umma::fence_after_sync();
-    umma::tmem_dealloc(tmem, kTmemCols);
+    if constexpr (kPair) umma::tmem_dealloc_pair(tmem, kTmemCols);
+    else umma::tmem_dealloc(tmem, kTmemCols);
   }
 }
 #endif  // __CUDACC__

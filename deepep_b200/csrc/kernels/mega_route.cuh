@@ -152,7 +152,7 @@ __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::g
   __threadfence();
   grid.sync();
 
-  // ---- tile layout: every expert starts at a multiple of 128 rows
+  // ---- tile layout: every expert starts at a multiple of 128 rows (256 with CTA pairs)
   for (int l = threadIdx.x; l < Lx + S; l += (int)blockDim.x) sh.rows[l] = min(__ldcg(a.expert_rows + l), cap);   // parallel loads
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -160,7 +160,8 @@ __device__ __forceinline__ void route_layout_phase(const MegaRouteArgs& a, cg::g
     for (int l = 0; l < Lx + S; ++l) {
       const int c = sh.rows[l];
       sh.base[l] = run;
-      const int tiles = (c + kGemmBM - 1) / kGemmBM;
+      const int unit = a.tile_pairs ? 2 * kGemmBM : kGemmBM;      // with CTA pairs an expert owns whole pairs of tiles
+      const int tiles = (c + unit - 1) / unit * (unit / kGemmBM);
       if (blockIdx.x == 0)
         for (int t = 0; t < tiles && run / kGemmBM + t < a.max_mtiles; ++t) a.mtile_expert[run / kGemmBM + t] = l;
       run += tiles * kGemmBM;
@@ -252,48 +253,61 @@ __device__ __forceinline__ void finish_phase(const MegaFinishArgs& a, bool bump_
       const int t = item / parts, part = item - t * parts;
       if (part * span >= units) continue;
       const int u_end = min(units, (part + 1) * span);
-      float wk[kMaxTopk];
-      unsigned valid = 0;
-      for (int k = 0; k < K; ++k) {
-        const int e = idx[(size_t)t * K + k];
-        wk[k] = w[(size_t)t * K + k];
-        if (e >= 0 && e < a.E) valid |= 1u << k;
+      // lane k holds slot k: its weight and whether it counts (shared experts: every token, weight one)
+      float w_mine = 0.f;
+      bool counts = false;
+      if (lane < K) {
+        const int e = idx[(size_t)t * K + lane];
+        w_mine = w[(size_t)t * K + lane];
+        counts = e >= 0 && e < a.E;
+      } else if (lane < Kp) {
+        w_mine = 1.f;
+        counts = true;
       }
-      for (int k = K; k < Kp; ++k) { wk[k] = 1.f; valid |= 1u << k; }     // shared experts: every token, weight one
+      const unsigned valid = __ballot_sync(0xffffffffu, counts);
       int4* out = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(a.y) + (size_t)t * H * 2);
       const uint8_t* rows = comb + (size_t)t * Kp * H * 2;
-      for (int u0 = part * span + lane; u0 < u_end; u0 += 64) {      // two 16-byte columns per step, all slots' loads issued first
-        const bool two = u0 + 32 < u_end;
-        int4 v0[kMaxTopk], v1[kMaxTopk];
-#pragma unroll
-        for (int k = 0; k < kMaxTopk; ++k) {
-          if (k < Kp && ((valid >> k) & 1u)) {
-            v0[k] = ld_cg_int4(rows + (size_t)k * H * 2 + (size_t)u0 * 16);
-            if (two) v1[k] = ld_cg_int4(rows + (size_t)k * H * 2 + (size_t)(u0 + 32) * 16);
-          }
-        }
+      // two 16-byte columns per lane and step; the trip count is the same for every lane, which all take part in the shuffles
+      for (int ub = part * span; ub < u_end; ub += 64) {
+        const int u0 = ub + lane;
+        const bool one = u0 < u_end, two = u0 + 32 < u_end;
         float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int kb = 0; kb < Kp; kb += 8) {     // eight slots' loads in flight at a time
+          int4 v0[8], v1[8];
 #pragma unroll
-        for (int k = 0; k < kMaxTopk; ++k) {
-          if (k < Kp && ((valid >> k) & 1u)) {
-            const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[k]);
-            const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[k]);
+          for (int k = 0; k < 8; ++k) {
+            if (kb + k < Kp && ((valid >> (kb + k)) & 1u)) {
+              if (one) v0[k] = ld_cg_int4(rows + (size_t)(kb + k) * H * 2 + (size_t)u0 * 16);
+              if (two) v1[k] = ld_cg_int4(rows + (size_t)(kb + k) * H * 2 + (size_t)(u0 + 32) * 16);
+            }
+          }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {   // product and sum rounded separately, as the CPU oracle does
-              a0[2 * i] = __fadd_rn(a0[2 * i], __fmul_rn(wk[k], __low2float(h0[i])));
-              a0[2 * i + 1] = __fadd_rn(a0[2 * i + 1], __fmul_rn(wk[k], __high2float(h0[i])));
-              if (two) {
-                a1[2 * i] = __fadd_rn(a1[2 * i], __fmul_rn(wk[k], __low2float(h1[i])));
-                a1[2 * i + 1] = __fadd_rn(a1[2 * i + 1], __fmul_rn(wk[k], __high2float(h1[i])));
+          for (int k = 0; k < 8; ++k) {
+            if (kb + k < Kp && ((valid >> (kb + k)) & 1u)) {     // warp-uniform
+              const float wk = __shfl_sync(0xffffffffu, w_mine, kb + k);
+              const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[k]);
+              const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[k]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {   // product and sum rounded separately, as the CPU oracle does
+                if (one) {
+                  a0[2 * i] = __fadd_rn(a0[2 * i], __fmul_rn(wk, __low2float(h0[i])));
+                  a0[2 * i + 1] = __fadd_rn(a0[2 * i + 1], __fmul_rn(wk, __high2float(h0[i])));
+                }
+                if (two) {
+                  a1[2 * i] = __fadd_rn(a1[2 * i], __fmul_rn(wk, __low2float(h1[i])));
+                  a1[2 * i + 1] = __fadd_rn(a1[2 * i + 1], __fmul_rn(wk, __high2float(h1[i])));
+                }
               }
             }
           }
         }
         int4 o;
         __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+        if (one) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(a0[2 * i], a0[2 * i + 1]);
-        out[u0] = o;
+          for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(a0[2 * i], a0[2 * i + 1]);
+          out[u0] = o;
+        }
         if (two) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(a1[2 * i], a1[2 * i + 1]);

@@ -37,12 +37,15 @@ void fill_gemm(MegaGemmParams& p, const py::dict& d, py::object session) {
   p.b_fp8 = geti(d, "b_fp8", 0) ? 1 : 0;
   if (!encode_operand_map(&p.tmap_b, ptr<const void>(d, "b"), b_rows * (k / kGemmBK), kGemmBK, !p.b_fp8, &err)) throw std::runtime_error(err);
   p.sfa = ptr<const uint8_t>(d, "sfa"); p.sfb = ptr<const uint8_t>(d, "sfb");
+  if (!encode_sf_map(&p.tmap_sfa, p.sfa, (rows_pad / kGemmBM) * (k / kGemmBK), &err)) throw std::runtime_error(err);
+  if (!encode_sf_map(&p.tmap_sfb, p.sfb, (b_rows / 128) * (k / kGemmBK), &err)) throw std::runtime_error(err);
   p.mtile_expert = ptr<const int>(d, "mtile_expert"); p.num_mtiles = ptr<const int>(d, "num_mtiles");
   p.a_ready = ptr<const int>(d, "a_ready");
   p.max_mtiles = (int)(rows_pad / kGemmBM);
   p.n_total = geti(d, "n_total"); p.n_tiles = p.n_total / kGemmBN; p.k_steps = (int)(k / kGemmBK);
   if (p.n_total % kGemmBN) throw std::invalid_argument("output width must be a multiple of 256");
   p.epi = geti(d, "epi");
+  p.pair = geti(d, "pair", 0) ? 1 : 0;
   p.b_tx_bytes = geti(d, "b_tx_bytes", p.b_fp8 ? 128 * kGemmBK : 128 * kGemmBK / 2);   // bytes counted per 128-row box of weights
   p.c = ptr<float>(d, "c"); p.ldc = geti(d, "ldc");
   p.a2 = ptr<uint8_t>(d, "a2"); p.a2_sf = ptr<uint8_t>(d, "a2_sf"); p.inter = geti(d, "inter");
@@ -71,6 +74,7 @@ void fill_route(MegaRouteArgs& a, const py::dict& d, py::object session) {
   a.expert_rows = ptr<int>(d, "expert_rows"); a.expert_list = ptr<int>(d, "expert_list");
   a.pulled = ptr<int>(d, "pulled");
   a.S = geti(d, "S", 0);
+  a.tile_pairs = geti(d, "tile_pairs", 0) ? 1 : 0;
   a.x_bf16 = ptr<const __nv_bfloat16>(d, "x_bf16");
   a.timer = ptr<unsigned long long>(d, "timer");
   if (a.S < 0 || a.K + a.S > kMaxTopk || a.E / a.ctx.world + a.S > kMaxExperts)
@@ -104,6 +108,8 @@ void op_mega_fused(const WsLayout& lay, const std::vector<py::object>& sessions,
     p.r[i].ready = ptr<int>(d, "ready");
     p.r[i].tile_counter = ptr<int>(d, "tile_counter");
     p.r[i].interleave = geti(d, "interleave", 1);
+    p.r[i].pair = geti(d, "pair", 0) ? 1 : 0;
+    if (p.r[i].pair && n > 1) throw std::invalid_argument("CTA pairs are for one rank per GPU (virtual ranks share the SMs)");
     if (!p.r[i].ready || !p.r[i].route.pulled) throw std::invalid_argument("the fused kernel needs the ready and pulled counter arrays");
   }
   check(launch_mega_fused(p, n, blocks, reinterpret_cast<cudaStream_t>(stream)), "mega_moe launch");

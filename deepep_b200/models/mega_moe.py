@@ -113,8 +113,16 @@ class MegaEngine:
         # GPU, 1951 against 2046 us on two, 2372 against 2399 us on four, so it stays an option (DEEPEP_MEGA_INTERLEAVE=<units>).
         default = "0"
         self.interleave = int(os.environ.get("DEEPEP_MEGA_INTERLEAVE", default) or 0)   # wave length in units of two CTA rounds
-        rows = self.world * self.M * min(self.K, self.L) + self.S * self.M + (self.L + self.S) * 127
-        self.max_mtiles = -(-rows // 128)
+        # CTA pairs (clusters of two CTAs share every weights tile: tcgen05.mma.cta_group::2): off by default.  The fused
+        # layer gains nothing from them (4096 tokens per rank over 32 local experts on one GPU: GEMM phases 1348 us with
+        # pairs, 1361 us without; experts padded to whole pairs of 128-row tiles carry 6 % more rows), the stand-alone GEMM
+        # of the first projection is 5-17 % faster with them.  DEEPEP_MEGA_PAIRS=1 turns them on, "auto" uses them when
+        # the local experts average 384 rows or more.  Only with one rank per GPU: virtual ranks share the SMs.
+        self.pairs = os.environ.get("DEEPEP_MEGA_PAIRS", "0").lower()
+        if self.pairs not in ("auto", "0", "1"):
+            raise ValueError("DEEPEP_MEGA_PAIRS must be auto, 0 or 1")
+        rows = self.world * self.M * min(self.K, self.L) + self.S * self.M + (self.L + self.S) * 255   # room for whole pairs
+        self.max_mtiles = -(-rows // 256) * 2
         self.rows_cap = self.max_mtiles * 128
         u8, i32 = dict(dtype=torch.uint8, device=device), dict(dtype=torch.int32, device=device)
         self.scratch = []
@@ -176,15 +184,17 @@ class MegaEngine:
                                    row_src=sc["row_src"].data_ptr(), comb_off=self.comb_off, max_tokens=self.M,
                                    topk=self.K + self.S, hidden=self.H))
         if fused:
+            pair = self.use_pairs(tokens)
             for i in range(self.n):    # the fused kernel overlaps the pull with the GEMMs through per-tile counters
                 sc = self.scratch[i]
                 route_args[i]["pulled"] = sc["pulled"].data_ptr()
+                route_args[i]["tile_pairs"] = int(pair)
                 gemm1_args[i]["a_ready"] = sc["pulled"].data_ptr()
             blocks = max(1, min(self.gemm_blocks, self.sm_count // self.n))
             C.mega_fused(lay, self.sessions, [dict(route=route_args[i], finish=finish_args[i], gemm1=gemm1_args[i],
                                                   gemm2=gemm2_args[i], ready=self.scratch[i]["ready"].data_ptr(),
                                                   tile_counter=self.scratch[i]["tile_counter"].data_ptr() if self.dynamic_tiles else None,
-                                                  interleave=int(self.interleave))
+                                                  interleave=int(self.interleave), pair=int(pair))
                                              for i in range(self.n)], blocks, s)
             return
         aux_blocks = max(1, min(self.sm_count // self.n, 128))
@@ -193,6 +203,16 @@ class MegaEngine:
             C.mega_gemm(gemm1_args[i], self.sessions[i], self.gemm_blocks, s)
             C.mega_gemm(gemm2_args[i], self.sessions[i], self.gemm_blocks, s)
         C.mega_finish(lay, self.sessions, finish_args, aux_blocks, s)
+
+    def use_pairs(self, tokens: Sequence[int]) -> bool:
+        """Whether this launch runs its GEMMs as CTA pairs (see ``self.pairs``)."""
+        if self.n != 1 or self.pairs == "0" or self.sm_count < 2:
+            return False
+        if self.pairs == "1":
+            return True
+        # expected rows per local expert if every rank sends what this one does, spread evenly over the experts
+        per_expert = self.world * max(tokens) * self.K / max(self.E, 1) if self.L else 0
+        return per_expert >= 384
 
     def check(self) -> None:
         for sc in self.scratch:

@@ -7,14 +7,14 @@ from deepep_b200.oracle import megamoe as O
 pytestmark = pytest.mark.gpu
 
 
-def _run(rows_per_expert, n_total, k, seed=0, b_tx=None):
+def _run(rows_per_expert, n_total, k, seed=0, b_tx=None, pair=False):
     from deepep_b200.ops import load_native
 
     C = load_native()
     dev = torch.device("cuda")
     g = torch.Generator().manual_seed(seed)
     experts = len(rows_per_expert)
-    tiles = [-(-r // 128) for r in rows_per_expert]
+    tiles = [-(-r // 256) * 2 if pair else -(-r // 128) for r in rows_per_expert]   # CTA pairs: whole pairs of tiles per expert
     rows_pad = 128 * sum(tiles)
     x = torch.randn((rows_pad, k), generator=g)
     a_codes, a_sf = O.quantize_mxfp8(x)
@@ -33,6 +33,8 @@ def _run(rows_per_expert, n_total, k, seed=0, b_tx=None):
                 n_total=n_total, epi=0, c=d["c"].data_ptr(), ldc=n_total, error_flag=d["err"].data_ptr())
     if b_tx is not None:
         args["b_tx_bytes"] = b_tx
+    if pair:
+        args["pair"] = 1
     C.mega_gemm(args, None, 148, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert d["err"].item() == 0, "a pipeline wait ran out inside the GEMM kernel"
@@ -52,3 +54,13 @@ def test_k_loop_and_tiles():
 
 def test_grouped_shapes():
     _run([100, 1, 300, 128], 512, 2048, seed=3)
+
+
+def test_cta_pairs_single_pair():
+    """One pair of row blocks, one N tile: the smallest case of the cta_group::2 path (two CTAs, M = 256)."""
+    _run([256], 256, 128, pair=True)
+
+
+def test_cta_pairs_grouped_shapes():
+    """Several experts (odd tile counts are padded to whole pairs), a K loop longer than the pipeline, several N tiles."""
+    _run([100, 1, 300, 256], 512, 2048, seed=3, pair=True)

@@ -17,7 +17,7 @@ def _mixed_error_ok(actual, expected, diff_thd=0.01, pct_thd=0.05, max_diff=0.1)
     return bad <= pct_thd and rel.max().item() <= max_diff, bad, rel.max().item()
 
 
-def _case(world, tokens, H, I, E, K, seed=0, interleave=None):
+def _case(world, tokens, H, I, E, K, seed=0, interleave=None, pairs=None):
     from deepep_b200.models.mega_moe import MegaEngine, transform_weights_for_mega_moe
     from deepep_b200.ops import load_native
     from deepep_b200.parallel.virtual import VirtualWorld
@@ -43,6 +43,8 @@ def _case(world, tokens, H, I, E, K, seed=0, interleave=None):
         eng = MegaEngine(sessions, layout, dev, E, I)
         if interleave is not None:
             eng.interleave = interleave
+        if pairs is not None:
+            eng.pairs = pairs
         w = [transform_weights_for_mega_moe((l1[0][r * L:(r + 1) * L], l1[1][r * L:(r + 1) * L]),
                                             (l2[0][r * L:(r + 1) * L], l2[1][r * L:(r + 1) * L]), device=dev) for r in range(world)]
         ys = [torch.zeros((t, H), dtype=torch.bfloat16, device=dev) for t in tokens]
@@ -81,6 +83,13 @@ def test_four_virtual_ranks_topk8():
 def test_interleaved_schedule_on_many_row_blocks():
     """Enough row blocks (48+) for the wave schedule to really interleave GEMM1 and GEMM2 tiles (waves of 19 blocks)."""
     _case(1, [768], 512, 2048, 8, 8, seed=9, interleave=1)
+
+
+def test_cta_pairs_in_the_fused_kernel():
+    """The fused kernel as clusters of two CTAs that share every weights tile (tcgen05.mma.cta_group::2): experts are
+    padded to whole pairs of row blocks, odd tile counts and empty experts included."""
+    _case(1, [300], 256, 128, 4, 2, seed=2, pairs="1")
+    _case(1, [768], 512, 2048, 8, 8, seed=9, pairs="1")
 
 
 def test_shared_experts_stats_bf16_input_and_timer():
