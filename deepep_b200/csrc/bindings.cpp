@@ -103,9 +103,12 @@ void op_dispatch(const WsLayout& lay, const std::vector<py::object>& sessions, c
 }
 
 void op_combine(const WsLayout& lay, const std::vector<py::object>& sessions, const std::vector<py::dict>& args, int send_blocks,
-                int recv_blocks, uintptr_t stream, bool local_direct, bool profile) {
+                int recv_blocks, uintptr_t stream, bool local_direct, bool profile, int t_begin, int t_end) {
   CombineParams p{};
   p.lay = lay; p.send_blocks = send_blocks; p.recv_blocks = recv_blocks; p.local_direct = local_direct; p.profile = profile;
+  p.t_begin = t_begin; p.t_end = t_end < 0 ? lay.max_tokens : t_end;
+  if (p.t_begin < 0 || p.t_end < p.t_begin || p.t_end - p.t_begin > lay.partial_tokens)
+    throw std::invalid_argument("combine: the token window does not fit the workspace's partial area");
   const int n = (int)args.size();
   if (n < 1 || n > kMaxRanks || (int)sessions.size() != n) throw std::invalid_argument("1..8 rank argument blocks expected");
   if (send_blocks < 0 || recv_blocks < 1) throw std::invalid_argument("the source-side block count must be positive, the expert-side count nonnegative");
@@ -169,10 +172,10 @@ PYBIND11_MODULE(_C, m) {
       .def_readonly("ll", &WsLayout::ll).def_readonly("mega", &WsLayout::mega).def_readonly("total", &WsLayout::total)
       .def_readonly("max_tokens", &WsLayout::max_tokens).def_readonly("hidden", &WsLayout::hidden)
       .def_readonly("topk", &WsLayout::topk).def_readonly("world", &WsLayout::world)
-      .def_readonly("stage_row_bytes", &WsLayout::stage_row_bytes);
+      .def_readonly("stage_row_bytes", &WsLayout::stage_row_bytes).def_readonly("partial_tokens", &WsLayout::partial_tokens);
   m.def("make_mega_layout", &make_mega_layout);
   m.def("make_layout", &make_layout, py::arg("world"), py::arg("max_tokens"), py::arg("hidden"), py::arg("topk"),
-        py::arg("ll_bytes") = 0, py::arg("mega_bytes") = 0);
+        py::arg("ll_bytes") = 0, py::arg("mega_bytes") = 0, py::arg("partial_tokens") = 0);
 
   py::class_<Session>(m, "Session")
       .def(py::init<int, int, size_t, double, const std::string&>(), py::arg("rank"), py::arg("world"), py::arg("bytes"),
@@ -239,7 +242,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("dispatch", &op_dispatch, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),
         py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);
   m.def("combine", &op_combine, py::arg("layout"), py::arg("sessions"), py::arg("args"), py::arg("send_blocks"),
-        py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false);
+        py::arg("recv_blocks"), py::arg("stream"), py::arg("local_direct") = true, py::arg("profile") = false,
+        py::arg("t_begin") = 0, py::arg("t_end") = -1);
   m.attr("group_tokens") = kGroupTokens;
   m.attr("row_block") = kRowBlock;
   m.attr("dispatch_prof_words") = kDispatchProfWords;

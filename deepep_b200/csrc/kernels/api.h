@@ -95,7 +95,9 @@ struct CombineArgs {
 };
 // local_direct: the source side sums the rows of its own rank straight from x (same rounding: fp32 sum -> bf16 ->
 // fp32), so no local partial is written and no flag is needed for it.
-struct CombineParams { WsLayout lay; int send_blocks, recv_blocks, local_direct, profile; CombineArgs r[kMaxRanks]; };
+// t_begin / t_end: the token window of this pass (all tokens unless the workspace holds the partials of fewer tokens than
+// num_max_tokens_per_rank: the combine then runs one launch per window, every rank with the same window).
+struct CombineParams { WsLayout lay; int send_blocks, recv_blocks, local_direct, profile; int t_begin, t_end; CombineArgs r[kMaxRanks]; };
 // per block: role (0 expert side, 1 source side), start ns, end ns, then summed over the block's warps: cycles spent
 // reading routing records, waiting for flags, reducing rows, publishing flags; rows read
 constexpr int kCombineProfWords = 8;

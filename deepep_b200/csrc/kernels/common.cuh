@@ -77,7 +77,7 @@ struct WsLayout {
   long long gather_idx;    // int   [P][Tmax][K]
   long long gather_w;      // float [P][Tmax][K]
   long long stage;         // byte  [P][Tmax][stage_row_bytes]   dispatch staging, written by sources
-  long long partial;       // bf16  [Tmax][P][H]                  combine partials, written by expert ranks
+  long long partial;       // bf16  [partial_tokens][P][H]        combine partials, written by expert ranks (a token window when smaller than Tmax)
   long long wret;          // float [Tmax][K]                     returned weights
   long long disp_flag;     // u64   [P][ceil(Tmax / kGroupTokens)] dispatch: the rows of (source, token group) have landed
   long long comb_flag;     // u64   [P][ceil(Tmax / kRowBlock)]    combine: the partials of (expert rank, block of its staged rows) have landed
@@ -85,7 +85,7 @@ struct WsLayout {
   long long mega;          // fused-MoE region
   long long total;
   int max_tokens, hidden, topk, world;
-  int stage_row_bytes, pad;
+  int stage_row_bytes, partial_tokens;   // partial_tokens: tokens per combine pass (Tmax unless the workspace was capped)
 };
 
 struct RankCtx {

@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
       uint8_t* partial = ctx.ws[r] + lay.partial;
       float* wret = reinterpret_cast<float*>(ctx.ws[r] + lay.wret);
       clk.mark(kProfMeta);
+      bool any = false;    // a record of this block belongs to the pass's token window
       for (int qq = 0; qq < cnt; ++qq) {
         const int t = __shfl_sync(0xffffffffu, f0, qq * 8), n = min(__shfl_sync(0xffffffffu, f0, qq * 8 + 1), kMaxTopk);
         const int rec3 = __shfl_sync(0xffffffffu, f0, qq * 8 + 3);
@@ -172,8 +173,9 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
         int my_row = entry & kRowMask;
         if (lane < n && a.x_rows > 0 && !DEP_INDEX_OK(ctx, my_row, a.x_rows, kOpCombine, 0)) my_row = 0;
         const int my_row0 = __shfl_sync(0xffffffffu, my_row, 0);
-        if (t < 0 || t >= Tmax) continue;
-        int4* dst = reinterpret_cast<int4*>(partial + ((size_t)t * P + me) * row_bytes);
+        if (t < p.t_begin || t >= min(p.t_end, Tmax)) continue;
+        any = true;
+        int4* dst = reinterpret_cast<int4*>(partial + ((size_t)(t - p.t_begin) * P + me) * row_bytes);
         if (n == 1) {
           copy_row_as_partial(reinterpret_cast<const int4*>(x + (size_t)my_row0 * row_bytes), dst, units, lane);
         } else {
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
       clk.mark(kProfData);
       // publish the block: every lane's stores are ordered before the flag by the warp barrier + release
       __syncwarp();
-      if (lane == 0)
+      if (lane == 0 && any)
         st_release_sys(reinterpret_cast<unsigned long long*>(ctx.ws[r] + lay.comb_flag) + (size_t)me * NB + jb, epoch);
       clk.mark(kProfPublish);
     }
@@ -215,7 +217,9 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
     const float* wret = reinterpret_cast<const float*>(ctx.ws[me] + lay.wret);
     const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(ctx.ws[me] + lay.comb_flag);
     const int Lx = a.E / P;
-    for (int t = next_ticket(&ctl->ticket[kOpCombine][1], lane); t < a.T; t = next_ticket(&ctl->ticket[kOpCombine][1], lane)) {
+    const int t_stop = min(a.T, p.t_end);
+    for (int t = p.t_begin + next_ticket(&ctl->ticket[kOpCombine][1], lane); t < t_stop;
+         t = p.t_begin + next_ticket(&ctl->ticket[kOpCombine][1], lane)) {
       const int ss = lane < P ? a.send_slot[(size_t)t * P + lane] : -1;
       const unsigned dmask = __ballot_sync(0xffffffffu, ss >= 0);
       const bool local = p.local_direct && ((dmask >> me) & 1u);
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_ht_kernel(const
           my_op = reinterpret_cast<unsigned long long>(x + (size_t)l_row_o * row_bytes);
         } else {
           const int d = __fns(rmask, 0, (lane < nlow ? lane : lane - n_local) + 1);
-          my_op = reinterpret_cast<unsigned long long>(partial + ((size_t)t * P + d) * row_bytes);
+          my_op = reinterpret_cast<unsigned long long>(partial + ((size_t)(t - p.t_begin) * P + d) * row_bytes);
         }
       }
       const int4* b0 = a.bias0 ? reinterpret_cast<const int4*>(a.bias0 + (size_t)t * H) : nullptr;

@@ -134,9 +134,19 @@ class ElasticBuffer:
         self._id, _next_buffer_id = _next_buffer_id, _next_buffer_id + 1
         self._destroyed = False
         needed = L.elastic_size_hint(self.world_size, num_max_tokens_per_rank, hidden, num_topk)
+        # Capacity fallback (parity: deep_ep/buffers/_combine_reuse.py of the reference): a workspace capped below the size
+        # hint keeps the partials of a window of tokens only, and combine runs one pass per window.
+        self.combine_window = 0
         if num_bytes not in (None, 0) and num_bytes < needed:
-            raise ValueError(f"num_bytes={num_bytes} is too small for this shape; get_buffer_size_hint gives {needed}")
-        self.num_bytes = needed if num_bytes in (None, 0) else int(num_bytes)
+            try:
+                self.combine_window = L.combine_window(self.world_size, num_max_tokens_per_rank, hidden, num_topk, int(num_bytes))
+            except ValueError as exc:
+                raise ValueError(f"num_bytes={num_bytes} is too small for this shape ({exc}); get_buffer_size_hint gives "
+                                 f"{needed}") from None
+            needed = L.workspace_bytes(self.world_size, num_max_tokens_per_rank, hidden, num_topk,
+                                       L.ll_region_bytes(self.world_size, num_max_tokens_per_rank, hidden, num_topk),
+                                       0, self.combine_window)
+        self.num_bytes = needed if num_bytes in (None, 0) or self.combine_window else int(num_bytes)
         self.on_cuda = torch.cuda.is_available() and (
             self.control.backend() != "gloo" or (device is not None and torch.device(device).type == "cuda"))
         self.runtime: Optional[Runtime] = None
@@ -154,7 +164,7 @@ class ElasticBuffer:
             C = require_native("ElasticBuffer")
             self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
             ll = L.ll_region_bytes(self.world_size, num_max_tokens_per_rank, hidden, num_topk)
-            self.layout = C.make_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, ll, 0)
+            self.layout = C.make_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, ll, 0, self.combine_window)
             assert self.layout.total == needed, "native and Python workspace layouts disagree"
             self.runtime = Runtime(self.control, self.layout, float(_timeout_seconds(num_gpu_timeout_secs)), self.device)
             self.engine = CudaEngine([self.runtime.native], self.layout, self.device, num_sms=num_sms)

@@ -348,8 +348,13 @@ class CudaEngine:
             send, recv = max(1, int(split[0])), max(1, int(split[1]))
             if send + recv > limit:
                 raise ValueError(f"combine_num_sms + reduce_num_sms must not exceed {limit} on this device")
-        self._timed("combine", stream, lambda: self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream),
-                                                              self.local_direct, self._device_profile))
+        # one launch per token window: all tokens at once unless the workspace holds the partials of fewer tokens
+        window, most = lay.partial_tokens, max([plan.num_tokens for plan in plans] + [1])
+        if self.n == 1 and self.world > 1 and window < lay.max_tokens:
+            most = lay.max_tokens         # real ranks cannot see each other's token counts: every rank runs every pass
+        for begin in range(0, most, window):
+            self._timed("combine", stream, lambda b=begin: self.C.combine(lay, self.sessions, args, send, recv, self._stream(stream),
+                                                                          self.local_direct, self._device_profile, b, b + window))
         return outs
 
     # ------------------------------------------------------------------ low latency

@@ -54,13 +54,16 @@ def ll_region_bytes(world: int, max_tokens: int, hidden: int, topk: int) -> int:
     return 2 * at
 
 
-def workspace_bytes(world: int, max_tokens: int, hidden: int, topk: int, ll_bytes: int = 0, mega_bytes: int = 0) -> int:
-    """Python mirror of the native ``make_layout`` (checked against it in the tests)."""
+def workspace_bytes(world: int, max_tokens: int, hidden: int, topk: int, ll_bytes: int = 0, mega_bytes: int = 0,
+                    partial_tokens: int = 0) -> int:
+    """Python mirror of the native ``make_layout`` (checked against it in the tests).  ``partial_tokens``: tokens whose
+    combine partials are held at a time (0 = all of them)."""
+    window = partial_tokens or max_tokens
     at = CONTROL_BYTES
     stage_row = align_up(hidden * 2, 128)
     groups, row_blocks = -(-max_tokens // GROUP_TOKENS), -(-max_tokens // ROW_BLOCK)
     for size in (world * 4 * 4, world * max_tokens * topk * 4, world * max_tokens * topk * 4,
-                 world * max_tokens * stage_row, max_tokens * world * hidden * 2, max_tokens * topk * 4,
+                 world * max_tokens * stage_row, window * world * hidden * 2, max_tokens * topk * 4,
                  world * groups * 8, world * row_blocks * 8, ll_bytes, mega_bytes):
         at = align_up(at + size, 1024)
     return align_up(at, ALIGN)
@@ -75,3 +78,23 @@ def elastic_size_hint(world: int, max_tokens: int, hidden: int, topk: int) -> in
         raise ValueError(f"num_topk must be in [1, {MAX_TOPK}]")
     validate_hidden(hidden)
     return workspace_bytes(world, max_tokens, hidden, topk, ll_region_bytes(world, max_tokens, hidden, topk))
+
+
+def combine_window(world: int, max_tokens: int, hidden: int, topk: int, capacity: int) -> int:
+    """Capacity fallback of the combine (parity: ``deep_ep/buffers/_combine_reuse.py:8-34`` of the reference): the largest
+    number of tokens whose partials fit a workspace of ``capacity`` bytes, found by bisection; 0 when all tokens fit.
+    The other regions (routing tables, dispatch staging, flags, low-latency region) are not windowed: a capacity that
+    cannot hold them plus one token's partials is an error."""
+    ll = ll_region_bytes(world, max_tokens, hidden, topk)
+    if workspace_bytes(world, max_tokens, hidden, topk, ll) <= capacity:
+        return 0
+    if workspace_bytes(world, max_tokens, hidden, topk, ll, 0, 1) > capacity:
+        raise ValueError("num_bytes cannot hold the fixed regions of the workspace and one token's combine partials")
+    low, high = 1, max_tokens
+    while low < high:
+        middle = (low + high + 1) // 2
+        if workspace_bytes(world, max_tokens, hidden, topk, ll, 0, middle) <= capacity:
+            low = middle
+        else:
+            high = middle - 1
+    return low

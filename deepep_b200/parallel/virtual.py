@@ -20,11 +20,11 @@ from .engine_cuda import CudaEngine
 
 class VirtualWorld:
     def __init__(self, world: int, num_max_tokens_per_rank: int, hidden: int, num_topk: int, device=None,
-                 timeout: float = 20.0, num_sms: int = 0, ll_bytes: int = 0, mega_bytes: int = 0):
+                 timeout: float = 20.0, num_sms: int = 0, ll_bytes: int = 0, mega_bytes: int = 0, partial_tokens: int = 0):
         C = require_native("VirtualWorld")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         torch.cuda.set_device(self.device)
-        self.layout = C.make_layout(world, num_max_tokens_per_rank, hidden, num_topk, ll_bytes, mega_bytes)
+        self.layout = C.make_layout(world, num_max_tokens_per_rank, hidden, num_topk, ll_bytes, mega_bytes, partial_tokens)
         self.sessions = [C.Session(r, world, self.layout.total, timeout) for r in range(world)]
         bases = [s.workspace for s in self.sessions]
         for s in self.sessions:

@@ -186,3 +186,56 @@ def test_index_checks_report_instead_of_reading_out_of_range():
         torch.cuda.synchronize()
         for s in vw.sessions:
             s.close()
+
+
+def test_combine_in_token_windows():
+    """Capacity fallback: the workspace holds the combine partials of 48 tokens at a time, so the combine of up to 200
+    tokens per rank runs as five passes (one launch per window) and must still match the oracle bit for bit."""
+    from deepep_b200.parallel.virtual import VirtualWorld
+
+    dev = torch.device("cuda")
+    world, tokens, hidden, experts, topk = 4, [130, 64, 1, 200], 512, 16, 4
+    xs = [torch.randn((t, hidden), generator=torch.Generator().manual_seed(r)).bfloat16() for r, t in enumerate(tokens)]
+    idx = [make_routes("invalid", t, experts, topk, world, 10 * r) for r, t in enumerate(tokens)]
+    wts = [make_weights(t, topk, r) for r, t in enumerate(tokens)]
+    ref, lays = R.dispatch(xs, idx, wts, experts, do_expand=True)
+    eouts = [(ref[r][0].float() * 0.5).bfloat16() for r in range(world)]
+    evals = [0.5 - ref[r][2] for r in range(world)]
+    cref = R.combine(eouts, lays, tokens, topk, topk_weights=evals)
+    for local_direct in (True, False):
+        with VirtualWorld(world, max(tokens), hidden, topk, timeout=10.0, partial_tokens=48) as vw:
+            eng = vw.engine
+            eng.local_direct = local_direct
+            assert vw.layout.partial_tokens == 48
+            plans = eng.notify([i.to(dev) for i in idx], [w.to(dev) for w in wts], experts, expand=True, alignment=1)
+            outs = eng.dispatch([x.to(dev) for x in xs], plans, 0)
+            for rep in range(2):
+                couts = eng.combine([e.to(dev) for e in eouts], plans, [v.to(dev) for v in evals])
+                torch.cuda.synchronize()
+                eng.check_status()
+                for r in range(world):
+                    assert bits_equal(outs[r][0], ref[r][0])
+                    assert bits_equal(couts[r][0], cref[r][0]), f"rank {r} combined payload differs"
+                    assert torch.equal(couts[r][1].cpu(), cref[r][1]), f"rank {r} returned weights differ"
+
+
+def test_public_api_with_a_capped_workspace():
+    """``num_bytes`` below the size hint: the buffer picks the largest token window that fits and combine still matches."""
+    from deepep_b200 import ElasticBuffer
+    from deepep_b200.parallel import layout as L
+
+    dev = torch.device("cuda")
+    T, H, E, K = 1024, 2048, 32, 6
+    need = ElasticBuffer.get_buffer_size_hint(None, T, H, K, world_size=1)
+    cap = need - (2 << 20)                  # 2 MiB short of the 4 MiB of partials: about half of the tokens fit at a time
+    buf = ElasticBuffer(None, num_bytes=cap, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True)
+    assert 0 < buf.combine_window < T and buf.num_bytes <= cap
+    x = torch.randn((T, H), generator=torch.Generator().manual_seed(1)).bfloat16()
+    idx = make_routes("random", T, E, K, 1, 3)
+    w = make_weights(T, K, 2)
+    rx, _, rw, handle, _ = buf.dispatch(x.to(dev), topk_idx=idx.to(dev), topk_weights=w.to(dev), num_experts=E, do_expand=True)
+    ref, lays = R.dispatch([x], [idx], [w], E, do_expand=True)
+    assert bits_equal(rx, ref[0][0])
+    out, _, _ = buf.combine(rx, handle)
+    assert bits_equal(out, R.combine([ref[0][0]], lays, [T], K)[0][0])
+    buf.destroy()

@@ -80,6 +80,10 @@ def test_native_layout_matches_python_mirror():
     for a in [(8, 4096, 7168, 8), (2, 128, 512, 4), (1, 100, 256, 2), (4, 16384, 4096, 6)]:
         ll = L.ll_region_bytes(*a)
         assert C.make_layout(*a, ll, 0).total == L.workspace_bytes(*a, ll)
+        window = max(1, a[1] // 3)          # a workspace that holds the combine partials of a third of the tokens
+        capped = C.make_layout(*a, ll, 0, window)
+        assert capped.total == L.workspace_bytes(*a, ll, 0, window) <= C.make_layout(*a, ll, 0).total
+        assert capped.partial_tokens == window and C.make_layout(*a, ll, 0).partial_tokens == a[1]
         if ll:
             assert C.ll_region_bytes(a[0], a[1], a[3], a[2]) == ll
 
@@ -229,3 +233,23 @@ def test_loader_refuses_a_binary_that_is_not_the_recorded_one(tmp_path, monkeypa
     monkeypatch.setattr(ops, "build_info", lambda: {"binary": ops.native_path().name, "binary_sha256": "0" * 64})
     with pytest.raises(ops.NativeUnavailable, match="not the one"):
         ops.load_native()
+
+
+def test_combine_window_for_a_capped_workspace():
+    """Capacity fallback: the largest token window whose combine partials fit the given bytes (bisection), 0 when
+    everything fits, an error when not even the fixed regions fit."""
+    a = (8, 4096, 7168, 8)
+    full = L.elastic_size_hint(*a)
+    assert L.combine_window(*a, full) == 0 and L.combine_window(*a, full + 12345) == 0
+    ll = L.ll_region_bytes(*a)
+    w = L.combine_window(*a, full - (200 << 20))
+    assert 0 < w < 4096
+    assert L.workspace_bytes(*a, ll, 0, w) <= full - (200 << 20) < L.workspace_bytes(*a, ll, 0, w + 64)
+    with pytest.raises(ValueError):
+        L.combine_window(*a, 1 << 20)
+    buf_args = dict(num_max_tokens_per_rank=64, hidden=256, num_topk=2, explicitly_destroy=True, device="cpu")
+    from deepep_b200 import ElasticBuffer
+    need = ElasticBuffer.get_buffer_size_hint(None, 64, 256, 2, world_size=1)
+    with pytest.raises(ValueError, match="too small"):
+        ElasticBuffer(None, num_bytes=4096, **buf_args)
+    assert need > 0
