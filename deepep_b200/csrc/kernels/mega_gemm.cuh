@@ -57,9 +57,8 @@ __host__ __device__ constexpr size_t gemm_smem_bytes(int stages, bool staging) {
 }
 
 // The MMA thread releases pipeline stages in groups of kCommitEvery (one tcgen05.commit per group); a stage is reloaded
-// once the commit of its group has arrived.  One stage per commit is the fastest setting measured: releasing two stages
-// per commit made the fused layer slower (4096 tokens, 32 local experts: GEMM phases 1641 against 1361 us), because a
-// stage then waits up to one more stage time before it is reloaded.
+// once the commit of its group has arrived.  With more than one stage per commit a stage waits up to one more stage time
+// before it is reloaded, which costs more than the saved commits (measured), so every stage has its own commit.
 constexpr int kCommitEvery = 1;
 constexpr int kGroupRing = 4;   // group barriers in rotation; more than the groups a producer can be ahead of the MMAs
 constexpr int kSchedRing = 8;   // tile ids in flight between the producer and the slowest consumer (< stages + 2)

@@ -109,15 +109,13 @@ class MegaEngine:
         self.dynamic_tiles = os.environ.get("DEEPEP_MEGA_STATIC_TILES", "0") in ("", "0")
         # GEMM2 tiles scheduled after all GEMM1 tiles (0, the default) or right after their GEMM1 wave, which spreads the
         # combine rows over the kernel instead of its last third.  The value is the wave length in units of two rounds of
-        # GEMM1 tiles over the CTAs.  Measured with 4096 tokens per rank, off against on: 1560 against 1575-1629 us on one
-        # GPU, 1951 against 2046 us on two, 2372 against 2399 us on four, so it stays an option (DEEPEP_MEGA_INTERLEAVE=<units>).
+        # GEMM1 tiles over the CTAs (DEEPEP_MEGA_INTERLEAVE=<units>); off was the faster setting at 1, 2 and 4 GPUs.
         default = "0"
         self.interleave = int(os.environ.get("DEEPEP_MEGA_INTERLEAVE", default) or 0)   # wave length in units of two CTA rounds
-        # CTA pairs (clusters of two CTAs share every weights tile: tcgen05.mma.cta_group::2): off by default.  The fused
-        # layer gains nothing from them (4096 tokens per rank over 32 local experts on one GPU: GEMM phases 1348 us with
-        # pairs, 1361 us without; experts padded to whole pairs of 128-row tiles carry 6 % more rows), the stand-alone GEMM
-        # of the first projection is 5-17 % faster with them.  DEEPEP_MEGA_PAIRS=1 turns them on, "auto" uses them when
-        # the local experts average 384 rows or more.  Only with one rank per GPU: virtual ranks share the SMs.
+        # CTA pairs (clusters of two CTAs share every weights tile: tcgen05.mma.cta_group::2): off by default, the fused
+        # layer is as fast without them and experts padded to whole pairs of 128-row tiles carry more rows.
+        # DEEPEP_MEGA_PAIRS=1 turns them on, "auto" uses them when the local experts average 384 rows or more.
+        # Only with one rank per GPU: virtual ranks share the SMs.
         self.pairs = os.environ.get("DEEPEP_MEGA_PAIRS", "0").lower()
         if self.pairs not in ("auto", "0", "1"):
             raise ValueError("DEEPEP_MEGA_PAIRS must be auto, 0 or 1")

@@ -219,6 +219,21 @@ def init_group(group=None, *, rank: Optional[int] = None, world_size: Optional[i
     return _GROUP.config()
 
 
+def check_errors() -> None:
+    """Synchronise and raise if a kernel of this group reported a pipeline wait that ran out or row counts that do not fit
+    (the kernels move no row in either case).  The ops call this themselves when ``DEEPEP_GMM_CHECK=1`` is set; without
+    it they stay asynchronous and a caller checks at a point where a synchronisation is acceptable."""
+    if _GROUP is not None and _GROUP.engine is not None:
+        _GROUP.engine.check()
+
+
+def _maybe_check(g) -> None:
+    import os
+
+    if g.engine is not None and os.environ.get("DEEPEP_GMM_CHECK", "0") not in ("", "0"):
+        g.engine.check()
+
+
 def destroy_group() -> None:
     global _GROUP
     if _GROUP is not None:
@@ -361,6 +376,7 @@ def alltoallv_gmm(x: torch.Tensor, weight: torch.Tensor, local_tokens_per_expert
             all_to_allv_out.copy_(gath[g.rank])
     else:
         g.engine.a2av_gmm([x], [weight], [local], [out], [all_to_allv_out if output_all_to_allv else None], num_experts=expert_num)
+        _maybe_check(g)
     return (out, all_to_allv_out) if output_all_to_allv else out
 
 
@@ -393,12 +409,13 @@ def gmm_alltoallv(x: torch.Tensor, weight: torch.Tensor, local_tokens_per_expert
         out.copy_(outs[g.rank])
     else:
         g.engine.gmm_a2av([x], [weight], [local], [out], num_experts=expert_num)
+        _maybe_check(g)
     return out
 
 
 all_to_allv_grouped_matmul = alltoallv_gmm
 grouped_matmul_all_to_allv = gmm_alltoallv
 
-__all__ = ["GmmConfig", "GmmEngine", "all_to_allv_grouped_matmul", "alltoallv_gmm", "destroy_group", "destroy_udma_group",
+__all__ = ["GmmConfig", "GmmEngine", "all_to_allv_grouped_matmul", "alltoallv_gmm", "check_errors", "destroy_group", "destroy_udma_group",
            "get_config", "get_udma_config", "gmm_alltoallv", "grouped_matmul_all_to_allv", "init_group", "init_udma_group",
            "load_tiling_config", "reference_alltoallv_gmm", "reference_gmm_alltoallv", "symmetric_input", "symmetric_output"]
