@@ -188,3 +188,18 @@ def test_high_throughput_without_host_sync_in_a_graph():
         cref = R.combine([ref[0][0]], lays, [T], K)
         assert bits_equal(out, cref[0][0])
     buf.destroy()
+
+
+def test_machine_detection_on_this_gpu():
+    """What the constructor's preflight sees on a real device: a capability-10 GPU that reaches every visible GPU of the
+    box by peer access, and a buffer that records the agreed machine kind."""
+    from deepep_b200 import ElasticBuffer
+    from deepep_b200.parallel import topology as T
+
+    m = T.detect(0, torch.device("cuda", 0))
+    assert m.kind in ("single", "nvswitch") and tuple(m.capability)[0] == 10 and m.sm_count > 0 and m.uuid
+    assert m.peer_access[m.device] and all(m.peer_access.values()), m.peer_access
+    assert T.check_consensus([m]) == "single"
+    buf = ElasticBuffer(None, num_max_tokens_per_rank=64, hidden=256, num_topk=2, explicitly_destroy=True)
+    assert buf.machine_type == "single"
+    buf.destroy()
