@@ -13,7 +13,6 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 def main():
@@ -28,7 +27,7 @@ def main():
     ap.add_argument("--fp8", action="store_true")
     args = ap.parse_args()
     from deepep_b200.parallel.virtual import VirtualWorld
-    from helpers import group_limited_routes
+    from deepep_b200.utils.routing import group_limited_routes
 
     dev = torch.device("cuda")
     P, T, H, E, K = args.world, args.tokens, args.hidden, args.experts, args.topk

@@ -25,6 +25,7 @@
 namespace dep {
 
 constexpr int kLLThreads = 512;
+constexpr int kLLSendWarps = 8;      // dispatch: warps that push rows; the other warps of the block derive the layout meanwhile
 constexpr int kLLWords = 8;  // 256 tokens as 8 x 32-bit masks
 
 // A row travels as kLLParts column parts, each with its own flag, so that a row is spread over several warps on both
@@ -98,14 +99,20 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
   __shared__ int s_tot[kMaxExperts];
   __shared__ int s_T[kMaxRanks];
   __shared__ int s_rows;
+  __shared__ int s_fail;                                // a wait of the layout warps ran out
 
-  // profile instantiation only: phase stamps (nanoseconds since kernel start) of block 0 in Control::dbg[0..7]
+  // profile instantiation only: phase stamps (nanoseconds since kernel start) of block 0 in Control::dbg[0..7]; the
+  // first thread of the sending warps and the first thread of the layout warps stamp their own phases
   unsigned long long t_start = 0;
   if constexpr (kProfile) t_start = global_timer_ns();
-  auto stamp = [&](int i) {
+  auto stamp = [&](int i, int who = 0) {
     if constexpr (kProfile)
-      if (blockIdx.x == 0 && threadIdx.x == 0) ctl->dbg[i] = global_timer_ns() - t_start;
+      if (blockIdx.x == 0 && (int)threadIdx.x == who) ctl->dbg[i] = global_timer_ns() - t_start;
   };
+  constexpr int kLayoutFirst = kLLSendWarps * 32, LT = kLLThreads - kLayoutFirst;   // the layout warps and their thread count
+  const int lt = (int)threadIdx.x - kLayoutFirst;
+  auto layout_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(LT) : "memory"); };
+  if (threadIdx.x == 0) s_fail = 0;
 
   // ---- bank reuse: the call before last must have been consumed everywhere
   int ok = 1;
@@ -164,8 +171,12 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
       }
     }
     stamp(6);
+    uint8_t* mine = ctx.ws[me] + bank_off;
+    const int* gidx = reinterpret_cast<const int*>(mine + ll.gather_idx);
+    if (warp < kLLSendWarps) {
+    // ================================================================ sending warps: every row part to its destination
     PendingFlags pending;
-    for (int item = gw; item < a.T * P * kLLParts; item += total_warps) {
+    for (int item = warp * gridDim.x + blockIdx.x; item < a.T * P * kLLParts; item += gridDim.x * kLLSendWarps) {
       const int part = item % kLLParts, td = item / kLLParts;
       const int t = td / P, d = (me + td % P) % P;
       if (!((s_own[d][t >> 5] >> (t & 31)) & 1u)) continue;
@@ -224,41 +235,37 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
       pending.add(reinterpret_cast<unsigned long long*>(base + ll.row_flag) + ((size_t)me * M + j) * kLLParts + part, epoch, lane);
     }
     pending.publish(epoch, lane);
-
     stamp(1);
-    // ---- receive: wait for all routing tables, derive the layout
-    uint8_t* mine = ctx.ws[me] + bank_off;
-    ok = 1;
-    if (threadIdx.x < P)
-      ok = wait_flag_ge(reinterpret_cast<unsigned long long*>(mine + ll.idx_flag) + threadIdx.x, epoch, ctx, kOpLLDispatch, 1, threadIdx.x);
-    alive = __syncthreads_and(ok);
-  }
-  if (alive) {
-    uint8_t* mine = ctx.ws[me] + bank_off;
-    const int* gidx = reinterpret_cast<const int*>(mine + ll.gather_idx);
-    const float* gw_ = reinterpret_cast<const float*>(mine + ll.gather_w);
-    stamp(2);
-    if (threadIdx.x < kMaxRanks)
-      s_T[threadIdx.x] = threadIdx.x < P ? __ldcg(reinterpret_cast<const int*>(mine + ll.gather_hdr) + threadIdx.x * 4) : 0;
-    for (int i = threadIdx.x; i < E * kLLWords; i += kLLThreads) (&s_emask[0][0])[i] = 0u;
-    for (int i = threadIdx.x; i < kMaxRanks * kLLWords; i += kLLThreads) (&s_hit[0][0])[i] = 0u;
-    __syncthreads();
+    } else {
+    // ================================================================ layout warps: wait for all routing tables, derive the layout
+    int ok = 1;
+    if (lt < P)
+      ok = wait_flag_ge(reinterpret_cast<unsigned long long*>(mine + ll.idx_flag) + lt, epoch, ctx, kOpLLDispatch, 1, lt);
+    if (!ok) s_fail = 1;
+    layout_sync();
+    stamp(2, kLayoutFirst);
+    if (!s_fail) {
+    if (lt < kMaxRanks)
+      s_T[lt] = lt < P ? __ldcg(reinterpret_cast<const int*>(mine + ll.gather_hdr) + lt * 4) : 0;
+    for (int i = lt; i < E * kLLWords; i += LT) (&s_emask[0][0])[i] = 0u;
+    for (int i = lt; i < kMaxRanks * kLLWords; i += LT) (&s_hit[0][0])[i] = 0u;
+    layout_sync();
     int maxT = 1;
     for (int r = 0; r < P; ++r) maxT = max(maxT, min(s_T[r], M));
     // one thread per (source, token); the loads of four items are issued before the first of them is used
     constexpr int kBatch = 4;
-    for (int i0 = threadIdx.x; i0 < P * maxT; i0 += kLLThreads * kBatch) {
+    for (int i0 = lt; i0 < P * maxT; i0 += LT * kBatch) {
       int row[kBatch][kMaxTopk];
 #pragma unroll
       for (int b = 0; b < kBatch; ++b) {
-        const int i = i0 + b * kLLThreads, r = i / maxT, t = i - r * maxT;
+        const int i = i0 + b * LT, r = i / maxT, t = i - r * maxT;
         const bool live = i < P * maxT && t < s_T[r];
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) row[b][k] = (live && k < K) ? __ldcg(gidx + ((size_t)r * M + t) * K + k) : -1;
       }
 #pragma unroll
       for (int b = 0; b < kBatch; ++b) {
-        const int i = i0 + b * kLLThreads, r = i / maxT, t = i - r * maxT;
+        const int i = i0 + b * LT, r = i / maxT, t = i - r * maxT;
         if (i >= P * maxT) break;
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {
@@ -269,20 +276,20 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
         }
       }
     }
-    __syncthreads();
-    for (int l = threadIdx.x; l < Lx; l += kLLThreads) {
+    layout_sync();
+    for (int l = lt; l < Lx; l += LT) {
       int tot = 0;
       for (int r = 0; r < P; ++r) tot += popc8(s_emask[r * Lx + l]);
       s_tot[l] = tot;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    layout_sync();
+    if (lt == 0) {
       int run = 0;
       for (int l = 0; l < Lx; ++l) { int v = s_tot[l]; s_tot[l] = run; run += v; }
       s_rows = run;
     }
-    __syncthreads();
-    for (int l = threadIdx.x; l < Lx; l += kLLThreads) {
+    layout_sync();
+    for (int l = lt; l < Lx; l += LT) {
       int run = s_tot[l];
       for (int r = 0; r < P; ++r) { s_off[r * Lx + l] = run; run += popc8(s_emask[r * Lx + l]); }
       if (blockIdx.x == 0) {
@@ -291,8 +298,8 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
         if (a.mailbox) a.mailbox[4 + l] = run - s_tot[l];
       }
     }
-    __syncthreads();
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
+    layout_sync();
+    if (blockIdx.x == 0 && lt == 0) {
       a.expert_offsets[Lx] = s_rows;
       *a.num_rows = s_rows;
       if (a.mailbox) {
@@ -302,7 +309,20 @@ __global__ void __launch_bounds__(kLLThreads) ep_dispatch_ll_kernel(const __grid
       }
     }
 
-    stamp(3);
+    }
+    stamp(3, kLayoutFirst);
+    }
+    // ---- both halves of the block meet: the rows are on their way and the layout is known
+    __syncthreads();
+    alive = !s_fail;
+  }
+  if (alive) {
+    uint8_t* mine = ctx.ws[me] + bank_off;
+    const int* gidx = reinterpret_cast<const int*>(mine + ll.gather_idx);
+    const float* gw_ = reinterpret_cast<const float*>(mine + ll.gather_w);
+    int maxT = 1;
+    for (int r = 0; r < P; ++r) maxT = max(maxT, min(s_T[r], M));
+
     // ---- poll row flags and write the output rows
     const uint8_t* stage = mine + ll.stage;
     uint8_t* recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
