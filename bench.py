@@ -273,6 +273,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
+    from deepep_b200.utils.numa import bind_to_gpu
+
+    numa_node = bind_to_gpu(local_rank)      # pinned staging buffers are then allocated on the GPU's NUMA node
     dev = torch.device("cuda", local_rank)
     group = None
     if world > 1:
@@ -441,7 +444,7 @@ def main():
     e2e = {"value": bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
            "what": "H2D of x/topk_idx/topk_weights from pinned memory (copy stream, double-buffered) + notify + dispatch + "
-                   "combine + D2H of a checksum, every step"}
+                   "combine + D2H of a checksum, every step", "host_numa_node": numa_node}
 
     buf.destroy()
     if rank == 0:

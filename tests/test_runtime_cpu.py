@@ -253,3 +253,27 @@ def test_combine_window_for_a_capped_workspace():
     with pytest.raises(ValueError, match="too small"):
         ElasticBuffer(None, num_bytes=4096, **buf_args)
     assert need > 0
+
+
+def test_numa_binding_reads_sysfs(tmp_path):
+    """The NUMA helper parses a node's CPU list from a (fake) sysfs tree, only ever narrows the affinity of this process,
+    and answers None where the host gives no information."""
+    import os
+
+    from deepep_b200.utils import numa
+
+    assert numa._parse_cpu_list("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert numa.bind_to_numa_node(None) is None
+    assert numa.bind_to_numa_node(3, sysfs=str(tmp_path)) is None             # no such node in this tree
+    mine = sorted(os.sched_getaffinity(0))
+    node = tmp_path / "devices/system/node/node0"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text(f"{mine[0]}\n")
+    before = os.sched_getaffinity(0)
+    try:
+        assert numa.bind_to_numa_node(0, sysfs=str(tmp_path)) == {mine[0]}
+        assert os.sched_getaffinity(0) == {mine[0]}
+        (node / "cpulist").write_text("100000\n")                              # a CPU this process may not use: unchanged
+        assert numa.bind_to_numa_node(0, sysfs=str(tmp_path)) is None and os.sched_getaffinity(0) == {mine[0]}
+    finally:
+        os.sched_setaffinity(0, before)
