@@ -52,10 +52,40 @@ def bind_to_numa_node(node: Optional[int], sysfs: str = "/sys") -> Optional[Set[
     return allowed
 
 
+def gpu_cpu_affinity(device_index: int) -> Optional[Set[int]]:
+    """The CPUs the driver names as closest to the device (NVML, read-only query), or None without NVML.  Containers
+    often hide the NUMA node of a PCI device in sysfs while NVML still knows the device's CPU affinity."""
+    try:
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        try:
+            props = torch.cuda.get_device_properties(device_index)
+            bdf = f"{getattr(props, 'pci_domain_id', 0):08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(bdf.encode())
+            words = (max(os.sched_getaffinity(0) | {os.cpu_count() or 1}) + 64) // 64
+            mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        finally:
+            pynvml.nvmlShutdown()
+    except Exception:      # no NVML, no such query in this driver, or a device NVML cannot see: nothing to go by
+        return None
+    return {64 * i + b for i, w in enumerate(mask) for b in range(64) if (int(w) >> b) & 1} or None
+
+
 def bind_to_gpu(device_index: int) -> Optional[int]:
-    """Move this process next to its GPU; returns the NUMA node it now runs on, or None when the host gave no answer."""
+    """Move this process next to its GPU.  Returns the NUMA node it now runs on, -1 when only the driver's CPU list was
+    available (and used), or None when the host gave no answer or the CPUs are outside this process's allowance."""
     node = gpu_numa_node(device_index)
-    return node if bind_to_numa_node(node) else None
+    if bind_to_numa_node(node):
+        return node
+    cpus = gpu_cpu_affinity(device_index)
+    if cpus and hasattr(os, "sched_setaffinity"):
+        allowed = os.sched_getaffinity(0) & cpus
+        if allowed and allowed != os.sched_getaffinity(0):
+            os.sched_setaffinity(0, allowed)
+            return -1
+    return None
 
 
-__all__ = ["bind_to_gpu", "bind_to_numa_node", "gpu_numa_node"]
+__all__ = ["bind_to_gpu", "bind_to_numa_node", "gpu_cpu_affinity", "gpu_numa_node"]

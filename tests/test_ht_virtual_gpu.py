@@ -239,3 +239,30 @@ def test_public_api_with_a_capped_workspace():
     out, _, _ = buf.combine(rx, handle)
     assert bits_equal(out, R.combine([ref[0][0]], lays, [T], K)[0][0])
     buf.destroy()
+
+
+def test_phase_stamps_of_the_profile_instantiations():
+    """`enable_device_profile` launches the profile instantiations; the routing pass stamps its phases (monotonic,
+    microseconds) and the high-throughput kernels fill one record per block.  Production launches leave no stamps."""
+    from deepep_b200.parallel.virtual import VirtualWorld
+
+    dev = torch.device("cuda")
+    world, T, H, E, K = 2, 96, 256, 8, 2
+    xs = [torch.randn((T, H), generator=torch.Generator().manual_seed(r)).bfloat16().to(dev) for r in range(world)]
+    idx = [make_routes("random", T, E, K, world, r).to(dev) for r in range(world)]
+    wts = [make_weights(T, K, r).to(dev) for r in range(world)]
+    with VirtualWorld(world, T, H, K, timeout=10.0) as vw:
+        eng = vw.engine
+        eng.enable_device_profile(True)
+        plans = eng.notify(idx, wts, E, expand=True, alignment=1)
+        outs = eng.dispatch(xs, plans, 0)
+        eng.combine([o[0] for o in outs], plans, [None] * world)
+        stamps = eng.phase_stamps("notify")
+        order = [stamps[k] for k in ("table_sent", "tables_in", "histograms", "scans", "records", "done")]
+        assert all(b >= a for a, b in zip(order, order[1:])) and 0 < order[-1] < 1e5, stamps
+        prof = eng.pop_device_profile()
+        assert {op for op, _ in prof} == {"dispatch", "combine"}
+        for blocks in prof.values():
+            assert blocks and all(b["end_us"] >= b["start_us"] >= 0 for b in blocks) and sum(b["rows"] for b in blocks) > 0
+        eng.enable_device_profile(False)
+        eng.check_status()
