@@ -22,6 +22,8 @@ __host__ __device__ inline long long sf_offset(long long row, long long k, long 
   return ((row / 128) * (K / 128) + k / 128) * kSfChunk + (row % 32) * 16 + (row % 128) / 32 * 4 + (k / 32) % 4;
 }
 
+constexpr int kGemmMaxStagesHost = 6;   // deepest operand pipeline of the grouped GEMM
+
 enum GemmEpilogue : int {
   kEpiStoreF32 = 0,        // C fp32 [rows, N] (tests)
   kEpiSwigluQuant = 1,     // tile = [128 gate | 128 up] columns -> silu(gate) * up -> e4m3 + ue8m0 per 32
@@ -40,7 +42,9 @@ struct MegaGemmParams {
   const int* num_mtiles;     // device scalar: tiles in use
   int max_mtiles, n_tiles, k_steps, n_total;
   int epi, b_tx_bytes;
-  int pair, pad3;            // stand-alone launch only: run as CTA pairs (the tile list must pair row blocks 2j, 2j + 1 of one expert)
+  int pair, stages;          // stand-alone launch only: run as CTA pairs (the tile list must pair row blocks 2j, 2j + 1 of one expert);
+                             // pipeline stages (0 = default)
+  int commit_every, pad3;    // stand-alone launch only: stages released per tcgen05.commit (0 = 1)
   // kEpiStoreF32
   float* c;
   int ldc, b_fp8;            // b_fp8: the weights are e4m3 (A8W8) instead of e2m1 (A8W4)

@@ -5,34 +5,41 @@ namespace dep {
 
 __global__ void __launch_bounds__(kGemmThreads, 1) mega_gemm_kernel(const __grid_constant__ MegaGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_phase<false>(p, nullptr, nullptr, smem_raw, p.epi == kEpiCombine ? 3 : 4, blockIdx.x, gridDim.x);
+  gemm_phase<false>(p, nullptr, nullptr, smem_raw, p.stages ? p.stages : (p.epi == kEpiCombine ? 3 : 4), blockIdx.x, gridDim.x, nullptr, 0,
+                    p.commit_every ? p.commit_every : 1);
 }
 // The same as CTA pairs: launched as clusters of two CTAs.
 __global__ void __launch_bounds__(kGemmThreads, 1) mega_gemm_pair_kernel(const __grid_constant__ MegaGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_phase<true>(p, nullptr, nullptr, smem_raw, 4, blockIdx.x / 2, gridDim.x / 2);
+  gemm_phase<true>(p, nullptr, nullptr, smem_raw, p.stages ? p.stages : 4, blockIdx.x / 2, gridDim.x / 2, nullptr, 0,
+                   p.commit_every ? p.commit_every : 1);
 }
 
 cudaError_t launch_mega_gemm(const MegaGemmParams& p, int blocks, cudaStream_t stream) {
-  const size_t a = gemm_smem_bytes(4, false), b = gemm_smem_bytes(3, true);
+  // shared memory: the operand pipeline (a CTA of a pair holds half of the weights tile), the scale chunks, the epilogue's
+  // staging area for the combine epilogue, barriers
+  const bool staging = p.epi == kEpiCombine;
+  const int stages = p.stages ? p.stages : (p.pair ? 4 : (staging ? 3 : 4));
+  const size_t stage_bytes = (size_t)kTileABytes + (p.pair ? 128 : kGemmBN) * kGemmBK + kSfStageBytes;
+  const size_t smem = 1024 + stages * stage_bytes + (staging ? kEpiStageBytes : 0) + 256;
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  const void* fn = p.pair ? (const void*)mega_gemm_pair_kernel : (const void*)mega_gemm_kernel;
   // the attribute belongs to the current device, so it is set on every launch (a process may drive several GPUs)
-  cudaError_t e = cudaFuncSetAttribute(mega_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(a > b ? a : b));
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   void* args[] = {const_cast<MegaGemmParams*>(&p)};
   if (p.pair) {
     if (blocks < 2) return cudaErrorInvalidValue;
-    e = cudaFuncSetAttribute(mega_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(a > b ? a : b));
-    if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks / 2 * 2); cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = a > b ? a : b; cfg.stream = stream;
+    cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelExC(&cfg, (const void*)mega_gemm_pair_kernel, args);
+    return cudaLaunchKernelExC(&cfg, fn, args);
   }
-  return cudaLaunchKernel((const void*)mega_gemm_kernel, dim3(blocks), dim3(kGemmThreads), args, p.epi == kEpiCombine ? b : a, stream);
+  return cudaLaunchKernel(fn, dim3(blocks), dim3(kGemmThreads), args, smem, stream);
 }
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

@@ -41,7 +41,7 @@ namespace dep {
 
 constexpr int kGemmThreads = 320;                    // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kEpiWarps = 8;
-constexpr int kGemmMaxStages = 4;
+constexpr int kGemmMaxStages = kGemmMaxStagesHost;
 constexpr int kTileABytes = kGemmBM * kGemmBK;       // 16 KB
 constexpr int kTileBBytes = kGemmBN * kGemmBK;       // 32 KB in shared memory (one byte per value)
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
@@ -56,15 +56,14 @@ __host__ __device__ constexpr size_t gemm_smem_bytes(int stages, bool staging) {
   return 1024 + (size_t)stages * (kStageBytes + kSfStageBytes) + (staging ? kEpiStageBytes : 0) + 256;
 }
 
-// The MMA thread releases pipeline stages in groups of kCommitEvery (one tcgen05.commit per group); a stage is reloaded
-// once the commit of its group has arrived.  With more than one stage per commit a stage waits up to one more stage time
-// before it is reloaded, which costs more than the saved commits (measured), so every stage has its own commit.
-constexpr int kCommitEvery = 1;
-constexpr int kGroupRing = 4;   // group barriers in rotation; more than the groups a producer can be ahead of the MMAs
+// The MMA thread releases pipeline stages in groups of `commit_every` (one tcgen05.commit per group); a stage is
+// reloaded once the commit of its group has arrived, so with groups of two the pipeline must be deep enough that a
+// whole group can be in flight while two others are consumed.
+constexpr int kGroupRing = 8;   // group barriers in rotation; more than the groups a producer can be ahead of the MMAs
 constexpr int kSchedRing = 8;   // tile ids in flight between the producer and the slowest consumer (< stages + 2)
 
 struct GemmBarriers {
-  uint64_t full[kGemmMaxStages], empty[kGemmMaxStages], acc_full, acc_empty, epi_done;
+  uint64_t full[kGemmMaxStages], acc_full, acc_empty, epi_done;
   uint64_t peer_acc_empty;         // CTA pairs: the odd CTA's acc_empty, forwarded to the even CTA
   uint64_t released[kGroupRing];   // the MMAs of a group of kCommitEvery stages have completed
   uint64_t sched[kSchedRing];      // the producer has published tile_id[slot]
@@ -163,7 +162,8 @@ __device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_til
 // make this call (cluster barriers).
 template <bool kPair>
 __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaGemmParams* g2, int* ready, uint8_t* smem_raw,
-                                           int stages, int cta, int num_ctas, int* tile_counter = nullptr, int interleave = 0) {
+                                           int stages, int cta, int num_ctas, int* tile_counter = nullptr, int interleave = 0,
+                                           int commit_every = 1) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
   uint8_t* tiles = smem;
@@ -177,7 +177,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kGemmMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int s = 0; s < kGemmMaxStages; ++s) mbar_init(&bars->full[s], 1);
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->acc_empty, kEpiWarps);
     mbar_init(&bars->epi_done, kEpiWarps);
@@ -246,7 +246,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
           const int s = it % stages;
           if (it >= (uint32_t)stages) {     // the stage's previous contents have been consumed: their group was released
-            const uint32_t grp = (it - (uint32_t)stages) / kCommitEvery;
+            const uint32_t grp = (it - (uint32_t)stages) / (uint32_t)commit_every;
             if (!bounded_wait(&bars->released[grp % kGroupRing], (grp / kGroupRing) & 1u, failed)) break;
           }
           uint8_t* a_dst = tiles + (size_t)s * kStage;
@@ -328,8 +328,8 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
             else
               umma::mma_block_scaled(tmem, da + 2 * k, db + 2 * k, umma::with_sf_ids(idesc, k, k), tsfa, tsfb, ks > 0 || k > 0);
           }
-          if (it % kCommitEvery == kCommitEvery - 1)      // stages (tiles, scale columns) reusable once these MMAs finished
-            commit_both(&bars->released[(it / kCommitEvery) % kGroupRing]);
+          if (it % (uint32_t)commit_every == (uint32_t)commit_every - 1)      // stages (tiles, scale columns) reusable once these MMAs finished
+            commit_both(&bars->released[(it / (uint32_t)commit_every) % kGroupRing]);
         }
         commit_both(&bars->acc_full);              // accumulator complete
       }

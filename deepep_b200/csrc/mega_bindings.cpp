@@ -46,6 +46,9 @@ void fill_gemm(MegaGemmParams& p, const py::dict& d, py::object session) {
   if (p.n_total % kGemmBN) throw std::invalid_argument("output width must be a multiple of 256");
   p.epi = geti(d, "epi");
   p.pair = geti(d, "pair", 0) ? 1 : 0;
+  p.stages = geti(d, "stages", 0); p.commit_every = geti(d, "commit_every", 0);
+  if (p.stages < 0 || p.stages > kGemmMaxStagesHost || p.stages == 1 || p.commit_every < 0 || p.commit_every > 2)
+    throw std::invalid_argument("stages must be 0 or 2..6, commit_every 0, 1 or 2");
   p.b_tx_bytes = geti(d, "b_tx_bytes", p.b_fp8 ? 128 * kGemmBK : 128 * kGemmBK / 2);   // bytes counted per 128-row box of weights
   p.c = ptr<float>(d, "c"); p.ldc = geti(d, "ldc");
   p.a2 = ptr<uint8_t>(d, "a2"); p.a2_sf = ptr<uint8_t>(d, "a2_sf"); p.inter = geti(d, "inter");

@@ -7,7 +7,7 @@ from deepep_b200.oracle import megamoe as O
 pytestmark = pytest.mark.gpu
 
 
-def _run(rows_per_expert, n_total, k, seed=0, b_tx=None, pair=False):
+def _run(rows_per_expert, n_total, k, seed=0, b_tx=None, pair=False, stages=0, commit_every=0):
     from deepep_b200.ops import load_native
 
     C = load_native()
@@ -35,6 +35,10 @@ def _run(rows_per_expert, n_total, k, seed=0, b_tx=None, pair=False):
         args["b_tx_bytes"] = b_tx
     if pair:
         args["pair"] = 1
+    if stages:
+        args["stages"] = stages
+    if commit_every:
+        args["commit_every"] = commit_every
     C.mega_gemm(args, None, 148, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert d["err"].item() == 0, "a pipeline wait ran out inside the GEMM kernel"
@@ -64,3 +68,12 @@ def test_cta_pairs_single_pair():
 def test_cta_pairs_grouped_shapes():
     """Several experts (odd tile counts are padded to whole pairs), a K loop longer than the pipeline, several N tiles."""
     _run([100, 1, 300, 256], 512, 2048, seed=3, pair=True)
+
+
+def test_pipeline_depth_and_commit_grouping():
+    """The operand pipeline with other depths and with two stages released per commit gives the same numbers (K loop of
+    16 steps, longer than any of the pipelines; plain and CTA-pair kernels)."""
+    _run([128, 256], 256, 2048, seed=5, stages=2)
+    _run([128, 256], 256, 2048, seed=5, stages=4, commit_every=2)
+    _run([256, 512], 512, 2048, seed=6, pair=True, stages=6, commit_every=2)
+    _run([256], 256, 2048, seed=7, pair=True, stages=3)
