@@ -119,6 +119,9 @@ class ElasticBuffer:
             raise ValueError("bootstrap must be 'default', 'group' or 'store'")
         if num_max_tokens_per_rank <= 0 or hidden <= 0 or num_topk <= 0:
             raise ValueError("num_max_tokens_per_rank, hidden and num_topk are required")
+        for name, value in (("num_gpu_timeout_secs", num_gpu_timeout_secs), ("num_cpu_timeout_secs", num_cpu_timeout_secs)):
+            if not 1 <= float(value) <= 3600:
+                raise ValueError(f"{name} must be in [1, 3600] seconds")
         if num_max_tokens_per_rank > L.MAX_TOKENS or num_topk > L.MAX_TOPK:
             raise ValueError(f"limits: tokens <= {L.MAX_TOKENS}, top-k <= {L.MAX_TOPK}")
         L.validate_hidden(hidden, use_fp8_dispatch)

@@ -1,0 +1,128 @@
+"""Argument validation and handle rules of ``ElasticBuffer`` on the CPU engine (one process): every documented
+rejection raises the documented exception and leaves the buffer usable."""
+import pytest
+import torch
+
+from helpers import make_weights
+
+
+T, H, K, E = 48, 256, 4, 8
+
+
+@pytest.fixture()
+def buf():
+    from deepep_b200 import ElasticBuffer
+
+    b = ElasticBuffer(None, num_max_tokens_per_rank=512, hidden=H, num_topk=K, explicitly_destroy=True, device="cpu")
+    yield b
+    b.destroy()
+
+
+def _inputs(tokens=T):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn((tokens, H), generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(tokens)]).to(torch.int64)
+    return x, idx, make_weights(tokens, K)
+
+
+@pytest.mark.parametrize("kwargs, message", [
+    (dict(num_max_tokens_per_rank=0, hidden=H, num_topk=K), "required"),
+    (dict(num_max_tokens_per_rank=1 << 20, hidden=H, num_topk=K), "limits"),
+    (dict(num_max_tokens_per_rank=64, hidden=H, num_topk=64), "limits"),
+    (dict(num_max_tokens_per_rank=64, hidden=H, num_topk=K, machine_type="mesh_clos"), "machine_type"),
+    (dict(num_max_tokens_per_rank=64, hidden=H, num_topk=K, bootstrap="mpi"), "bootstrap"),
+    (dict(num_max_tokens_per_rank=64, hidden=H, num_topk=K, num_gpu_timeout_secs=0), "seconds"),
+    (dict(num_max_tokens_per_rank=64, hidden=100, num_topk=K, use_fp8_dispatch=True), "hidden"),
+])
+def test_constructor_rejections(kwargs, message):
+    from deepep_b200 import ElasticBuffer
+
+    with pytest.raises(ValueError, match=message):
+        ElasticBuffer(None, explicitly_destroy=True, device="cpu", **kwargs)
+
+
+def test_dispatch_rejections_leave_the_buffer_usable(buf):
+    x, idx, w = _inputs()
+    bad = [
+        (dict(x=x[:, :128], topk_idx=idx, num_experts=E), "tokens,"),                       # wrong hidden
+        (dict(x=x.t().contiguous().t(), topk_idx=idx, num_experts=E), "contiguous"),
+        (dict(x=torch.zeros((600, H), dtype=torch.bfloat16), topk_idx=torch.zeros((600, K), dtype=torch.int64), num_experts=E), "exceed"),
+        (dict(x=x.float(), topk_idx=idx, num_experts=E), "bf16"),
+        (dict(x=x, topk_idx=idx.int(), num_experts=E), "topk_idx"),
+        (dict(x=x, topk_idx=idx[:, :2].contiguous(), num_experts=E), "topk_idx"),
+        (dict(x=x, topk_idx=idx, topk_weights=w.double(), num_experts=E), "topk_weights"),
+        (dict(x=x, topk_idx=idx, num_experts=0), "num_experts"),
+        (dict(x=x, topk_idx=idx, num_experts=2048), "num_experts"),
+        (dict(x=x, num_experts=E), "fresh dispatch"),
+        (dict(x=x, topk_idx=idx, num_experts=E, expert_alignment=0, do_expand=True), "positive"),
+        (dict(x=x, topk_idx=idx, num_experts=E, expert_alignment=16), "do_expand"),
+        (dict(x=(x, torch.ones((T, H // 128))), topk_idx=idx, num_experts=E), "fp8 pair"),
+    ]
+    for kwargs, message in bad:
+        xin = kwargs.pop("x")
+        with pytest.raises(ValueError, match=message):
+            buf.dispatch(xin, **kwargs)
+    rx, _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)   # still fine
+    assert rx.shape[0] == T * K and handle.num_recv_tokens_per_expert_list is not None
+
+
+def test_combine_and_handle_rules(buf):
+    from deepep_b200 import ElasticBuffer
+
+    x, idx, w = _inputs()
+    rx, _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+    with pytest.raises(ValueError, match="rows"):
+        buf.combine(rx[:-1], handle)
+    with pytest.raises(ValueError, match="bf16"):
+        buf.combine(rx.float(), handle)
+    with pytest.raises(ValueError, match="contiguous"):
+        buf.combine(torch.zeros((H, rx.shape[0]), dtype=torch.bfloat16).t(), handle)
+    with pytest.raises(ValueError, match="topk_weights"):
+        buf.combine(rx, handle, topk_weights=rw.double())
+    with pytest.raises(ValueError, match="bias"):
+        buf.combine(rx, handle, bias=torch.zeros((T, H)))
+    with pytest.raises(ValueError, match="together"):
+        buf.combine(rx, handle, combine_num_sms=8)
+    with pytest.raises(ValueError, match="nonnegative"):
+        buf.combine(rx, handle, combine_num_sms=-1, reduce_num_sms=4)
+    with pytest.raises(TypeError, match="EPHandle"):
+        buf.combine(rx, object())
+    with pytest.raises(ValueError, match="token count"):
+        buf.dispatch(x[:10].contiguous(), handle=handle)
+    with pytest.raises(ValueError, match="not both"):
+        buf.dispatch(x, topk_idx=idx, num_experts=E, handle=handle)
+    other = ElasticBuffer(None, num_max_tokens_per_rank=512, hidden=H, num_topk=K, explicitly_destroy=True, device="cpu")
+    try:
+        with pytest.raises(ValueError, match="another buffer"):
+            other.combine(rx, handle)
+    finally:
+        other.destroy()
+    out, ow, _ = buf.combine(rx, handle, topk_weights=rw)                       # the handle survived all of the above
+    assert out.shape == (T, H) and torch.equal(ow, w)
+    again = buf.dispatch(x, handle=handle)[0]                                   # cached dispatch re-uses the routing
+    assert torch.equal(again.view(torch.int16), rx.view(torch.int16))
+    handle.topk_idx[0, 0] = (handle.topk_idx[0, 0] + 1) % E                     # in-place edit of saved routing is detected
+    with pytest.raises(RuntimeError, match="modified"):
+        buf.combine(rx, handle)
+
+
+def test_low_latency_selection_rules():
+    """A buffer of at most 256 tokens serves a default fresh dispatch with weights on the low-latency path; every option
+    that path does not have (``do_expand``, alignment, statistics, an SM budget, a cached handle) selects the other one."""
+    from deepep_b200 import ElasticBuffer
+
+    small = ElasticBuffer(None, num_max_tokens_per_rank=64, hidden=H, num_topk=K, explicitly_destroy=True, device="cpu")
+    try:
+        x, idx, w = _inputs(32)
+        assert small.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E)[3].is_low_latency
+        assert not small.dispatch(x, topk_idx=idx, num_experts=E)[3].is_low_latency                         # no weights
+        assert not small.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)[3].is_low_latency
+        stats = torch.zeros(E, dtype=torch.int64)
+        h = small.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, cumulative_local_expert_recv_stats=stats)[3]
+        assert not h.is_low_latency and int(stats.sum()) == 32 * K
+        assert not small.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, num_sms=24)[3].is_low_latency
+        ll = small.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E)
+        with pytest.raises(ValueError, match="saved at dispatch"):
+            small.combine(ll[0], ll[3], topk_weights=ll[2])
+    finally:
+        small.destroy()
