@@ -56,7 +56,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -314,12 +314,14 @@ def main():
         combined, _, _ = buf.combine(out_x, handle)
         return combined
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    sync_all()
+    # the sampler runs from the warm-up steps (the same kernels under the same load) to the end of the timed steps: the
+    # timed region alone lasts a few milliseconds, less than one sampling period of nvidia-smi
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(3, args.warmup)):
+        step()
+    sync_all()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     start.record()
