@@ -71,7 +71,8 @@ bool encode_sf_map(CUtensorMap* map, const void* base, long long chunks, const c
 // Phase stamps of the fused kernel, one record per CTA (globaltimer nanoseconds): kernel start, inputs quantised and
 // handshake done, routing layout done, token pull done (pull warps), GEMM tile loop done, finish handshake done, end.
 constexpr int kMegaTimerWords = 8;
-enum MegaTimerSlot : int { kTimStart = 0, kTimHandshake = 1, kTimLayout = 2, kTimPull = 3, kTimGemm = 4, kTimFinishSync = 5, kTimEnd = 6 };
+enum MegaTimerSlot : int { kTimStart = 0, kTimHandshake = 1, kTimLayout = 2, kTimPull = 3, kTimGemm = 4, kTimFinishSync = 5, kTimEnd = 6,
+                            kTimMmaThread = 7 };   // word 7: the MMA thread's cycles / 16, (waiting for operands) << 32 | (whole tile loop)
 
 // ---------------------------------------------------------------- routing + token pull
 struct MegaRouteArgs {

@@ -39,8 +39,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_kernel(const __grid
   // The token pull overlaps the GEMMs: rows are pulled tile by tile, a GEMM1 tile starts once its rows have arrived.
   const int warp = threadIdx.x >> 5;
   if (warp < kGemmThreads / 32) {
-    if constexpr (kPair) gemm_phase<true>(a.g1, &a.g2, a.ready, smem_raw, 4, blockIdx.x / 2, gridDim.x / 2, a.tile_counter, a.interleave);
-    else gemm_phase<false>(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x, a.tile_counter, a.interleave);
+    unsigned long long* stats = a.route.timer ? a.route.timer + (size_t)blockIdx.x * kMegaTimerWords + kTimMmaThread : nullptr;
+    if constexpr (kPair) gemm_phase<true>(a.g1, &a.g2, a.ready, smem_raw, 4, blockIdx.x / 2, gridDim.x / 2, a.tile_counter, a.interleave, 1, stats);
+    else gemm_phase<false>(a.g1, &a.g2, a.ready, smem_raw, 3, blockIdx.x, gridDim.x, a.tile_counter, a.interleave, 1, stats);
   } else {
     // the pull warps take part in the block (and, for CTA pairs, cluster) barriers of gemm_phase's set-up and tear-down
     if constexpr (kPair) { __syncthreads(); umma::cluster_sync_all(); }

@@ -163,7 +163,7 @@ __device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_til
 template <bool kPair>
 __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaGemmParams* g2, int* ready, uint8_t* smem_raw,
                                            int stages, int cta, int num_ctas, int* tile_counter = nullptr, int interleave = 0,
-                                           int commit_every = 1) {
+                                           int commit_every = 1, unsigned long long* mma_stats = nullptr) {
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);       // tiles need 1024-byte alignment
   uint8_t* tiles = smem;
@@ -293,6 +293,8 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         }
       };
       uint32_t it = 0;
+      long long waited = 0;                      // cycles spent waiting for operands (only counted when asked for)
+      const long long loop_start = mma_stats ? clock64() : 0;
       for (uint32_t local_tile = 0;; ++local_tile) {
         const int tile = fetch_tile(bars, local_tile, failed);
         if (tile < 0) break;
@@ -304,7 +306,9 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         umma::fence_after_sync();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % stages;
+          const long long w0 = mma_stats ? clock64() : 0;
           if (!bounded_wait(&bars->full[s], (it / stages) & 1u, failed)) break;
+          if (mma_stats) waited += clock64() - w0;
           umma::fence_after_sync();
           const uint32_t a_addr = smem_u32(tiles + (size_t)s * kStage);
           const uint32_t sf_addr = smem_u32(sf_smem + (size_t)s * kSfStageBytes);
@@ -333,6 +337,8 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         }
         commit_both(&bars->acc_full);              // accumulator complete
       }
+      if (mma_stats)
+        *mma_stats = ((unsigned long long)(waited >> 4) << 32) | (unsigned long long)(((clock64() - loop_start) >> 4) & 0xffffffffll);
     } else if (kPair && lane == 0) {
       // ---- odd CTA of a pair: no MMAs to issue; forward "accumulator drained" to the even CTA, once per tile
       const uint32_t acc_fwd = umma::map_to_cta(smem_u32(&bars->peer_acc_empty), 0);

@@ -102,7 +102,8 @@ def parse_timer(timer: torch.Tensor) -> Dict[str, float]:
     Every CTA stamps ``%globaltimer`` at: kernel start, inputs quantised + handshake done, routing layout done, its pull
     warps done, its GEMM tile loop done, finish handshake done, end.  The result holds, in microseconds, the time
     from the earliest start to the latest stamp of each boundary (so the phases add up to ``total_us``), plus the
-    spread of the CTAs' GEMM end (``gemm_tail_us``: how long the slowest CTA worked after the fastest was done).
+    spread of the CTAs' GEMM end (``gemm_tail_us``: how long the slowest CTA worked after the fastest was done) and
+    ``mma_thread_wait_share``: the share of its tile loop that the thread issuing the MMAs spent waiting for operands.
     Parity: the reference's timer tooling (``timer/protocol.py``, ``timer/parse_timer_csv.py``, ``timer/breakdown.py``).
     """
     rec = timer.detach().cpu().to(torch.int64)
@@ -118,6 +119,12 @@ def parse_timer(timer: torch.Tensor) -> Dict[str, float]:
                pull_done_us=last["pull"], gemm_us=max(0.0, last["gemm"] - last["layout"]),
                finish_sync_us=max(0.0, last["finish_sync"] - last["gemm"]), reduce_us=max(0.0, last["end"] - last["finish_sync"]),
                gemm_tail_us=(int(gemm_ends.max()) - int(gemm_ends.min())) / 1e3 if gemm_ends.numel() else 0.0)
+    if rec.shape[1] > 7:      # word 7: cycles / 16 of the thread that issues the MMAs, (waiting for operands) << 32 | (its whole tile loop)
+        word = rec[:, 7]
+        word = word[word != 0]
+        if word.numel():
+            waited, total = (word >> 32) & 0xffffffff, word & 0xffffffff
+            out["mma_thread_wait_share"] = float(waited.sum()) / max(float(total.sum()), 1.0)
     return out
 
 
