@@ -213,12 +213,18 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
     // ============================================================ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
+      // The ticket of the NEXT tile is taken while the current tile is being loaded, so the round trip of the atomic is
+      // off the path between two tiles.  A CTA still works through its tickets in increasing order, which is all the
+      // argument for the end of every GEMM2 wait needs.
+      const bool takes_tickets = tile_counter != nullptr && !(kPair && crank != 0);
+      int ticket = takes_tickets ? atomicAdd(tile_counter, 1) : 0;
       for (uint32_t local_tile = 0;; ++local_tile) {
         int tile;
         if (kPair && crank != 0) {
           tile = fetch_tile(bars, local_tile, failed, true);      // the even CTA hands out the pair's tiles
         } else {
-          tile = tile_counter ? atomicAdd(tile_counter, 1) : cta + (int)local_tile * num_ctas;
+          tile = takes_tickets ? ticket : cta + (int)local_tile * num_ctas;
+          if (takes_tickets && tile < total_tiles) ticket = atomicAdd(tile_counter, 1);
           if (tile >= total_tiles || *failed) tile = -1;
           else if (g2 && ready && interleave > 0)   // wave = row blocks whose GEMM1 tiles fill `2 * interleave` rounds of the CTAs
             tile = schedule_to_tile(tile, num_mtiles, g1.n_tiles, g2->n_tiles, (2 * interleave * num_ctas + g1.n_tiles - 1) / g1.n_tiles);
