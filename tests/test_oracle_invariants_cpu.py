@@ -29,7 +29,7 @@ def routing_cases(draw):
     return world, experts, topk, hidden, tokens, idx, xs, ws, align
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(routing_cases())
 def test_expanded_layout_invariants(case):
     world, experts, topk, hidden, tokens, idx, xs, ws, align = case
@@ -58,7 +58,7 @@ def test_expanded_layout_invariants(case):
         assert torch.equal(back[r][0].float(), xs[r].float() * n_valid)
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(routing_cases())
 def test_rank_layout_matches_expanded_layout(case):
     world, experts, topk, hidden, tokens, idx, xs, ws, _ = case
@@ -99,7 +99,7 @@ def test_hand_calculated_anchor():
     assert back[0][0][:, 0].tolist() == [1.5, 2.25] and back[1][0][:, 0].tolist() == [3.75]
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(routing_cases())
 def test_low_latency_combine_is_the_weighted_sum(case):
     """Identity experts and weights that are powers of two (products and sums exact): the low-latency combine returns
