@@ -71,8 +71,8 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 # Share of the blocks on the side that drives NVLink (dispatch: senders, combine: expert side), by world size.
-DISPATCH_SEND_FRACTION = {1: 1.0, 2: 0.5, 4: 0.4, 8: 0.35}
-COMBINE_SEND_FRACTION = {1: 0.0, 2: 0.5, 4: 0.55, 8: 0.6}
+DISPATCH_SEND_FRACTION = {1: 1.0, 2: 0.5, 4: 0.35, 8: 0.35}
+COMBINE_SEND_FRACTION = {1: 0.0, 2: 0.5, 4: 0.6, 8: 0.6}
 
 
 class CudaEngine:
