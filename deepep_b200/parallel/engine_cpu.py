@@ -119,7 +119,10 @@ class CpuEngine:
         plan = plans[0]
         x = xs[0]
         x = tuple(t.cpu() for t in x) if isinstance(x, (tuple, list)) else x.cpu()
-        all_x = self._gather(x)
+        if isinstance(x, tuple):     # e4m3 tensors do not survive the object pickling of the control plane: send their bytes
+            all_x = [(codes.view(torch.float8_e4m3fn), sf) for codes, sf in self._gather((x[0].view(torch.uint8), x[1]))]
+        else:
+            all_x = self._gather(x)
         outs, _ = R.dispatch(all_x, plan.all_idx, None, plan.num_experts, do_expand=plan.expand,
                              quantize_fp8=(mode == 2), layouts=plan.layouts)
         out = outs[self.rank][0]

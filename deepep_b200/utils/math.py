@@ -51,7 +51,8 @@ def per_token_cast_to_fp8(x: torch.Tensor, use_ue8m0: bool = False) -> Tuple[tor
     """
     assert x.dim() == 2, "x must be [tokens, hidden]"
     t, h = x.shape
-    blocks = _pad_last(x, FP8_BLOCK).view(t, -1, FP8_BLOCK)
+    nblocks = align(h, FP8_BLOCK) // FP8_BLOCK
+    blocks = _pad_last(x, FP8_BLOCK).view(t, nblocks, FP8_BLOCK)       # explicit sizes: an empty batch is legal
     amax = blocks.abs().float().amax(dim=2).clamp(1e-4)
     if use_ue8m0:
         scale = torch.exp2(torch.ceil(torch.log2(amax / FP8_MAX)))
@@ -59,7 +60,7 @@ def per_token_cast_to_fp8(x: torch.Tensor, use_ue8m0: bool = False) -> Tuple[tor
     else:
         scale = amax / FP8_MAX
         q = (blocks * (FP8_MAX / amax.unsqueeze(2))).to(torch.float8_e4m3fn)
-    return q.view(t, -1)[:, :h].contiguous(), scale
+    return q.view(t, nblocks * FP8_BLOCK)[:, :h].contiguous(), scale
 
 
 def per_token_cast_back(x_fp8: torch.Tensor, x_scales: torch.Tensor) -> torch.Tensor:
