@@ -340,7 +340,8 @@ class ElasticBuffer:
         if expert_alignment not in (None, 1) or do_zero_padding or col_major_sf:
             return False
         m = num_max or self.num_max_tokens_per_rank
-        return 0 < tokens <= m <= L.LL_MAX_TOKENS and self.num_max_tokens_per_rank <= L.LL_MAX_TOKENS
+        # nothing here may depend on this rank's own batch (an empty batch included): all ranks must choose alike
+        return tokens <= m <= L.LL_MAX_TOKENS and self.num_max_tokens_per_rank <= L.LL_MAX_TOKENS
 
     def dispatch(self, x, topk_idx=None, topk_weights=None, cumulative_local_expert_recv_stats=None, num_experts=None,
                  num_max_tokens_per_rank=None, expert_alignment=None, num_sms=0, num_qps=0, previous_event=None,

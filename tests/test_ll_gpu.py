@@ -102,3 +102,22 @@ def test_ll_graph_replay_public_api():
         expect = x.float().cpu() * (make_weights(T, K, seed) * ok).sum(1, keepdim=True)
         assert torch.allclose(out.float().cpu(), expect, rtol=0.02, atol=0.05)
     buf.destroy()
+
+
+def test_ll_empty_batch_takes_the_same_path():
+    """The path is chosen from the buffer and the options, never from a rank's own token count: an empty batch on a
+    decode buffer runs the low-latency kernels too (with peers, a rank that chose differently would never be answered)."""
+    from deepep_b200 import ElasticBuffer
+
+    dev = torch.device("cuda")
+    H, E, K = 512, 16, 4
+    buf = ElasticBuffer(None, num_max_tokens_per_rank=64, hidden=H, num_topk=K, explicitly_destroy=True)
+    x = torch.zeros((0, H), dtype=torch.bfloat16, device=dev)
+    idx = torch.zeros((0, K), dtype=torch.int64, device=dev)
+    w = torch.zeros((0, K), dtype=torch.float32, device=dev)
+    rx, _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E)
+    assert handle.is_low_latency and rx.shape == (0, H) and handle.num_recv_tokens_per_expert_list == [0] * E
+    out, _, _ = buf.combine(rx, handle)
+    torch.cuda.synchronize()
+    assert out.shape == (0, H)
+    buf.destroy()
