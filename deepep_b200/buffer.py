@@ -47,7 +47,12 @@ class Buffer:
     def _ensure(self, tokens: int, hidden: int, topk: int) -> ElasticBuffer:
         """V1 sizes its buffer in bytes only; the workspace is created on first use from the tensors' shape."""
         if self._elastic is None:
-            self._elastic = ElasticBuffer(self.group, num_max_tokens_per_rank=tokens, hidden=hidden, num_topk=topk,
+            if self.group is not None and not all(self._shape):
+                # sized on first use: the ranks' batches may differ, the workspace may not, so they agree on the largest
+                from .parallel.runtime import ControlPlane
+
+                tokens = max(ControlPlane(self.group).all_gather_object(int(tokens)))
+            self._elastic = ElasticBuffer(self.group, num_max_tokens_per_rank=max(tokens, 1), hidden=hidden, num_topk=topk,
                                           explicitly_destroy=self.explicitly_destroy)
         eb = self._elastic
         if tokens > eb.num_max_tokens_per_rank or hidden != eb.hidden or topk != eb.num_topk:

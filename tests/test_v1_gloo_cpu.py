@@ -53,6 +53,11 @@ def _worker(rank, port, results):
     again = buf.dispatch(xs[rank], handle=handle)[0]                      # cached dispatch: same rows without a layout pass
     checks["cached"] = bits_equal(again, ref[rank][0])
     buf.destroy()
+    # a buffer sized on first use: the ranks' batches differ (50 and 23 tokens), the workspace they agree on does not
+    lazy = deep_ep.Buffer(dist.group.WORLD)
+    rx2 = lazy.dispatch(xs[rank], topk_idx=idx[rank], topk_weights=ws[rank], num_tokens_per_expert=per_expert)[0]
+    checks["lazy"] = bits_equal(rx2, ref[rank][0]) and lazy._elastic.num_max_tokens_per_rank == max(TOKENS)
+    lazy.destroy()
     results[rank] = checks
     dist.destroy_process_group()
 
