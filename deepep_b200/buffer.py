@@ -148,14 +148,18 @@ class Buffer:
     def dispatch(self, x, handle=None, num_tokens_per_rank=None, num_tokens_per_rdma_rank=None, is_token_in_rank=None,
                  num_tokens_per_expert=None, topk_idx=None, topk_weights=None, expert_alignment: int = 1, num_worst_tokens: int = 0,
                  config: Optional[Config] = None, previous_event=None, async_finish: bool = False,
-                 allocate_on_comm_stream: bool = False):
+                 allocate_on_comm_stream: bool = False, zero_copy: bool = False):
         """(recv_x, recv_topk_idx, recv_topk_weights, num_recv_tokens_per_expert_list, handle, event).
 
         ``expert_alignment`` rounds the per-expert counts of the returned list up (the rows themselves keep the rank
         layout).  ``num_worst_tokens > 0`` gives outputs of exactly that many rows without any host synchronisation
         (the list is empty then); it must equal ``group size x num_max_tokens_per_rank`` and is required while the
-        current stream is being captured into a CUDA graph."""
+        current stream is being captured into a CUDA graph.  ``zero_copy`` (the reference's extension,
+        ``deep_ep/backends/direct/buffer.py:481-496``: outputs may alias the workspace) is accepted; the outputs here
+        always own their storage, which satisfies either setting."""
         del num_tokens_per_rank, num_tokens_per_rdma_rank
+        if not isinstance(zero_copy, bool):
+            raise TypeError("zero_copy must be a bool")
         if expert_alignment < 1:
             raise ValueError("expert_alignment must be positive")
         data = x[0] if isinstance(x, (tuple, list)) else x

@@ -59,4 +59,8 @@ def test_layout_dispatch_combine_and_stale_handles():
         buf.combine(rx, last)
     with pytest.raises(ValueError, match="num_worst_tokens"):
         buf.dispatch(x, topk_idx=idx, num_tokens_per_expert=per_expert, num_worst_tokens=5)
+    with pytest.raises(TypeError, match="zero_copy"):
+        buf.dispatch(x, topk_idx=idx, num_tokens_per_expert=per_expert, zero_copy=1)
+    zc = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_expert=per_expert, zero_copy=True)[0]
+    assert torch.equal(zc, rx)
     buf.destroy()
