@@ -292,6 +292,14 @@ class ElasticBuffer:
             comm.wait_stream(cur)
         return comm
 
+    @staticmethod
+    def _allocates_on_comm(allocate_on_comm_stream: bool, *events) -> bool:
+        """Outputs come from the communication stream's memory pool when the caller asks for it, and also whenever the
+        call is ordered after an event instead of after the current stream: a block that the current stream's pool
+        hands out may still be read by kernels queued there after that event was recorded, and the communication
+        kernels, which only wait for the event, would overwrite it under them."""
+        return bool(allocate_on_comm_stream) or any(_as_event(e) is not None for e in events)
+
     def _leave(self, comm, async_with_compute_stream: bool, resources: Sequence[Any],
                allocated_on_comm: bool = False) -> EventOverlap:
         """Sync mode: the current stream waits for the call.  Async mode: the caller waits on the returned event."""
@@ -380,6 +388,7 @@ class ElasticBuffer:
         self._preflight("dispatch", (tokens > self.num_max_tokens_per_rank, self.hidden, self.num_topk, num_experts, expand,
                                      alignment, mode, low_latency, cpu_sync))
         comm = self._enter(previous_event, previous_event_before_epilogue)
+        allocate_on_comm_stream = self._allocates_on_comm(allocate_on_comm_stream, previous_event, previous_event_before_epilogue)
         try:
             with self._on(comm if allocate_on_comm_stream else None):
                 if low_latency and hasattr(self.engine, "ll_dispatch"):
@@ -424,6 +433,7 @@ class ElasticBuffer:
         mode = self._mode(x_data, x_sf)
         self._preflight("cached_dispatch", (x_data.shape[0] > 0, self.hidden, mode))
         comm = self._enter(previous_event, previous_event_before_epilogue)
+        allocate_on_comm_stream = self._allocates_on_comm(allocate_on_comm_stream, previous_event, previous_event_before_epilogue)
         with self._on(comm if allocate_on_comm_stream else None):
             if handle.is_low_latency and hasattr(self.engine, "ll_dispatch"):
                 recv_x, recv_sf = self.engine.ll_dispatch_cached([x_data if x_sf is None else (x_data, x_sf)], [handle._plan],
@@ -504,6 +514,7 @@ class ElasticBuffer:
         if split is not None and (handle.is_low_latency or not hasattr(self.engine, "split_blocks")):
             split = None                      # one kernel role per SM only exists on the high-throughput CUDA path
         comm = self._enter(previous_event, previous_event_before_epilogue)
+        allocate_on_comm_stream = self._allocates_on_comm(allocate_on_comm_stream, previous_event, previous_event_before_epilogue)
         with self._on(comm if allocate_on_comm_stream else None):
             if handle.is_low_latency:
                 if topk_weights is not None or bias is not None:
