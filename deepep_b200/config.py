@@ -3,7 +3,7 @@
 Parity: ``deep_ep/_config.py:9-71`` and ``deep_ep/backends/direct/config.py:44-260`` of the reference
 (``num_sms`` plus chunk sizes and buffer-size hints).  On B200 ``num_sms`` is the number of SMs a
 dispatch or combine launch may occupy; the chunk sizes are kept for signature compatibility (this
-implementation signals completion per 64-token chunk and needs no ring-buffer sizing).
+implementation signals completion with one flag per few rows and needs no ring-buffer sizing).
 """
 from __future__ import annotations
 
