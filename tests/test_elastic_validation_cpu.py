@@ -126,3 +126,43 @@ def test_low_latency_selection_rules():
             small.combine(ll[0], ll[3], topk_weights=ll[2])
     finally:
         small.destroy()
+
+
+def test_column_major_scales_and_topology_queries(buf):
+    """``use_tma_aligned_col_major_sf`` returns the same scales stored column by column with the row count padded to 4
+    (16-byte columns); the sizing queries answer for one NVLink domain."""
+    from deepep_b200.utils.math import per_token_cast_to_fp8
+
+    x, idx, w = _inputs(37)
+    pair = per_token_cast_to_fp8(x)
+    (rx, sf), _, _, handle, _ = buf.dispatch(pair, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+    (rx2, sf2), _, _, _, _ = buf.dispatch(pair, handle=handle)
+    (rx3, sf3), _, _, _, _ = buf.dispatch(pair, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True,
+                                         use_tma_aligned_col_major_sf=True)
+    rows = sf.shape[0]
+    assert torch.equal(sf, sf2) and torch.equal(sf3, sf) and torch.equal(rx3.view(torch.uint8), rx.view(torch.uint8))
+    assert sf.is_contiguous() and sf3.stride() == (1, -(-rows // 4) * 4)
+    assert buf.get_physical_domain_size() == (1, 1) and buf.get_logical_domain_size() == (1, 1)
+    assert buf.get_theoretical_num_qps(24) == 0
+    sms = buf.get_theoretical_num_sms(E, K)
+    assert 8 <= sms <= 128 and buf.get_theoretical_num_compute_units(E, K) == sms
+    assert buf.pop_profile() == []
+
+
+def test_a_failed_launch_poisons_the_buffer(buf, monkeypatch):
+    """A wait that ran out surfaces as ``CommunicationError``; every later call on the buffer is refused."""
+    from deepep_b200.parallel.engine_cuda import CommunicationError
+
+    x, idx, w = _inputs()
+
+    def broken(*a, **k):
+        raise CommunicationError("rank 0: dispatch timeout at wait site 1 on peer 0 (expected 3, saw 2)")
+
+    monkeypatch.setattr(buf.engine, "dispatch", broken)
+    with pytest.raises(CommunicationError, match="wait site"):
+        buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+    monkeypatch.undo()
+    with pytest.raises(RuntimeError, match="restart the distributed job"):
+        buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+    with pytest.raises(RuntimeError, match="restart the distributed job"):
+        buf.barrier()
