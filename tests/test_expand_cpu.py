@@ -76,6 +76,28 @@ def test_validation():
         X.aggregate(x, h)
 
 
+def test_every_argument_rejection():
+    x, idx, w, counts, caps = _case(seed=5)
+    _, _, h = X.expand(x, idx, w, caps, 4)
+    for call, kind, message in (
+            (lambda: X.expand(x, idx, w, caps, 4.0), TypeError, "integer"),
+            (lambda: X.expand(x, idx, w, caps, 0), ValueError, "positive"),
+            (lambda: X.expand(x, idx, w, [], 4), TypeError, "non-empty"),
+            (lambda: X.expand(x, idx, w, [float(c) for c in caps], 4), TypeError, "integers"),
+            (lambda: X.expand(x, idx, w, [-4] + caps[1:], 4), ValueError, "nonnegative"),
+            (lambda: X.expand(x.t().contiguous().t(), idx, w, caps, 4), ValueError, "contiguous"),
+            (lambda: X.expand((x, torch.ones((x.shape[0] + 1, 1))), idx, w, caps, 4), ValueError, "scales"),
+            (lambda: X.expand(x, idx, w, None, 4), ValueError, "num_tokens_per_expert is required"),
+            (lambda: X.expand(x, idx.to(torch.int32), w, caps, 4), ValueError, "int64"),
+            (lambda: X.expand(x, idx, w.double(), caps, 4), ValueError, "fp32"),
+            (lambda: X.expand(x, handle=object()), TypeError, "ExpandHandle"),
+            (lambda: X.expand(x, num_tokens_per_expert=caps, handle=h), ValueError, "num_tokens_per_expert=None"),
+            (lambda: X.expand(x, expert_alignment=8, handle=h), ValueError, "match the handle")):
+        with pytest.raises(kind, match=message):
+            call()
+    assert X.expand(x, expert_alignment=4, handle=h)[2] is h              # the handle's own alignment is accepted
+
+
 def test_buffer_methods_return_events():
     x, idx, w, counts, caps = _case(seed=4)
     buf = deep_ep.Buffer(None)
