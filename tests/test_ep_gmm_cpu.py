@@ -89,3 +89,67 @@ def test_tiling_argument_is_checked(tmp_path):
     assert G.load_tiling_config(good) == shape
     with pytest.raises(ValueError):
         G.load_tiling_config(bad)
+
+
+def test_one_process_round_trip_and_every_rejection():
+    """World size 1 on the CPU engine: both operators against the restatement, then every argument rule."""
+    if torch.cuda.is_available():
+        pytest.skip("CPU-engine test")
+    E, K, N = 3, 64, 128
+    counts = [4, 0, 6]
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn((10, K), generator=gen).bfloat16()
+    w = (torch.randn((E, K, N), generator=gen) / 8).bfloat16()
+    with pytest.raises(RuntimeError, match="not initialised"):
+        G.symmetric_input(4, K)
+    with pytest.raises(ValueError, match="multiples of 64"):
+        G.init_group(None, max_rows=16, max_k=K, max_n=100)
+    cfg = G.init_group(None, max_rows=16, max_k=N, max_n=N)
+    try:
+        assert (cfg.rank, cfg.world_size, cfg.backend) == (0, 1, "cpu")
+        with pytest.raises(RuntimeError, match="already initialised"):
+            G.init_group(None, max_rows=16, max_k=K, max_n=N)
+        assert G.symmetric_input(10, K).shape == (10, K) and G.symmetric_output(10, N).dtype == torch.bfloat16
+        G.check_errors()                                               # nothing to check without device kernels
+        out = G.all_to_allv_grouped_matmul(x, w, counts, torch.tensor(counts), ep_size=1, expert_num=E)
+        ref, gathered = G.reference_alltoallv_gmm([x], [w], [counts], E)
+        assert torch.equal(out, ref[0]) and torch.equal(gathered[0], x)
+        w2 = (torch.randn((E, N, K), generator=gen) / 8).bfloat16()
+        given = torch.empty((10, K), dtype=torch.bfloat16)
+        back = G.grouped_matmul_all_to_allv(out, w2, counts, counts, ep_size=1, expert_num=E, out=given)
+        assert back is given and torch.equal(back, G.reference_gmm_alltoallv([out], [w2], [counts], E)[0])
+        a2a = lambda *a, **k: G.alltoallv_gmm(*a, **{**dict(ep_size=1, expert_num=E), **k})
+        g2a = lambda *a, **k: G.gmm_alltoallv(*a, **{**dict(ep_size=1, expert_num=E), **k})
+        for call, kind, message in (
+                (lambda: a2a(x, w, counts, counts, ep_size=2), ValueError, "ep_size == group world_size"),
+                (lambda: a2a(x, w, counts, counts, expert_num=0), ValueError, "divisible"),
+                (lambda: a2a(x.float(), w, counts, counts), TypeError, "bf16"),
+                (lambda: a2a(x, w[0], counts, counts), ValueError, "contiguous"),
+                (lambda: a2a(x, w[:2], counts, counts), ValueError, "expert_num / ep_size"),
+                (lambda: a2a(x[:, :32].contiguous(), w[:, :32].contiguous(), counts, counts), ValueError, "multiples of 64"),
+                (lambda: a2a(x, w, counts[:2], counts), ValueError, "expert_num=3 elements"),
+                (lambda: a2a(x, w, [4, -1, 7], counts), ValueError, "negative"),
+                (lambda: a2a(x, w, torch.tensor([[4, 0, 6]]), counts), ValueError, "flat tensor"),
+                (lambda: a2a(x, w, torch.tensor([4.0, 0.0, 6.0]), counts), TypeError, "int64 or int32"),
+                (lambda: a2a(x, w, [4, 0, 5], counts), ValueError, "must equal x.shape"),
+                (lambda: a2a(x, w, counts, counts, received_rows=-1), ValueError, "out of range"),
+                (lambda: a2a(x, w, counts, counts, received_rows=9), ValueError, "does not match"),
+                (lambda: a2a(x, w, counts, counts, all_to_allv_out=torch.empty((10, K), dtype=torch.bfloat16)), ValueError,
+                 "requires output_all_to_allv"),
+                (lambda: a2a(x, w, counts, counts, out=torch.empty((9, N), dtype=torch.bfloat16)), ValueError, "received_rows, n"),
+                (lambda: a2a(x, w, counts, counts, output_all_to_allv=True, all_to_allv_out=torch.empty((10, K + 64), dtype=torch.bfloat16)),
+                 ValueError, "all_to_allv_out must have shape"),
+                (lambda: g2a(out, w2, counts, [4, 0, 5]), ValueError, "must equal x.shape"),
+                (lambda: g2a(out, w2, counts, counts, out=torch.empty((10, K), dtype=torch.float32)), ValueError, "contiguous bf16"),
+                (lambda: g2a(out, w2, counts, counts, out=torch.empty((9, K), dtype=torch.bfloat16)), ValueError,
+                 "sum\\(local_tokens_per_expert\\), n")):
+            with pytest.raises(kind, match=message):
+                call()
+        big = torch.zeros((17, K), dtype=torch.bfloat16)
+        with pytest.raises(ValueError, match="at most 16"):
+            a2a(big, w, [17, 0, 0], [17, 0, 0])
+        with pytest.raises(ValueError, match="at most 16"):
+            g2a(torch.zeros((17, N), dtype=torch.bfloat16), w2, [17, 0, 0], [17, 0, 0])
+    finally:
+        G.destroy_group()
+    G.destroy_group()                                                  # idempotent
