@@ -33,6 +33,8 @@ def main() -> int:
     ap.add_argument("--sweep-fractions", type=float, nargs="*", default=[0.3, 0.4, 0.5, 0.6],
                     help="share of the blocks that drives NVLink (dispatch senders / combine expert side)")
     ap.add_argument("--device-profile", action="store_true", help="per-block records of the profile kernels (CUDA engine)")
+    ap.add_argument("--trace", default=None, help="with --device-profile: write the records of every rank as Chrome-trace / "
+                                                  "Perfetto JSON to this path (rank 0 writes)")
     args = ap.parse_args()
 
     from deepep_b200 import ElasticBuffer
@@ -180,8 +182,22 @@ def sweep(buf, cfg, x, handle, back, routes, rank, world, args, fresh):
         say(profile="notify", phases_us={k: round(v, 1) for k, v in eng.phase_stamps("notify").items()})
         eng.dispatch([x], [plan], mode)
         eng.combine([back], [plan], [None])
+        notify_stamps = eng.phase_stamps("notify")
         prof = eng.pop_device_profile()
         eng.enable_device_profile(False)
+        if args.trace:
+            from deepep_b200.utils import trace as TR
+
+            # one timeline per rank: notify, then dispatch, then combine, laid end to end (they ran one after the other)
+            mine, at = TR.from_phase_stamps("notify", notify_stamps, rank), max(list(notify_stamps.values()) + [0.0])
+            for op in ("dispatch", "combine"):
+                part = {k: v for k, v in prof.items() if k[0] == op}
+                mine += [dict(e, pid=rank) for e in TR.from_device_profile(part, offset_us=at)]
+                at += max([b["end_us"] for blocks in part.values() for b in blocks] + [0.0])
+            everyone = buf.control.all_gather_object(mine)
+            if rank == 0:
+                TR.write_trace(args.trace, [e for part in everyone for e in part])
+                say(trace=args.trace, spans=sum(len(part) for part in everyone))
         for (op, _), blocks in prof.items():
             for side in sorted({b["role"] for b in blocks}):
                 sel = [b for b in blocks if b["role"] == side]

@@ -26,6 +26,7 @@ def main():
     ap.add_argument("--bf16", action="store_true", help="bf16 dispatch instead of the fused fp8 quantiser")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--phases", action="store_true")
+    ap.add_argument("--trace", default=None, help="with --phases: write the phase stamps of every rank as Chrome-trace / Perfetto JSON")
     args = ap.parse_args()
     from deepep_b200 import ElasticBuffer
 
@@ -103,6 +104,15 @@ def main():
         else:
             gathered = [mine]
         out["phases_us_by_rank"] = gathered
+        if args.trace and rank == 0:
+            from deepep_b200.utils import trace as TR
+
+            events = []
+            for r, stamps in enumerate(gathered):
+                first = TR.from_phase_stamps("ll_dispatch", stamps["ll_dispatch"], r)
+                events += first + TR.from_phase_stamps("ll_combine", stamps["ll_combine"], r,
+                                                       offset_us=max(list(stamps["ll_dispatch"].values()) + [0.0]))
+            TR.write_trace(args.trace, events)
     if rank == 0:
         print(json.dumps(out), flush=True)
     buf.destroy()

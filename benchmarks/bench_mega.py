@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--no-profiler", action="store_true", help="skip the torch.profiler breakdown (needed under ncu)")
     ap.add_argument("--pairs", choices=["auto", "0", "1"], default=None, help="CTA pairs in the fused kernel (default: the engine's rule)")
     ap.add_argument("--phases", action="store_true", help="one extra launch with the per-CTA phase timer; prints the breakdown")
+    ap.add_argument("--trace", default=None, help="with --phases: write the per-CTA phase spans as Chrome-trace / Perfetto JSON")
     args = ap.parse_args()
     from deepep_b200.models.mega_moe import MegaEngine, MegaWeights
     from deepep_b200.ops import load_native
@@ -93,6 +94,10 @@ def main():
         eng.forward(ys, [T] * P, w1, w2, fused=True, timer=timer)
         torch.cuda.synchronize()
         phases = {k: round(v, 1) if isinstance(v, float) else v for k, v in parse_timer(timer).items()}
+        if args.trace:
+            from deepep_b200.utils import trace as TR
+
+            TR.write_trace(args.trace, TR.from_mega_timer(timer))
     rows = P * T * K
     flops = 2.0 * rows * (2 * I) * H + 2.0 * rows * H * I
     print(json.dumps({"world": P, "tokens": T, "hidden": H, "inter": I, "experts": E, "topk": K, "total_us": total_us,
