@@ -108,4 +108,33 @@ def agree(control, device: Optional[torch.device], machine_type: Optional[str] =
     return check_consensus(reports, machine_type)
 
 
-__all__ = ["KINDS", "RankMachine", "agree", "check_consensus", "detect"]
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    """``python -m deepep_b200.parallel.topology [--ranks N]``: print what this process sees, as JSON, and whether N
+    ranks (default: one per visible GPU) on this machine would pass the constructor's check.  Read-only.
+    Parity: the reference's machine probe (``scripts/check_machine.py``)."""
+    import argparse
+    import json
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--ranks", type=int, default=0, help="ranks of the planned job (0: one per visible GPU)")
+    args = ap.parse_args(argv)
+    gpus = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    ranks = args.ranks or max(gpus, 1)
+    if gpus:
+        reports = [detect(r, torch.device("cuda", r % gpus)) for r in range(ranks)]
+    else:
+        reports = [detect(r, None) for r in range(ranks)]
+    out = {"host": reports[0].host, "visible_gpus": gpus, "ranks": ranks, "reports": [asdict(m) for m in reports]}
+    try:
+        out["machine_type"], out["ok"] = check_consensus(reports), True
+    except RuntimeError as exc:
+        out["machine_type"], out["ok"], out["error"] = None, False, str(exc)
+    print(json.dumps(out, indent=1, default=list))
+    return 0 if out["ok"] else 1
+
+
+__all__ = ["KINDS", "RankMachine", "agree", "check_consensus", "detect", "main"]
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -56,3 +56,28 @@ def test_buffer_records_the_agreed_machine():
     with pytest.raises(RuntimeError, match="requested"):
         ElasticBuffer(None, num_max_tokens_per_rank=16, hidden=128, num_topk=2, explicitly_destroy=True, device="cpu",
                       machine_type="nvswitch")
+
+
+def test_probe_command_reports_and_judges(capsys, monkeypatch):
+    """``python -m deepep_b200.parallel.topology``: prints the reports as JSON; the exit code says whether the planned
+    ranks would pass the constructor's check."""
+    import json
+
+    import torch
+
+    from deepep_b200.parallel import topology as TP
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    assert TP.main(["--ranks", "3"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["ok"] and out["machine_type"] == "cpu" and out["ranks"] == 3 and len(out["reports"]) == 3
+    # two planned ranks on a machine with one GPU: the check refuses (one GPU per rank)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: 1)
+    monkeypatch.setattr(TP, "detect", lambda rank, device=None: TP.RankMachine(
+        rank=rank, host="h", kind="single", device=0, uuid="GPU-1", name="NVIDIA B200", capability=(10, 0), sm_count=148,
+        visible=1, peer_access={0: True}))
+    assert TP.main(["--ranks", "2"]) == 1
+    out = json.loads(capsys.readouterr().out)
+    assert not out["ok"] and "same GPU" in out["error"]
+    assert TP.main([]) == 0 and json.loads(capsys.readouterr().out)["machine_type"] == "single"
