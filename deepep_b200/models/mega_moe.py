@@ -46,6 +46,7 @@ class MegaWeights:
     n: int
     k: int
     fp8: bool = False           # e4m3 weights (mma_type "fp8xfp8") instead of e2m1 ("fp8xfp4")
+    source: Optional[Tuple[torch.Tensor, torch.Tensor]] = None   # (weights, scales) as given; kept for CPU targets only
 
 
 def _sf_chunks(sf: torch.Tensor) -> torch.Tensor:
@@ -81,8 +82,9 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
     w1_sft = w1_sf.view(torch.uint8).reshape(L, n1, hidden // 32)[:, order].reshape(L * n1, hidden // 32)
     w2t = tile_rows(w2.view(torch.uint8).reshape(L * hidden, inter // per_byte).contiguous(), width)
     w2_sft = w2_sf.view(torch.uint8).reshape(L * hidden, inter // 32)
-    return (MegaWeights(w1t.to(device), _sf_chunks(w1_sft).to(device), L, n1, hidden, fp8),
-            MegaWeights(w2t.to(device), _sf_chunks(w2_sft).to(device), L, hidden, inter, fp8))
+    on_cpu = torch.device(device).type == "cpu"      # the CPU engine evaluates the restatement from the weights as given
+    return (MegaWeights(w1t.to(device), _sf_chunks(w1_sft).to(device), L, n1, hidden, fp8, (w1, w1_sf) if on_cpu else None),
+            MegaWeights(w2t.to(device), _sf_chunks(w2_sft).to(device), L, hidden, inter, fp8, (w2, w2_sf) if on_cpu else None))
 
 
 class MegaEngine:
@@ -218,6 +220,50 @@ class MegaEngine:
                 raise RuntimeError("a pipeline wait ran out inside a MegaMoE GEMM kernel")
 
 
+class MegaCpuEngine:
+    """The fused MoE forward without a GPU: every rank gathers all ranks' expert weights and routing tables through the
+    control plane and evaluates the CPU restatement (``oracle/megamoe.py``) for its own tokens.  Meant for tests of the
+    API on Gloo or store-only ranks, with small shapes."""
+
+    def __init__(self, control, num_experts: int, num_shared_experts: int):
+        self.control, self.E, self.S = control, num_experts, int(num_shared_experts)
+        self.L = num_experts // control.size
+        self.sm_count = 0
+
+    @staticmethod
+    def _source(weights: MegaWeights, what: str):
+        if weights.source is None:
+            raise ValueError(f"{what} were transformed for a GPU; pass device='cpu' to transform_weights_for_mega_moe")
+        return weights.source
+
+    def forward(self, y: torch.Tensor, sym: "SymmBuffer", l1: MegaWeights, l2: MegaWeights, shared_l1: Optional[MegaWeights],
+                shared_l2: Optional[MegaWeights], x_bf16: Optional[torch.Tensor], stats: Optional[torch.Tensor]) -> None:
+        from ..oracle import megamoe as O
+
+        bs = y.shape[0]
+        codes, sf = O.quantize_mxfp8(x_bf16) if x_bf16 is not None else (sym.x[:bs], sym.x_sf[:bs])
+        idx, w = sym.topk_idx[:bs].long(), sym.topk_weights[:bs]
+        parts = self.control.all_gather_object((self._source(l1, "l1 weights"), self._source(l2, "l2 weights"), idx))
+        cat = lambda which, item: torch.cat([p[which][item] for p in parts])
+        everyone1, everyone2 = (cat(0, 0), cat(0, 1)), (cat(1, 0), cat(1, 1))
+        own1 = None if shared_l1 is None else self._source(shared_l1, "shared l1 weights")
+        own2 = None if shared_l2 is None else self._source(shared_l2, "shared l2 weights")
+        y.copy_(O.mega_moe_reference([(codes, sf)], [idx], [w], everyone1, everyone2, self.E, own1, own2)[0])
+        if stats is not None:       # rows every routed local expert received from all ranks (first occurrence of an id in a row)
+            mine = torch.zeros(self.L, dtype=torch.int64)
+            for p in parts:
+                t = p[2]
+                first = torch.ones_like(t, dtype=torch.bool)
+                for k in range(1, t.shape[1]):
+                    first[:, k] = ~(t[:, :k] == t[:, k:k + 1]).any(dim=1)
+                hit = t[first & (t >= self.control.rank * self.L) & (t < (self.control.rank + 1) * self.L)] - self.control.rank * self.L
+                mine += torch.bincount(hit, minlength=self.L)
+            stats.add_(mine.to(stats.dtype))
+
+    def check(self) -> None:
+        return None
+
+
 class SymmBuffer:
     """Symmetric input/output block of the fused MoE forward; construction is collective."""
 
@@ -231,23 +277,38 @@ class SymmBuffer:
             raise NotImplementedError("only SwiGLU is implemented")
         from ..parallel.runtime import ControlPlane, Runtime
 
-        C = require_native("MegaMoE SymmBuffer")
         self.control = ControlPlane(group, rank, world_size)
         self.rank, self.world_size = self.control.rank, self.control.size
-        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.num_experts, self.num_topk, self.hidden, self.intermediate_hidden = num_experts, num_topk, hidden, intermediate_hidden
         self.num_max_tokens_per_rank = num_max_tokens_per_rank
         self.num_shared_experts, self.mma_type = int(num_shared_experts), mma_type
+        self._joined: dict = {}
+        self.batch_size = 0
+        self._destroyed = False
+        if not torch.cuda.is_available() or (device is not None and torch.device(device).type == "cpu"):
+            # no GPU: plain tensors for the inputs and the CPU restatement as the engine (tests of the API on CPU ranks)
+            if num_experts % self.world_size or hidden % 256 or intermediate_hidden % 128 or num_topk + self.num_shared_experts > 16:
+                raise ValueError("experts must divide by the world size, hidden by 256, the intermediate size by 128; top-k plus "
+                                 "shared experts must not exceed 16")
+            self.device, self.runtime, self.layout = torch.device("cpu"), None, None
+            self.engine = MegaCpuEngine(self.control, num_experts, self.num_shared_experts)
+            m = num_max_tokens_per_rank
+            self.x = torch.zeros((m, hidden), dtype=torch.float8_e4m3fn)
+            self.x_sf = torch.zeros((m, hidden // 32), dtype=torch.uint8)
+            self.topk_idx = torch.full((m, num_topk), -1, dtype=torch.int32)
+            self.topk_weights = torch.zeros((m, num_topk), dtype=torch.float32)
+            self.control.barrier()
+            return
+        C = require_native("MegaMoE SymmBuffer")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         mega = MegaEngine.mega_bytes(C, num_max_tokens_per_rank, hidden, num_topk, self.num_shared_experts)
         # the generic regions are sized for one token: this buffer only uses the fused-MoE region
         self.layout = C.make_mega_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, mega)
         self.runtime = Runtime(self.control, self.layout, float(num_gpu_timeout_secs), self.device)
         self.engine = MegaEngine([self.runtime.native], self.layout, self.device, num_experts, intermediate_hidden, num_sms,
                                  self.num_shared_experts)
-        self._joined: dict = {}          # routed + shared weights joined once per weight set
+        # self._joined: routed + shared weights joined once per weight set
         self.x, self.x_sf, self.topk_idx, self.topk_weights = self.engine.input_views(0)
-        self.batch_size = 0
-        self._destroyed = False
 
     def prepare(self, batch_size: int) -> "SymmBuffer":
         if not 0 <= batch_size <= self.num_max_tokens_per_rank:
@@ -286,6 +347,8 @@ class SymmBuffer:
         """A zeroed int64 ``[SMs, words]`` tensor for ``fp8_fp4_mega_moe(..., timer=...)``: the kernel writes one record
         of phase stamps per CTA; ``mega_tools.parse_timer`` turns it into a per-phase breakdown.
         Parity: ``SymmBuffer.allocate_timer`` (``api.py:226-233`` of the reference)."""
+        if self.runtime is None:
+            raise NotImplementedError("the phase timer is written by the CUDA kernel; there is none on the CPU engine")
         C = require_native("MegaMoE timer")
         return torch.zeros((self.engine.sm_count, C.mega_timer_words), dtype=torch.int64, device=self.device)
 
@@ -311,7 +374,10 @@ class SymmBuffer:
     def destroy(self) -> None:
         if not self._destroyed:
             self._destroyed = True
-            self.runtime.close()
+            if self.runtime is not None:
+                self.runtime.close()
+            else:
+                self.control.barrier()
 
 
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaWeights, sym_buffer: SymmBuffer,
@@ -363,6 +429,11 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaW
     if timer is not None and (not fused or timer.dtype != torch.int64 or not timer.is_contiguous()):
         raise ValueError("timer must come from SymmBuffer.allocate_timer() and needs the fused kernel")
     engine = sym_buffer.engine
+    if isinstance(engine, MegaCpuEngine):
+        if timer is not None:
+            raise ValueError("timer must come from SymmBuffer.allocate_timer() and needs the fused kernel")
+        engine.forward(y, sym_buffer, l1_weights, l2_weights, shared_l1_weights, shared_l2_weights, x, stats)
+        return None
     engine.forward([y], [bs], [sym_buffer.joined_weights(l1_weights, shared_l1_weights)],
                    [sym_buffer.joined_weights(l2_weights, shared_l2_weights)], fused=fused,
                    x_bf16=None if x is None else [x], timer=timer)

@@ -22,6 +22,8 @@ class StoreAborted(RuntimeError):
 
 
 class StoreGroup:
+    _sessions_opened = 0          # groups this process has opened with from_env
+
     def __init__(self, store, rank: int, size: int, *, prefix: str, timeout: float = 300):
         if not 0 <= rank < size <= 128 or not prefix or timeout <= 0:
             raise ValueError("StoreGroup requires rank in [0, size), size <= 128, a prefix and a positive timeout")
@@ -38,7 +40,10 @@ class StoreGroup:
         rank, size = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
         store = TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), None, False,
                          timedelta(seconds=timeout))
-        key = f"{prefix}/session/" + os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")
+        # one session per call: the n-th group of a process meets the n-th group of its peers (construction is
+        # collective and ordered), so a second group never picks up the first one's session name
+        cls._sessions_opened += 1
+        key = f"{prefix}/session/" + os.environ.get("TORCHELASTIC_RESTART_COUNT", "0") + f"/{cls._sessions_opened}"
         if rank == 0:
             store.set(key, uuid.uuid4().hex)
         session = store.get(key).decode("ascii")

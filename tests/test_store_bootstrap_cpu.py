@@ -50,8 +50,8 @@ def _worker(rank, port, results):
         except RuntimeError as exc:
             checks["disagreement"] = "disagree" in str(exc)
         buf.destroy()
-        # an explicit StoreGroup as the group
-        group = StoreGroup.from_env(timeout=30, prefix="second")
+        # an explicit StoreGroup as the group; a second group of the same job and prefix gets a session of its own
+        group = StoreGroup.from_env(timeout=30)
         buf2 = deep_ep.ElasticBuffer(group, num_max_tokens_per_rank=32, hidden=H, num_topk=K, explicitly_destroy=True, device="cpu")
         rx2, ridx2, _, h2, _ = buf2.dispatch(xs[rank], topk_idx=idx[rank], num_experts=E)
         ref2, _ = R.dispatch(xs, idx, None, E, do_expand=False)
