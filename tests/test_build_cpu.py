@@ -65,7 +65,8 @@ def test_compiler_lookup(monkeypatch, tmp_path):
 
 
 def _text_files():
-    skip = {".git", "_work", "gpurun_out", "__pycache__", "build", "_ref", ".pytest_cache"}
+    ignored = (REPO / ".gitignore").read_text().split() if (REPO / ".gitignore").exists() else []
+    skip = {".git", "__pycache__", "build", ".pytest_cache"} | {entry.strip("/").split("/")[-1] for entry in ignored if entry.endswith("/")}
     for root, dirs, files in os.walk(REPO):
         dirs[:] = [d for d in dirs if d not in skip]
         for name in files:

@@ -58,7 +58,7 @@ def test_buffer_records_the_agreed_machine():
                       machine_type="nvswitch")
 
 
-def test_probe_command_reports_and_judges(capsys, monkeypatch):
+def test_probe_command_reports_and_decides(capsys, monkeypatch):
     """``python -m deepep_b200.parallel.topology``: prints the reports as JSON; the exit code says whether the planned
     ranks would pass the constructor's check."""
     import json
