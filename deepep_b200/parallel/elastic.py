@@ -125,7 +125,7 @@ class ElasticBuffer:
         if num_max_tokens_per_rank > L.MAX_TOKENS or num_topk > L.MAX_TOPK:
             raise ValueError(f"limits: tokens <= {L.MAX_TOKENS}, top-k <= {L.MAX_TOPK}")
         L.validate_hidden(hidden, use_fp8_dispatch)
-        self.control = ControlPlane(group, rank, world_size, bootstrap)
+        self.control = ControlPlane(group, rank, world_size, bootstrap, timeout=float(num_cpu_timeout_secs))
         self.group, self.rank, self.world_size = group, self.control.rank, self.control.size
         if self.world_size not in L.WORLD_SIZES:
             raise ValueError(f"world size must be one of {L.WORLD_SIZES}")

@@ -26,10 +26,12 @@ class ControlPlane:
     """Small host-collective interface with three backends: ProcessGroup, TCPStore, single process."""
 
     def __init__(self, group: Any = None, rank: Optional[int] = None, world_size: Optional[int] = None,
-                 bootstrap: str = "default"):
+                 bootstrap: str = "default", timeout: float = 300.0):
+        """``timeout`` (seconds) bounds the host-side waits this object owns: the operations of a store group it opens
+        itself and the hand-over of file descriptors between the ranks."""
         import torch.distributed as dist
 
-        self.group, self.store = None, None
+        self.group, self.store, self.timeout = None, None, float(timeout)
         if isinstance(group, StoreGroup):
             self.store, self.rank, self.size = group, group.rank(), group.size()
         elif group is not None:
@@ -44,7 +46,7 @@ class ControlPlane:
                 raise ValueError("rank= and world_size= are both required when no group is given")
             os.environ.setdefault("RANK", str(rank))
             os.environ.setdefault("WORLD_SIZE", str(world_size))
-            self.store = StoreGroup.from_env()
+            self.store = StoreGroup.from_env(timeout=self.timeout)
             self.rank, self.size = rank, world_size
         if rank is not None and rank != self.rank:
             raise ValueError(f"rank={rank} contradicts the group's rank {self.rank}")
@@ -87,7 +89,7 @@ class ControlPlane:
 _busy_runtimes = 0
 
 
-def exchange_fds(control: ControlPlane, fd: int, timeout: float = 60.0) -> List[int]:
+def exchange_fds(control: ControlPlane, fd: int, timeout: Optional[float] = None) -> List[int]:
     """Every rank hands ``fd`` to every peer over Unix-domain sockets (SCM_RIGHTS); returns one descriptor per rank
     (``-1`` at this rank's own index).  The caller owns the returned descriptors.
 
@@ -101,6 +103,7 @@ def exchange_fds(control: ControlPlane, fd: int, timeout: float = 60.0) -> List[
     rank, size = control.rank, control.size
     if size == 1:
         return [-1]
+    timeout = min(60.0, getattr(control, "timeout", 60.0)) if timeout is None else timeout
     token = control.all_gather_object(secrets.token_hex(8) if rank == 0 else None)[0]
     name = lambda r: f"\0deepep-{token}-{r}"
     server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)

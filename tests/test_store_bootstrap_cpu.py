@@ -75,3 +75,24 @@ def test_ranks_meet_through_a_store_only():
         got = dict(results)
     for rank in range(WORLD):
         assert got[rank] == dict(backend=True, machine=True, dispatch=True, combine=True, disagreement=True, store_group=True), got
+
+
+def test_a_rank_that_never_joins_ends_the_host_wait(monkeypatch):
+    """``num_cpu_timeout_secs`` bounds the host-side waits of the bootstrap: with a peer that never shows up the
+    constructor raises after about that long instead of waiting for ever (the failure is made on the host)."""
+    import time
+
+    from torch.distributed import TCPStore
+
+    import deepep_b200 as deep_ep
+
+    if torch.cuda.is_available():
+        pytest.skip("CPU-engine test")
+    server = TCPStore("127.0.0.1", 0, None, True, timedelta(seconds=60), wait_for_workers=False)
+    for name, value in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", str(server.port)), ("RANK", "0"), ("WORLD_SIZE", "2")):
+        monkeypatch.setenv(name, value)
+    started = time.monotonic()
+    with pytest.raises(TimeoutError, match="did not appear"):
+        deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=8, hidden=64, num_topk=2, rank=0, world_size=2, bootstrap="store",
+                              device="cpu", num_cpu_timeout_secs=2)
+    assert time.monotonic() - started < 30
