@@ -170,7 +170,10 @@ class ElasticBuffer:
             self.layout = C.make_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, ll, 0, self.combine_window)
             assert self.layout.total == needed, "native and Python workspace layouts disagree"
             self.runtime = Runtime(self.control, self.layout, float(_timeout_seconds(num_gpu_timeout_secs)), self.device)
-            self.engine = CudaEngine([self.runtime.native], self.layout, self.device, num_sms=num_sms)
+            from ..utils.hostwait import cpu_timeout_seconds
+
+            self.engine = CudaEngine([self.runtime.native], self.layout, self.device, num_sms=num_sms,
+                                     host_timeout=cpu_timeout_seconds(num_cpu_timeout_secs))
         else:
             from .engine_cpu import CpuEngine
 

@@ -76,8 +76,9 @@ COMBINE_SEND_FRACTION = {1: 0.0, 2: 0.5, 4: 0.6, 8: 0.6}
 
 
 class CudaEngine:
-    def __init__(self, sessions: Sequence, layout, device: torch.device, num_sms: int = 0):
+    def __init__(self, sessions: Sequence, layout, device: torch.device, num_sms: int = 0, host_timeout: float = 300.0):
         self.C = require_native("ElasticBuffer")
+        self.host_timeout = float(host_timeout)       # limit of the host's waits for a kernel whose results it reads back
         self.sessions = list(sessions)
         self.layout = layout
         self.device = device
@@ -203,6 +204,19 @@ class CudaEngine:
         self._timings.clear()
         return out
 
+    def _host_wait(self, stream, what: str) -> None:
+        """The host needs the results of what was just queued on ``stream``: wait for it, but not for ever."""
+        from ..utils.hostwait import HostTimeout, wait_for_event
+
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        done = torch.cuda.Event()
+        done.record(st)
+        try:
+            wait_for_event(done, self.host_timeout, what)
+        except HostTimeout as exc:
+            raise CommunicationError(f"{exc}; restart the distributed job") from None
+        st.synchronize()                               # returns at once: everything before the event is complete
+
     def check_status(self) -> None:
         for s in self.sessions:
             st = s.status()
@@ -280,7 +294,7 @@ class CudaEngine:
                 with torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext():
                     plan.send_chunk_prefix = sc["own_hits"][:tiles * P].view(tiles, P).t().contiguous()
         if cpu_sync:
-            (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
+            self._host_wait(stream, "the routing layout pass")
             self.check_status()
             for plan, s in zip(plans, self.sessions):
                 box = s.mailbox(4 + local)
@@ -400,7 +414,7 @@ class CudaEngine:
         self._timed("ll_dispatch", stream, lambda: self.C.ll_dispatch(lay, self.sessions, args, self.ll_blocks(), self._stream(stream),
                                                                              self._device_profile))
         if cpu_sync:
-            (stream if stream is not None else torch.cuda.current_stream(dev)).synchronize()
+            self._host_wait(stream, "the low-latency dispatch")
             self.check_status()
             out = []
             for (plan, rx, rsf), s in zip(res, self.sessions):
