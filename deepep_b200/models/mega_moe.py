@@ -472,4 +472,4 @@ def quantize_mxfp8_cuda(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return quantize_mxfp8(x)
 
 
-__all__ = ["MegaEngine", "MegaWeights", "SymmBuffer", "fp8_fp4_mega_moe", "mega_moe", "transform_weights_for_mega_moe"]
+__all__ = ["MegaCpuEngine", "MegaEngine", "MegaWeights", "SymmBuffer", "fp8_fp4_mega_moe", "mega_moe", "transform_weights_for_mega_moe"]

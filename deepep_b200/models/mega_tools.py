@@ -188,4 +188,4 @@ def accuracy_report(actual: Sequence[torch.Tensor], spec: Dict, directory: Optio
 
 
 __all__ = ["accuracy_report", "cache_path", "check_routing", "collective_check", "compare", "contract", "digest",
-           "error_metrics", "generate", "make_case"]
+           "error_metrics", "generate", "make_case", "parse_timer"]
