@@ -128,6 +128,44 @@ def parse_timer(timer: torch.Tensor) -> Dict[str, float]:
     return out
 
 
+# ------------------------------------------------------------------------------------------------ model configurations
+MODEL_FIELDS = ("hidden", "intermediate_hidden", "num_experts", "num_topk", "num_shared_experts")
+
+
+def load_model_config(path: str) -> Dict:
+    """A benchmark configuration in the reference's schema (``configs/*.json`` of its megamoe package):
+    ``{"schema_version": 1, "model": {hidden, intermediate_hidden, num_experts, num_topk, num_shared_experts},
+    "bs_values": [...], "warmup": n, "iters": n, "seed": n}``.  Unknown keys, missing keys and values this library cannot
+    run (hidden not a multiple of 256, intermediate size not a multiple of 128, top-k plus shared experts above 16)
+    are errors; returns the validated dictionary."""
+    with open(path) as fh:
+        cfg = json.load(fh)
+    if not isinstance(cfg, dict) or cfg.get("schema_version") != 1:
+        raise ValueError("a model configuration is a JSON object with schema_version 1")
+    unknown = set(cfg) - {"schema_version", "model", "bs_values", "warmup", "iters", "seed"}
+    if unknown:
+        raise ValueError("unknown configuration fields: " + ", ".join(sorted(unknown)))
+    model = cfg.get("model")
+    if not isinstance(model, dict) or set(model) != set(MODEL_FIELDS):
+        raise ValueError("model must hold exactly " + ", ".join(MODEL_FIELDS))
+    if any(type(model[k]) is not int or model[k] < 0 for k in MODEL_FIELDS):
+        raise ValueError("model fields are nonnegative integers")
+    if model["hidden"] <= 0 or model["hidden"] % 256 or model["intermediate_hidden"] <= 0 or model["intermediate_hidden"] % 128:
+        raise ValueError("hidden must be a positive multiple of 256 and intermediate_hidden of 128")
+    if not 1 <= model["num_topk"] <= model["num_experts"] or model["num_topk"] + model["num_shared_experts"] > 16:
+        raise ValueError("num_topk must be in [1, num_experts] and num_topk + num_shared_experts at most 16")
+    sizes = cfg.get("bs_values")
+    if not isinstance(sizes, list) or not sizes or any(type(b) is not int or not 1 <= b <= 16384 for b in sizes):
+        raise ValueError("bs_values is a non-empty list of batch sizes in [1, 16384]")
+    out = dict(schema_version=1, model={k: model[k] for k in MODEL_FIELDS}, bs_values=list(sizes))
+    for key, default, low in (("warmup", 3, 0), ("iters", 10, 1), ("seed", 0, 0)):
+        value = cfg.get(key, default)
+        if type(value) is not int or value < low:
+            raise ValueError(f"{key} must be an integer >= {low}")
+        out[key] = value
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ goldens
 def contract(*, world: int, tokens: Sequence[int], hidden: int, intermediate: int, experts: int, topk: int, seed: int,
              routing: str = "random") -> Dict:
@@ -188,4 +226,4 @@ def accuracy_report(actual: Sequence[torch.Tensor], spec: Dict, directory: Optio
 
 
 __all__ = ["accuracy_report", "cache_path", "check_routing", "collective_check", "compare", "contract", "digest",
-           "error_metrics", "generate", "make_case", "parse_timer"]
+           "error_metrics", "generate", "load_model_config", "make_case", "parse_timer"]

@@ -78,3 +78,73 @@ def test_alias_package_shares_module_objects():
     import deep_ep
 
     assert deep_ep.ElasticBuffer is elastic.ElasticBuffer
+
+
+def test_model_configurations_in_the_reference_schema(tmp_path):
+    """The shipped model configurations load; malformed ones are refused with the reason."""
+    import glob
+    import json
+    import os
+
+    import pytest
+
+    from deepep_b200.models import mega_tools as MT
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "configs")
+    shipped = sorted(glob.glob(os.path.join(root, "mega_*.json")))
+    assert len(shipped) == 3
+    for path in shipped:
+        cfg = MT.load_model_config(path)
+        assert set(cfg["model"]) == set(MT.MODEL_FIELDS) and cfg["bs_values"] and cfg["iters"] >= 1
+    pro = MT.load_model_config(os.path.join(root, "mega_deepseek_v4_pro_shared1.json"))["model"]
+    assert pro == dict(hidden=7168, intermediate_hidden=3072, num_experts=384, num_topk=6, num_shared_experts=1)
+    good = dict(schema_version=1, model=dict(hidden=256, intermediate_hidden=128, num_experts=4, num_topk=2, num_shared_experts=1),
+                bs_values=[3])
+
+    def load(**changes):
+        doc = json.loads(json.dumps(good))
+        for key, value in changes.items():
+            if key in doc["model"]:
+                doc["model"][key] = value
+            elif value is None:
+                doc.pop(key)
+            else:
+                doc[key] = value
+        path = tmp_path / "c.json"
+        path.write_text(json.dumps(doc))
+        return MT.load_model_config(str(path))
+
+    assert load() == dict(good, warmup=3, iters=10, seed=0)
+    for changes, message in ((dict(schema_version=2), "schema_version 1"), (dict(extra=1), "unknown configuration fields: extra"),
+                             (dict(hidden=200), "multiple of 256"), (dict(intermediate_hidden=100), "multiple of 256"),
+                             (dict(num_topk=5), "num_topk"), (dict(num_shared_experts=15), "at most 16"),
+                             (dict(bs_values=[]), "non-empty"), (dict(bs_values=[0]), "batch sizes"), (dict(iters=0), "iters"),
+                             (dict(model={"hidden": 256}), "exactly")):
+        with pytest.raises(ValueError, match=message):
+            load(**changes)
+
+
+def test_config_driven_benchmark_on_the_cpu_engine(tmp_path):
+    """``benchmarks/bench_mega_config.py`` end to end without a GPU: a small model with a shared expert, checked against the
+    restatement, one JSON line on stdout."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import pytest
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("CPU-engine test")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = tmp_path / "tiny.json"
+    path.write_text(json.dumps(dict(schema_version=1, bs_values=[2, 5], warmup=0, iters=1, seed=3,
+                                    model=dict(hidden=256, intermediate_hidden=128, num_experts=4, num_topk=2, num_shared_experts=1))))
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    res = subprocess.run([sys.executable, os.path.join(root, "benchmarks", "bench_mega_config.py"), "--config", str(path), "--check"],
+                         capture_output=True, text=True, timeout=240, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    out = json.loads(res.stdout.strip().splitlines()[-1])
+    assert out["engine"] == "cpu" and out["world"] == 1 and [r["bs"] for r in out["results"]] == [2, 5]
+    assert all(r["ok"] and r["us"] > 0 for r in out["results"])
