@@ -96,10 +96,13 @@ class EventOverlap:
         return out
 
     def current_stream_wait(self, release_handle: bool = False) -> Any:
-        assert self.event is not None, "an empty EventOverlap has nothing to wait for"
-        self.event.current_stream_wait()
+        """Make the current stream wait for the call.  On the empty wrapper of a synchronous call there is nothing left
+        to wait for (the current stream was already ordered after the call), so callers may use one code path for both
+        forms, as the usage examples of the reference do (``README.md:168-196``)."""
+        if self.event is not None:
+            self.event.current_stream_wait()
         cuda = _cuda()
-        if cuda is not None and self._stream_tensors:
+        if self.event is not None and cuda is not None and self._stream_tensors:
             cur = cuda.current_stream(self.event._device)
             for t in self._stream_tensors:  # the consumer stream uses them from now on
                 t.record_stream(cur)
