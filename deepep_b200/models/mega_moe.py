@@ -56,7 +56,7 @@ def _sf_chunks(sf: torch.Tensor) -> torch.Tensor:
 
 
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor], l2_weights: Tuple[torch.Tensor, torch.Tensor],
-                                   device=None) -> Tuple[MegaWeights, MegaWeights]:
+                                   activation: str = "swiglu", *, shared: bool = False, device=None) -> Tuple[MegaWeights, MegaWeights]:
     """Rearrange ``(w1 [L, 2I, H/2], w1_sf [L, 2I, H/32])`` and ``(w2 [L, H, I/2], w2_sf [L, H, I/32])`` for the kernel.
 
     Weights are packed e2m1 pairs (uint8, two values per byte: ``mma_type="fp8xfp4"``) or, for ``mma_type="fp8xfp8"``,
@@ -64,6 +64,9 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
     W1 rows are regrouped so every 256-row tile holds 128 gate rows followed by the 128 matching up rows
     (gate = first I rows, up = last I rows); scales go into the tensor-memory chunk layout.
     """
+    if activation != "swiglu":
+        raise NotImplementedError("only SwiGLU is implemented")
+    del shared       # the reference lays shared experts out differently; here they use the routed experts' layout
     (w1, w1_sf), (w2, w2_sf) = l1_weights, l2_weights
     fp8 = w1.dtype == torch.float8_e4m3fn
     if (w2.dtype == torch.float8_e4m3fn) != fp8:
@@ -268,9 +271,16 @@ class SymmBuffer:
     """Symmetric input/output block of the fused MoE forward; construction is collective."""
 
     def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
-                 intermediate_hidden: int, *, num_shared_experts: int = 0, mma_type: str = "fp8xfp4", activation: str = "swiglu",
-                 rank: Optional[int] = None, world_size: Optional[int] = None, device=None,
-                 num_gpu_timeout_secs: float = 100, num_sms: int = 0):
+                 intermediate_hidden: int, num_shared_experts: int = 0, mma_type: str = "fp8xfp4", activation: str = "swiglu",
+                 *, ranks_per_node: int = 0, timeout: Optional[float] = None, rank: Optional[int] = None,
+                 world_size: Optional[int] = None, device=None, num_gpu_timeout_secs: float = 100, num_sms: int = 0):
+        """``group``: a process group, a ``StoreGroup``, or ``None`` (one process, or ``rank=`` / ``world_size=`` over the
+        launcher's TCPStore).  ``ranks_per_node`` is accepted for the reference's signature (``api.py:70-84``; all ranks
+        share one NVLink domain here); ``timeout`` (seconds), when given, is the limit of the waits inside the kernel
+        (otherwise ``num_gpu_timeout_secs``)."""
+        del ranks_per_node
+        if timeout is not None:
+            num_gpu_timeout_secs = float(timeout)
         if mma_type not in ("fp8xfp4", "fp8xfp8"):
             raise ValueError("mma_type must be 'fp8xfp4' (e2m1 weights) or 'fp8xfp8' (e4m3 weights)")
         if activation != "swiglu":

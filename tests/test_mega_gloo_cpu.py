@@ -102,3 +102,64 @@ def test_weights_transformed_for_a_gpu_are_refused_by_the_cpu_engine():
     with pytest.raises(ValueError):
         MM.SymmBuffer(None, E, 8, K, 200, I)
     sym.destroy()
+
+
+def _readme_worker(rank, port, results):
+    """The MegaMoE example of the reference's README (``README.md:232-272``) with the device lines taken out."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(WORLD),
+                      LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(WORLD))
+    from deep_ep_experimental.megamoe import StoreGroup, SymmBuffer, fp8_fp4_mega_moe, transform_weights_for_mega_moe
+
+    spec = MT.contract(world=WORLD, tokens=[6, 6], hidden=H, intermediate=I, experts=E, topk=K, seed=8)
+    xs, idx, ws, all_l1, all_l2 = MT.make_case(spec)
+    mine = slice(rank * (E // WORLD), (rank + 1) * (E // WORLD))
+    l1_weights, l2_weights = (all_l1[0][mine], all_l1[1][mine]), (all_l2[0][mine], all_l2[1][mine])
+    shared_l1_weights, shared_l2_weights = O.make_weights(1, H, I, 70 + rank)
+    x_fp8, x_sf, topk_idx, topk_weights = xs[rank][0], xs[rank][1], idx[rank].to(torch.int32), ws[rank]
+    ok = False
+    group = StoreGroup.from_env()
+    try:
+        buffer = SymmBuffer(
+            group, num_experts=E, num_max_tokens_per_rank=16,
+            num_topk=K, hidden=H, intermediate_hidden=I,
+            num_shared_experts=1, mma_type="fp8xfp4",
+            ranks_per_node=int(os.environ["LOCAL_WORLD_SIZE"]),
+        )
+        w1, w2 = transform_weights_for_mega_moe(l1_weights, l2_weights)
+        shared_w1, shared_w2 = transform_weights_for_mega_moe(
+            shared_l1_weights, shared_l2_weights, shared=True,
+        )
+        num_tokens = x_fp8.shape[0]
+        buffer.x[:num_tokens].copy_(x_fp8)
+        buffer.x_sf[:num_tokens].copy_(x_sf)
+        buffer.topk_idx[:num_tokens].copy_(topk_idx)
+        buffer.topk_weights[:num_tokens].copy_(topk_weights)
+        buffer.validate_inputs(num_tokens)
+        buffer.prepare(num_tokens)
+        y = torch.empty((num_tokens, H), dtype=torch.bfloat16)
+        fp8_fp4_mega_moe(
+            y, w1, w2, buffer,
+            shared_l1_weights=shared_w1, shared_l2_weights=shared_w2,
+        )
+        want = O.mega_moe_reference([xs[rank]], [idx[rank]], [ws[rank]], all_l1, all_l2, E, shared_l1_weights, shared_l2_weights)[0]
+        ok = torch.equal(y, want)
+        group.barrier("before SHMEM teardown")
+        buffer.destroy()
+        group.close()
+    except BaseException as error:
+        group.abort(f"MegaMoE: {type(error).__name__}: {error}")
+        results[rank] = repr(error)
+        raise
+    results[rank] = ok
+
+
+def test_the_fused_moe_example_of_the_reference_readme():
+    from torch.distributed import TCPStore
+
+    if torch.cuda.is_available():
+        pytest.skip("CPU-engine test")
+    server = TCPStore("127.0.0.1", 0, None, True, timedelta(seconds=60), wait_for_workers=False)
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_readme_worker, args=(server.port, results), nprocs=WORLD, join=True)
+        assert dict(results) == {0: True, 1: True}
