@@ -175,8 +175,8 @@ class GmmConfig:
 
 
 class _Group:
-    def __init__(self, group, rank, world_size, max_rows, max_k, max_n, device, timeout, num_sms):
-        self.control = ControlPlane(group, rank, world_size)
+    def __init__(self, group, rank, world_size, max_rows, max_k, max_n, device, timeout, num_sms, control=None):
+        self.control = control if control is not None else ControlPlane(group, rank, world_size)
         self.rank, self.world_size = self.control.rank, self.control.size
         self.max_rows, self.max_k, self.max_n = int(max_rows), int(max_k), int(max_n)
         if self.max_rows < 1 or self.max_k % 64 or self.max_n % 64 or self.max_k < 64 or self.max_n < 64:
@@ -205,18 +205,55 @@ class _Group:
 
 
 _GROUP: Optional[_Group] = None
+_PENDING: Optional[dict] = None      # a group initialised by bytes (heap_size=): sized by the first operator call
+_LEASES = 0                          # udma_group contexts that are open
+_CONTEXT_OWNS = False
 
 
-def init_group(group=None, *, rank: Optional[int] = None, world_size: Optional[int] = None, max_rows: int, max_k: int,
-               max_n: int, device=None, timeout: float = 100.0, num_sms: int = 0) -> GmmConfig:
+def init_group(group=None, *, rank: Optional[int] = None, world_size: Optional[int] = None, max_rows: Optional[int] = None,
+               max_k: Optional[int] = None, max_n: Optional[int] = None, device=None, timeout: float = 100.0, num_sms: int = 0,
+               heap_size: Optional[int] = None, local_rank: Optional[int] = None, init_method: Optional[str] = None) -> GmmConfig:
     """Collective: allocates and exchanges the symmetric workspace (staged inputs ``[max_rows, max_k]`` and returned
     rows ``[max_rows, max_n]`` per rank).  ``max_rows`` bounds the rows a rank sends (``alltoallv_gmm``) or gets back
-    (``gmm_alltoallv``) in one call."""
-    global _GROUP
-    if _GROUP is not None:
+    (``gmm_alltoallv``) in one call.
+
+    The reference's form (``init_udma_group(*, group, rank, world_size, local_rank, init_method, heap_size=1 << 30)``,
+    ``runtime.py:87-99`` there) gives bytes instead of shapes: the workspace is then created by the first operator call,
+    which knows ``k`` and ``n``: both row widths become ``max(k, n)`` rounded up to 64 and ``max_rows`` what
+    ``heap_size`` bytes hold.  ``local_rank`` selects the CUDA device; ``init_method`` is accepted and unused (the ranks
+    meet through ``group`` or the launcher's TCPStore)."""
+    global _GROUP, _PENDING
+    del init_method
+    if _GROUP is not None or _PENDING is not None:
         raise RuntimeError("ep_gmm_fused group is already initialised; call destroy_group() first")
+    if local_rank is not None and device is None and torch.cuda.is_available():
+        device = torch.device("cuda", int(local_rank))
+    shapes = (max_rows, max_k, max_n)
+    if all(v is None for v in shapes):
+        heap_size = (1 << 30) if heap_size is None else int(heap_size)
+        if heap_size < (1 << 20):
+            raise ValueError("heap_size must be at least 1 MiB")
+        control = ControlPlane(group, rank, world_size)
+        _PENDING = dict(control=control, group=group, rank=rank, world_size=world_size, heap_size=heap_size, device=device,
+                        timeout=timeout, num_sms=num_sms)
+        use_cuda = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
+        return GmmConfig(control.rank, control.size, 0, 0, 0, "cuda" if use_cuda else "cpu")
+    if any(v is None for v in shapes) or heap_size is not None:
+        raise ValueError("pass max_rows, max_k and max_n together, or heap_size alone")
     _GROUP = _Group(group, rank, world_size, max_rows, max_k, max_n, device, timeout, num_sms)
     return _GROUP.config()
+
+
+def _materialize(k: int, n: int) -> None:
+    """First operator call of a group that was initialised by bytes: create the workspace for these row widths."""
+    global _GROUP, _PENDING
+    if _PENDING is None:
+        return
+    p, _PENDING = _PENDING, None
+    width = -(-max(int(k), int(n)) // 64) * 64
+    rows = max(1, p["heap_size"] // (4 * width))          # one staged bf16 row and one returned bf16 row per slot
+    _GROUP = _Group(p["group"], p["rank"], p["world_size"], rows, width, width, p["device"], p["timeout"], p["num_sms"],
+                    control=p["control"])
 
 
 def check_errors() -> None:
@@ -235,24 +272,55 @@ def _maybe_check(g) -> None:
 
 
 def destroy_group() -> None:
-    global _GROUP
+    global _GROUP, _PENDING
+    if _LEASES:
+        raise RuntimeError("cannot destroy the group while udma_group contexts are active")
     if _GROUP is not None:
         _GROUP.close()
         _GROUP = None
+    _PENDING = None
 
 
 def get_config() -> GmmConfig:
+    if _GROUP is None and _PENDING is not None:
+        c = _PENDING["control"]
+        return GmmConfig(c.rank, c.size, 0, 0, 0, "pending")
     if _GROUP is None:
         raise RuntimeError("ep_gmm_fused group is not initialised; call init_group(...) on every rank first")
     return _GROUP.config()
 
 
 init_udma_group, destroy_udma_group, get_udma_config = init_group, destroy_group, get_config
+UdmaConfig = GmmConfig
+
+
+import contextlib  # noqa: E402
+
+
+@contextlib.contextmanager
+def udma_group(**kwargs):
+    """``with udma_group(group=ep_group): ...`` initialises the group on entry and destroys it on exit of the outermost
+    context that created it; a group that was initialised explicitly is borrowed and left alone
+    (parity: ``runtime.py:211-231`` of the reference)."""
+    global _LEASES, _CONTEXT_OWNS
+    existed = _GROUP is not None or _PENDING is not None
+    config = get_config() if existed else init_group(**kwargs)
+    if _LEASES == 0:
+        _CONTEXT_OWNS = not existed
+    _LEASES += 1
+    try:
+        yield config
+    finally:
+        _LEASES -= 1
+        if _LEASES == 0 and _CONTEXT_OWNS:
+            _CONTEXT_OWNS = False
+            destroy_group()
 
 
 def symmetric_input(rows: int, k: int) -> torch.Tensor:
     """bf16 ``[rows, k]`` view of this rank's staged-input area.  Passing it as ``x`` to :func:`alltoallv_gmm` skips
     the staging copy (the peers read it in place).  CPU engine: an ordinary tensor."""
+    _materialize(k, k)
     get_config()
     if _GROUP.engine is None:
         return torch.empty((rows, k), dtype=torch.bfloat16)
@@ -262,6 +330,7 @@ def symmetric_input(rows: int, k: int) -> torch.Tensor:
 def symmetric_output(rows: int, n: int) -> torch.Tensor:
     """bf16 ``[rows, n]`` view of this rank's returned-rows area.  Passing it as ``out`` to :func:`gmm_alltoallv` skips
     the final copy; it stays valid until the next :func:`gmm_alltoallv` call.  CPU engine: an ordinary tensor."""
+    _materialize(n, n)
     get_config()
     if _GROUP.engine is None:
         return torch.empty((rows, n), dtype=torch.bfloat16)
@@ -294,6 +363,55 @@ def _check_tiling(tiling: Optional[Mapping[str, int]]) -> None:
     for key, value in tiling.items():
         if int(value) != TILE_SHAPE[key]:
             raise ValueError(f"tiling {key}={value} is not available: the kernel is built for {TILE_SHAPE}")
+
+
+# ------------------------------------------------------------------------------------------------ balanced routes
+def build_global_route_matrix(m: int, ep_size: int, expert_num: int) -> List[List[int]]:
+    """``[source rank][global expert]`` row counts of the balanced benchmark routing: every source rank has ``m`` rows,
+    every destination rank receives ``m`` rows, and inside a (source, destination) pair the rows are spread over the
+    destination's local experts.  Remainders rotate: of the ``m mod ep_size`` extra rows of source ``s`` the first goes
+    to rank ``s``, the next to ``s + 1``, ...; inside the pair the extra rows start at local expert ``(s + d) mod L``.
+    Parity: ``build_global_route_matrix`` of the reference (``ep_gmm_fused/routing.py:24-56``), whose counts these are."""
+    if m <= 0 or ep_size <= 0 or expert_num <= 0:
+        raise ValueError("m, ep_size, and expert_num must be positive")
+    if ep_size > 8:
+        raise ValueError("ep_size must not exceed 8")
+    if expert_num % ep_size:
+        raise ValueError("expert_num must be divisible by ep_size")
+    L = expert_num // ep_size
+    if L > 64:
+        raise ValueError("local expert count must not exceed 64")
+    src = torch.arange(ep_size).view(-1, 1, 1)
+    dst = torch.arange(ep_size).view(1, -1, 1)
+    loc = torch.arange(L).view(1, 1, -1)
+    pair = m // ep_size + ((dst - src) % ep_size < m % ep_size).long()              # rows of source s for destination d
+    counts = pair // L + ((loc - (src + dst)) % L < pair % L).long()                # ... for local expert l of d
+    matrix = counts.reshape(ep_size, expert_num)
+    assert bool((matrix.sum(1) == m).all()) and bool((counts.sum((0, 2)) == m).all())
+    return matrix.tolist()
+
+
+def build_rank_route_tables(m: int, rank: int, ep_size: int, expert_num: int) -> Tuple[List[int], List[int]]:
+    """The two flat route inputs of one rank: ``local_tokens_per_expert`` (its row of the matrix) and
+    ``global_tokens_per_local_expert`` (ordered by source rank, then local expert)."""
+    if not 0 <= rank < ep_size:
+        raise ValueError("rank must be in [0, ep_size)")
+    matrix = build_global_route_matrix(m, ep_size, expert_num)
+    L = expert_num // ep_size
+    return list(matrix[rank]), [matrix[s][rank * L + l] for s in range(ep_size) for l in range(L)]
+
+
+def build_rank_route(m: int, rank: int, ep_size: int, expert_num: int, device):
+    """``(local_tokens_per_expert, global_tokens_per_local_expert, received_rows)``: flat int64 tensors on ``device``
+    plus the row count this rank receives, known on the host (pass it as ``received_rows=`` to avoid a read-back)."""
+    local, received = build_rank_route_tables(m, rank, ep_size, expert_num)
+    return (torch.tensor(local, dtype=torch.int64, device=device), torch.tensor(received, dtype=torch.int64, device=device),
+            sum(received))
+
+
+def build_rank_route_tensors(m: int, rank: int, ep_size: int, expert_num: int, device):
+    local, received, _ = build_rank_route(m, rank, ep_size, expert_num, device)
+    return local, received
 
 
 # ------------------------------------------------------------------------------------------------ ops
@@ -339,6 +457,8 @@ def alltoallv_gmm(x: torch.Tensor, weight: torch.Tensor, local_tokens_per_expert
                   all_to_allv_out: Optional[torch.Tensor] = None, tiling: Optional[Mapping[str, int]] = None):
     """Dispatch rows to their experts' ranks and apply the destination rank's grouped matmuls (one kernel)."""
     _check_tiling(tiling)
+    if _PENDING is not None and x.dim() == 2 and weight.dim() == 3:
+        _materialize(x.shape[1], weight.shape[2])
     g = _GROUP
     cfg = get_config()
     _check_operands(x, weight, ep_size, expert_num, cfg)
@@ -385,6 +505,8 @@ def gmm_alltoallv(x: torch.Tensor, weight: torch.Tensor, local_tokens_per_expert
                   out: Optional[torch.Tensor] = None, tiling: Optional[Mapping[str, int]] = None) -> torch.Tensor:
     """Apply this rank's grouped matmuls and return the products to the ranks their rows came from (one kernel)."""
     _check_tiling(tiling)
+    if _PENDING is not None and x.dim() == 2 and weight.dim() == 3:
+        _materialize(x.shape[1], weight.shape[2])
     g = _GROUP
     cfg = get_config()
     _check_operands(x, weight, ep_size, expert_num, cfg)
@@ -416,6 +538,7 @@ def gmm_alltoallv(x: torch.Tensor, weight: torch.Tensor, local_tokens_per_expert
 all_to_allv_grouped_matmul = alltoallv_gmm
 grouped_matmul_all_to_allv = gmm_alltoallv
 
-__all__ = ["GmmConfig", "GmmEngine", "all_to_allv_grouped_matmul", "alltoallv_gmm", "check_errors", "destroy_group", "destroy_udma_group",
+__all__ = ["GmmConfig", "GmmEngine", "UdmaConfig", "udma_group", "build_global_route_matrix", "build_rank_route", "build_rank_route_tables",
+           "build_rank_route_tensors", "all_to_allv_grouped_matmul", "alltoallv_gmm", "check_errors", "destroy_group", "destroy_udma_group",
            "get_config", "get_udma_config", "gmm_alltoallv", "grouped_matmul_all_to_allv", "init_group", "init_udma_group",
            "load_tiling_config", "reference_alltoallv_gmm", "reference_gmm_alltoallv", "symmetric_input", "symmetric_output"]

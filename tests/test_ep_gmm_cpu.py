@@ -153,3 +153,70 @@ def test_one_process_round_trip_and_every_rejection():
     finally:
         G.destroy_group()
     G.destroy_group()                                                  # idempotent
+
+
+def test_balanced_route_builders():
+    """Every source sends ``m`` rows, every destination receives ``m`` rows, neighbours differ by at most one row, and the
+    per-rank tables are the matrix's row and column block (values for 7 rows over 2 ranks x 2 experts worked out by hand)."""
+    assert G.build_global_route_matrix(7, 2, 4) == [[2, 2, 1, 2], [1, 2, 2, 2]]
+    assert G.build_rank_route_tables(7, 1, 2, 4) == ([1, 2, 2, 2], [1, 2, 2, 2])
+    for m, ep, experts in ((1, 1, 1), (4096, 4, 8), (4097, 8, 256), (13, 8, 8), (5, 4, 64)):
+        matrix = torch.tensor(G.build_global_route_matrix(m, ep, experts))
+        L = experts // ep
+        assert matrix.shape == (ep, experts) and bool((matrix.sum(1) == m).all())
+        per_destination = matrix.view(ep, ep, L).sum((0, 2))
+        assert bool((per_destination == m).all())
+        pairs = matrix.view(ep, ep, L)
+        assert int(pairs.sum(2).max() - pairs.sum(2).min()) <= 1 and int((pairs.max(2).values - pairs.min(2).values).max()) <= 1
+        for rank in range(ep):
+            local, received = G.build_rank_route_tables(m, rank, ep, experts)
+            assert local == matrix[rank].tolist() and received == matrix[:, rank * L:(rank + 1) * L].reshape(-1).tolist()
+    lt, gt, rows = G.build_rank_route(100, 2, 4, 8, "cpu")
+    assert lt.dtype == torch.int64 and gt.dtype == torch.int64 and rows == 100 == int(gt.sum()) == int(lt.sum())
+    a, b = G.build_rank_route_tensors(100, 2, 4, 8, "cpu")
+    assert torch.equal(a, lt) and torch.equal(b, gt)
+    for args, message in (((0, 2, 4), "positive"), ((8, 9, 9), "exceed 8"), ((8, 2, 5), "divisible"), ((8, 1, 65), "exceed 64")):
+        with pytest.raises(ValueError, match=message):
+            G.build_global_route_matrix(*args)
+    with pytest.raises(ValueError, match="rank must be"):
+        G.build_rank_route_tables(8, 2, 2, 4)
+
+
+def test_group_given_in_bytes_and_the_context_manager():
+    """The reference's forms: ``with udma_group(...)`` and ``init_udma_group(heap_size=...)``; the workspace is sized by
+    the first operator call.  One process, CPU engine."""
+    if torch.cuda.is_available():
+        pytest.skip("CPU-engine test")
+    E, K, N, m = 4, 64, 128, 24
+    gen = torch.Generator().manual_seed(2)
+    x = torch.randn((m, K), generator=gen).bfloat16()
+    w1 = (torch.randn((E, K, N), generator=gen) / 8).bfloat16()
+    w2 = (torch.randn((E, N, K), generator=gen) / 8).bfloat16()
+    local_counts, received_counts, rows = G.build_rank_route(m, 0, 1, E, "cpu")
+    with G.udma_group(heap_size=2 << 20) as cfg:
+        assert cfg.world_size == 1 and G.get_udma_config().backend == "pending"
+        with G.udma_group():                                            # nested: borrows, does not destroy on exit
+            h = G.alltoallv_gmm(x, w1, local_counts, received_counts, ep_size=1, expert_num=E, received_rows=rows)
+        sized = G.get_udma_config()
+        assert isinstance(sized, G.UdmaConfig) and (sized.max_k, sized.max_n) == (128, 128) and sized.max_rows == (2 << 20) // 512
+        y = G.gmm_alltoallv(h, w2, local_counts, received_counts, ep_size=1, expert_num=E)
+        with pytest.raises(RuntimeError, match="contexts are active"):
+            G.destroy_udma_group()
+    with pytest.raises(RuntimeError, match="not initialised"):
+        G.get_udma_config()                                              # the outermost context destroyed what it created
+    ref_h, _ = G.reference_alltoallv_gmm([x], [w1], [local_counts.tolist()], E)
+    assert torch.equal(h, ref_h[0]) and torch.equal(y, G.reference_gmm_alltoallv([h], [w2], [local_counts.tolist()], E)[0])
+    # an explicitly initialised group is borrowed by a context and survives it
+    G.init_udma_group(rank=0, world_size=1, heap_size=1 << 20, init_method="tcp://127.0.0.1:1")
+    try:
+        with G.udma_group():
+            assert G.symmetric_input(4, K).shape == (4, K)               # sizes the workspace for this width
+        assert G.get_udma_config().max_k == 64
+        with pytest.raises(RuntimeError, match="already initialised"):
+            G.init_udma_group(heap_size=1 << 20)
+    finally:
+        G.destroy_udma_group()
+    with pytest.raises(ValueError, match="together"):
+        G.init_group(None, max_rows=8)
+    with pytest.raises(ValueError, match="1 MiB"):
+        G.init_udma_group(heap_size=1000)
