@@ -57,3 +57,41 @@ def test_environment_overrides_the_constructor(monkeypatch):
     monkeypatch.setenv("DEEPEP_CPU_TIMEOUT_SECONDS", "0")
     with pytest.raises(ValueError, match="3600"):
         HW.cpu_timeout_seconds(300)
+
+
+def test_the_engine_turns_a_host_timeout_into_a_communication_error(monkeypatch):
+    """``CudaEngine._host_wait`` with stand-ins for the stream and the event: it records an event on the stream it was
+    given, polls it, synchronises the stream at the end, and raises ``CommunicationError`` when the limit passes."""
+    import types
+
+    import torch
+
+    from deepep_b200.parallel import engine_cuda as EC
+
+    log = []
+
+    class FakeEvent:
+        polls_until_done = 2
+
+        def record(self, stream):
+            log.append(("record", stream.name))
+            self.left = self.polls_until_done
+
+        def query(self):
+            self.left -= 1
+            return self.left < 0
+
+    class FakeStream:
+        name = "comm"
+
+        def synchronize(self):
+            log.append(("synchronize", self.name))
+
+    monkeypatch.setattr(torch.cuda, "Event", FakeEvent)
+    engine = types.SimpleNamespace(device=torch.device("cpu"), host_timeout=5.0)
+    EC.CudaEngine._host_wait(engine, FakeStream(), "the routing layout pass")
+    assert log == [("record", "comm"), ("synchronize", "comm")]
+    FakeEvent.polls_until_done = 10 ** 9
+    engine.host_timeout = 0.05
+    with pytest.raises(EC.CommunicationError, match=r"\[DEEPEP_CPU_TIMEOUT\] the routing layout pass .* restart the distributed job"):
+        EC.CudaEngine._host_wait(engine, FakeStream(), "the routing layout pass")
