@@ -58,3 +58,20 @@ def public_keywords(function, names, *, aliases=None):
 ELASTIC_INIT_ALIASES = {"num_device_timeout_secs": "num_gpu_timeout_secs", "num_host_timeout_secs": "num_cpu_timeout_secs"}
 CALL_ALIASES = {"num_compute_units": "num_sms", "num_queue_pairs": "num_qps",
                 "use_aligned_col_major_sf": "use_tma_aligned_col_major_sf"}
+COMBINE_ALIASES = {"num_compute_units": "num_sms", "num_queue_pairs": "num_qps"}
+ESTIMATOR_ALIASES = {"scaleup_gbs": "nvlink_gbs", "scaleout_gbs": "rdma_gbs", "compute_unit_read_gbs": "sm_read_gbs",
+                     "compute_unit_write_gbs": "sm_write_gbs", "compute_read_gbs": "sm_read_gbs", "compute_write_gbs": "sm_write_gbs"}
+QPS_ALIASES = {"num_compute_units": "num_sms"}
+HANDLE_ALIASES = {"num_compute_units": "num_sms"}
+BUFFER_INIT_ALIASES = {"num_scaleup_bytes": "num_nvl_bytes", "num_scaleout_bytes": "num_rdma_bytes",
+                       "allow_memory_transport_for_low_latency_mode": "allow_nvlink_for_low_latency_mode",
+                       "allow_multinode_memory_transport": "allow_mnnvl"}
+BUFFER_DISPATCH_ALIASES = {"num_tokens_per_scaleout_rank": "num_tokens_per_rdma_rank"}
+SET_UNITS_ALIASES = {"new_num_compute_units": "new_num_sms"}
+CONFIG_ALIASES = {"num_compute_units": "num_sms", "num_aiv": "num_sms",
+                  "num_max_scaleup_chunked_send_tokens": "num_max_nvl_chunked_send_tokens",
+                  "num_max_scaleup_chunked_recv_tokens": "num_max_nvl_chunked_recv_tokens",
+                  "num_max_shmem_chunked_send_tokens": "num_max_nvl_chunked_send_tokens",
+                  "num_max_shmem_chunked_recv_tokens": "num_max_nvl_chunked_recv_tokens",
+                  "num_max_scaleout_chunked_send_tokens": "num_max_rdma_chunked_send_tokens",
+                  "num_max_scaleout_chunked_recv_tokens": "num_max_rdma_chunked_recv_tokens"}

@@ -41,3 +41,10 @@ class Config:
 
     def __repr__(self) -> str:
         return f"Config(num_sms={self.num_sms})"
+
+
+from ._compat import CONFIG_ALIASES, keyword_aliases  # noqa: E402
+
+Config.__init__ = keyword_aliases(Config.__init__, CONFIG_ALIASES)
+Config.num_compute_units = property(lambda self: self.num_sms, lambda self, value: setattr(self, "num_sms", value))
+Config.num_aiv = Config.num_compute_units          # the reference's spelling of the same count

@@ -19,7 +19,8 @@ from typing import Any, List, Optional, Sequence, Tuple, Union
 
 import torch
 
-from .._compat import CALL_ALIASES, ELASTIC_INIT_ALIASES, keyword_aliases
+from .._compat import (CALL_ALIASES, COMBINE_ALIASES, ELASTIC_INIT_ALIASES, ESTIMATOR_ALIASES, HANDLE_ALIASES, QPS_ALIASES,
+                       keyword_aliases)
 from ..utils.event import EventHandle, EventOverlap
 from . import layout as L
 from .runtime import ControlPlane, Runtime
@@ -589,6 +590,12 @@ def _col_major(sf: torch.Tensor) -> torch.Tensor:
 
 ElasticBuffer.__init__ = keyword_aliases(ElasticBuffer.__init__, ELASTIC_INIT_ALIASES)
 ElasticBuffer.dispatch = keyword_aliases(ElasticBuffer.dispatch, CALL_ALIASES)
-ElasticBuffer.combine = keyword_aliases(ElasticBuffer.combine, CALL_ALIASES)
+ElasticBuffer.combine = keyword_aliases(ElasticBuffer.combine, COMBINE_ALIASES)
+ElasticBuffer.get_theoretical_num_sms = keyword_aliases(ElasticBuffer.get_theoretical_num_sms, ESTIMATOR_ALIASES)
+ElasticBuffer.get_theoretical_num_compute_units = ElasticBuffer.get_theoretical_num_sms
+ElasticBuffer.get_theoretical_num_qps = keyword_aliases(ElasticBuffer.get_theoretical_num_qps, QPS_ALIASES)
+EPHandle.__init__ = keyword_aliases(EPHandle.__init__, HANDLE_ALIASES)
+# the platform-neutral spelling of the handle's SM budget reads and writes the same value
+EPHandle.num_compute_units = property(lambda self: self.num_sms, lambda self, value: setattr(self, "num_sms", value))
 
 __all__ = ["ElasticBuffer", "EPHandle"]
