@@ -45,3 +45,39 @@ def test_previous_event_async_and_comm_stream_allocation():
     assert ev.event is None and bits_equal(again, rx)
     torch.cuda.synchronize()
     buf.destroy()
+
+
+def test_two_live_buffers_in_one_process():
+    """A prefill buffer and a decode buffer alive at the same time, their calls interleaved (each has its own workspace,
+    control block and communication stream); a handle of one is refused by the other.  Parity: the reference's
+    multi-buffer tests (``tests/clos/source/test_multi_buffer.py``)."""
+    import deepep_b200 as deep_ep
+
+    dev = torch.device("cuda")
+    H, E, K = 512, 16, 4
+    big = deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=400, hidden=H, num_topk=K, explicitly_destroy=True)
+    small = deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=64, hidden=H, num_topk=K, explicitly_destroy=True)
+    xs, idxs, ws = {}, {}, {}
+    for name, tokens, seed in (("big", 333, 1), ("small", 48, 2)):
+        xs[name] = torch.randn((tokens, H), generator=torch.Generator().manual_seed(seed)).bfloat16()
+        idxs[name], ws[name] = group_limited_routes(tokens, E, K, 4, 2, seed=seed), make_weights(tokens, K, seed)
+    rb, _, _, hb, _ = big.dispatch(xs["big"].to(dev), topk_idx=idxs["big"].to(dev), topk_weights=ws["big"].to(dev), num_experts=E,
+                                   do_expand=True)
+    rs, _, rws, hs, _ = small.dispatch(xs["small"].to(dev), topk_idx=idxs["small"].to(dev), topk_weights=ws["small"].to(dev),
+                                       num_experts=E)                                    # decode buffer: low-latency path
+    assert hs.is_low_latency and not hb.is_low_latency
+    ref_b, lay_b = R.dispatch([xs["big"]], [idxs["big"]], [ws["big"]], E, do_expand=True)
+    ref_s, lay_s = R.dispatch([xs["small"]], [idxs["small"]], [ws["small"]], E, do_expand=True)
+    assert bits_equal(rb, ref_b[0][0]) and bits_equal(rs, ref_s[0][0])
+    with pytest.raises(ValueError, match="another buffer"):
+        small.combine(rs, hb)
+    out_s, _, _ = small.combine(rs, hs)
+    out_b, _, _ = big.combine(rb, hb)
+    assert bits_equal(out_b, R.combine([ref_b[0][0]], lay_b, [333], K)[0][0])
+    assert bits_equal(out_s, R.low_latency_combine([ref_s[0][0]], lay_s, [ws["small"]], [48])[0])
+    again = big.dispatch(xs["big"].to(dev), handle=hb)[0]
+    assert bits_equal(again, rb)
+    small.destroy()
+    out_b2, _, _ = big.combine(rb, hb)                  # the other buffer is unaffected by its neighbour's teardown
+    assert bits_equal(out_b2, out_b)
+    big.destroy()
