@@ -1,0 +1,107 @@
+"""The accuracy metrics and the upstream-dtype emulation (``deepep_b200/utils/precision.py``) against the numbers the
+reference checks in: for every case of its golden manifest (``tests/golden/deepep_reference_v2.json``) the MARE, MERE,
+RMSE and the small-value counts of "inputs rounded the way upstream DeepEP's dispatch rounds them, then combined"
+against the float64 combine.  The inputs come from closed formulas (``tests/utils/cases.py:110-176`` of the reference: a
+31-bit linear congruential value per element, four distributions), restated here with tensors.  Also: the production
+quantiser ``per_token_cast_to_fp8`` (float32 arithmetic) against the float64 emulation, and the acceptance rule itself.
+"""
+import json
+import os
+
+import pytest
+import torch
+
+from deepep_b200.utils import precision as P
+from deepep_b200.utils.math import per_token_cast_back, per_token_cast_to_fp8
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(__file__), "data", "reference_golden.json")))["cases"]
+
+
+def unit(seed: torch.Tensor) -> torch.Tensor:
+    return ((seed * 1103515245 + 12345) & 0x7FFFFFFF).double() / float(1 << 31)
+
+
+def inputs_of(case, rank):
+    tokens, hidden, dist, dtype = case["tokens_per_rank"][rank], case["hidden"], case["distribution"], case["dtype"]
+    t = torch.arange(tokens, dtype=torch.int64).view(-1, 1)
+    c = torch.arange(hidden, dtype=torch.int64).view(1, -1)
+    seed = (rank + 1) * 1000003 + (t + 1) * 1009 + c
+    if dist == "uniform":
+        return unit(seed) * 10.0 - 5.0
+    if dist == "normal":
+        standard = sum(unit(seed + offset * 7919) for offset in range(12)) - 6.0
+        mean = ((rank * 17 + t * 3) % 201 - 100).double()
+        deviation = (1 + (rank * 11 + t * 5) % 25).double()
+        return mean + standard * deviation
+    if dist == "small":
+        return (unit(seed) * 2.0 - 1.0) * (2.0 ** -8 if dtype == "bfloat16" else 2.0 ** -4)
+    assert dist == "outlier"
+    base = unit(seed) * 0.01 - 0.005
+    total = tokens * hidden
+    count = max(1, total // 1000) if total else 0
+    marked = torch.zeros(total, dtype=torch.bool)
+    for index in range(count):
+        marked[min(total - 1, index * total // count)] = True
+    return torch.where(marked.view(tokens, hidden), base * 1000.0, base)
+
+
+def factors_of(case, rank):
+    """Sum of (expert id + 1) over the valid slots of every token: what the manifest's combine multiplies ``x`` by."""
+    t = torch.arange(case["tokens_per_rank"][rank]).view(-1, 1)
+    s = torch.arange(case["topk"]).view(1, -1)
+    expert = (rank * 11 + t * 7 + s * 13) % case["experts"]
+    masked = (rank * 5 + t * 3 + s + 1) % 97 == 0
+    return torch.where(masked, torch.zeros_like(expert), expert + 1).sum(1, keepdim=True).double()
+
+
+@pytest.mark.parametrize("case", GOLDEN, ids=[c["name"] for c in GOLDEN])
+def test_metrics_of_the_upstream_dtype_path_match_the_manifest(case):
+    golden, benchmark = [], []
+    for rank in range(case["world_size"]):
+        x, factor = inputs_of(case, rank), factors_of(case, rank)
+        golden.append((x * factor).reshape(-1))
+        benchmark.append(P.to_bf16_values(P.emulate_upstream(x, case["dtype"]) * factor).reshape(-1))
+    got = P.error_metrics(torch.cat(benchmark), torch.cat(golden), dtype=case["dtype"])
+    want = case["upstream_dtype_error"]
+    assert (got["normal_count"], got["small_count"], got["small_error_count"]) == \
+        (want["normal_count"], want["small_count"], want["small_error_count"])
+    for name in ("mare", "mere", "rmse"):
+        assert got[name] == pytest.approx(want[name], rel=1e-12, abs=1e-300), name
+
+
+def test_production_quantiser_agrees_with_the_float64_emulation():
+    """``per_token_cast_to_fp8`` works in float32; the emulation in float64.  They may differ only where the float32
+    product lands on the other side of a rounding boundary, which is rare and never more than one e4m3 step."""
+    x = (torch.randn((64, 1024), generator=torch.Generator().manual_seed(5)) * 3).bfloat16()
+    restored = per_token_cast_back(*per_token_cast_to_fp8(x)).double()
+    emulated = P.emulate_upstream(x.double(), "float8_e4m3fn")
+    differ = restored != emulated
+    assert float(differ.double().mean()) < 0.01
+    step = emulated.abs() / 8 + 1e-6                            # one e4m3 step is at most 1/8 of the value
+    assert bool(((restored - emulated).abs() <= step)[differ].all())
+    report = P.compare_dual(restored, emulated, x.double(), dtype="float8_e4m3fn")
+    assert report["passed"] and report["ratios"]["mare"] <= 1.2
+
+
+def test_rounding_helpers_and_the_acceptance_rule():
+    assert P.to_e4m3_values(torch.tensor([0.0, 1.0, 1.0625, 1.1875, 500.0, -0.0009765625, 2.0 ** -10])).tolist() == \
+        [0.0, 1.0, 1.0, 1.25, 448.0, -0.0, 0.0]                 # ties go to the even code; 2^-10 is half the smallest step
+    assert P.to_bf16_values(torch.tensor([1.00390625, 1.01171875])).tolist() == [1.0, 1.015625]
+    golden = torch.linspace(-4, 4, 4001, dtype=torch.float64)
+    benchmark = P.to_bf16_values(golden)
+    assert P.compare_dual(benchmark, benchmark, golden, dtype="bfloat16")["passed"]
+    worse = golden + (benchmark - golden) * 3.0                  # three times the benchmark's error everywhere
+    verdict = P.compare_dual(worse, benchmark, golden, dtype="bfloat16")
+    assert not verdict["passed"] and verdict["ratios"]["rmse"] == pytest.approx(3.0, rel=1e-6)
+    assert P.compare_dual(worse, benchmark, golden, dtype="bfloat16", level="L0")["ratios"]["mere"] > 2.0
+    tiny = torch.full((10,), 1e-4, dtype=torch.float64)
+    m = P.error_metrics(tiny + 1e-3, tiny, dtype="bfloat16")      # small goldens: counted, not divided by
+    assert (m["normal_count"], m["small_count"], m["small_error_count"]) == (0, 10, 10) and m["mare"] == 0.0
+    with pytest.raises(ValueError, match="finite"):
+        P.error_metrics(torch.tensor([float("nan")]), torch.tensor([1.0]), dtype="bfloat16")
+    with pytest.raises(ValueError, match="unknown"):
+        P.compare_dual(golden, golden, golden, dtype="float16")
+    few = P.bootstrap_median_recheck([0.9] * 50)
+    assert not few["passed"] and few["reason"] == "sample_count_below_200"
+    assert P.bootstrap_median_recheck([0.95] * 150 + [1.3] * 100)["passed"]
+    assert not P.bootstrap_median_recheck([1.4] * 300)["passed"]
