@@ -15,6 +15,7 @@ from typing import Optional, Tuple
 
 import torch
 
+from ._compat import BUFFER_DISPATCH_ALIASES, BUFFER_INIT_ALIASES, SET_UNITS_ALIASES, keyword_aliases
 from .config import Config
 from .parallel.elastic import ElasticBuffer
 from .resources import Handle, SlotPool, SlotState
@@ -261,8 +262,6 @@ __all__ = ["Buffer", "Handle", "topk_idx_t"]
 
 
 # platform-neutral spellings next to the upstream ones (parity: ``deep_ep/backends/direct/api.py:8-20`` of the reference)
-from ._compat import BUFFER_DISPATCH_ALIASES, BUFFER_INIT_ALIASES, SET_UNITS_ALIASES, keyword_aliases  # noqa: E402
-
 Buffer.__init__ = keyword_aliases(Buffer.__init__, BUFFER_INIT_ALIASES)
 Buffer.dispatch = keyword_aliases(Buffer.dispatch, BUFFER_DISPATCH_ALIASES)
 Buffer.set_num_sms = staticmethod(keyword_aliases(Buffer.__dict__["set_num_sms"].__func__, SET_UNITS_ALIASES))

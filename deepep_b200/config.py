@@ -7,6 +7,7 @@ implementation signals completion with one flag per few rows and needs no ring-b
 """
 from __future__ import annotations
 
+from ._compat import CONFIG_ALIASES, keyword_aliases
 from .parallel import layout as L
 
 
@@ -42,8 +43,6 @@ class Config:
     def __repr__(self) -> str:
         return f"Config(num_sms={self.num_sms})"
 
-
-from ._compat import CONFIG_ALIASES, keyword_aliases  # noqa: E402
 
 Config.__init__ = keyword_aliases(Config.__init__, CONFIG_ALIASES)
 Config.num_compute_units = property(lambda self: self.num_sms, lambda self, value: setattr(self, "num_sms", value))

@@ -22,6 +22,7 @@ any other request is rejected instead of being ignored.
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 from typing import List, Mapping, Optional, Sequence, Tuple, Union
 
@@ -292,9 +293,6 @@ def get_config() -> GmmConfig:
 
 init_udma_group, destroy_udma_group, get_udma_config = init_group, destroy_group, get_config
 UdmaConfig = GmmConfig
-
-
-import contextlib  # noqa: E402
 
 
 @contextlib.contextmanager
