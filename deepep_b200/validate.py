@@ -6,7 +6,8 @@ and how it must behave at import) and ``scripts/validate_ep.py`` (an expert-para
 * package: importing ``deepep_b200`` / ``deep_ep`` loads neither torch nor the native extension; the lazy names
   resolve; the native binary is the one its provenance file describes and speaks the expected runtime protocol;
 * smoke: one process dispatches to identity experts and combines, in the expanded and in the rank layout, on the GPU
-  when there is one (native kernels) and through the CPU engine otherwise; results must equal ``sum_k w_k * x``.
+  when there is one (native kernels) and through the CPU engine otherwise; results must equal ``sum_k w_k * x``.  Then
+  one tiny fused MoE forward and one ``alltoallv_gmm`` call, each against its restatement.
 
 Prints one JSON object and exits non-zero when a check fails.
 """
@@ -64,8 +65,51 @@ def smoke() -> dict:
         out["rank_layout"] = bool(torch.equal(rx2, x) and torch.allclose(y2.float(), x.float(), rtol=0.01, atol=0.03))
     finally:
         buf.destroy()
-    out["ok"] = bool(out.get("expanded_layout") and out.get("rank_layout"))
+    out["fused_moe"] = _smoke_fused_moe(dev)
+    out["alltoallv_gmm"] = _smoke_gmm(dev, g)
+    out["ok"] = bool(out.get("expanded_layout") and out.get("rank_layout") and out["fused_moe"] and out["alltoallv_gmm"])
     return out
+
+
+def _smoke_fused_moe(dev) -> bool:
+    """The fused MoE layer on one rank against its CPU restatement (tcgen05 kernel on a GPU, CPU engine otherwise)."""
+    import torch
+
+    from .models import mega_tools as MT
+    from .models.mega_moe import SymmBuffer, fp8_fp4_mega_moe, transform_weights_for_mega_moe
+
+    spec = MT.contract(world=1, tokens=[48], hidden=512, intermediate=256, experts=4, topk=2, seed=3)
+    xs, idx, ws, l1, l2 = MT.make_case(spec)
+    sym = SymmBuffer(None, 4, 64, 2, 512, 256)
+    try:
+        w1, w2 = transform_weights_for_mega_moe(l1, l2, device=dev)
+        sym.load_inputs(xs[0][0].to(dev), xs[0][1].to(dev), idx[0].to(dev), ws[0].to(dev))
+        y = torch.zeros((48, 512), dtype=torch.bfloat16, device=dev)
+        fp8_fp4_mega_moe(y, w1, w2, sym, check=dev.type == "cuda")
+        ok, _ = MT.accuracy_report([y.cpu()], spec)
+        return bool(ok)
+    finally:
+        sym.destroy()
+
+
+def _smoke_gmm(dev, g) -> bool:
+    """``alltoallv_gmm`` on one rank against an fp32 matmul of the same rows."""
+    import torch
+
+    from .ops import ep_gmm_fused as G
+
+    counts = [40, 0, 70, 18]
+    x = torch.randn((sum(counts), 128), generator=g).bfloat16()
+    w = (torch.randn((4, 128, 128), generator=g) / 11).bfloat16()
+    G.init_group(None, max_rows=256, max_k=128, max_n=128)
+    try:
+        out = G.alltoallv_gmm(x.to(dev), w.to(dev), counts, counts, ep_size=1, expert_num=4)
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        ref, _ = G.reference_alltoallv_gmm([x], [w], [counts], 4)
+        return bool(torch.allclose(out.float().cpu(), ref[0].float(), rtol=0.03, atol=0.03))
+    finally:
+        G.destroy_group()
 
 
 def main() -> int:
