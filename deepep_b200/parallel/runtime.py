@@ -23,7 +23,7 @@ from .store import StoreGroup
 
 
 class ControlPlane:
-    """Small host-collective interface with three backends: ProcessGroup, TCPStore, single process."""
+    """Small host-collective interface with four backends: ProcessGroup, TCPStore, an MPI communicator, single process."""
 
     def __init__(self, group: Any = None, rank: Optional[int] = None, world_size: Optional[int] = None,
                  bootstrap: str = "default", timeout: float = 300.0):
@@ -31,9 +31,12 @@ class ControlPlane:
         itself and the hand-over of file descriptors between the ranks."""
         import torch.distributed as dist
 
-        self.group, self.store, self.timeout = None, None, float(timeout)
+        self.group, self.store, self.mpi, self.timeout = None, None, None, float(timeout)
         if isinstance(group, StoreGroup):
             self.store, self.rank, self.size = group, group.rank(), group.size()
+        elif all(hasattr(group, name) for name in ("Get_rank", "Get_size", "allgather", "Barrier")):
+            # an MPI communicator (mpi4py): the reference's MPI bootstrap (``deep_ep/_runtime.py:94-104`` there)
+            self.mpi, self.rank, self.size = group, int(group.Get_rank()), int(group.Get_size())
         elif group is not None:
             self.group, self.rank, self.size = group, dist.get_rank(group), dist.get_world_size(group)
         elif world_size in (None, 1) and rank in (None, 0) and bootstrap != "store":
@@ -58,6 +61,8 @@ class ControlPlane:
 
         if self.size == 1:
             return [obj]
+        if self.mpi is not None:
+            return list(self.mpi.allgather(obj))
         if self.group is not None:
             out = [None] * self.size
             dist.all_gather_object(out, obj, group=self.group)
@@ -73,7 +78,9 @@ class ControlPlane:
 
         if self.size == 1:
             return
-        if self.group is not None:
+        if self.mpi is not None:
+            self.mpi.Barrier()
+        elif self.group is not None:
             dist.barrier(group=self.group)
         else:
             self.store.barrier()
@@ -81,6 +88,8 @@ class ControlPlane:
     def backend(self) -> str:
         import torch.distributed as dist
 
+        if self.mpi is not None:
+            return "mpi"
         if self.group is not None:
             return dist.get_backend(self.group)
         return "store" if self.store is not None else "single"
