@@ -87,31 +87,37 @@ __device__ __forceinline__ bool try_wait_cluster(uint64_t* bar, uint32_t parity)
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool bounded_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* failed) {
+// Which wait ran out: the value a CTA leaves in its failure word (any nonzero value stops the CTA's other warps) and,
+// through the kernel's error flag, what the host reports.
+enum GemmWaitSite : int {
+  kWaitAny = 1, kWaitTileTicket = 2, kWaitRowBlockDone = 3, kWaitRowsPulled = 4, kWaitGroupReleased = 5, kWaitAccEmpty = 6,
+  kWaitPeerAccEmpty = 7, kWaitStageFull = 8, kWaitAccFull = 9, kWaitEpilogueDone = 10
+};
+__device__ __forceinline__ bool bounded_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* failed, int site = kWaitAny) {
   for (unsigned i = 0; i < (1u << 24); ++i) {
     if (try_wait_cluster(bar, parity)) return true;
     if ((i & 63u) == 63u && *failed) return false;
   }
-  *failed = 1;
+  *failed = site;
   return false;
 }
-__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* failed, int site = kWaitAny) {
   for (unsigned i = 0; i < (1u << 24); ++i) {
     if (try_wait_now(bar, parity)) return true;
     if ((i & 63u) == 63u && *failed) return false;
   }
-  *failed = 1;
+  *failed = site;
   return false;
 }
 // Producer-side wait for "all `need` GEMM1 tiles of this row block have been written".
-__device__ __forceinline__ bool wait_rows_ready(const int* counter, int need, volatile int* failed) {
+__device__ __forceinline__ bool wait_rows_ready(const int* counter, int need, volatile int* failed, int site = kWaitAny) {
   for (unsigned i = 0; i < (1u << 26); ++i) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
     if (v >= need) return true;
     if ((i & 63u) == 63u) { if (*failed) return false; __nanosleep(100); }
   }
-  *failed = 1;
+  *failed = site;
   return false;
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -141,8 +147,8 @@ __device__ __forceinline__ int schedule_to_tile(int pos, int num_mtiles, int n1,
 // Next tile of this CTA: the producer publishes it to the MMA and epilogue warps through a small ring.
 __device__ __forceinline__ int fetch_tile(GemmBarriers* bars, uint32_t local_tile, volatile int* failed, bool from_peer = false) {
   const uint32_t slot = local_tile % kSchedRing;
-  const bool ok = from_peer ? bounded_wait_cluster(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed)
-                            : bounded_wait(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed);
+  const bool ok = from_peer ? bounded_wait_cluster(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed, kWaitTileTicket)
+                            : bounded_wait(&bars->sched[slot], (local_tile / kSchedRing) & 1u, failed, kWaitTileTicket);
   return ok ? *reinterpret_cast<volatile int*>(&bars->tile_id[slot]) : -1;
 }
 
@@ -243,17 +249,17 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         const int mt = kPair ? 2 * (local / p.n_tiles) + (int)crank : local / p.n_tiles, nb = local % p.n_tiles;
         const int brow = p.mtile_expert[mt] * p.n_total + nb * kGemmBN;        // first of the tile's 256 weight rows
         if (second && ready) {
-          if (!wait_rows_ready(ready + mt, g1.n_tiles, failed)) break;
+          if (!wait_rows_ready(ready + mt, g1.n_tiles, failed, kWaitRowBlockDone)) break;
           fence_proxy_async();          // rows written by other SMs' stores are about to be read by the copy engine
         } else if (!second && p.a_ready) {
-          if (!wait_rows_ready(p.a_ready + mt, kGemmBM, failed)) break;
+          if (!wait_rows_ready(p.a_ready + mt, kGemmBM, failed, kWaitRowsPulled)) break;
           fence_proxy_async();
         }
         for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
           const int s = it % stages;
           if (it >= (uint32_t)stages) {     // the stage's previous contents have been consumed: their group was released
             const uint32_t grp = (it - (uint32_t)stages) / (uint32_t)commit_every;
-            if (!bounded_wait(&bars->released[grp % kGroupRing], (grp / kGroupRing) & 1u, failed)) break;
+            if (!bounded_wait(&bars->released[grp % kGroupRing], (grp / kGroupRing) & 1u, failed, kWaitGroupReleased)) break;
           }
           uint8_t* a_dst = tiles + (size_t)s * kStage;
           uint8_t* sf_dst = sf_smem + (size_t)s * kSfStageBytes;
@@ -306,14 +312,14 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         if (tile < 0) break;
         const int k_steps = tile >= tiles1 ? g2->k_steps : g1.k_steps;
         const uint32_t idesc = tile >= tiles1 ? idesc2 : idesc1;
-        if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed)) break;
+        if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed, kWaitAccEmpty)) break;
         if constexpr (kPair)      // the odd CTA forwards one arrival per tile, the first as soon as it starts
-          if (!bounded_wait_cluster(&bars->peer_acc_empty, local_tile & 1u, failed)) break;
+          if (!bounded_wait_cluster(&bars->peer_acc_empty, local_tile & 1u, failed, kWaitPeerAccEmpty)) break;
         umma::fence_after_sync();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % stages;
           const long long w0 = mma_stats ? clock64() : 0;
-          if (!bounded_wait(&bars->full[s], (it / stages) & 1u, failed)) break;
+          if (!bounded_wait(&bars->full[s], (it / stages) & 1u, failed, kWaitStageFull)) break;
           if (mma_stats) waited += clock64() - w0;
           umma::fence_after_sync();
           const uint32_t a_addr = smem_u32(tiles + (size_t)s * kStage);
@@ -351,7 +357,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
       for (uint32_t local_tile = 0;; ++local_tile) {
         const int tile = fetch_tile(bars, local_tile, failed, true);
         if (tile < 0) break;
-        if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed)) break;
+        if (!bounded_wait(&bars->acc_empty, (local_tile & 1u) ^ 1u, failed, kWaitAccEmpty)) break;
         umma::remote_arrive(acc_fwd);
       }
     }
@@ -369,7 +375,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
       const MegaGemmParams& p = second ? *g2 : g1;
       const int local = second ? tile - tiles1 : tile;
       const int mt = kPair ? 2 * (local / p.n_tiles) + (int)crank : local / p.n_tiles, nb = local % p.n_tiles;
-      if (!bounded_wait(&bars->acc_full, local_tile & 1u, failed)) break;
+      if (!bounded_wait(&bars->acc_full, local_tile & 1u, failed, kWaitAccFull)) break;
       umma::fence_after_sync();
       const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
       const long long row = (long long)mt * kGemmBM + row_in_tile;
@@ -514,7 +520,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
         __threadfence();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->epi_done);
-        if (warp == 2 && lane == 0 && bounded_wait(&bars->epi_done, first_done & 1u, failed)) {
+        if (warp == 2 && lane == 0 && bounded_wait(&bars->epi_done, first_done & 1u, failed, kWaitEpilogueDone)) {
           __threadfence();
           atomicAdd(ready + mt, 1);
         }
@@ -526,7 +532,7 @@ __device__ __forceinline__ void gemm_phase(const MegaGemmParams& g1, const MegaG
 
   umma::fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0 && *failed && g1.error_flag) *g1.error_flag = 1;
+  if (threadIdx.x == 0 && *failed && g1.error_flag) *g1.error_flag = *failed;   // which wait ran out (GemmWaitSite)
   if constexpr (kPair) umma::cluster_sync_all();    // both CTAs are done with each other's shared and tensor memory
   if (warp == 1) {
     umma::fence_after_sync();

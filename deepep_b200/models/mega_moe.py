@@ -217,10 +217,18 @@ class MegaEngine:
         per_expert = self.world * max(tokens) * self.K / max(self.E, 1) if self.L else 0
         return per_expert >= 384
 
+    WAIT_SITES = {1: "a pipeline barrier", 2: "the tile ticket from the producer warp", 3: "the first projection of a row block",
+                  4: "rows pulled from the peers", 5: "the release of a group of operand stages", 6: "the drain of an accumulator",
+                  7: "the drain of the partner CTA's accumulator", 8: "operands arriving in a stage", 9: "a finished accumulator",
+                  10: "the epilogue of the previous tile"}
+
     def check(self) -> None:
-        for sc in self.scratch:
-            if int(sc["err"].item()) != 0:
-                raise RuntimeError("a pipeline wait ran out inside a MegaMoE GEMM kernel")
+        """Raises when a wait inside the kernel ran out, naming what the CTA was waiting for (the kernel's ``GemmWaitSite``)."""
+        for i, sc in enumerate(self.scratch):
+            code = int(sc["err"].item())
+            if code != 0:
+                raise RuntimeError(f"a wait ran out inside the MegaMoE kernel of local rank {i}: it was waiting for "
+                                   f"{self.WAIT_SITES.get(code, f'site {code}')}")
 
 
 class MegaCpuEngine:

@@ -149,3 +149,17 @@ def test_weight_transform_shapes_and_rules():
     assert g1.fp8 and g2.fp8 and g1.packed.numel() == f1.numel() and (g1.k, g2.k) == (H, I)
     with pytest.raises(ValueError, match="same kind"):
         MM.transform_weights_for_mega_moe((f1, f1_sf), (w2, w2_sf))
+
+
+def test_kernel_failure_report_names_the_wait():
+    """``MegaEngine.check`` turns the kernel's error word (which wait ran out) into a message; zero means no failure."""
+    eng = object.__new__(MM.MegaEngine)
+    eng.scratch = [dict(err=torch.zeros(1, dtype=torch.int32)), dict(err=torch.zeros(1, dtype=torch.int32))]
+    eng.check()
+    eng.scratch[1]["err"][0] = 8
+    with pytest.raises(RuntimeError, match="local rank 1: it was waiting for operands arriving in a stage"):
+        eng.check()
+    eng.scratch[1]["err"][0] = 77
+    with pytest.raises(RuntimeError, match="site 77"):
+        eng.check()
+    assert set(MM.MegaEngine.WAIT_SITES) == set(range(1, 11))
