@@ -22,7 +22,21 @@ import torch
 from ..ops import require_native
 
 STATUS_NAMES = {0: "ok", 1: "timeout", 2: "bad argument", 3: "aborted"}
-OP_NAMES = {0: "barrier", 1: "notify", 2: "dispatch", 3: "combine", 4: "ll_dispatch", 5: "ll_combine", 6: "mega_moe"}
+OP_NAMES = {0: "barrier", 1: "notify", 2: "dispatch", 3: "combine", 4: "ll_dispatch", 5: "ll_combine", 6: "mega_moe",
+            7: "alltoallv_gmm", 8: "gmm_alltoallv"}
+# what a kernel was waiting for at each wait site (operation, site) when its time limit ran out; sites of 100 and above are
+# index checks of the index-checking build
+WAIT_SITES = {
+    (0, 0): "the peer to reach the barrier", (0, 99): "a flag that nothing sets (the wait probe of the tests)",
+    (1, 0): "the peer to finish reading the previous routing tables", (1, 1): "the peer's routing table",
+    (2, 0): "the peer to finish the previous dispatch", (2, 1): "rows of a source rank to land in the staging area",
+    (3, 0): "the peer to finish the previous combine", (3, 1): "the partial sums of an expert rank",
+    (4, 0): "the peer to release the bank used two calls ago", (4, 1): "the peer's routing table", (4, 2): "a part of a row from a source rank",
+    (5, 0): "the peer to release the bank used two calls ago", (5, 1): "a part of an expert's row",
+    (6, 0): "the peer's inputs and routing table", (6, 1): "the peer's combine rows",
+    (7, 0): "the peer to finish the previous call", (7, 1): "the peer's staged rows and row table",
+    (8, 0): "the peer's row table", (8, 1): "the rows returned by the peer",
+}
 
 
 class CommunicationError(RuntimeError):
@@ -221,10 +235,11 @@ class CudaEngine:
         for s in self.sessions:
             st = s.status()
             if st["code"] != 0:
+                what = WAIT_SITES.get((st["op"], st["where"]))
                 raise CommunicationError(
                     f"rank {st['rank']}: {OP_NAMES.get(st['op'], st['op'])} {STATUS_NAMES.get(st['code'], st['code'])} "
-                    f"at wait site {st['where']} on peer {st['peer']} (expected {st['expected']}, saw {st['seen']}); "
-                    "restart the distributed job")
+                    f"at wait site {st['where']}" + (f" ({what})" if what else "") + f" on peer {st['peer']} "
+                    f"(expected {st['expected']}, saw {st['seen']}); restart the distributed job")
 
     def split_blocks(self, total: int, send_fraction: float, default: int = 0) -> Tuple[int, int]:
         """(blocks of the NVLink side, blocks of the local side).  A fraction of 1.0 / 0.0 gives every block to one

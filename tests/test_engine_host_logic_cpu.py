@@ -72,3 +72,24 @@ def test_combine_runs_one_pass_per_token_window():
     assert [(c["begin"], c["end"], c["send"], c["recv"]) for c in calls] == [(0, 1024, 40, 24)] and out[0][1].shape == (0, 8)
     with pytest.raises(ValueError, match="must not exceed 148"):
         eng.combine([x], [plan_for(4, 8)], [None], split=(100, 60))
+
+
+def test_status_block_becomes_a_readable_error():
+    class Session:
+        def __init__(self, **status):
+            self._status = dict(code=0, op=0, rank=0, peer=0, where=0, expected=0, seen=0, **status) if not status else status
+
+        def status(self):
+            return self._status
+
+    eng = object.__new__(EC.CudaEngine)
+    eng.sessions = [Session()]
+    eng.check_status()                                                     # code 0: nothing to report
+    eng.sessions = [Session(), Session(code=1, op=3, rank=5, peer=2, where=1, expected=7, seen=6)]
+    with pytest.raises(EC.CommunicationError, match=r"rank 5: combine timeout at wait site 1 \(the partial sums of an expert rank\) on "
+                                                     r"peer 2 \(expected 7, saw 6\); restart"):
+        eng.check_status()
+    eng.sessions = [Session(code=2, op=2, rank=0, peer=-1, where=103, expected=10, seen=12)]
+    with pytest.raises(EC.CommunicationError, match=r"dispatch bad argument at wait site 103 on peer -1"):
+        eng.check_status()
+    assert all(op in EC.OP_NAMES for op, _ in EC.WAIT_SITES)
