@@ -11,7 +11,7 @@ Internode and the V1 low-latency entry points belong to multi-node RDMA deployme
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 

@@ -19,7 +19,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 import os
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 

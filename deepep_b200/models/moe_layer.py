@@ -6,7 +6,6 @@ The reference documents the rule (``README.md:168-219``, ``docs/elastic.md:7-17`
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

@@ -22,7 +22,7 @@ Ordering and value rules (parity: ``tests/utils/reference.py:39-73`` dispatch,
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple, Union
 
 import torch

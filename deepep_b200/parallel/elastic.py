@@ -15,7 +15,7 @@ domain.  Work is issued on the buffer's private communication stream; see
 """
 from __future__ import annotations
 
-from typing import Any, List, Optional, Sequence, Tuple, Union
+from typing import Any, List, Optional, Sequence, Tuple
 
 import torch
 

@@ -13,7 +13,7 @@ single host synchronisation of a fresh dispatch
 from __future__ import annotations
 
 import contextlib
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 import os
 from typing import List, Optional, Sequence, Tuple
 

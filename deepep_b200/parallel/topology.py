@@ -12,7 +12,7 @@ from __future__ import annotations
 import os
 import socket
 from dataclasses import asdict, dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import torch
 

@@ -10,8 +10,6 @@ one cooperative launch guarantees that all of them are resident.)
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
-
 import torch
 
 from ..ops import require_native

@@ -13,7 +13,7 @@ Everything here is tensor arithmetic in float64, so the numbers are those of the
 from __future__ import annotations
 
 import math
-from typing import Dict, Sequence, Tuple
+from typing import Dict, Sequence
 
 import torch
 

@@ -11,7 +11,7 @@ import json
 import os
 import time
 from dataclasses import asdict, dataclass, fields
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, Sequence, Tuple
 
 import torch
 

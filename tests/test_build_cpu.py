@@ -7,8 +7,6 @@ import json
 import os
 from pathlib import Path
 
-import pytest
-
 from deepep_b200 import _build as B
 
 REPO = Path(__file__).resolve().parent.parent
