@@ -88,3 +88,43 @@ def test_no_file_names_a_closed_call_or_a_multicast_load():
             if bulk in line and multi in line:
                 bad.append((str(path.relative_to(REPO)), f"line {number}: bulk load with cluster multicast"))
     assert not bad, bad
+
+
+def test_no_python_module_uses_a_name_it_never_binds():
+    """A misspelt or forgotten import only fails when its line runs, which for GPU-only paths is on a GPU: every name a
+    module loads must be bound somewhere in it (assignment, definition, import, parameter) or be a builtin."""
+    import ast
+    import builtins
+
+    known = set(dir(builtins)) | {"__file__", "__name__", "__doc__"}
+    bad = {}
+    for path in _text_files():
+        if path.suffix != ".py":
+            continue
+        tree = ast.parse(path.read_text())
+        bound, loaded, star = set(), {}, False
+        for node in ast.walk(tree):
+            if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.ClassDef)):
+                bound.add(node.name)
+            if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.Lambda)):
+                args = node.args
+                bound |= {a.arg for a in args.args + args.kwonlyargs + args.posonlyargs}
+                bound |= {a.arg for a in (args.vararg, args.kwarg) if a is not None}
+            elif isinstance(node, ast.Import):
+                bound |= {(a.asname or a.name).split(".")[0] for a in node.names}
+            elif isinstance(node, ast.ImportFrom):
+                star = star or any(a.name == "*" for a in node.names)
+                bound |= {a.asname or a.name for a in node.names}
+            elif isinstance(node, ast.Name):
+                if isinstance(node.ctx, ast.Load):
+                    loaded.setdefault(node.id, node.lineno)
+                else:
+                    bound.add(node.id)
+            elif isinstance(node, ast.ExceptHandler) and node.name:
+                bound.add(node.name)
+            elif isinstance(node, (ast.Global, ast.Nonlocal)):
+                bound |= set(node.names)
+        unbound = {name: line for name, line in loaded.items() if name not in bound and name not in known}
+        if unbound and not star:
+            bad[str(path.relative_to(REPO))] = unbound
+    assert not bad, bad
