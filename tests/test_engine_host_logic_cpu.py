@@ -93,3 +93,44 @@ def test_status_block_becomes_a_readable_error():
     with pytest.raises(EC.CommunicationError, match=r"dispatch bad argument at wait site 103 on peer -1"):
         eng.check_status()
     assert all(op in EC.OP_NAMES for op, _ in EC.WAIT_SITES)
+
+
+def test_argument_keys_agree_between_python_and_the_bindings():
+    """The engine hands every kernel its arguments as a dict; the bindings read the keys they know and treat a missing one
+    as null / zero.  A misspelt key would therefore go unnoticed until a kernel dereferences the null: the two key sets
+    must be equal for every operation."""
+    import ast
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def cpp_keys(path, func):
+        src = open(os.path.join(root, "deepep_b200", "csrc", path)).read()
+        start = src.index("{", src.index(func + "("))
+        depth, at = 0, start
+        while True:
+            depth += {"{": 1, "}": -1}.get(src[at], 0)
+            if depth == 0:
+                break
+            at += 1
+        body = src[start:at]
+        return set(re.findall(r'\(d, "([A-Za-z0-9_]+)"', body)) | set(re.findall(r'd\["([A-Za-z0-9_]+)"\]', body))
+
+    tree = ast.parse(open(os.path.join(root, "deepep_b200", "parallel", "engine_cuda.py")).read())
+    methods = {f.name: f for n in ast.walk(tree) if isinstance(n, ast.ClassDef) and n.name == "CudaEngine"
+               for f in n.body if isinstance(f, ast.FunctionDef)}
+
+    def py_keys(method):
+        keys = set()
+        for call in ast.walk(methods[method]):
+            if isinstance(call, ast.Call) and getattr(call.func, "attr", None) == "append" and call.args \
+                    and isinstance(call.args[0], ast.Call) and getattr(call.args[0].func, "id", None) == "dict":
+                keys |= {k.arg for k in call.args[0].keywords}
+        return keys
+
+    for func, path, method in (("op_notify", "bindings.cpp", "notify"), ("op_dispatch", "bindings.cpp", "dispatch"),
+                               ("op_combine", "bindings.cpp", "combine"), ("op_ll_dispatch", "ll_bindings.cpp", "ll_dispatch"),
+                               ("op_ll_combine", "ll_bindings.cpp", "ll_combine")):
+        native, python = cpp_keys(path, func), py_keys(method)
+        assert python and native == python, (func, sorted(python - native), sorted(native - python))
