@@ -45,6 +45,7 @@ class CpuPlan:
     low_latency: bool = False
     rank_matrix: Optional[torch.Tensor] = None
     send_chunk_prefix: Optional[torch.Tensor] = None
+    exact_rows: int = 0                 # rows that carry data; ``num_rows`` is larger when the counts were not read back
 
     def tensors(self):
         return [t for t in (self.topk_idx, self.expert_counts, self.expert_offsets, self.recv_row_src, self.recv_w,
@@ -66,7 +67,7 @@ class CpuEngine:
     def notify(self, topk_idx: Sequence[torch.Tensor], topk_w: Sequence[Optional[torch.Tensor]], num_experts: int,
                expand: bool = True, alignment: int = 1, cpu_sync: bool = True, blocks: int = 0, stream=None,
                rank_matrix: bool = False) -> List[CpuPlan]:
-        del cpu_sync, blocks, stream
+        del blocks, stream
         idx = topk_idx[0].cpu().long()
         w = None if topk_w[0] is None else topk_w[0].cpu().float()
         gathered = self._gather((idx, w))
@@ -89,6 +90,21 @@ class CpuEngine:
                        lay.expert_counts.tolist(), topk_idx[0], layouts, [i.shape[0] for i in all_idx], all_idx, all_w,
                        lay.expert_counts.int(), lay.expert_offsets.int(), rank_rows, src, recv_w,
                        lay.recv_topk_idx, has_weights=all_w is not None)
+        plan.exact_rows = lay.num_rows
+        if not cpu_sync:
+            # No read-back of the counts: like the CUDA engine, hand out the worst-case number of rows (the rows past the
+            # real count carry no data) and no per-expert list.
+            local = num_experts // self.world
+            capacity = self.world * self.max_tokens * (min(k, local) if expand else 1)
+            if expand and alignment > 1:
+                capacity += local * (alignment - 1)
+            extra = capacity - lay.num_rows
+            plan.num_rows, plan.expert_counts_list = capacity, None
+            plan.recv_row_src = torch.cat([src, torch.full((extra,), -1, dtype=torch.int32)])
+            if plan.recv_w is not None:
+                plan.recv_w = torch.cat([plan.recv_w, plan.recv_w.new_zeros((extra,) + tuple(plan.recv_w.shape[1:]))])
+            if plan.recv_idx is not None:
+                plan.recv_idx = torch.cat([plan.recv_idx, plan.recv_idx.new_full((extra, k), -1)])
         if rank_matrix:     # what the V1 handle is built from (the CUDA engine gets these from the layout kernel)
             local, chunk = num_experts // self.world, 64
             hits = []
@@ -126,13 +142,19 @@ class CpuEngine:
         outs, _ = R.dispatch(all_x, plan.all_idx, None, plan.num_experts, do_expand=plan.expand,
                              quantize_fp8=(mode == 2), layouts=plan.layouts)
         out = outs[self.rank][0]
-        return [(out[0], out[1]) if isinstance(out, tuple) else (out, None)]
+        data, sf = (out[0], out[1]) if isinstance(out, tuple) else (out, None)
+        extra = plan.num_rows - data.shape[0]
+        if extra > 0:           # worst-case outputs: rows past the real count are zero
+            data = torch.cat([data, data.new_zeros((extra, data.shape[1]))])
+            sf = None if sf is None else torch.cat([sf, sf.new_zeros((extra, sf.shape[1]))])
+        return [(data, sf)]
 
     def combine(self, xs: Sequence[torch.Tensor], plans: Sequence[CpuPlan], ws: Sequence[Optional[torch.Tensor]],
                 bias: Sequence = None, blocks: int = 0, stream=None):
         del blocks, stream
         plan = plans[0]
-        gathered = self._gather((xs[0].cpu(), None if ws[0] is None else ws[0].cpu().float(),
+        rows = plan.exact_rows or plan.num_rows
+        gathered = self._gather((xs[0].cpu()[:rows], None if ws[0] is None else ws[0].cpu().float()[:rows],
                                  None if bias is None else bias[0]))
         all_x = [g[0] for g in gathered]
         all_w = None if any(g[1] is None for g in gathered) else [g[1] for g in gathered]
@@ -142,7 +164,7 @@ class CpuEngine:
 
     def ll_combine(self, xs: Sequence[torch.Tensor], plans: Sequence[CpuPlan], stream=None):
         plan = plans[0]
-        all_x = self._gather(xs[0].cpu())
+        all_x = self._gather(xs[0].cpu()[:plan.exact_rows or plan.num_rows])
         return [R.low_latency_combine(all_x, plan.layouts, plan.all_w, plan.all_tokens)[self.rank]]
 
     def barrier(self, stream=None) -> None:

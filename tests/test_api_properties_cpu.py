@@ -2,6 +2,7 @@
 engine): whatever the layout, the alignment or the path, a round trip through identity experts returns ``x`` times
 the number of rows the token was sent as, the handle's counts describe the rows, cached dispatches repeat the
 fresh one, and the weights channel returns what was sent.  Small integers keep every sum exact in bf16."""
+import pytest
 import torch
 from hypothesis import given, settings, strategies as st
 
@@ -66,5 +67,36 @@ def test_round_trip_properties(case):
                 assert torch.equal(out_w, torch.where(idx >= 0, w, torch.zeros_like(w)))
             else:
                 assert out_w is None
+    finally:
+        buf.destroy()
+
+
+@settings(max_examples=40, deadline=None, derandomize=True)
+@given(calls())
+def test_outputs_without_a_read_back_of_the_counts(case):
+    """``do_cpu_sync=False``: nothing is read back, so outputs have the worst-case number of rows; the first rows are those
+    of the synchronous call, the rest carries no data, the handle has no per-expert list, and combine takes the rows as
+    they came and returns the same result."""
+    experts, topk, hidden, cap, idx, x, w, expand, align, with_weights = case
+    if not expand:
+        align = 1
+    buf = deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=cap, hidden=hidden, num_topk=topk, explicitly_destroy=True, device="cpu")
+    try:
+        kwargs = dict(topk_idx=idx, topk_weights=w if with_weights else None, num_experts=experts, do_expand=expand,
+                      expert_alignment=align if align > 1 else None)
+        rx, ridx, rw, handle, _ = buf.dispatch(x, **kwargs)
+        fx, fidx, fw, fixed, _ = buf.dispatch(x, do_cpu_sync=False, **kwargs)
+        expanded = expand or fixed.is_low_latency
+        worst = cap * (min(topk, experts) if expanded else 1) + (experts * (align - 1) if align > 1 else 0)
+        exact = rx.shape[0]
+        assert fx.shape[0] == worst >= exact and fixed.num_recv_tokens_per_expert_list is None
+        assert torch.equal(fx[:exact], rx) and not fx[exact:].any()
+        assert (fw is None) == (rw is None) and (fw is None or (fw.shape[0] == worst and torch.equal(fw[:exact], rw)))
+        assert (fidx is None) == (ridx is None) and (fidx is None or torch.equal(fidx[:exact], ridx))
+        out, out_w, _ = buf.combine(rx, handle, topk_weights=None if handle.is_low_latency else rw)
+        out2, out_w2, _ = buf.combine(fx, fixed, topk_weights=None if fixed.is_low_latency else fw)
+        assert torch.equal(out, out2) and (out_w is None) == (out_w2 is None) and (out_w is None or torch.equal(out_w, out_w2))
+        with pytest.raises(ValueError, match="rows"):
+            buf.combine(fx[:exact] if exact != worst else fx[:-1], fixed)
     finally:
         buf.destroy()

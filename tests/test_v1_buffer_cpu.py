@@ -59,6 +59,13 @@ def test_layout_dispatch_combine_and_stale_handles():
         buf.combine(rx, last)
     with pytest.raises(ValueError, match="num_worst_tokens"):
         buf.dispatch(x, topk_idx=idx, num_tokens_per_expert=per_expert, num_worst_tokens=5)
+    # fixed-size outputs: group size x num_max_tokens_per_rank rows, no per-expert list, the same rows first
+    fx, fidx, fw, fcounts, fhandle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_expert=per_expert,
+                                                     num_worst_tokens=128)
+    assert fx.shape[0] == 128 and fcounts == [] and torch.equal(fx[:rx.shape[0]], rx) and not fx[rx.shape[0]:].any()
+    assert torch.equal(fidx[:rx.shape[0]], ridx) and bool((fidx[rx.shape[0]:] == -1).all())
+    fout, _, _ = buf.combine(fx, fhandle, topk_weights=fw)
+    assert torch.equal(fout, out)
     with pytest.raises(TypeError, match="zero_copy"):
         buf.dispatch(x, topk_idx=idx, num_tokens_per_expert=per_expert, zero_copy=1)
     zc = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_expert=per_expert, zero_copy=True)[0]
