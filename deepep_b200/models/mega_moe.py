@@ -284,8 +284,8 @@ class SymmBuffer:
                  world_size: Optional[int] = None, device=None, num_gpu_timeout_secs: float = 100, num_sms: int = 0):
         """``group``: a process group, a ``StoreGroup``, or ``None`` (one process, or ``rank=`` / ``world_size=`` over the
         launcher's TCPStore).  ``ranks_per_node`` is accepted for the reference's signature (``api.py:70-84``; all ranks
-        share one NVLink domain here); ``timeout`` (seconds), when given, is the limit of the waits inside the kernel
-        (otherwise ``num_gpu_timeout_secs``)."""
+        share one NVLink domain here); ``timeout`` (seconds), when given, is the limit of the host-side waits of the
+        set-up and of the waits inside the kernel (otherwise 300 s and ``num_gpu_timeout_secs``)."""
         del ranks_per_node
         if timeout is not None:
             num_gpu_timeout_secs = float(timeout)
@@ -295,7 +295,7 @@ class SymmBuffer:
             raise NotImplementedError("only SwiGLU is implemented")
         from ..parallel.runtime import ControlPlane, Runtime
 
-        self.control = ControlPlane(group, rank, world_size)
+        self.control = ControlPlane(group, rank, world_size, timeout=300.0 if timeout is None else float(timeout))
         self.rank, self.world_size = self.control.rank, self.control.size
         self.num_experts, self.num_topk, self.hidden, self.intermediate_hidden = num_experts, num_topk, hidden, intermediate_hidden
         self.num_max_tokens_per_rank = num_max_tokens_per_rank

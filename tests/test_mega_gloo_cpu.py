@@ -29,7 +29,7 @@ def _worker(rank, port, results):
         mine = slice(rank * L, (rank + 1) * L)
         w1, w2 = transform_weights_for_mega_moe((l1[0][mine], l1[1][mine]), (l2[0][mine], l2[1][mine]))
         # the ranks meet through the launcher's TCPStore only (no process group), as the reference's MegaMoE does
-        sym = SymmBuffer(None, E, 16, K, H, I, rank=rank, world_size=WORLD)
+        sym = SymmBuffer(None, E, 16, K, H, I, rank=rank, world_size=WORLD, timeout=60)
         checks["cpu_engine"] = sym.device.type == "cpu" and sym.runtime is None and (sym.rank, sym.world_size) == (rank, WORLD)
         bs = TOKENS[rank]
         sym.load_inputs(xs[rank][0], xs[rank][1], idx[rank], ws[rank])
@@ -56,7 +56,7 @@ def _worker(rank, port, results):
         # one shared expert per rank (each rank its own weights): every local token passes through it with weight one
         s1, s2 = O.make_weights(1, H, I, 50 + rank)
         sw1, sw2 = transform_weights_for_mega_moe(s1, s2)
-        sym = SymmBuffer(None, E, 16, K, H, I, num_shared_experts=1, rank=rank, world_size=WORLD)
+        sym = SymmBuffer(None, E, 16, K, H, I, num_shared_experts=1, rank=rank, world_size=WORLD, timeout=60)
         sym.load_inputs(xs[rank][0], xs[rank][1], idx[rank], ws[rank])
         fp8_fp4_mega_moe(y, w1, w2, sym, sw1, sw2)
         alone = O.mega_moe_reference([xs[rank]], [idx[rank]], [ws[rank]], l1, l2, E, s1, s2)[0]
@@ -117,7 +117,7 @@ def _readme_worker(rank, port, results):
     shared_l1_weights, shared_l2_weights = O.make_weights(1, H, I, 70 + rank)
     x_fp8, x_sf, topk_idx, topk_weights = xs[rank][0], xs[rank][1], idx[rank].to(torch.int32), ws[rank]
     ok = False
-    group = StoreGroup.from_env()
+    group = StoreGroup.from_env(timeout=60)
     try:
         buffer = SymmBuffer(
             group, num_experts=E, num_max_tokens_per_rank=16,

@@ -36,7 +36,8 @@ def _worker(rank, port, results):
         ref, lays = R.dispatch(xs, idx, ws, E, do_expand=True)
         cref = R.combine([r[0] for r in ref], lays, T, K)
         buf = deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=32, hidden=H, num_topk=K, explicitly_destroy=True,
-                                    rank=rank, world_size=WORLD, bootstrap="store", device="cpu", debug_collectives=True)
+                                    rank=rank, world_size=WORLD, bootstrap="store", device="cpu", debug_collectives=True,
+                                    num_cpu_timeout_secs=60)
         checks["backend"] = buf.control.backend() == "store" and (buf.rank, buf.world_size) == (rank, WORLD)
         checks["machine"] = buf.machine_type == "cpu"
         rx, _, rw, handle, _ = buf.dispatch(xs[rank], topk_idx=idx[rank], topk_weights=ws[rank], num_experts=E, do_expand=True)
