@@ -26,7 +26,7 @@ def _routes(tokens, experts, topk, seed):
 
 def _worker(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=120))
     import deepep_b200 as deep_ep
 
     T, H, E, K = 128, 512, 16, 4

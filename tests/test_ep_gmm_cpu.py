@@ -24,7 +24,7 @@ def test_restatements_are_inverse_layouts():
 
 def _worker(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=120))
     try:
         E, K, N = 4, 64, 128
         counts = [[3, 0, 2, 5], [1, 4, 0, 2]]

@@ -23,7 +23,7 @@ def _free_port():
 
 def _worker(rank, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD, timeout=__import__("datetime").timedelta(seconds=120))
     from deepep_b200 import ElasticBuffer
 
     buf = ElasticBuffer(dist.group.WORLD, num_max_tokens_per_rank=128, hidden=H, num_topk=K, explicitly_destroy=True)

@@ -32,7 +32,7 @@ def _inputs(mode, seed):
 
 def _worker(rank, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD, timeout=__import__("datetime").timedelta(seconds=120))
     from deepep_b200 import ElasticBuffer
     from deepep_b200.utils.math import per_token_cast_to_fp8
 

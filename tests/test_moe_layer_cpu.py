@@ -46,7 +46,7 @@ def _dense_reference(xs, idxs, ws, w1, w2, grads):
 
 def _worker(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=120))
     from deepep_b200 import ElasticBuffer
     from deepep_b200.models.moe_layer import ExpertParallelMoE
 

@@ -149,7 +149,7 @@ class _Layout:
 
 def _rank_main(rank, world, port, transport, fault, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), DEEPEP_TRANSPORT=transport)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=120))
     from deepep_b200.ops import load_native
     from deepep_b200.parallel.runtime import ControlPlane, Runtime
 

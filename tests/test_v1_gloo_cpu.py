@@ -22,7 +22,7 @@ def _free_port():
 
 def _worker(rank, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD, timeout=__import__("datetime").timedelta(seconds=120))
     import deepep_b200 as deep_ep
 
     xs = [torch.randn((t, H), generator=torch.Generator().manual_seed(r)).bfloat16() for r, t in enumerate(TOKENS)]

@@ -17,7 +17,7 @@ def _free_port():
 
 def _worker(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=120))
     import deepep_b200 as deep_ep
     from deepep_b200.utils import verify as V
 
