@@ -128,3 +128,16 @@ def test_no_python_module_uses_a_name_it_never_binds():
         if unbound and not star:
             bad[str(path.relative_to(REPO))] = unbound
     assert not bad, bad
+
+
+def test_package_metadata_agrees():
+    import re
+
+    import deepep_b200
+
+    declared = re.search(r'^version = "([^"]+)"', (REPO / "pyproject.toml").read_text(), re.M).group(1)
+    assert deepep_b200.__version__ == declared
+    listed = re.search(r"^packages = \[(.*?)\]", (REPO / "pyproject.toml").read_text(), re.M | re.S).group(1)
+    for package in ("deepep_b200", "deepep_b200.models", "deepep_b200.ops", "deepep_b200.oracle", "deepep_b200.parallel",
+                    "deepep_b200.utils", "deep_ep", "deep_ep_experimental"):
+        assert f'"{package}"' in listed and (REPO / package.replace(".", "/") / "__init__.py").exists()
