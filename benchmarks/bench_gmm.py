@@ -149,6 +149,8 @@ def distributed(args):
 
 
 if __name__ == "__main__":
+    if not torch.cuda.is_available():
+        raise SystemExit("this benchmark drives the CUDA kernels and needs a GPU; bench_ep.py and bench_mega_config.py also run on the CPU engine")
     ap = argparse.ArgumentParser()
     ap.add_argument("--world", type=int, default=1, help="virtual ranks on one GPU (ignored under torchrun)")
     ap.add_argument("--rows", type=int, default=32768, help="rows per rank (tokens x top-k)")

@@ -18,6 +18,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def main():
+    if not torch.cuda.is_available():
+        raise SystemExit("this benchmark drives the CUDA kernels and needs a GPU; bench_ep.py and bench_mega_config.py also run on the CPU engine")
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=128)
     ap.add_argument("--hidden", type=int, default=7168)

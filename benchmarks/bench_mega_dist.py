@@ -16,6 +16,8 @@ sys.path.insert(0, ROOT)
 
 
 def main():
+    if not torch.cuda.is_available():
+        raise SystemExit("this benchmark drives the CUDA kernels and needs a GPU; bench_ep.py and bench_mega_config.py also run on the CPU engine")
     import bench
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
