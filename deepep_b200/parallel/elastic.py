@@ -68,14 +68,19 @@ class EPHandle:
         self._saved_weights = None         # low-latency: source weights applied by combine
         self._snapshots: Tuple = ()
 
+    @staticmethod
+    def _stamp(t: torch.Tensor):
+        # inference tensors (created under torch.inference_mode) keep no version counter: only their storage is compared
+        return t.data_ptr(), (None if t.is_inference() else t._version)
+
     def _snapshot(self) -> None:
-        self._snapshots = tuple((t.data_ptr(), t._version) for t in self._tracked())
+        self._snapshots = tuple(self._stamp(t) for t in self._tracked())
 
     def _tracked(self) -> List[torch.Tensor]:
         return [] if self._plan is None else list(self._plan.tensors())
 
     def _check_unchanged(self) -> None:
-        now = tuple((t.data_ptr(), t._version) for t in self._tracked())
+        now = tuple(self._stamp(t) for t in self._tracked())
         if now != self._snapshots:
             raise RuntimeError("handle metadata (or its topk_idx) was modified in place after dispatch")
 
@@ -364,7 +369,7 @@ class ElasticBuffer:
 
         Returns ``(recv_x | (recv_x, recv_x_sf), recv_topk_idx, recv_topk_weights, handle, event)``.
         """
-        del num_qps, do_handle_copy
+        del num_qps
         self._alive()
         x_data, x_sf = (x if isinstance(x, (tuple, list)) else (x, None))
         self._validate_x(x_data, x_sf)
@@ -393,6 +398,12 @@ class ElasticBuffer:
                                      alignment, mode, low_latency, cpu_sync))
         comm = self._enter(previous_event, previous_event_before_epilogue)
         allocate_on_comm_stream = self._allocates_on_comm(allocate_on_comm_stream, previous_event, previous_event_before_epilogue)
+        if do_handle_copy and topk_idx.is_inference():
+            # The handle watches ordinary tensors for in-place changes through their version counters.  An inference tensor
+            # (torch.inference_mode) has none, so the handle keeps a copy of its own instead; do_handle_copy=False leaves
+            # it to the caller to keep the indices unchanged while the handle lives.
+            with self._on(comm):
+                topk_idx = topk_idx.clone()
         try:
             with self._on(comm if allocate_on_comm_stream else None):
                 if low_latency and hasattr(self.engine, "ll_dispatch"):

@@ -166,3 +166,37 @@ def test_a_failed_launch_poisons_the_buffer(buf, monkeypatch):
         buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
     with pytest.raises(RuntimeError, match="restart the distributed job"):
         buf.barrier()
+
+
+def test_calls_under_inference_mode(buf):
+    """Serving code runs under ``torch.inference_mode``: tensors made there keep no version counter, so the handle cannot
+    watch them for in-place changes and keeps a copy of the indices instead (``do_handle_copy=True``, the default); with
+    ``do_handle_copy=False`` the caller's tensor is used as it is.  Parity: ``docs/elastic.md`` of the reference
+    ("HT may be called under torch.inference_mode(); an inference tensor as index needs the default do_handle_copy")."""
+    import torch
+
+    with torch.inference_mode():
+        x, idx, w = _inputs()
+        x, idx, w = x.clone(), idx.clone(), w.clone()                       # inference tensors
+        assert idx.is_inference()
+        rx, _, rw, handle, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+        assert handle.topk_idx is not idx and torch.equal(handle.topk_idx, idx)
+        out, _, _ = buf.combine((rx.float() * rw[:, None]).bfloat16(), handle)
+        assert torch.allclose(out.float(), x.float() * w.sum(1, keepdim=True), rtol=0.02, atol=0.03)
+        idx.fill_(-1)                                                       # the caller's tensor is free again
+        again = buf.dispatch(x, handle=handle)[0]
+        assert torch.equal(again, rx)
+        x2, idx2, w2 = _inputs()
+        idx2 = idx2.clone()
+        _, _, _, borrowed, _ = buf.dispatch(x2.clone(), topk_idx=idx2, topk_weights=w2.clone(), num_experts=E, do_expand=True,
+                                            do_handle_copy=False)
+        assert borrowed.topk_idx is idx2
+        rr, ridx, _, h3, _ = buf.dispatch(x2.clone(), topk_idx=idx2, num_experts=E)       # rank layout
+        assert torch.equal(buf.combine(rr, h3)[0].float(), x2.float())
+    # outside inference mode nothing is copied and changes are detected as before
+    x, idx, w = _inputs()
+    _, _, _, watched, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+    assert watched.topk_idx is idx
+    idx[0, 0] = idx[0, 0]
+    with pytest.raises(RuntimeError, match="modified in place"):
+        buf.dispatch(x, handle=watched)

@@ -81,3 +81,34 @@ def test_two_live_buffers_in_one_process():
     out_b2, _, _ = big.combine(rb, hb)                  # the other buffer is unaffected by its neighbour's teardown
     assert bits_equal(out_b2, out_b)
     big.destroy()
+
+
+def test_dispatch_and_combine_under_inference_mode():
+    """The serving configuration: every call under ``torch.inference_mode`` (tensors without version counters), on the
+    high-throughput and on the low-latency path, against the oracle."""
+    import deepep_b200 as deep_ep
+
+    dev = torch.device("cuda")
+    H, E, K = 512, 16, 4
+    big = deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=300, hidden=H, num_topk=K, explicitly_destroy=True)
+    small = deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=64, hidden=H, num_topk=K, explicitly_destroy=True)
+    x = torch.randn((200, H), generator=torch.Generator().manual_seed(21)).bfloat16()
+    idx, w = group_limited_routes(200, E, K, 4, 2, seed=8), make_weights(200, K, 3)
+    ref, lays = R.dispatch([x], [idx], [w], E, do_expand=True)
+    sref, slays = R.dispatch([x[:40]], [idx[:40]], [w[:40]], E, do_expand=True)
+    with torch.inference_mode():
+        xd, idxd, wd = x.to(dev), idx.to(dev), w.to(dev)
+        assert idxd.is_inference()
+        rx, _, rw, handle, _ = big.dispatch(xd, topk_idx=idxd, topk_weights=wd, num_experts=E, do_expand=True)
+        assert handle.topk_idx is not idxd and bits_equal(rx, ref[0][0]) and bits_equal(rw, ref[0][2])
+        out, _, _ = big.combine(rx, handle)
+        assert bits_equal(out, R.combine([ref[0][0]], lays, [200], K)[0][0])
+        idxd.fill_(-1)                                                  # the handle owns a copy of the indices
+        assert bits_equal(big.dispatch(xd, handle=handle)[0], rx)
+        xs, idxs, ws = x[:40].to(dev), idx[:40].to(dev), w[:40].to(dev)
+        rs, _, _, hs, _ = small.dispatch(xs, topk_idx=idxs, topk_weights=ws, num_experts=E)
+        assert hs.is_low_latency and bits_equal(rs, sref[0][0])
+        outs, _, _ = small.combine(rs, hs)
+        assert bits_equal(outs, R.low_latency_combine([sref[0][0]], slays, [w[:40]], [40])[0])
+    small.destroy()
+    big.destroy()
