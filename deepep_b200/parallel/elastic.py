@@ -372,13 +372,19 @@ class ElasticBuffer:
         del num_qps
         self._alive()
         x_data, x_sf = (x if isinstance(x, (tuple, list)) else (x, None))
+        # Scales travel bit for bit, so int32 scales (four ue8m0 exponents per 128 values, the MXFP8 form) are carried as
+        # the fp32 words they occupy and handed back as int32.
+        packed = x_sf is not None and x_sf.dtype == torch.int32
+        if packed:
+            x_sf = x_sf.view(torch.float32)
+            x = (x_data, x_sf)
         self._validate_x(x_data, x_sf)
         tokens = x_data.shape[0]
         if handle is not None:
             if topk_idx is not None or topk_weights is not None:
                 raise ValueError("pass either routing tensors or a handle, not both")
             return self._dispatch_cached(x_data, x_sf, handle, num_sms, previous_event, previous_event_before_epilogue,
-                                         async_with_compute_stream, allocate_on_comm_stream)
+                                         async_with_compute_stream, allocate_on_comm_stream, packed)
         if topk_idx is None or num_experts is None:
             raise ValueError("a fresh dispatch needs topk_idx and num_experts")
         self._validate_routing(topk_idx, topk_weights, tokens, num_experts)
@@ -408,7 +414,7 @@ class ElasticBuffer:
             with self._on(comm if allocate_on_comm_stream else None):
                 if low_latency and hasattr(self.engine, "ll_dispatch"):
                     return self._dispatch_low_latency(x_data, x_sf, topk_idx, topk_weights, num_experts, mode, cpu_sync,
-                                                      comm, async_with_compute_stream, allocate_on_comm_stream)
+                                                      comm, async_with_compute_stream, allocate_on_comm_stream, packed)
                 plan = self.engine.notify([topk_idx], [topk_weights], num_experts, expand=expand, alignment=alignment,
                                           cpu_sync=cpu_sync, stream=comm, **({"rank_matrix": True} if _rank_matrix else {}))[0]
                 recv_x, recv_sf = self.engine.dispatch([x if x_sf is not None else x_data], [plan], mode,
@@ -427,7 +433,7 @@ class ElasticBuffer:
             h._saved_weights = topk_weights
         if recv_sf is not None and use_tma_aligned_col_major_sf:
             recv_sf = _col_major(recv_sf)
-        out_x = recv_x if recv_sf is None else (recv_x, recv_sf)
+        out_x = recv_x if recv_sf is None else (recv_x, recv_sf.view(torch.int32) if packed else recv_sf)
         event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, recv_w, recv_idx, x_data, x_sf, topk_idx,
                                                                topk_weights] + h._tracked(), allocate_on_comm_stream)
         return out_x, recv_idx, recv_w, h, event
@@ -440,7 +446,7 @@ class ElasticBuffer:
                 self.runtime.failed = True
 
     def _dispatch_cached(self, x_data, x_sf, handle: EPHandle, num_sms, previous_event, previous_event_before_epilogue,
-                         async_with_compute_stream, allocate_on_comm_stream=False):
+                         async_with_compute_stream, allocate_on_comm_stream=False, packed=False):
         self._own(handle)
         handle._check_unchanged()
         if x_data.shape[0] != handle._tokens:
@@ -456,20 +462,20 @@ class ElasticBuffer:
             else:
                 recv_x, recv_sf = self.engine.dispatch([x_data if x_sf is None else (x_data, x_sf)], [handle._plan], mode,
                                                        blocks=num_sms or self.num_sms, stream=comm)[0]
-        out_x = recv_x if recv_sf is None else (recv_x, recv_sf)
+        out_x = recv_x if recv_sf is None else (recv_x, recv_sf.view(torch.int32) if packed else recv_sf)
         event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, x_data, x_sf] + handle._tracked(),
                             allocate_on_comm_stream)
         return out_x, None, None, handle, event
 
     def _dispatch_low_latency(self, x_data, x_sf, topk_idx, topk_weights, num_experts, mode, cpu_sync, comm,
-                              async_with_compute_stream, allocated_on_comm=False):
+                              async_with_compute_stream, allocated_on_comm=False, packed=False):
         plan, recv_x, recv_sf = self.engine.ll_dispatch([x_data if x_sf is None else (x_data, x_sf)], [topk_idx],
                                                         [topk_weights], num_experts, mode, cpu_sync=cpu_sync, stream=comm)[0]
         rows = plan.num_rows
         h = self._make_handle(plan, True, num_experts, 1, 0, topk_idx, x_data.shape[0], True)
         h._saved_weights = topk_weights
         recv_w = plan.recv_w[:rows]
-        out_x = recv_x if recv_sf is None else (recv_x, recv_sf)
+        out_x = recv_x if recv_sf is None else (recv_x, recv_sf.view(torch.int32) if packed else recv_sf)
         event = self._leave(comm, async_with_compute_stream, [recv_x, recv_sf, recv_w, x_data, x_sf, topk_idx, topk_weights]
                             + h._tracked(), allocated_on_comm)
         return out_x, None, recv_w, h, event
@@ -576,7 +582,7 @@ class ElasticBuffer:
                 raise ValueError("the fused fp8 dispatch quantises bf16 input")
         else:
             if x_data.dtype != torch.float8_e4m3fn or x_sf.dtype != torch.float32:
-                raise ValueError("the fp8 pair must be (float8_e4m3fn [T, H], float32 [T, H / 128])")
+                raise ValueError("the fp8 pair must be (float8_e4m3fn [T, H], float32 or int32 [T, H / 128])")
             if self.hidden % 128 or tuple(x_sf.shape) != (x_data.shape[0], self.hidden // 128) or not x_sf.is_contiguous():
                 raise ValueError("scales must be contiguous [tokens, hidden / 128]")
 

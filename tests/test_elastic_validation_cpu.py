@@ -200,3 +200,26 @@ def test_calls_under_inference_mode(buf):
     idx[0, 0] = idx[0, 0]
     with pytest.raises(RuntimeError, match="modified in place"):
         buf.dispatch(x, handle=watched)
+
+
+def test_packed_exponent_scales_travel_bit_for_bit(buf):
+    """MXFP8 activations carry four ue8m0 exponents per 128 values packed into an int32 where the fp32 recipe has one
+    fp32 scale.  Dispatch moves scale words without touching them, so it accepts either and returns the kind it got."""
+    import torch
+
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn((20, H), generator=g).to(torch.float8_e4m3fn)
+    exponents = torch.randint(100, 140, (20, H // 128, 4), generator=g, dtype=torch.uint8)
+    exponents[0, 0] = torch.tensor([255, 255, 192, 0], dtype=torch.uint8)          # a NaN pattern if read as fp32: still copied as is
+    sf = exponents.view(torch.int32).view(20, H // 128)
+    _, idx, w = _inputs(20)
+    (rx, rsf), _, _, handle, _ = buf.dispatch((x, sf), topk_idx=idx, topk_weights=w, num_experts=E, do_expand=True)
+    assert rsf.dtype == torch.int32 and rsf.shape == (rx.shape[0], H // 128)
+    token = (handle.recv_src_metadata[:rx.shape[0]].long() // K) % buf.num_max_tokens_per_rank
+    assert torch.equal(rsf, sf[token]) and torch.equal(rx.view(torch.uint8), x.view(torch.uint8)[token])
+    (rx2, rsf2), _, _, _, _ = buf.dispatch((x, sf), handle=handle)
+    assert rsf2.dtype == torch.int32 and torch.equal(rsf2, rsf)
+    (_, cm), _, _, _, _ = buf.dispatch((x, sf), topk_idx=idx, num_experts=E, do_expand=True, use_tma_aligned_col_major_sf=True)
+    assert cm.dtype == torch.int32 and torch.equal(cm, rsf) and cm.stride(0) == 1
+    with pytest.raises(ValueError, match="float32 or int32"):
+        buf.dispatch((x, sf.to(torch.int64)), topk_idx=idx, num_experts=E)
