@@ -392,7 +392,9 @@ class ElasticBuffer:
         low_latency = self._wants_low_latency(handle, topk_weights, tokens, num_max_tokens_per_rank, expert_alignment, stats,
                                               num_sms, do_zero_padding, use_tma_aligned_col_major_sf, do_expand)
         low_latency = low_latency and hasattr(self.engine, "ll_combine")
-        expand = True if low_latency else bool(do_expand)
+        # do_expand=None is the reference's "not given": its fresh dispatch is expanded then (upstream's default, False,
+        # gives the rank layout)
+        expand = True if (low_latency or do_expand is None) else bool(do_expand)
         alignment = 1 if expert_alignment is None else int(expert_alignment)
         if alignment < 1:
             raise ValueError("expert_alignment must be positive")

@@ -223,3 +223,16 @@ def test_packed_exponent_scales_travel_bit_for_bit(buf):
     assert cm.dtype == torch.int32 and torch.equal(cm, rsf) and cm.stride(0) == 1
     with pytest.raises(ValueError, match="float32 or int32"):
         buf.dispatch((x, sf.to(torch.int64)), topk_idx=idx, num_experts=E)
+
+
+def test_do_expand_none_means_the_expanded_layout(buf):
+    """The reference's fresh dispatch is expanded when ``do_expand`` is not given (``None`` there); upstream's default is
+    ``False``.  Both spellings are honoured: the default gives the rank layout, an explicit ``None`` the expanded one."""
+    import torch
+
+    x, idx, w = _inputs()
+    by_default = buf.dispatch(x, topk_idx=idx, num_experts=E)
+    assert by_default[1] is not None and by_default[3].do_expand is False
+    as_reference = buf.dispatch(x, topk_idx=idx, num_experts=E, do_expand=None)
+    explicit = buf.dispatch(x, topk_idx=idx, num_experts=E, do_expand=True)
+    assert as_reference[1] is None and as_reference[3].do_expand is True and torch.equal(as_reference[0], explicit[0])
