@@ -65,6 +65,7 @@ class EPHandle:
         self._buffer_id = None
         self._tokens = 0
         self._hidden = 0
+        self._owner = None                 # the buffer that made the handle
         self._saved_weights = None         # low-latency: source weights applied by combine
         self._snapshots: Tuple = ()
 
@@ -490,6 +491,7 @@ class ElasticBuffer:
                      plan.expert_counts, plan.recv_row_src, getattr(plan, "slot_row", None),
                      getattr(plan, "stage_meta", None), getattr(plan, "chunk_start", None), is_low_latency=low_latency)
         h._plan, h._buffer_id, h._tokens, h._hidden = plan, self._id, tokens, self.hidden
+        h._owner = self      # a live handle keeps its buffer alive (replacing the caller's variable does not end the buffer)
         h._snapshot()
         return h
 

@@ -236,3 +236,28 @@ def test_do_expand_none_means_the_expanded_layout(buf):
     as_reference = buf.dispatch(x, topk_idx=idx, num_experts=E, do_expand=None)
     explicit = buf.dispatch(x, topk_idx=idx, num_experts=E, do_expand=True)
     assert as_reference[1] is None and as_reference[3].do_expand is True and torch.equal(as_reference[0], explicit[0])
+
+
+def test_a_live_handle_keeps_its_buffer():
+    """Replacing the variable that held a buffer does not end the buffer while one of its handles is alive; after an
+    explicit ``destroy`` the handle is refused."""
+    import gc
+    import weakref
+
+    from deepep_b200 import ElasticBuffer
+
+    x, idx, w = _inputs()
+    first = ElasticBuffer(None, num_max_tokens_per_rank=64, hidden=H, num_topk=K, explicitly_destroy=True, device="cpu")
+    rx, _, _, handle, _ = first.dispatch(x, topk_idx=idx, num_experts=E, do_expand=True)
+    watcher = weakref.ref(first)
+    first = ElasticBuffer(None, num_max_tokens_per_rank=128, hidden=H, num_topk=K, explicitly_destroy=True, device="cpu")
+    gc.collect()
+    assert watcher() is not None and handle._owner is watcher()
+    out, _, _ = watcher().combine(rx, handle)                       # the old buffer still serves its handle
+    assert out.shape == x.shape
+    with pytest.raises(ValueError, match="another buffer"):
+        first.combine(rx, handle)
+    watcher().destroy()
+    with pytest.raises(RuntimeError, match="destroyed"):
+        handle._owner.combine(rx, handle)
+    first.destroy()
