@@ -60,6 +60,15 @@ class Buffer:
             raise ValueError("this Buffer was created for another (tokens, hidden, top-k) shape")
         return eb
 
+    @property
+    def machine_type(self) -> Optional[str]:
+        """What the ranks run on (``None`` until the workspace exists); see ``ElasticBuffer.machine_type``."""
+        return None if self._elastic is None else self._elastic.machine_type
+
+    @property
+    def machine_selection(self) -> Optional[dict]:
+        return None if self._elastic is None else self._elastic.machine_selection
+
     # ------------------------------------------------------------------ resources
     def destroy(self) -> None:
         if self._elastic is not None:

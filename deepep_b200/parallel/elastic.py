@@ -166,7 +166,7 @@ class ElasticBuffer:
         cuda_device = None
         if self.on_cuda:
             cuda_device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self.machine_type = topology.agree(self.control, cuda_device, machine_type)
+        self.machine_type, self.machine_selection = topology.agree(self.control, cuda_device, machine_type, details=True)
         if self.on_cuda:
             from ..ops import require_native
             from .engine_cuda import CudaEngine

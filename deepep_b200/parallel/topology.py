@@ -100,12 +100,19 @@ def check_consensus(machines: Sequence[RankMachine], machine_type: Optional[str]
     return kind
 
 
-def agree(control, device: Optional[torch.device], machine_type: Optional[str] = "auto") -> str:
+def agree(control, device: Optional[torch.device], machine_type: Optional[str] = "auto", details: bool = False):
     """Collective: every rank detects its machine, all ranks exchange the findings and apply the same rules, so all of
-    them return the same kind or raise the same error."""
+    them return the same kind or raise the same error.  ``details=True`` returns ``(kind, selection)`` where
+    ``selection`` records what was asked for, what was found and every rank's report (the reference's
+    ``buffer.machine_selection``)."""
     mine = detect(control.rank, device)
-    reports = [RankMachine(**r) for r in control.all_gather_object(asdict(mine))]
-    return check_consensus(reports, machine_type)
+    gathered = control.all_gather_object(asdict(mine))
+    reports = [RankMachine(**r) for r in gathered]
+    kind = check_consensus(reports, machine_type)
+    if not details:
+        return kind
+    return kind, {"machine_type": kind, "requested": machine_type or "auto", "source": "detected and agreed by all ranks",
+                  "ranks": [dict(r) for r in gathered]}
 
 
 def main(argv: Optional[Sequence[str]] = None) -> int:

@@ -81,3 +81,22 @@ def test_probe_command_reports_and_decides(capsys, monkeypatch):
     out = json.loads(capsys.readouterr().out)
     assert not out["ok"] and "same GPU" in out["error"]
     assert TP.main([]) == 0 and json.loads(capsys.readouterr().out)["machine_type"] == "single"
+
+
+def test_buffers_report_their_machine_selection():
+    """``buffer.machine_type`` / ``buffer.machine_selection`` (the reference prints both after construction): what was asked
+    for, what all ranks agreed on, and every rank's report."""
+    import deepep_b200 as deep_ep
+
+    buf = deep_ep.ElasticBuffer(None, num_max_tokens_per_rank=8, hidden=64, num_topk=2, device="cpu", machine_type="cpu")
+    try:
+        sel = buf.machine_selection
+        assert buf.machine_type == "cpu" == sel["machine_type"] and sel["requested"] == "cpu"
+        assert [r["rank"] for r in sel["ranks"]] == [0] and sel["ranks"][0]["kind"] == "cpu"
+    finally:
+        buf.destroy()
+    lazy = deep_ep.Buffer(None)
+    assert lazy.machine_type is None and lazy.machine_selection is None        # no workspace yet
+    sized = deep_ep.Buffer(None, num_max_tokens_per_rank=8, hidden=64, num_topk=2)
+    assert sized.machine_type == "cpu" and sized.machine_selection["machine_type"] == "cpu"
+    sized.destroy()
