@@ -466,9 +466,11 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: MegaWeights, l2_weights: MegaW
 def mega_moe(x, topk_idx: torch.Tensor, topk_weights: torch.Tensor, l1_weights: MegaWeights,
              l2_weights: MegaWeights, sym_buffer: SymmBuffer, *, shared_l1_weights: Optional[MegaWeights] = None,
              shared_l2_weights: Optional[MegaWeights] = None, out: Optional[torch.Tensor] = None,
-             timer: Optional[torch.Tensor] = None) -> torch.Tensor:
+             timer: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Explicit-input convenience API (parity: ``mega_moe``, ``api.py:380-412``): ``x`` is bf16 ``[bs, hidden]`` (quantised
-    to MXFP8 here) or an ``(e4m3, ue8m0)`` pair that is copied as is; fills the symmetric inputs and runs the fused forward."""
+    to MXFP8 here) or an ``(e4m3, ue8m0)`` pair that is copied as is; fills the symmetric inputs and runs the fused forward.
+    Returns ``(y, per_call_counts)`` as the reference does: the output and, int32 ``[experts per rank]``, the rows every
+    routed local expert received in this call."""
     if isinstance(x, (tuple, list)):
         codes, sf = x
     else:
@@ -479,8 +481,9 @@ def mega_moe(x, topk_idx: torch.Tensor, topk_weights: torch.Tensor, l1_weights: 
     sym_buffer.topk_idx[:bs].copy_(topk_idx.to(torch.int32))
     sym_buffer.topk_weights[:bs].copy_(topk_weights.float())
     y = torch.empty((bs, sym_buffer.hidden), dtype=torch.bfloat16, device=codes.device) if out is None else out
-    fp8_fp4_mega_moe(y, l1_weights, l2_weights, sym_buffer.prepare(bs), shared_l1_weights, shared_l2_weights, timer=timer)
-    return y
+    counts = torch.zeros(sym_buffer.num_experts // sym_buffer.world_size, dtype=torch.int32, device=y.device)
+    fp8_fp4_mega_moe(y, l1_weights, l2_weights, sym_buffer.prepare(bs), shared_l1_weights, shared_l2_weights, counts, timer=timer)
+    return y, counts
 
 
 def quantize_mxfp8_cuda(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

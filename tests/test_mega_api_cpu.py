@@ -149,6 +149,11 @@ def test_weight_transform_shapes_and_rules():
     assert g1.fp8 and g2.fp8 and g1.packed.numel() == f1.numel() and (g1.k, g2.k) == (H, I)
     with pytest.raises(ValueError, match="same kind"):
         MM.transform_weights_for_mega_moe((f1, f1_sf), (w2, w2_sf))
+    # the reference documents the scales as [L, N, K / 64, 2]: the same bytes, accepted as they are
+    r1, r2 = MM.transform_weights_for_mega_moe((w1, w1_sf.view(E, 2 * I, H // 64, 2)), (w2, w2_sf.view(E, H, I // 64, 2)), shared=True)
+    assert torch.equal(r1.sf_chunks, l1.sf_chunks) and torch.equal(r2.sf_chunks, l2.sf_chunks) and torch.equal(r1.packed, l1.packed)
+    with pytest.raises(NotImplementedError, match="SwiGLU"):
+        MM.transform_weights_for_mega_moe((w1, w1_sf), (w2, w2_sf), "gelu")
 
 
 def test_kernel_failure_report_names_the_wait():

@@ -48,8 +48,9 @@ def _worker(rank, port, results):
         fp8_fp4_mega_moe(y2, w1, w2, sym, x=xb)
         requant = [O.quantize_mxfp8(O.dequantize_mxfp8(*x).bfloat16()) for x in xs]
         want = O.mega_moe_reference(requant, idx, ws, l1, l2, E)[rank]
-        y3 = mega_moe(xb, idx[rank], ws[rank], w1, w2, sym)
-        checks["bf16_input"] = torch.equal(y2, want) and torch.equal(y3, want)
+        y3, per_call = mega_moe(xb, idx[rank], ws[rank], w1, w2, sym)
+        checks["bf16_input"] = (torch.equal(y2, want) and torch.equal(y3, want)
+                                and per_call.tolist() == torch.bincount(everyone[everyone >= 0], minlength=E)[mine].tolist())
         with pytest.raises(NotImplementedError, match="timer"):
             sym.allocate_timer()
         sym.destroy()

@@ -126,9 +126,10 @@ def test_shared_experts_stats_bf16_input_and_timer():
         assert phases["ctas"] > 0 and phases["total_us"] > 0
         assert all(phases[k] >= 0 for k in ("handshake_us", "layout_us", "gemm_us", "finish_sync_us", "reduce_us"))
         # pre-quantised inputs through the convenience wrapper give the same rows
-        y2 = mega_moe((codes.to(dev), sf.to(dev)), idx.to(dev), w.to(dev), w1, w2, buf, shared_l1_weights=sw1, shared_l2_weights=sw2)
+        y2, per_call = mega_moe((codes.to(dev), sf.to(dev)), idx.to(dev), w.to(dev), w1, w2, buf, shared_l1_weights=sw1,
+                                shared_l2_weights=sw2)
         torch.cuda.synchronize()
-        assert torch.equal(y2, y)
+        assert torch.equal(y2, y) and torch.equal(per_call.cpu(), counts)       # the rows of this call alone
         with pytest.raises(ValueError, match="shared"):
             fp8_fp4_mega_moe(y, w1, w2, buf)                                # the buffer was built for two shared experts
     finally:
