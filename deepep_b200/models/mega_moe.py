@@ -382,7 +382,14 @@ class SymmBuffer:
                                             routed.experts + shared.experts, routed.n, routed.k, routed.fp8)
         return self._joined[key]
 
-    def validate_inputs(self, batch_size: int) -> None:
+    def validate_inputs(self, batch_size: int, *, x: Optional[torch.Tensor] = None) -> None:
+        """Scan the inputs of the next call (synchronises; keep it outside timed regions).  ``x``: the bf16 override that
+        will be passed to ``fp8_fp4_mega_moe(..., x=...)``, if any (parity: ``api.py:235`` of the reference)."""
+        if not 0 < batch_size <= self.num_max_tokens_per_rank:
+            raise ValueError(f"batch size must be in [1, {self.num_max_tokens_per_rank}]")
+        if x is not None and (x.dtype != torch.bfloat16 or tuple(x.shape) != (batch_size, self.hidden) or not x.is_contiguous()
+                              or not bool(torch.isfinite(x.float()).all())):
+            raise ValueError("the x override must be finite contiguous bf16 [batch, hidden]")
         idx = self.topk_idx[:batch_size]
         if bool(((idx >= self.num_experts)).any()):
             raise ValueError("topk_idx holds expert ids outside [0, num_experts)")

@@ -72,6 +72,11 @@ def test_load_inputs_converts_power_of_two_block_scales():
         sym.load_inputs(big, torch.ones((M + 1, H // 128)), idx, w)
     with pytest.raises(ValueError, match="batch size"):
         sym.prepare(M + 1)
+    sym.validate_inputs(5, x=torch.zeros((5, H), dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="x override"):
+        sym.validate_inputs(5, x=torch.zeros((5, H)))
+    with pytest.raises(ValueError, match="batch size"):
+        sym.validate_inputs(0)
     sym.topk_idx[0, 0] = E
     with pytest.raises(ValueError, match="outside"):
         sym.validate_inputs(5)
