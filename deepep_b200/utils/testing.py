@@ -87,21 +87,37 @@ def bandwidth_gbps(effective_bytes: float, mean_rank_max_us: float) -> float:
 
 def bench_kineto(fn: Callable[[], Any], kernel_names, num_tests: int = 30, suppress_kineto_output: bool = True,
                  trace_path: Optional[str] = None, barrier_comm_profiling: bool = False,
-                 num_kernels_per_period: int = 1):
+                 num_kernels_per_period: int = 1, *, flush_l2: bool = True, barrier: Optional[Callable[[], Any]] = None):
     """Average device seconds of the kernels whose name contains ``kernel_names``.
 
-    Uses ``torch.profiler`` (CUPTI).  Returns one float per requested name
-    (a single float when a string was passed).
+    Uses ``torch.profiler`` (CUPTI).  Returns one float per requested name (a single float when a string was passed).
+    ``flush_l2`` writes a buffer larger than the L2 before every call; with ``barrier_comm_profiling`` the ranks are
+    aligned before every call, by ``barrier()`` when one is given, else by an all-reduce of one element (the reference's
+    keyword extensions, ``deep_ep/utils/testing.py:131-141`` there).
     """
+    if not isinstance(kernel_names, (str, tuple, list)):
+        raise TypeError("kernel_names must be a string or a tuple of strings")
+    names = (kernel_names,) if isinstance(kernel_names, str) else tuple(kernel_names)
+    if not names or not all(isinstance(name, str) for name in names):
+        raise TypeError("kernel_names must contain strings")
+    if any(not name for name in names):
+        raise ValueError("kernel names must not be empty")
+    if num_tests <= 0:
+        raise ValueError("num_tests must be greater than zero")
+    if num_kernels_per_period <= 0:
+        raise ValueError("num_kernels_per_period must be greater than zero")
     from torch.profiler import ProfilerActivity, profile
 
-    names = (kernel_names,) if isinstance(kernel_names, str) else tuple(kernel_names)
     fn()
     torch.cuda.synchronize()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         for _ in range(num_tests):
-            if barrier_comm_profiling and torch.distributed.is_initialized():
-                torch.distributed.all_reduce(torch.ones(1, device="cuda"))
+            flush_l2_cache(flush_l2)
+            if barrier_comm_profiling:
+                if barrier is not None:
+                    barrier()
+                elif torch.distributed.is_initialized():
+                    torch.distributed.all_reduce(torch.ones(1, device="cuda"))
             fn()
         torch.cuda.synchronize()
     if trace_path is not None:

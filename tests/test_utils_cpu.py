@@ -124,3 +124,14 @@ def test_v1_buffer_argument_errors():
     fresh = deep_ep.Buffer(None)
     with pytest.raises(RuntimeError, match="produced the handle"):
         fresh.combine(x, handle)
+
+
+def test_bench_kineto_argument_rules():
+    """The profiler-based timer checks its arguments before it touches a device."""
+    for names, kind in ((5, TypeError), ((), TypeError), (("a", 3), TypeError), (("a", ""), ValueError)):
+        with pytest.raises(kind):
+            TU.bench_kineto(lambda: None, names)
+    with pytest.raises(ValueError, match="num_tests"):
+        TU.bench_kineto(lambda: None, "kernel", num_tests=0)
+    with pytest.raises(ValueError, match="num_kernels_per_period"):
+        TU.bench_kineto(lambda: None, "kernel", num_kernels_per_period=0)
