@@ -23,19 +23,22 @@ def calc_diff(x: torch.Tensor, y: torch.Tensor) -> float:
 
 
 def safe_div(a, b):
-    if b == 0:
-        if a == 0:
-            return 0
+    """``a / b`` with ``0 / 0 == 0`` (a rate over an empty interval); any other division by zero still raises."""
+    if b:
+        return a / b
+    if a:
         raise ZeroDivisionError("division by zero")
-    return a / b
+    return 0
 
 
 def ceil_div(x: int, y: int) -> int:
+    """Smallest integer not below ``x / y``."""
     return -(-x // y)
 
 
 def align(x: int, y: int) -> int:
-    return ceil_div(x, y) * y
+    """``x`` rounded up to a multiple of ``y``."""
+    return x + (-x) % y
 
 
 def _pad_last(x: torch.Tensor, multiple: int) -> torch.Tensor:
@@ -96,28 +99,34 @@ def create_grouped_scores(scores: torch.Tensor, group_idx: torch.Tensor, num_gro
     return (scores.view(t, num_groups, -1) * keep.unsqueeze(-1)).view(t, e)
 
 
+def _leaves(items):
+    """Tensors of a nest of tuples and lists, depth first; anything else is skipped."""
+    for item in items:
+        if isinstance(item, torch.Tensor):
+            yield item
+        elif isinstance(item, (tuple, list)):
+            yield from _leaves(item)
+
+
 def hash_tensor(t: torch.Tensor) -> int:
-    return t.contiguous().view(torch.int).sum().item()
+    """Sum of the tensor's bytes read as int32 words (as bytes when their count is not a multiple of four): equal bits
+    give equal values on every machine, so ranks can compare a number instead of a buffer."""
+    flat = t.contiguous().reshape(-1).view(torch.uint8)
+    words = flat.view(torch.int32) if flat.numel() % 4 == 0 else flat.to(torch.int32)
+    return int(words.sum().item())
 
 
 def hash_tensors(*tensors) -> int:
+    """Exclusive-or of :func:`hash_tensor` over every tensor of the (nested) arguments."""
     value = 0
-    for t in tensors:
-        if isinstance(t, (tuple, list)):
-            value ^= hash_tensors(*t)
-        elif isinstance(t, torch.Tensor):
-            value ^= hash_tensor(t)
+    for leaf in _leaves(tensors):
+        value ^= hash_tensor(leaf)
     return value
 
 
 def count_bytes(*tensors) -> int:
-    total = 0
-    for t in tensors:
-        if isinstance(t, (tuple, list)):
-            total += count_bytes(*t)
-        elif t is not None:
-            total += t.numel() * t.element_size()
-    return total
+    """Bytes held by every tensor of the (nested) arguments; ``None`` entries count nothing."""
+    return sum(leaf.numel() * leaf.element_size() for leaf in _leaves(tensors))
 
 
 __all__ = [
