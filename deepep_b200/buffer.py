@@ -18,6 +18,7 @@ import torch
 from ._compat import BUFFER_DISPATCH_ALIASES, BUFFER_INIT_ALIASES, SET_UNITS_ALIASES, keyword_aliases
 from .config import Config
 from .parallel.elastic import ElasticBuffer
+from .parallel.streams import get_global_comm_stream
 from .resources import Handle, SlotPool, SlotState
 from .utils.event import EventHandle, EventOverlap
 
@@ -30,7 +31,7 @@ class Buffer:
     def __init__(self, group, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0, low_latency_mode: bool = False,
                  num_qps_per_rank: int = 24, allow_nvlink_for_low_latency_mode: bool = True, allow_mnnvl: bool = False,
                  explicitly_destroy: bool = False, enable_shrink: bool = False, comm=None, *, machine_type="auto",
-                 rootinfo_path=None, hidden: int = 0, num_topk: int = 0, num_max_tokens_per_rank: int = 0):
+                 rootinfo_path=None, hidden: int = 0, num_topk: int = 0, num_max_tokens_per_rank: int = 0, comm_stream=None):
         del num_qps_per_rank, allow_nvlink_for_low_latency_mode, allow_mnnvl, comm, machine_type, rootinfo_path
         if num_rdma_bytes:
             raise NotImplementedError("internode (RDMA) buffers are outside this single-NVLink-domain library")
@@ -40,6 +41,7 @@ class Buffer:
             raise NotImplementedError("rank shrinking is not supported")
         self.group, self.num_nvl_bytes, self.explicitly_destroy = group, num_nvl_bytes, explicitly_destroy
         self._shape = (num_max_tokens_per_rank, hidden, num_topk)
+        self._comm_stream = comm_stream                     # None: a stream of its own; "global": the process-wide one
         self._elastic: Optional[ElasticBuffer] = None
         self._slots = SlotPool()
         if all(self._shape):
@@ -54,7 +56,7 @@ class Buffer:
 
                 tokens = max(ControlPlane(self.group).all_gather_object(int(tokens)))
             self._elastic = ElasticBuffer(self.group, num_max_tokens_per_rank=max(tokens, 1), hidden=hidden, num_topk=topk,
-                                          explicitly_destroy=self.explicitly_destroy)
+                                          explicitly_destroy=self.explicitly_destroy, comm_stream=self._comm_stream)
         eb = self._elastic
         if tokens > eb.num_max_tokens_per_rank or hidden != eb.hidden or topk != eb.num_topk:
             raise ValueError("this Buffer was created for another (tokens, hidden, top-k) shape")
@@ -267,7 +269,7 @@ class Buffer:
     def get_next_low_latency_combine_buffer(self, *a, **k): raise NotImplementedError("V1 low-latency mode: use ElasticBuffer")
 
 
-__all__ = ["Buffer", "Handle", "topk_idx_t"]
+__all__ = ["Buffer", "Handle", "get_global_comm_stream", "topk_idx_t"]
 
 
 # platform-neutral spellings next to the upstream ones (parity: ``deep_ep/backends/direct/api.py:8-20`` of the reference)

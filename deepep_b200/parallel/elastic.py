@@ -24,6 +24,7 @@ from .._compat import (CALL_ALIASES, COMBINE_ALIASES, ELASTIC_INIT_ALIASES, ESTI
 from ..utils.event import EventHandle, EventOverlap
 from . import layout as L
 from .runtime import ControlPlane, Runtime
+from .streams import get_global_comm_stream
 
 METADATA_VERSION = 1
 _next_buffer_id = 0
@@ -115,7 +116,7 @@ class ElasticBuffer:
                  prefer_overlap_with_compute=True, sl_idx=3, num_allocated_qps=0, num_cpu_timeout_secs=300,
                  num_gpu_timeout_secs=100, explicitly_destroy=False, *, rank=None, world_size=None, bootstrap="default",
                  combine_only=False, use_1g_huge_pages=True, debug_collectives=False, machine_type="auto",
-                 rootinfo_path=None, device=None, num_sms=0):
+                 rootinfo_path=None, device=None, num_sms=0, comm_stream=None):
         global _next_buffer_id
         del num_cpu_bytes, allow_hybrid_mode, allow_multiple_reduction, prefer_overlap_with_compute, sl_idx
         del num_allocated_qps, use_1g_huge_pages, rootinfo_path, combine_only
@@ -124,6 +125,9 @@ class ElasticBuffer:
                              "only multi-GPU topology")
         if bootstrap not in ("default", "auto", "group", "store"):
             raise ValueError("bootstrap must be 'default', 'group' or 'store'")
+        if isinstance(comm_stream, str) and comm_stream != "global":
+            raise ValueError("comm_stream must be None (a stream of this buffer's own), 'global' (the stream that "
+                             "get_global_comm_stream returns, shared by every buffer of the process) or a CUDA stream")
         if num_max_tokens_per_rank <= 0 or hidden <= 0 or num_topk <= 0:
             raise ValueError("num_max_tokens_per_rank, hidden and num_topk are required")
         for name, value in (("num_gpu_timeout_secs", num_gpu_timeout_secs), ("num_cpu_timeout_secs", num_cpu_timeout_secs)):
@@ -176,7 +180,8 @@ class ElasticBuffer:
             ll = L.ll_region_bytes(self.world_size, num_max_tokens_per_rank, hidden, num_topk)
             self.layout = C.make_layout(self.world_size, num_max_tokens_per_rank, hidden, num_topk, ll, 0, self.combine_window)
             assert self.layout.total == needed, "native and Python workspace layouts disagree"
-            self.runtime = Runtime(self.control, self.layout, float(_timeout_seconds(num_gpu_timeout_secs)), self.device)
+            self.runtime = Runtime(self.control, self.layout, float(_timeout_seconds(num_gpu_timeout_secs)), self.device,
+                                   comm_stream=comm_stream)
             from ..utils.hostwait import cpu_timeout_seconds
 
             self.engine = CudaEngine([self.runtime.native], self.layout, self.device, num_sms=num_sms,
@@ -619,4 +624,4 @@ EPHandle.__init__ = keyword_aliases(EPHandle.__init__, HANDLE_ALIASES)
 # the platform-neutral spelling of the handle's SM budget reads and writes the same value
 EPHandle.num_compute_units = property(lambda self: self.num_sms, lambda self, value: setattr(self, "num_sms", value))
 
-__all__ = ["ElasticBuffer", "EPHandle"]
+__all__ = ["ElasticBuffer", "EPHandle", "get_global_comm_stream"]

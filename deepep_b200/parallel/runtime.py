@@ -20,6 +20,7 @@ from typing import Any, List, Optional
 import torch
 
 from .store import StoreGroup
+from .streams import resolve_comm_stream
 
 
 class ControlPlane:
@@ -177,7 +178,7 @@ def shutdown_session(control: ControlPlane, native, synchronize=None) -> None:
 class Runtime:
     """Owns the native session of this process for one buffer."""
 
-    def __init__(self, control: ControlPlane, layout, timeout: float, device: torch.device):
+    def __init__(self, control: ControlPlane, layout, timeout: float, device: torch.device, comm_stream: Any = None):
         from ..ops import require_native
 
         global _busy_runtimes
@@ -237,7 +238,7 @@ class Runtime:
                 raise RuntimeError("mapping the peers' workspaces failed: " + "; ".join(errors))
         if not self.native.mapped():
             raise RuntimeError("a peer workspace is not mapped")
-        self.stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self.stream = resolve_comm_stream(comm_stream, device)
         control.barrier()
         _busy_runtimes += 1
 

@@ -142,8 +142,9 @@ class EventOverlap:
         handle = self.event
         if handle is not None:
             handle.current_stream_wait()
-            if handle.device is not None and self._lease.tensors:      # the consumer stream uses them from now on
-                self._lease.announce(torch.cuda.current_stream(handle.device))
+            device = getattr(handle, "device", None)                   # a duck-typed event carries no lease
+            if device is not None and self._lease.tensors:             # the consumer stream uses them from now on
+                self._lease.announce(torch.cuda.current_stream(device))
         hook, self.hook_after_wait = self.hook_after_wait, None
         outcome = hook() if hook is not None else None
         if release_handle:

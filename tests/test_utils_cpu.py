@@ -135,3 +135,25 @@ def test_bench_kineto_argument_rules():
         TU.bench_kineto(lambda: None, "kernel", num_tests=0)
     with pytest.raises(ValueError, match="num_kernels_per_period"):
         TU.bench_kineto(lambda: None, "kernel", num_kernels_per_period=0)
+
+
+def test_event_overlap_accepts_a_duck_typed_event():
+    """Any object with ``current_stream_wait`` serves as the event; the hook's result comes back from the wait."""
+    from deepep_b200.utils.event import EventHandle, EventOverlap
+
+    class Mine:
+        waits = 0
+
+        def current_stream_wait(self):
+            self.waits += 1
+
+    mine = Mine()
+    overlap = EventOverlap(mine, extra_tensors=(torch.zeros(2),))
+    overlap.register_hook_after_wait(lambda: "epilogue")
+    assert overlap.wait() == "epilogue" and mine.waits == 1 and overlap.wait() is None and mine.waits == 2
+    with overlap(release_handle=True):
+        pass
+    assert overlap.event is None and mine.waits == 3 and overlap.extra_tensors is not None
+    handle = EventHandle()
+    assert handle.query() and handle.device is None and handle.stream is None
+    handle.synchronize()
