@@ -145,8 +145,10 @@ class EventOverlap:
             device = getattr(handle, "device", None)                   # a duck-typed event carries no lease
             if device is not None and self._lease.tensors:             # the consumer stream uses them from now on
                 self._lease.announce(torch.cuda.current_stream(device))
-        hook, self.hook_after_wait = self.hook_after_wait, None
-        outcome = hook() if hook is not None else None
+        outcome = None
+        if self.hook_after_wait is not None:
+            outcome = self.hook_after_wait()                           # a hook that raises stays registered for a retry
+            self.hook_after_wait = None
         if release_handle:
             self.event = None
             self._lease.release()

@@ -157,3 +157,36 @@ def test_event_overlap_accepts_a_duck_typed_event():
     handle = EventHandle()
     assert handle.query() and handle.device is None and handle.stream is None
     handle.synchronize()
+
+
+def test_event_overlap_failure_paths_keep_state():
+    """A hook that raises stays registered and nothing is released, so the wait can be retried; the wait at the end of
+    a ``with`` block also runs when the body raised.  Parity: ``tests/runtime/test_runtime.py:85-92,154-170`` there."""
+    from deepep_b200.utils.event import EventOverlap
+
+    class Mine:
+        waits = 0
+
+        def current_stream_wait(self):
+            self.waits += 1
+
+    attempts = []
+
+    def hook():
+        attempts.append(1)
+        if len(attempts) == 1:
+            raise ValueError("epilogue failed")
+        return 7
+
+    overlap = EventOverlap(Mine())
+    overlap.register_hook_after_wait(hook)
+    with pytest.raises(ValueError, match="epilogue"):
+        overlap.current_stream_wait(True)
+    assert overlap.event is not None and overlap.hook_after_wait is hook
+    assert overlap.current_stream_wait(True) == 7 and overlap.event is None and overlap.hook_after_wait is None
+    mine = Mine()
+    other = EventOverlap(mine)
+    with pytest.raises(KeyError):
+        with other(True):
+            raise KeyError("body")
+    assert mine.waits == 1 and other.event is None
