@@ -6,6 +6,8 @@
 Every rank times each iteration with CUDA events (host clock on the CPU engine); rank 0 gathers the samples, takes
 the per-iteration maximum over ranks and prints one JSON record (schema in deepep_b200/utils/workload.py).  The
 outputs of the first iteration are compared with the all-rank CPU oracle unless --no-check is given.
+``--set name=value`` changes a field of the configuration, ``--dry-run`` prints the validated plan without measuring,
+``--csv FILE`` appends a one-row summary (with ``--baseline-us`` a speed-up column).
 
 ``--sweep-blocks B... --sweep-fractions F...`` additionally times the cached dispatch and the combine of the same
 workload for every (blocks per rank, share of the blocks on the NVLink side) pair and prints one JSON line each
@@ -29,6 +31,12 @@ def main() -> int:
     ap.add_argument("--config", required=True)
     ap.add_argument("--results-dir", default=None, help="write the record there (existing files are never overwritten)")
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--set", dest="overrides", action="append", default=[], metavar="NAME=VALUE",
+                    help="change one field of the configuration (JSON value), e.g. --set iterations=50 --set route=skew")
+    ap.add_argument("--dry-run", action="store_true", help="validate, print the planned record and stop: nothing is measured")
+    ap.add_argument("--csv", default=None, help="rank 0 appends the record's summary row to this CSV file")
+    ap.add_argument("--baseline-us", type=float, default=None, help="latency measured elsewhere for this configuration; "
+                                                                   "fills the CSV's baseline and speed-up columns")
     ap.add_argument("--sweep-blocks", type=int, nargs="*", default=[], help="blocks (SMs) per rank to try")
     ap.add_argument("--sweep-fractions", type=float, nargs="*", default=[0.3, 0.4, 0.5, 0.6],
                     help="share of the blocks that drives NVLink (dispatch senders / combine expert side)")
@@ -42,7 +50,15 @@ def main() -> int:
     from deepep_b200.utils import workload as W
     from deepep_b200.utils.testing import flush_l2_cache
 
-    cfg = W.WorkloadConfig.from_json(args.config)
+    cfg = W.with_overrides(W.WorkloadConfig.from_json(args.config), args.overrides)
+    if args.dry_run:              # no framework state, no device: the plan carries the configuration and its fingerprint only
+        planned = W.plan(cfg)
+        print(json.dumps(planned))
+        if args.results_dir:
+            os.makedirs(args.results_dir, exist_ok=True)
+            with open(os.path.join(args.results_dir, "plan.json"), "x") as f:
+                json.dump(planned, f, indent=1, sort_keys=True)
+        return 0
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     if world != cfg.world_size:
         raise SystemExit(f"the configuration is for {cfg.world_size} ranks, this job has {world}")
@@ -126,6 +142,10 @@ def main() -> int:
         print(json.dumps(slim))
         if args.results_dir:
             print("written:", W.write_result(args.results_dir, record), file=sys.stderr)
+        if args.csv:
+            new = not os.path.exists(args.csv) or os.path.getsize(args.csv) == 0
+            with open(args.csv, "a") as f:
+                f.write(W.summary_csv(record, args.baseline_us, header=new))
     if world > 1:
         import torch.distributed as dist
 

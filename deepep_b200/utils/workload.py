@@ -6,12 +6,14 @@ result directories that are never overwritten) of the reference.  ``benchmarks/b
 """
 from __future__ import annotations
 
+import csv
 import hashlib
+import io
 import json
 import os
 import time
 from dataclasses import asdict, dataclass, fields
-from typing import Dict, Sequence, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 
@@ -205,4 +207,67 @@ def write_result(directory: str, record: Dict) -> str:
     raise RuntimeError("too many results for one configuration in this directory")
 
 
-__all__ = ["SCHEMA_VERSION", "TIMING", "WorkloadConfig", "complete", "make_routes", "plan", "traffic", "write_result"]
+def verify_record(record: Dict) -> Dict:
+    """Checks a measured record against itself: the configuration must validate and hash to the stored fingerprint, and
+    the statistics and the bandwidth must follow from the stored per-rank samples (they are recomputed, never trusted).
+    Returns the recomputed statistics."""
+    cfg = WorkloadConfig.from_dict(record.get("config"))
+    if record.get("config_fingerprint") != cfg.fingerprint():
+        raise ValueError("the record's fingerprint does not belong to its configuration")
+    if record.get("status") != "measured":
+        raise ValueError("only measured records carry statistics")
+    samples = record.get("rank_samples_us")
+    if not isinstance(samples, list) or len(samples) != cfg.world_size or any(len(r) != cfg.iterations for r in samples):
+        raise ValueError("incomplete rank samples")
+    stats = aggregate_rank_max(samples)
+    for name, value in stats.items():
+        if abs(float(record["statistics"].get(name, float("nan"))) - value) > 1e-9 * max(1.0, abs(value)):
+            raise ValueError(f"stored statistic {name} does not follow from the samples")
+    want = bandwidth_gbps(float(record["effective_bytes"]), stats["mean_rank_max_us"])
+    if abs(float(record["bandwidth_gbps"]) - want) > 1e-9 * max(1.0, want):
+        raise ValueError("stored bandwidth does not follow from the samples")
+    return stats
+
+
+CSV_FIELDS = ("config_fingerprint", "operation", "dtype", "layout", "dispatch_mode", "world_size", "tokens_per_rank", "hidden",
+              "topk", "experts", "route", "iterations", "latency_mean_us", "latency_p50_us", "latency_p95_us", "latency_max_us",
+              "effective_bytes", "bandwidth_gbps", "correctness_result", "baseline_latency_us", "speedup")
+
+
+def summary_csv(record: Dict, baseline_latency_us: Optional[float] = None, header: bool = True) -> str:
+    """One CSV row (after the header line) for a measured record; ``baseline_latency_us`` (a number measured elsewhere for
+    the same configuration) fills the last two columns, which stay empty without it."""
+    stats, cfg = verify_record(record), record["config"]
+    row = {name: cfg[name] for name in CSV_FIELDS if name in cfg}
+    row.update(config_fingerprint=record["config_fingerprint"], tokens_per_rank=" ".join(map(str, cfg["tokens_per_rank"])),
+               latency_mean_us=stats["mean_rank_max_us"], latency_p50_us=stats["p50_us"], latency_p95_us=stats["p95_us"],
+               latency_max_us=stats["max_us"], effective_bytes=record["effective_bytes"], bandwidth_gbps=record["bandwidth_gbps"],
+               correctness_result=record["correctness_result"], baseline_latency_us="", speedup="")
+    if baseline_latency_us is not None:
+        if not baseline_latency_us > 0:
+            raise ValueError("a baseline latency is a positive number of microseconds")
+        row.update(baseline_latency_us=float(baseline_latency_us), speedup=float(baseline_latency_us) / stats["mean_rank_max_us"])
+    out = io.StringIO()
+    writer = csv.DictWriter(out, fieldnames=CSV_FIELDS, lineterminator="\n")
+    if header:
+        writer.writeheader()
+    writer.writerow(row)
+    return out.getvalue()
+
+
+def with_overrides(cfg: WorkloadConfig, assignments: Sequence[str]) -> WorkloadConfig:
+    """``cfg`` with ``name=value`` assignments applied (values in JSON syntax; a bare word is a string), validated."""
+    data = cfg.to_dict()
+    for item in assignments:
+        name, sep, text = item.partition("=")
+        if not sep or name not in data:
+            raise ValueError(f"override {item!r}: expected name=value with a configuration field's name")
+        try:
+            data[name] = json.loads(text, object_pairs_hook=_no_duplicate_keys)
+        except json.JSONDecodeError:
+            data[name] = text
+    return WorkloadConfig.from_dict(data)
+
+
+__all__ = ["CSV_FIELDS", "SCHEMA_VERSION", "TIMING", "WorkloadConfig", "complete", "make_routes", "plan", "summary_csv", "traffic",
+           "verify_record", "with_overrides", "write_result"]

@@ -83,12 +83,17 @@ def test_records_and_result_files(tmp_path):
 def test_config_driven_benchmark_runs_on_the_cpu_engine(tmp_path):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
     out = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", "bench_ep.py"), "--config",
-                          os.path.join(ROOT, "benchmarks", "configs", "smoke.json"), "--results-dir", str(tmp_path)],
+                          os.path.join(ROOT, "benchmarks", "configs", "smoke.json"), "--results-dir", str(tmp_path / "records"),
+                          "--csv", str(tmp_path / "summary.csv"), "--baseline-us", "1000"],
                          capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
     rec = json.loads(out.stdout.strip().splitlines()[-1])
     assert rec["status"] == "measured" and rec["correctness_result"] == "passed" and rec["statistics"]["iterations"] == 3
-    assert len(os.listdir(tmp_path)) == 1
+    stored = os.listdir(tmp_path / "records")
+    assert len(stored) == 1
+    W.verify_record(json.load(open(tmp_path / "records" / stored[0])))
+    lines = (tmp_path / "summary.csv").read_text().splitlines()
+    assert len(lines) == 2 and lines[0].split(",") == list(W.CSV_FIELDS) and lines[1].split(",")[-1] != ""
 
 
 def test_reference_arm_reports_unavailable():
@@ -97,3 +102,61 @@ def test_reference_arm_reports_unavailable():
     assert out.returncode == 0, out.stderr[-1000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
+
+
+def _measured(cfg, samples, nbytes=3.0e6):
+    return W.complete(W.plan(cfg), samples, nbytes, "passed")
+
+
+def test_a_record_is_checked_against_its_own_samples():
+    cfg = W.WorkloadConfig.from_dict({"world_size": 2, "tokens_per_rank": [4, 4], "iterations": 2, "warmup": 0})
+    rec = _measured(cfg, [[10.0, 20.0], [20.0, 40.0]])
+    assert W.verify_record(rec)["mean_rank_max_us"] == 30.0
+    for change in ({"statistics": {**rec["statistics"], "mean_rank_max_us": 1.0}}, {"bandwidth_gbps": 1e9},
+                   {"rank_samples_us": [[10.0, 20.0]]}, {"config_fingerprint": "0" * 64}, {"status": "planned"},
+                   {"config": {**rec["config"], "iterations": 0}}):
+        with pytest.raises(ValueError):
+            W.verify_record({**rec, **change})
+    # no logical traffic is a bandwidth of zero, not a missing latency
+    empty = _measured(cfg, [[1.0, 1.0], [2.0, 2.0]], nbytes=0.0)
+    assert empty["bandwidth_gbps"] == 0 and W.verify_record(empty)["mean_rank_max_us"] == 2.0
+
+
+def test_summary_csv_has_one_row_and_optional_speedup():
+    import csv
+    import io
+
+    cfg = W.WorkloadConfig.from_dict({"world_size": 2, "tokens_per_rank": [4, 4], "iterations": 2, "warmup": 0})
+    rec = _measured(cfg, [[10.0, 20.0], [20.0, 40.0]])
+    rows = list(csv.DictReader(io.StringIO(W.summary_csv(rec))))
+    assert len(rows) == 1 and set(rows[0]) == set(W.CSV_FIELDS)
+    assert rows[0]["latency_mean_us"] == "30.0" and rows[0]["baseline_latency_us"] == rows[0]["speedup"] == ""
+    assert rows[0]["tokens_per_rank"] == "4 4" and rows[0]["config_fingerprint"] == cfg.fingerprint()
+    with_base = list(csv.DictReader(io.StringIO(W.summary_csv(rec, baseline_latency_us=60.0))))[0]
+    assert float(with_base["speedup"]) == 2.0
+    assert W.summary_csv(rec, header=False).count("\n") == 1
+    with pytest.raises(ValueError):
+        W.summary_csv(rec, baseline_latency_us=0.0)
+
+
+def test_overrides_are_validated_like_the_file():
+    cfg = W.WorkloadConfig.from_dict({"world_size": 2, "tokens_per_rank": [4, 4]})
+    changed = W.with_overrides(cfg, ["iterations=50", "route=skew", "with_weights=false", "tokens_per_rank=[8, 0]"])
+    assert (changed.iterations, changed.route, changed.with_weights, changed.tokens_per_rank) == (50, "skew", False, (8, 0))
+    assert changed.fingerprint() != cfg.fingerprint() and W.with_overrides(cfg, []) == cfg
+    for bad in (["iterations"], ["speed=3"], ["iterations=0"], ["route=uphill"]):
+        with pytest.raises(ValueError):
+            W.with_overrides(cfg, bad)
+
+
+def test_dry_run_plans_without_measuring(tmp_path):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, os.path.join(ROOT, "benchmarks", "bench_ep.py"), "--config",
+           os.path.join(ROOT, "benchmarks", "configs", "smoke.json"), "--dry-run", "--set", "iterations=7", "--results-dir", str(tmp_path)]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rec = json.loads(out.stdout.strip().splitlines()[-1])
+    assert rec["status"] == "planned" and rec["config"]["iterations"] == 7 and "statistics" not in rec
+    assert os.listdir(tmp_path) == ["plan.json"]
+    again = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)        # a plan is never overwritten
+    assert again.returncode != 0 and "FileExistsError" in again.stderr
