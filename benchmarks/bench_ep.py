@@ -6,7 +6,8 @@
 Every rank times each iteration with CUDA events (host clock on the CPU engine); rank 0 gathers the samples, takes
 the per-iteration maximum over ranks and prints one JSON record (schema in deepep_b200/utils/workload.py).  The
 outputs of the first iteration are compared with the all-rank CPU oracle unless --no-check is given.
-``--set name=value`` changes a field of the configuration, ``--dry-run`` prints the validated plan without measuring,
+``--set name=value`` changes a field of the configuration, ``--matrix name=[v1,v2]`` runs every combination of the listed
+values as cases of their own (one record each), ``--dry-run`` prints the validated plan without measuring,
 ``--csv FILE`` appends a one-row summary (with ``--baseline-us`` a speed-up column).
 
 ``--sweep-blocks B... --sweep-fractions F...`` additionally times the cached dispatch and the combine of the same
@@ -33,6 +34,8 @@ def main() -> int:
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--set", dest="overrides", action="append", default=[], metavar="NAME=VALUE",
                     help="change one field of the configuration (JSON value), e.g. --set iterations=50 --set route=skew")
+    ap.add_argument("--matrix", action="append", default=[], metavar="NAME=[V1,V2,...]",
+                    help="run one case per value (several --matrix flags: every combination), one record per case")
     ap.add_argument("--dry-run", action="store_true", help="validate, print the planned record and stop: nothing is measured")
     ap.add_argument("--csv", default=None, help="rank 0 appends the record's summary row to this CSV file")
     ap.add_argument("--baseline-us", type=float, default=None, help="latency measured elsewhere for this configuration; "
@@ -50,18 +53,19 @@ def main() -> int:
     from deepep_b200.utils import workload as W
     from deepep_b200.utils.testing import flush_l2_cache
 
-    cfg = W.with_overrides(W.WorkloadConfig.from_json(args.config), args.overrides)
-    if args.dry_run:              # no framework state, no device: the plan carries the configuration and its fingerprint only
-        planned = W.plan(cfg)
-        print(json.dumps(planned))
+    cases = W.expand_matrix(W.with_overrides(W.WorkloadConfig.from_json(args.config), args.overrides), args.matrix)
+    if args.dry_run:              # no framework state, no device: a plan carries the configuration and its fingerprint only
+        planned = [W.plan(cfg) for cfg in cases]
+        for one in planned:
+            print(json.dumps(one))
         if args.results_dir:
             os.makedirs(args.results_dir, exist_ok=True)
             with open(os.path.join(args.results_dir, "plan.json"), "x") as f:
-                json.dump(planned, f, indent=1, sort_keys=True)
+                json.dump(planned[0] if len(planned) == 1 else planned, f, indent=1, sort_keys=True)
         return 0
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
-    if world != cfg.world_size:
-        raise SystemExit(f"the configuration is for {cfg.world_size} ranks, this job has {world}")
+    if any(world != cfg.world_size for cfg in cases):
+        raise SystemExit(f"the configuration is for {cases[0].world_size} ranks, this job has {world}")
     cuda = torch.cuda.is_available()
     group = None
     if world > 1:
@@ -73,84 +77,88 @@ def main() -> int:
         group = dist.group.WORLD
     dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
 
-    routes = [W.make_routes(cfg, r) for r in range(world)]           # every rank can rebuild all inputs (oracle, traffic)
-    xs = [torch.randn((cfg.tokens_per_rank[r], cfg.hidden), generator=torch.Generator().manual_seed(cfg.seed + 77 * r)).bfloat16()
-          for r in range(world)]
-    x, idx, w = xs[rank].to(dev), routes[rank][0].to(dev), (routes[rank][1].to(dev) if cfg.with_weights else None)
-    expand = cfg.layout == "expanded"
-    buf = ElasticBuffer(group, num_max_tokens_per_rank=max(max(cfg.tokens_per_rank), 257), hidden=cfg.hidden, num_topk=cfg.topk,
-                        use_fp8_dispatch=cfg.dtype == "fp8", explicitly_destroy=True)
+    def run_case(cfg):
+        routes = [W.make_routes(cfg, r) for r in range(world)]           # every rank can rebuild all inputs (oracle, traffic)
+        xs = [torch.randn((cfg.tokens_per_rank[r], cfg.hidden), generator=torch.Generator().manual_seed(cfg.seed + 77 * r)).bfloat16()
+              for r in range(world)]
+        x, idx, w = xs[rank].to(dev), routes[rank][0].to(dev), (routes[rank][1].to(dev) if cfg.with_weights else None)
+        expand = cfg.layout == "expanded"
+        buf = ElasticBuffer(group, num_max_tokens_per_rank=max(max(cfg.tokens_per_rank), 257), hidden=cfg.hidden, num_topk=cfg.topk,
+                            use_fp8_dispatch=cfg.dtype == "fp8", explicitly_destroy=True)
 
-    def fresh():
-        return buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=cfg.experts, do_expand=expand,
-                            expert_alignment=cfg.alignment)
+        def fresh():
+            return buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=cfg.experts, do_expand=expand,
+                                expert_alignment=cfg.alignment)
 
-    recv, _, recv_w, handle, _ = fresh()
-    rows = recv[0] if isinstance(recv, tuple) else recv
-    back = torch.randn(rows.shape, device=dev).bfloat16() if cfg.dtype == "fp8" else rows
+        recv, _, recv_w, handle, _ = fresh()
+        rows = recv[0] if isinstance(recv, tuple) else recv
+        back = torch.randn(rows.shape, device=dev).bfloat16() if cfg.dtype == "fp8" else rows
 
-    correctness = "not_run"
-    if not args.no_check:
-        ref, lays = R.dispatch(xs, [r[0] for r in routes], [r[1] for r in routes] if cfg.with_weights else None, cfg.experts,
-                               do_expand=expand, expert_alignment=cfg.alignment)
-        good = True
-        if cfg.dtype == "bf16":
-            good = torch.equal(rows.cpu().view(torch.int16), ref[rank][0].view(torch.int16))
-            out = buf.combine(rows, handle)[0]
-            cref = R.combine([r[0] for r in ref], lays, list(cfg.tokens_per_rank), cfg.topk)
-            good = good and torch.equal(out.cpu().view(torch.int16), cref[rank][0].view(torch.int16))
-        else:
-            good = rows.shape[0] == ref[rank][0].shape[0]
-        verdicts = buf.control.all_gather_object(bool(good)) if world > 1 else [good]
-        correctness = "passed" if all(verdicts) else "failed"
+        correctness = "not_run"
+        if not args.no_check:
+            ref, lays = R.dispatch(xs, [r[0] for r in routes], [r[1] for r in routes] if cfg.with_weights else None, cfg.experts,
+                                   do_expand=expand, expert_alignment=cfg.alignment)
+            good = True
+            if cfg.dtype == "bf16":
+                good = torch.equal(rows.cpu().view(torch.int16), ref[rank][0].view(torch.int16))
+                out = buf.combine(rows, handle)[0]
+                cref = R.combine([r[0] for r in ref], lays, list(cfg.tokens_per_rank), cfg.topk)
+                good = good and torch.equal(out.cpu().view(torch.int16), cref[rank][0].view(torch.int16))
+            else:
+                good = rows.shape[0] == ref[rank][0].shape[0]
+            verdicts = buf.control.all_gather_object(bool(good)) if world > 1 else [good]
+            correctness = "passed" if all(verdicts) else "failed"
 
-    ops = {"dispatch": (fresh if cfg.dispatch_mode == "fresh" else (lambda: buf.dispatch(x, handle=handle))),
-           "combine": lambda: buf.combine(back, handle)}
+        ops = {"dispatch": (fresh if cfg.dispatch_mode == "fresh" else (lambda: buf.dispatch(x, handle=handle))),
+               "combine": lambda: buf.combine(back, handle)}
 
-    def roundtrip():
-        r, _, _, h, _ = fresh() if cfg.dispatch_mode == "fresh" else buf.dispatch(x, handle=handle)
-        rr = r[0] if isinstance(r, tuple) else r
-        buf.combine(back if cfg.dtype == "fp8" else rr, h)
-    ops["roundtrip"] = roundtrip
-    fn = ops[cfg.operation]
+        def roundtrip():
+            r, _, _, h, _ = fresh() if cfg.dispatch_mode == "fresh" else buf.dispatch(x, handle=handle)
+            rr = r[0] if isinstance(r, tuple) else r
+            buf.combine(back if cfg.dtype == "fp8" else rr, h)
+        ops["roundtrip"] = roundtrip
+        fn = ops[cfg.operation]
 
-    samples = []
-    for it in range(cfg.warmup + cfg.iterations):
-        buf.barrier()
-        if cuda:
-            flush_l2_cache()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            fn()
-            e.record()
-            e.synchronize()
-            us = s.elapsed_time(e) * 1e3
-        else:
-            t0 = time.perf_counter_ns()
-            fn()
-            us = (time.perf_counter_ns() - t0) / 1e3
-        if it >= cfg.warmup:
-            samples.append(max(us, 1e-3))
-    if cuda and (args.sweep_blocks or args.device_profile):
-        sweep(buf, cfg, x, handle, back, routes, rank, world, args, fresh)
-    gathered = buf.control.all_gather_object(samples) if world > 1 else [samples]
-    record = W.complete(W.plan(cfg), gathered, W.traffic(cfg, [r[0] for r in routes])["effective_bytes"], correctness)
-    record["engine"] = "cuda" if cuda else "cpu"
-    buf.destroy()
-    if rank == 0:
-        slim = {k: v for k, v in record.items() if k != "rank_samples_us"}
-        print(json.dumps(slim))
-        if args.results_dir:
-            print("written:", W.write_result(args.results_dir, record), file=sys.stderr)
-        if args.csv:
-            new = not os.path.exists(args.csv) or os.path.getsize(args.csv) == 0
-            with open(args.csv, "a") as f:
-                f.write(W.summary_csv(record, args.baseline_us, header=new))
+        samples = []
+        for it in range(cfg.warmup + cfg.iterations):
+            buf.barrier()
+            if cuda:
+                flush_l2_cache()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                fn()
+                e.record()
+                e.synchronize()
+                us = s.elapsed_time(e) * 1e3
+            else:
+                t0 = time.perf_counter_ns()
+                fn()
+                us = (time.perf_counter_ns() - t0) / 1e3
+            if it >= cfg.warmup:
+                samples.append(max(us, 1e-3))
+        if cuda and (args.sweep_blocks or args.device_profile):
+            sweep(buf, cfg, x, handle, back, routes, rank, world, args, fresh)
+        gathered = buf.control.all_gather_object(samples) if world > 1 else [samples]
+        record = W.complete(W.plan(cfg), gathered, W.traffic(cfg, [r[0] for r in routes])["effective_bytes"], correctness)
+        record["engine"] = "cuda" if cuda else "cpu"
+        buf.destroy()
+        if rank == 0:
+            slim = {k: v for k, v in record.items() if k != "rank_samples_us"}
+            print(json.dumps(slim))
+            if args.results_dir:
+                print("written:", W.write_result(args.results_dir, record), file=sys.stderr)
+            if args.csv:
+                new = not os.path.exists(args.csv) or os.path.getsize(args.csv) == 0
+                with open(args.csv, "a") as f:
+                    f.write(W.summary_csv(record, args.baseline_us, header=new))
+        return correctness
+
+    verdicts = [run_case(cfg) for cfg in cases]
     if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()
-    return 0 if correctness != "failed" else 1
+    return 0 if "failed" not in verdicts else 1
 
 
 def sweep(buf, cfg, x, handle, back, routes, rank, world, args, fresh):

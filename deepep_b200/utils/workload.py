@@ -9,11 +9,13 @@ from __future__ import annotations
 import csv
 import hashlib
 import io
+import itertools
 import json
+import math
 import os
 import time
 from dataclasses import asdict, dataclass, fields
-from typing import Dict, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -21,6 +23,7 @@ from .testing import aggregate_rank_max, bandwidth_gbps
 
 SCHEMA_VERSION = 1
 MAX_CONFIG_BYTES = 65536
+MAX_MATRIX_CASES = 4096
 TIMING = {
     "clock": "cuda_events_on_the_launching_stream",
     "rank_aggregation": "max_per_iteration_then_statistics",
@@ -269,5 +272,36 @@ def with_overrides(cfg: WorkloadConfig, assignments: Sequence[str]) -> WorkloadC
     return WorkloadConfig.from_dict(data)
 
 
-__all__ = ["CSV_FIELDS", "SCHEMA_VERSION", "TIMING", "WorkloadConfig", "complete", "make_routes", "plan", "summary_csv", "traffic",
+def expand_matrix(cfg: WorkloadConfig, axes: Sequence[str]) -> List[WorkloadConfig]:
+    """Every combination of the values listed by ``name=[v1, v2, ...]`` axes applied to ``cfg`` (field names in sorted
+    order, the last one varying fastest).  Each member is validated like a configuration file; combinations that give the
+    same configuration are run once.  No axes: ``[cfg]``."""
+    choices: Dict[str, list] = {}
+    for item in axes:
+        name, sep, text = item.partition("=")
+        try:
+            values = json.loads(text) if sep else None
+        except json.JSONDecodeError:
+            values = None
+        if name not in cfg.to_dict() or not isinstance(values, list) or not values:
+            raise ValueError(f"matrix axis {item!r}: expected name=[value, ...] with a configuration field's name")
+        if name in choices:
+            raise ValueError(f"matrix axis {name!r} is given twice")
+        choices[name] = values
+    names = sorted(choices)
+    if math.prod(len(choices[n]) for n in names) > MAX_MATRIX_CASES:
+        raise ValueError(f"a matrix holds at most {MAX_MATRIX_CASES} cases")
+    out, seen = [], set()
+    for combo in itertools.product(*(choices[n] for n in names)):
+        try:
+            member = WorkloadConfig.from_dict({**cfg.to_dict(), **dict(zip(names, combo))})
+        except (ValueError, TypeError) as exc:
+            raise ValueError(f"matrix member {dict(zip(names, combo))}: {exc}") from None
+        if member.fingerprint() not in seen:
+            seen.add(member.fingerprint())
+            out.append(member)
+    return out
+
+
+__all__ = ["CSV_FIELDS", "SCHEMA_VERSION", "TIMING", "WorkloadConfig", "complete", "expand_matrix", "make_routes", "plan", "summary_csv", "traffic",
            "verify_record", "with_overrides", "write_result"]

@@ -160,3 +160,31 @@ def test_dry_run_plans_without_measuring(tmp_path):
     assert os.listdir(tmp_path) == ["plan.json"]
     again = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)        # a plan is never overwritten
     assert again.returncode != 0 and "FileExistsError" in again.stderr
+
+
+def test_matrix_is_the_product_of_its_axes_without_repeats():
+    cfg = W.WorkloadConfig.from_dict({"world_size": 2, "tokens_per_rank": [4, 4]})
+    cases = W.expand_matrix(cfg, ['route=["balanced", "skew"]', "hidden=[256, 512, 256]", "tokens_per_rank=[[4, 4], [8, 0]]"])
+    assert len(cases) == 2 * 2 * 2 and len({c.fingerprint() for c in cases}) == 8
+    assert [c.hidden for c in cases[:4]] == [256, 256, 256, 256] and cases[0].route == "balanced" and cases[1].tokens_per_rank == (8, 0)
+    assert W.expand_matrix(cfg, []) == [cfg]
+    for bad in (["route"], ["route=skew"], ["route=[]"], ["speed=[1]"], ["hidden=[256]", "hidden=[512]"]):
+        with pytest.raises(ValueError, match="matrix axis"):
+            W.expand_matrix(cfg, bad)
+    with pytest.raises(ValueError, match="matrix member .*hidden"):
+        W.expand_matrix(cfg, ["hidden=[256, 200]"])
+    with pytest.raises(ValueError, match="at most"):
+        W.expand_matrix(cfg, ["seed=" + json.dumps(list(range(100))), "iterations=" + json.dumps(list(range(1, 101)))])
+
+
+def test_matrix_run_writes_one_record_per_case(tmp_path):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", "bench_ep.py"), "--config",
+                          os.path.join(ROOT, "benchmarks", "configs", "smoke.json"), "--matrix", 'layout=["expanded", "rank"]',
+                          "--matrix", "hidden=[128, 256]", "--csv", str(tmp_path / "all.csv")],
+                         capture_output=True, text=True, env=env, timeout=900)
+    assert out.returncode == 0, out.stderr[-2000:]
+    records = [json.loads(line) for line in out.stdout.strip().splitlines()]
+    assert len(records) == 4 and all(r["correctness_result"] == "passed" for r in records)
+    assert {(r["config"]["layout"], r["config"]["hidden"]) for r in records} == {("expanded", 128), ("expanded", 256), ("rank", 128), ("rank", 256)}
+    assert len((tmp_path / "all.csv").read_text().splitlines()) == 5          # one header, four rows
