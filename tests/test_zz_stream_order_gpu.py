@@ -112,3 +112,38 @@ def test_dispatch_and_combine_under_inference_mode():
         assert bits_equal(outs, R.low_latency_combine([sref[0][0]], slays, [w[:40]], [40])[0])
     small.destroy()
     big.destroy()
+
+
+def test_shared_and_user_communication_streams():
+    """``comm_stream="global"`` puts two buffers on the one stream of the process and GPU; a stream of the caller's is
+    used as given; the default stays a stream per buffer.  Results against the oracle on each."""
+    import deepep_b200 as deep_ep
+    from deepep_b200.buffer import get_global_comm_stream
+
+    dev = torch.device("cuda")
+    T, H, E, K = 300, 512, 16, 4
+    x = torch.randn((T, H), generator=torch.Generator().manual_seed(4)).bfloat16()
+    idx, w = group_limited_routes(T, E, K, 4, 2, seed=6), make_weights(T, K, 2)
+    ref, lays = R.dispatch([x], [idx], [w], E, do_expand=True)
+    want = R.combine([ref[0][0]], lays, [T], K)[0][0]
+    mine = torch.cuda.Stream()
+    shape = dict(num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True)
+    a = deep_ep.ElasticBuffer(None, comm_stream="global", **shape)
+    b = deep_ep.ElasticBuffer(None, comm_stream="global", **shape)
+    c = deep_ep.ElasticBuffer(None, comm_stream=mine, **shape)
+    d = deep_ep.ElasticBuffer(None, **shape)
+    shared = get_global_comm_stream()
+    assert a.get_comm_stream() == shared and b.get_comm_stream() == shared and c.get_comm_stream() == mine
+    assert d.get_comm_stream() != shared and d.get_comm_stream() != mine
+    xd, idxd, wd = x.to(dev), idx.to(dev), w.to(dev)
+    for buf in (a, b, c, d):
+        rx, _, _, handle, event = buf.dispatch(xd, topk_idx=idxd, topk_weights=wd, num_experts=E, do_expand=True,
+                                               async_with_compute_stream=True)
+        event.current_stream_wait()
+        assert bits_equal(rx, ref[0][0])
+        out, _, _ = buf.combine(rx, handle)
+        assert bits_equal(out, want)
+    torch.cuda.synchronize()
+    for buf in (a, b, c, d):
+        buf.destroy()
+    assert get_global_comm_stream() == shared                # outlives the buffers that used it
